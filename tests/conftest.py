@@ -1,0 +1,41 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (REPO, os.path.join(REPO, "oracle")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+GOLDEN = os.path.join(REPO, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def load_golden(name):
+    with np.load(os.path.join(GOLDEN, name)) as z:
+        return {k: z[k] for k in z.files}
+
+
+def rel_inf(a, b):
+    """Norm-wise relative error  max|a-b| / max|b|  (0 when both are all-zero)."""
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    den = np.abs(b).max() if b.size else 0.0
+    num = np.abs(a - b).max() if b.size else 0.0
+    return 0.0 if num == 0.0 else num / max(den, 1e-300)
+
+
+# Parity tolerances of the path (relative, norm-wise): activations and traces within
+# 1e-5 in float32 and 1e-12 in float64 of the reference `cpu` backend.
+TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}
+
+
+@pytest.fixture(scope="session")
+def port_kernels():
+    import oracle
+    return oracle.PortKernels()
