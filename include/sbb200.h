@@ -1,0 +1,211 @@
+/* sbb200.h -- C ABI of the B200 BCPNN layer backend (libsbb200.so).
+ *
+ * Every function returns SBB_OK (0) or an SBB_ERR_* code; sbb_last_error() gives
+ * the message of the calling thread's last failure.  Nothing here calls exit(),
+ * traps on the device, or falls back to the CPU: without a CUDA device every
+ * compute entry point returns SBB_ERR_NO_DEVICE.
+ *
+ * All matrices are row-major and C-contiguous.  N = in_features, H =
+ * hypercolumns, Mc = minicolumns, M = H*Mc = out_features, B = batch rows.
+ * `dtype` selects float (SBB_F32) or double (SBB_F64) for every REAL pointer.
+ * Scalars are passed as double and rounded to REAL inside, as pybind11 does for
+ * the reference's Python floats.
+ *
+ * Citations name the StreamBrain interface each entry point replaces, by path
+ * inside the StreamBrain repository (K/ = BCPNN/backend/_kernels/).
+ */
+#ifndef SBB200_H
+#define SBB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SBB_OK 0
+#define SBB_ERR_INVALID 1     /* bad argument (null pointer, size, dtype, range) */
+#define SBB_ERR_CUDA 2        /* a CUDA runtime call or kernel launch failed */
+#define SBB_ERR_NO_DEVICE 3   /* no usable CUDA device */
+#define SBB_ERR_UNSUPPORTED 4 /* shape or mode this build does not handle */
+#define SBB_ERR_TIMEOUT 5     /* a bounded device-side wait gave up */
+
+#define SBB_F32 0
+#define SBB_F64 1
+
+#define SBB_LAYER_DENSE 0   /* DenseLayer: traces + weights each step, bias at finalize */
+#define SBB_LAYER_PLASTIC 1 /* StructuralPlasticityLayer: + regularised bias + mask */
+
+/* Which state array sbb_layer_{set,get}_state / sbb_layer_state_ptr address. */
+#define SBB_STATE_WEIGHTS 0 /* REAL [N, M] */
+#define SBB_STATE_BIAS 1    /* REAL [M]    */
+#define SBB_STATE_CI 2      /* REAL [N]    */
+#define SBB_STATE_CJ 3      /* REAL [M]    */
+#define SBB_STATE_CIJ 4     /* REAL [N, M] */
+#define SBB_STATE_KBI 5     /* REAL [M]     (plastic only) */
+#define SBB_STATE_WMASK 6   /* uint8 [N, H] (plastic only) */
+
+int sbb_version(void);
+const char *sbb_last_error(void);
+/* Number of CUDA devices visible (0 without a driver); never fails. */
+int sbb_device_count(void);
+
+/* ------------------------------------------------------------------------
+ * Stateless kernels on HOST buffers.  Each call stages its operands to the
+ * current CUDA device, runs the kernels, copies the mutated arrays back and
+ * synchronises -- the calling convention of the reference's native kernel
+ * modules, whose pybind11 functions take numpy arrays and mutate them in place.
+ * ---------------------------------------------------------------------- */
+
+/* activation[B,M] = inputs[B,N] * weights[N,M] + bias[M].
+ * Replaces update_state_float{32,64}: K/kernels_openmp_internal.cc:342-358, 464-465. */
+int sbb_update_state(int dtype, void *activation, const void *inputs, const void *weights,
+                     const void *bias, long B, long N, long M);
+
+/* a[rows,M] += bias[M].  Replaces add_bias_float{32,64}: K/kernels_cuda_internal.cu:915-936
+ * (wrapper K/kernels_cuda.py:18-26). */
+int sbb_add_bias(int dtype, void *a, const void *bias, long rows, long M);
+
+/* Softmax over each group of Mc consecutive entries of a[rows, H*Mc], in place.
+ * Replaces softmax_minicolumns: K/kernels_numpy.py:13-25 (used by the cpu backend,
+ * BCPNN/backend/cpu_backend.py:10,24) and K/kernels_cuda.py:29-37. */
+int sbb_softmax_minicolumns(int dtype, void *a, long rows, long H, long Mc);
+
+/* Un-fused trace update C = max(0, (1-t)C + t*mean_b(.)) for Ci, Cj, Cij.
+ * Replaces update_counters: K/kernels_numpy.py:28-49, K/kernels_cuda.py:40-48. */
+int sbb_update_counters(int dtype, void *Ci, void *Cj, void *Cij, const void *a_i, const void *a_o,
+                        double taupdt, long B, long N, long M);
+
+/* Fused trace update + log-ratio weights (new Ci, Cj, Cij, weights in place).
+ * Replaces update_weights_float{32,64} of the OpenMP module:
+ * K/kernels_openmp_internal.cc:89-205, 361-383, 461-462 (wrapper K/kernels_openmp.py:16-25). */
+int sbb_update_weights(int dtype, void *Ci, void *Cj, void *Cij, const void *a_i, const void *a_o,
+                       double taupdt, long B, long N, long M, void *weights, double cthr);
+
+/* weights = 0 where Ci<cthr or Cj<cthr, else log(max(Cij,cthr^4)/(Ci*Cj)).
+ * Replaces the un-fused update_weights: K/kernels_numpy.py:52-64, K/kernels_cuda.py:51-59. */
+int sbb_recompute_weights(int dtype, void *weights, const void *Ci, const void *Cj, const void *Cij,
+                          double cthr, long N, long M);
+
+/* bias = log(Cj), or log(2 cthr) where Cj < cthr.
+ * Replaces update_bias_float{32,64}: K/kernels_openmp_internal.cc:207-220, 386-396. */
+int sbb_update_bias(int dtype, void *bias, const void *Cj, double cthr, long M);
+
+/* Regularised bias with the gain trace kbi.
+ * Replaces update_bias_regularized_float{32,64}: K/kernels_openmp_internal.cc:222-246, 399-415. */
+int sbb_update_bias_regularized(int dtype, void *bias, void *kbi, const void *Cj, double cthr,
+                                double khalf, double pmin, double taubdt, long M);
+
+/* Structural-plasticity swap for hypercolumn h: up to `iterations` times the
+ * silent connection with the highest score replaces the active one with the lowest.
+ * Replaces update_mask_float{32,64}: K/kernels_openmp_internal.cc:248-320, 418-441. */
+int sbb_update_mask(int dtype, uint8_t *wmask, const void *weights, const void *Ci, const void *Cj,
+                    const void *Cij, double cthr, long N, long M, long H, long Mc, long h,
+                    long iterations);
+
+/* weights[i,j] = 0 where wmask[i, j/Mc] == 0.
+ * Replaces apply_mask_float{32,64}: K/kernels_openmp_internal.cc:322-335, 444-458. */
+int sbb_apply_mask(int dtype, void *weights, const uint8_t *wmask, long N, long M, long H, long Mc);
+
+/* ------------------------------------------------------------------------
+ * Device-resident layer.  State lives in HBM for the life of the handle; a train
+ * step allocates nothing after the first call at a given batch size.  Handles
+ * are bound to the device current at creation and are not thread-safe.
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ * calls enqueue work and return without synchronising unless stated.
+ * Replaces the layer objects of BCPNN/backend/_cpu_base_backend.py:7-172 as
+ * specialised by BCPNN/backend/cpu_backend.py:7-52.
+ * ---------------------------------------------------------------------- */
+typedef struct sbb_layer sbb_layer;
+
+typedef struct sbb_layer_desc {
+  int dtype;            /* SBB_F32 / SBB_F64 */
+  int kind;             /* SBB_LAYER_DENSE / SBB_LAYER_PLASTIC */
+  long in_features;     /* N */
+  long hypercolumns;    /* H */
+  long minicolumns;     /* Mc */
+  double taupdt;        /* trace time constant; cthr = taupdt/2 */
+  double khalf, pmin, taubdt; /* regularised-bias parameters (plastic) */
+  long mask_iterations; /* swaps attempted per mask update (the cpu backend uses 16) */
+} sbb_layer_desc;
+
+int sbb_layer_create(const sbb_layer_desc *desc, sbb_layer **out);
+int sbb_layer_destroy(sbb_layer *layer);
+
+/* Copy one state array from / to host memory (synchronous).  `bytes` must equal
+ * the array's size.  These are the lazy attribute views (weights, bias, Ci, Cj,
+ * Cij, kbi, wmask) of the reference's layer objects. */
+int sbb_layer_set_state(sbb_layer *layer, int which, const void *host, size_t bytes);
+int sbb_layer_get_state(sbb_layer *layer, int which, void *host, size_t bytes);
+/* Device address of a state array (for callers that keep tensors on the device). */
+int sbb_layer_state_ptr(sbb_layer *layer, int which, void **device_ptr);
+
+/* y[B,M] = softmax_minicolumns(x[B,N] * weights + bias); x, y on the device.
+ * compute_activation: BCPNN/backend/_cpu_base_backend.py:44-51, 126-133. */
+int sbb_layer_forward(sbb_layer *layer, const void *x_dev, long B, void *y_dev, void *stream);
+
+/* One train step from device buffers x[B,N] (layer input) and y[B,M] (layer
+ * output, or the one-hot labels for the classifier).  `hypercolumn` >= 0 also
+ * runs the mask update for that hypercolumn (plastic only); pass -1 for none.
+ * train_step: BCPNN/backend/cpu_backend.py:13-15, 29-52. */
+int sbb_layer_train_step(sbb_layer *layer, const void *x_dev, const void *y_dev, long B,
+                         long hypercolumn, void *stream);
+
+/* Dense: bias = log(Cj).  Plastic: no-op.  train_finalize: cpu_backend.py:17-18. */
+int sbb_layer_train_finalize(sbb_layer *layer, void *stream);
+
+/* Same two calls with HOST buffers: inputs are copied to the device, results
+ * copied back (y_host may be NULL for sbb_layer_step_host) and the call returns
+ * after synchronising.  sbb_layer_step_host runs forward + train step, the body
+ * of the reference's training loop (BCPNN/backend/_cpu_base_backend.py:290-309);
+ * `target_host` is NULL for a hidden layer (it trains on its own activation) or
+ * the labels [B,M] for the classifier. */
+int sbb_layer_forward_host(sbb_layer *layer, const void *x_host, long B, void *y_host);
+/* train_step alone from host buffers x[B,N], y[B,M] (the reference signature
+ * train_step(inputs, outputs[, hypercolumn]): cpu_backend.py:13, 29). */
+int sbb_layer_train_step_host(sbb_layer *layer, const void *x_host, const void *y_host, long B,
+                              long hypercolumn);
+int sbb_layer_step_host(sbb_layer *layer, const void *x_host, const void *target_host, long B,
+                        long hypercolumn, void *y_host);
+
+/* ------------------------------------------------------------------------
+ * Batch data-parallel step, split around the one exchange the path has.
+ * `delta` is a device buffer of N + M + N*M REALs laid out [sum_b x | sum_b y |
+ * x^T y].  Each rank calls sbb_layer_dp_local on its slice of the batch, the
+ * caller sum-reduces `delta` across ranks (NCCL), then every rank calls
+ * sbb_layer_dp_apply_vectors once, sbb_layer_dp_apply_rows over all rows and
+ * sbb_layer_dp_finish.  Row ranges let the caller pipeline the reduction of one
+ * block of rows behind the product of the next; row_begin must be a multiple of
+ * 128.  Semantics: K/kernels_mpi_internal.cc:71-250 (per-rank partial sums,
+ * Allreduce, update with divisor batch*world_size).
+ * ---------------------------------------------------------------------- */
+size_t sbb_layer_delta_elems(const sbb_layer *layer);
+/* x^T y for rows [row_begin,row_end) of the trace matrix into delta; with
+ * row_begin == 0 also the two column sums. */
+int sbb_layer_dp_local(sbb_layer *layer, const void *x_dev, const void *y_dev, long B_local,
+                       void *delta_dev, long row_begin, long row_end, void *stream);
+/* Ci, Cj moving averages from the reduced sums (divisor B_global). */
+int sbb_layer_dp_apply_vectors(sbb_layer *layer, const void *delta_dev, long B_global, void *stream);
+/* Cij moving average + weights (+ mask) for rows [row_begin,row_end). */
+int sbb_layer_dp_apply_rows(sbb_layer *layer, const void *delta_dev, long B_global, long row_begin,
+                            long row_end, void *stream);
+/* Regularised bias and, with hypercolumn >= 0, the mask update (plastic only). */
+int sbb_layer_dp_finish(sbb_layer *layer, long hypercolumn, void *stream);
+
+/* Count argmax(pred[r,:]) == argmax(labels[r,:]) over rows, device buffers;
+ * writes the count to *correct_host after synchronising the stream.
+ * Network.evaluate: BCPNN/backend/_cpu_base_backend.py:239-240. */
+int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, long rows, long classes,
+                      long *correct_host, void *stream);
+
+/* Number of kernels this library has launched in this process (all threads). */
+unsigned long long sbb_kernel_launches(void);
+
+/* Block until all work on `stream` has finished. */
+int sbb_stream_sync(void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SBB200_H */

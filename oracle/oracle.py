@@ -69,6 +69,8 @@ class PortKernels:
         dt = state.dtype
         B, N = inputs.shape
         M = weights.shape[1]
+        if weights.shape[0] != N or state.shape != (B, M) or bias.shape != (M,):
+            raise ValueError("update_state: shape mismatch")
         self._fn("orc_update_state", dt)(_check(state, dt), _check(inputs, dt), _check(weights, dt),
                                          _check(bias, dt), _c_long(B), _c_long(N), _c_long(M))
         return state
@@ -85,6 +87,9 @@ class PortKernels:
         R = self._real(dt)
         B, N = a_i.shape
         M = a_o.shape[1]
+        if Ci.shape != (N,) or Cj.shape != (M,) or Cij.shape != (N, M) or weights.shape != (N, M) \
+                or a_o.shape[0] != B:
+            raise ValueError("update_weights: shape mismatch")
         self._fn("orc_update_weights", dt, R)(R(1.0), _check(Ci, dt), _check(Cj, dt), _check(Cij, dt),
                                               _check(a_i, dt), _check(a_o, dt), R(taupdt), _c_long(B),
                                               _c_long(N), _c_long(M), _check(weights, dt), R(cthr))
@@ -95,6 +100,8 @@ class PortKernels:
         R = self._real(dt)
         B, N = a_i.shape
         M = a_o.shape[1]
+        if Ci.shape != (N,) or Cj.shape != (M,) or Cij.shape != (N, M) or a_o.shape[0] != B:
+            raise ValueError("update_counters: shape mismatch")
         self._fn("orc_update_counters", dt)(_check(Ci, dt), _check(Cj, dt), _check(Cij, dt),
                                             _check(a_i, dt), _check(a_o, dt), R(taupdt), _c_long(B),
                                             _c_long(N), _c_long(M))
@@ -126,6 +133,9 @@ class PortKernels:
         dt = weights.dtype
         R = self._real(dt)
         N, M = weights.shape
+        if M != hypercolumns * minicolumns or wmask.shape != (N, hypercolumns) or Cij.shape != (N, M) \
+                or Ci.shape != (N,) or Cj.shape != (M,) or not 0 <= h < hypercolumns:
+            raise ValueError("update_mask: shape mismatch")
         self._fn("orc_update_mask", dt)(_check(wmask, np.uint8), _check(weights, dt), _check(Ci, dt),
                                         _check(Cj, dt), _check(Cij, dt), R(cthr), _c_long(N), _c_long(M),
                                         _c_long(h), _c_long(hypercolumns), _c_long(minicolumns),
@@ -135,6 +145,8 @@ class PortKernels:
     def apply_mask(self, weights, wmask, hypercolumns, minicolumns):
         dt = weights.dtype
         N, M = weights.shape
+        if M != hypercolumns * minicolumns or wmask.shape != (N, hypercolumns):
+            raise ValueError("apply_mask: shape mismatch")
         self._fn("orc_apply_mask", dt)(_check(weights, dt), _check(wmask, np.uint8), _c_long(N),
                                        _c_long(M), _c_long(hypercolumns), _c_long(minicolumns))
         return weights

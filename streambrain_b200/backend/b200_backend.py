@@ -1,0 +1,445 @@
+"""``BCPNN_BACKEND=b200``: the device-resident layer objects and the network driver.
+
+Exports ``Network``, ``DenseLayer`` and ``StructuralPlasticityLayer`` with the
+constructor signatures, methods and attributes of the reference's backends
+(BCPNN/backend/_cpu_base_backend.py:7-314, specialised as in
+BCPNN/backend/cpu_backend.py:7-52).  Differences are confined to where the state
+lives: traces, weights, bias, gain and mask stay in HBM inside a C-ABI layer
+handle; the attributes ``weights, bias, Ci, Cj, Cij, kbi, wmask`` are properties
+that copy device -> host on read and host -> device on assignment.
+
+``compute_activation`` / ``train_step`` accept either numpy arrays (host buffers,
+copied in and out by the C ABI) or CUDA ``torch`` tensors (device buffers, no
+copies, asynchronous on torch's current stream).
+
+Like the reference's ``cpu`` backend, a structural-plasticity layer always runs 16
+swap iterations per mask update whatever ``mask_iterations`` says
+(cpu_backend.py:47); pass ``use_mask_iterations=True`` to honour the argument as
+the ``numpy``/``gpu`` backends do (_cpu_base_backend.py:154-164).
+"""
+from __future__ import annotations
+
+import ctypes
+from contextlib import nullcontext
+
+import numpy as np
+
+from .. import _lib
+from .._lib import STATE, LayerDesc, check, dtype_code, host_ptr, lib
+from ..parallel import pipelined_dp_step
+
+try:  # torch is plumbing only: device tensors, streams, torch.distributed
+    import torch
+except Exception:  # pragma: no cover
+    torch = None
+
+__all__ = ["Network", "DenseLayer", "StructuralPlasticityLayer"]
+
+
+def _is_tensor(a) -> bool:
+    return torch is not None and isinstance(a, torch.Tensor)
+
+
+def _stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _torch_dtype(dtype):
+    return torch.float32 if np.dtype(dtype) == np.float32 else torch.float64
+
+
+class _DeviceLayer:
+    """Owns one ``sbb_layer`` handle."""
+
+    _kind = _lib.DENSE
+    _state_names = ("weights", "bias", "Ci", "Cj", "Cij")
+
+    def _create(self, dtype, init):
+        self.dtype = np.dtype(dtype).type
+        desc = LayerDesc(dtype_code(dtype), self._kind, self.in_features, self.hypercolumns, self.minicolumns,
+                         float(self.taupdt), float(getattr(self, "khalf", 0.0)), float(getattr(self, "pmin", 0.0)),
+                         float(getattr(self, "taubdt", 0.0)), int(self._mask_iterations_used()))
+        handle = ctypes.c_void_p()
+        check(lib.sbb_layer_create(ctypes.byref(desc), ctypes.byref(handle)))
+        self._handle = handle
+        self._delta = None
+        for name, value in init.items():
+            self._set(name, value)
+
+    def _mask_iterations_used(self):
+        return 0
+
+    def _shape(self, name):
+        N, M, H = self.in_features, self.out_features, self.hypercolumns
+        return {"weights": (N, M), "Cij": (N, M), "bias": (M,), "Cj": (M,), "kbi": (M,), "Ci": (N,),
+                "wmask": (N, H)}[name]
+
+    def _np_dtype(self, name):
+        return np.uint8 if name == "wmask" else self.dtype
+
+    def _get(self, name):
+        out = np.empty(self._shape(name), dtype=self._np_dtype(name))
+        check(lib.sbb_layer_get_state(self._handle, STATE[name], host_ptr(out), out.nbytes))
+        return out
+
+    def _set(self, name, value):
+        a = np.ascontiguousarray(np.asarray(value), dtype=self._np_dtype(name))
+        if a.shape != self._shape(name):
+            raise ValueError("%s must have shape %s, got %s" % (name, self._shape(name), a.shape))
+        check(lib.sbb_layer_set_state(self._handle, STATE[name], host_ptr(a), a.nbytes))
+
+    def state_tensor(self, name):
+        """A torch view (no copy) of a state array in device memory."""
+        ptr = ctypes.c_void_p()
+        check(lib.sbb_layer_state_ptr(self._handle, STATE[name], ctypes.byref(ptr)))
+        shape = self._shape(name)
+        typestr = "|u1" if name == "wmask" else "<f%d" % np.dtype(self.dtype).itemsize
+        iface = {"shape": tuple(shape), "typestr": typestr, "data": (ptr.value, False), "version": 2}
+        holder = type("_DevicePtr", (), {"__cuda_array_interface__": iface})()
+        return torch.as_tensor(holder, device="cuda")
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h is not None and h.value:
+            try:
+                lib.sbb_layer_destroy(h)
+            except Exception:
+                pass
+            self._handle = None
+
+    # -- reference API ---------------------------------------------------
+    def compute_activation(self, inputs):
+        """softmax_minicolumns(inputs . weights + bias): _cpu_base_backend.py:44-51, 126-133."""
+        B = inputs.shape[0]
+        if _is_tensor(inputs):
+            x = self._dev_input(inputs, self.in_features)
+            y = torch.empty((B, self.out_features), dtype=x.dtype, device=x.device)
+            check(lib.sbb_layer_forward(self._handle, x.data_ptr(), B, y.data_ptr(), _stream_ptr()))
+            return y
+        x = np.ascontiguousarray(inputs, dtype=self.dtype)
+        if x.shape[1] != self.in_features:
+            raise ValueError("inputs must have %d columns" % self.in_features)
+        y = np.empty((B, self.out_features), dtype=self.dtype)
+        check(lib.sbb_layer_forward_host(self._handle, host_ptr(x), B, host_ptr(y)))
+        return y
+
+    def _dev_input(self, t, cols):
+        if not t.is_cuda:
+            raise TypeError("torch inputs must be CUDA tensors (pass numpy arrays for host data)")
+        if t.dtype != _torch_dtype(self.dtype) or t.dim() != 2 or t.shape[1] != cols:
+            raise TypeError("expected a [B, %d] %s tensor" % (cols, np.dtype(self.dtype)))
+        return t if t.is_contiguous() else t.contiguous()
+
+    def _train(self, inputs, outputs, h):
+        B = inputs.shape[0]
+        if _is_tensor(inputs) != _is_tensor(outputs):
+            raise TypeError("inputs and outputs must both be numpy arrays or both be CUDA tensors")
+        if _is_tensor(inputs):
+            x = self._dev_input(inputs, self.in_features)
+            y = self._dev_input(outputs, self.out_features)
+            check(lib.sbb_layer_train_step(self._handle, x.data_ptr(), y.data_ptr(), B, h, _stream_ptr()))
+            return
+        x = np.ascontiguousarray(inputs, dtype=self.dtype)
+        y = np.ascontiguousarray(outputs, dtype=self.dtype)
+        if x.shape[1] != self.in_features or y.shape != (B, self.out_features):
+            raise ValueError("train_step: shape mismatch")
+        check(lib.sbb_layer_train_step_host(self._handle, host_ptr(x), host_ptr(y), B, h))
+
+    def step_host(self, inputs, targets=None, hypercolumn=None, want_activation=True):
+        """Forward + train step from host buffers in ONE call (one upload of the
+        inputs): the body of the reference's training loop,
+        _cpu_base_backend.py:290-309.  ``targets`` = labels for the classifier,
+        None for a hidden layer (which trains on its own activation)."""
+        B = inputs.shape[0]
+        x = np.ascontiguousarray(inputs, dtype=self.dtype)
+        t = None if targets is None else np.ascontiguousarray(targets, dtype=self.dtype)
+        y = np.empty((B, self.out_features), dtype=self.dtype) if want_activation else None
+        h = -1 if hypercolumn is None else int(hypercolumn)
+        check(lib.sbb_layer_step_host(self._handle, host_ptr(x), None if t is None else host_ptr(t), B, h,
+                                      None if y is None else host_ptr(y)))
+        return y
+
+    def train_finalize(self):
+        check(lib.sbb_layer_train_finalize(self._handle, _stream_ptr() if torch is not None and
+                                           torch.cuda.is_available() else None))
+
+    def convert(self, dtype):
+        """Change the precision of the layer (_cpu_base_backend.py:53-59, 135-142)."""
+        if np.dtype(dtype) == np.dtype(self.dtype):
+            return
+        state = {n: self._get(n) for n in self._state_names}
+        lib.sbb_layer_destroy(self._handle)
+        self._handle = None
+        self._create(dtype, {n: (v if n == "wmask" else v.astype(dtype)) for n, v in state.items()})
+
+    # -- data-parallel step (one exchange: sum of the batch deltas) -------
+    def delta_buffer(self):
+        if self._delta is None:
+            n = int(lib.sbb_layer_delta_elems(self._handle))
+            self._delta = torch.empty(n, dtype=_torch_dtype(self.dtype), device="cuda")
+        return self._delta
+
+    def dp_train_step(self, inputs, outputs, hypercolumn, world_size, all_reduce, row_blocks=4):
+        """Data-parallel train step: see :func:`streambrain_b200.parallel.pipelined_dp_step`.
+        ``all_reduce(tensor)`` must start an in-place sum over ranks and return a
+        handle with ``wait()``, e.g. ``dist.all_reduce(t, async_op=True)``."""
+        x = self._dev_input(inputs, self.in_features)
+        y = self._dev_input(outputs, self.out_features)
+        pipelined_dp_step(_DeviceDPOps(self), x, y, hypercolumn, x.shape[0], world_size, all_reduce, row_blocks)
+
+
+class _DeviceDPOps:
+    """CUDA implementation of the ``ops`` protocol of :mod:`streambrain_b200.parallel`."""
+
+    def __init__(self, layer):
+        self.layer = layer
+        self.delta = layer.delta_buffer()
+        self.n_rows, self.n_cols = layer.in_features, layer.out_features
+
+    def local(self, x, y, rb, re):
+        check(lib.sbb_layer_dp_local(self.layer._handle, x.data_ptr(), y.data_ptr(), x.shape[0],
+                                     self.delta.data_ptr(), rb, re, _stream_ptr()))
+
+    def apply_vectors(self, batch):
+        check(lib.sbb_layer_dp_apply_vectors(self.layer._handle, self.delta.data_ptr(), batch, _stream_ptr()))
+
+    def apply_rows(self, batch, rb, re):
+        check(lib.sbb_layer_dp_apply_rows(self.layer._handle, self.delta.data_ptr(), batch, rb, re, _stream_ptr()))
+
+    def finish(self, h):
+        check(lib.sbb_layer_dp_finish(self.layer._handle, -1 if h is None else int(h), _stream_ptr()))
+
+
+for _name in ("weights", "bias", "Ci", "Cj", "Cij", "kbi", "wmask"):
+    def _getter(self, _n=_name):
+        if _n not in self._state_names:
+            raise AttributeError(_n)
+        return self._get(_n)
+
+    def _setter(self, value, _n=_name):
+        if _n not in self._state_names:
+            raise AttributeError(_n)
+        self._set(_n, value)
+
+    setattr(_DeviceLayer, _name, property(_getter, _setter))
+
+
+class DenseLayer(_DeviceLayer):
+    """Classifier layer: traces and weights every step, bias at ``train_finalize``
+    (_cpu_base_backend.py:14-70; cpu_backend.py:13-18).  Initial state follows the
+    reference's draw order on the global NumPy stream: randn(N,M) then rand(M)."""
+
+    _kind = _lib.DENSE
+
+    def __init__(self, in_features, hypercolumns, minicolumns, taupdt, initial_counters, dtype=np.float64):
+        self.in_features = in_features
+        self.hypercolumns = hypercolumns
+        self.minicolumns = minicolumns
+        self.out_features = hypercolumns * minicolumns
+        self.taupdt = taupdt
+        N, M = in_features, self.out_features
+        init = {
+            "weights": (0.1 * np.random.randn(N, M)).astype(dtype),
+            "bias": (0.1 * np.random.rand(M)).astype(dtype),
+            "Ci": (initial_counters[0] * np.ones([N])).astype(dtype),
+            "Cj": (initial_counters[1] * np.ones([M])).astype(dtype),
+            "Cij": (initial_counters[2] * np.ones([N, M])).astype(dtype),
+        }
+        self._create(dtype, init)
+
+    def train_step(self, inputs, outputs):
+        self._train(inputs, outputs, -1)
+
+
+class StructuralPlasticityLayer(_DeviceLayer):
+    """Hidden layer with regularised bias and a learned connection mask
+    (_cpu_base_backend.py:80-172; cpu_backend.py:29-52).  Draw order:
+    randn(N,M), rand(M), rand(N,H) < density."""
+
+    _kind = _lib.PLASTIC
+    _state_names = ("weights", "bias", "Ci", "Cj", "Cij", "kbi", "wmask")
+
+    def __init__(self, in_features, hypercolumns, minicolumns, taupdt, khalf, pmin, taubdt, density,
+                 mask_iterations, initial_counters, dtype=np.float64, use_mask_iterations=False):
+        self.in_features = in_features
+        self.hypercolumns = hypercolumns
+        self.minicolumns = minicolumns
+        self.out_features = hypercolumns * minicolumns
+        self.taupdt = taupdt
+        self.khalf = khalf
+        self.pmin = pmin
+        self.taubdt = taubdt
+        self.density = density
+        self.mask_iterations = mask_iterations
+        self.use_mask_iterations = use_mask_iterations
+        N, M = in_features, self.out_features
+        init = {
+            "weights": (0.1 * np.random.randn(N, M)).astype(dtype),
+            "bias": (0.1 * np.random.rand(M)).astype(dtype),
+            "Ci": (initial_counters[0] * np.ones([N])).astype(dtype),
+            "Cj": (initial_counters[1] * np.ones([M])).astype(dtype),
+            "Cij": (initial_counters[2] * np.ones([N, M])).astype(dtype),
+            "kbi": np.ones([M]).astype(dtype),
+        }
+        init["wmask"] = (np.random.rand(N, hypercolumns) < density).astype(np.uint8)
+        self._create(dtype, init)
+
+    def _mask_iterations_used(self):
+        return self.mask_iterations if self.use_mask_iterations else 16
+
+    def train_step(self, inputs, outputs, hypercolumn=None):
+        self._train(inputs, outputs, -1 if hypercolumn is None else int(hypercolumn))
+
+
+class Network:
+    """Layer container with the reference's ``fit`` / ``evaluate`` loops
+    (_cpu_base_backend.py:174-314): per epoch one sample permutation and one
+    hypercolumn permutation from the global NumPy stream, batches of
+    ``maximal_batch_size`` (last one partial), every rank taking the slice
+    ``[start + rank*local, +local)`` with ``local = batch // world_size``, a mask
+    update every ``nb // (H+1)`` batches from the second epoch on, and
+    ``train_finalize`` after every epoch.
+
+    The loop is written against the layer interface only, so it drives any layer
+    type.  Layers that offer ``dp_train_step`` are trained with one sum-allreduce
+    of the batch deltas per step when ``world_size > 1`` (``all_reduce`` must be
+    supplied, see :meth:`set_data_parallel`).
+    """
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+        self._layers = []
+        self.world_rank = 0
+        self.world_size = 1
+        self._all_reduce = None
+        self._sum_counts = None
+        self.verbose = True
+        self.device_resident = True
+
+    def set_data_parallel(self, rank, world_size, all_reduce=None, sum_counts=None):
+        """``all_reduce(tensor) -> handle with wait()`` sums a device tensor over
+        ranks in place; ``sum_counts(np.ndarray) -> np.ndarray`` sums evaluation
+        counters (the mpi backend's Allreduce, mpi_backend.py:63-69)."""
+        self.world_rank, self.world_size = rank, world_size
+        self._all_reduce, self._sum_counts = all_reduce, sum_counts
+
+    def add_layer(self, layer):
+        if layer.dtype != self.dtype:
+            layer.convert(self.dtype)
+        self._layers.append(layer)
+
+    def fit(self, training_data, training_labels, maximal_batch_size, schedule):
+        training_data = training_data.astype(self.dtype)
+        training_labels = training_labels.astype(self.dtype)
+        for layer, epochs in schedule:
+            self._train_layer(layer, maximal_batch_size, training_data, training_labels, epochs)
+
+    def _progress(self, total, description):
+        if self.world_rank == 0 and self.verbose:
+            from tqdm import tqdm
+            bar = tqdm(total=total)
+            bar.set_description(description)
+            return bar
+        return nullcontext()
+
+    def _on_device(self):
+        return (self.device_resident and torch is not None and torch.cuda.is_available()
+                and all(isinstance(l, _DeviceLayer) for l in self._layers))
+
+    def _to_device(self, a):
+        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    def evaluate(self, images, labels, maximal_batch_size):
+        images = images.astype(self.dtype)
+        labels = labels.astype(self.dtype)
+        correct = np.array([0])
+        total = np.array([0])
+        number_of_batches = (images.shape[0] + maximal_batch_size - 1) // maximal_batch_size
+        on_dev = self._on_device()
+        if on_dev:
+            images, labels = self._to_device(images), self._to_device(labels)
+        with self._progress(number_of_batches, "Evaluation") as pbar:
+            for i in range(number_of_batches):
+                global_start = i * maximal_batch_size
+                global_end = min(global_start + maximal_batch_size, images.shape[0])
+                local_batch_size = (global_end - global_start) // self.world_size
+                start_sample = global_start + self.world_rank * local_batch_size
+                end_sample = start_sample + local_batch_size
+                batch_images = images[start_sample:end_sample, :]
+                batch_labels = labels[start_sample:end_sample, :]
+                if batch_images.shape[0] > 0:
+                    activations = batch_images
+                    for layer in self._layers:
+                        activations = layer.compute_activation(activations)
+                    if on_dev:
+                        hit = ctypes.c_long(0)
+                        batch_labels = batch_labels.contiguous()
+                        check(lib.sbb_count_correct(dtype_code(self.dtype), activations.data_ptr(),
+                                                    batch_labels.data_ptr(), activations.shape[0],
+                                                    activations.shape[1], ctypes.byref(hit), _stream_ptr()))
+                        correct += hit.value
+                    else:
+                        correct += (np.argmax(activations, axis=1) == np.argmax(batch_labels, axis=1)).sum()
+                total += batch_images.shape[0]
+                if pbar is not None:
+                    pbar.update(1)
+        if self.world_size > 1 and self._sum_counts is not None:
+            correct, total = self._sum_counts(correct), self._sum_counts(total)
+        return correct, total
+
+    def _train_layer(self, layer, maximal_batch_size, images, labels, epochs):
+        on_dev = self._on_device()
+        if on_dev:
+            images, labels = self._to_device(images), self._to_device(labels)
+        for epoch in range(epochs):
+            if self.world_rank == 0 and self.verbose:
+                print('Layer - %d/%d' % (layer + 1, len(self._layers)), flush=True)
+            idx = np.random.permutation(range(images.shape[0]))
+            if on_dev:
+                tidx = torch.from_numpy(idx).cuda()
+                shuffled_images = images.index_select(0, tidx)
+                shuffled_labels = labels.index_select(0, tidx)
+            else:
+                shuffled_images = images[idx, :]
+                shuffled_labels = labels[idx, :]
+            n_hypercolumns = self._layers[layer].hypercolumns
+            hypercolumns_shuffled = np.random.permutation(range(n_hypercolumns))
+            number_of_batches = (images.shape[0] + maximal_batch_size - 1) // maximal_batch_size
+            # The reference divides by this (raising ZeroDivisionError when there are
+            # fewer batches than hypercolumns + 1); kept, so short runs fail the same way.
+            mask_period = number_of_batches // (n_hypercolumns + 1)
+            with self._progress(number_of_batches, 'Epoch %d/%d' % (epoch + 1, epochs)) as pbar:
+                for i in range(number_of_batches):
+                    global_start = i * maximal_batch_size
+                    global_end = min(global_start + maximal_batch_size, images.shape[0])
+                    local_batch_size = (global_end - global_start) // self.world_size
+                    start_sample = global_start + self.world_rank * local_batch_size
+                    end_sample = start_sample + local_batch_size
+                    batch_images = shuffled_images[start_sample:end_sample, :]
+                    batch_labels = shuffled_labels[start_sample:end_sample, :]
+
+                    prev_activation = None
+                    activation = batch_images
+                    for l in range(layer + 1):
+                        prev_activation = activation
+                        activation = self._layers[l].compute_activation(prev_activation)
+
+                    if epoch > 0 and i % mask_period == 0:
+                        h = i // mask_period
+                        h = hypercolumns_shuffled[h] if h < n_hypercolumns else None
+                    else:
+                        h = None
+
+                    target = self._layers[layer]
+                    last = layer + 1 == len(self._layers)
+                    outputs = batch_labels if last else activation
+                    if self.world_size > 1 and hasattr(target, "dp_train_step") and self._all_reduce is not None:
+                        target.dp_train_step(prev_activation, outputs, None if last else h, self.world_size,
+                                             self._all_reduce)
+                    elif last:
+                        target.train_step(prev_activation, outputs)
+                    else:
+                        target.train_step(prev_activation, outputs, h)
+                    if pbar is not None:
+                        pbar.update(1)
+                self._layers[layer].train_finalize()

@@ -1,0 +1,777 @@
+// C ABI of libsbb200.so: the device-resident layer object, the stateless
+// host-buffer kernel mirrors and the data-parallel split step.  See
+// include/sbb200.h for the contract of every entry point.
+#include "../../include/sbb200.h"
+#include "sbb_kernels.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  return fail(SBB_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+#define SBB_CUDA(call)                                   \
+  do {                                                   \
+    cudaError_t e__ = (call);                            \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+  } while (0)
+
+#define SBB_TRY(call)               \
+  do {                              \
+    int rc__ = (call);              \
+    if (rc__ != SBB_OK) return rc__; \
+  } while (0)
+
+int device_count() {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int need_device() {
+  if (device_count() <= 0) return fail(SBB_ERR_NO_DEVICE, "no CUDA device is available; this library has no CPU path");
+  return SBB_OK;
+}
+
+size_t esize(int dtype) { return dtype == SBB_F32 ? 4 : 8; }
+
+int check_dtype(int dtype) {
+  if (dtype != SBB_F32 && dtype != SBB_F64) return fail(SBB_ERR_INVALID, "invalid dtype %d", dtype);
+  return SBB_OK;
+}
+
+// Device buffer that lives for one host-buffer call.
+struct Staged {
+  void *d = nullptr;
+  size_t bytes = 0;
+  ~Staged() {
+    if (d) cudaFree(d);
+  }
+  int alloc(size_t n) {
+    bytes = n;
+    if (n == 0) return SBB_OK;
+    SBB_CUDA(cudaMalloc(&d, n));
+    return SBB_OK;
+  }
+  int upload(const void *h, size_t n) {
+    SBB_TRY(alloc(n));
+    if (n) SBB_CUDA(cudaMemcpy(d, h, n, cudaMemcpyHostToDevice));
+    return SBB_OK;
+  }
+  int download(void *h) const {
+    if (bytes) SBB_CUDA(cudaMemcpy(h, d, bytes, cudaMemcpyDeviceToHost));
+    return SBB_OK;
+  }
+  template <typename T>
+  T *as() const {
+    return static_cast<T *>(d);
+  }
+};
+
+// Scratch that grows on demand and is kept (no allocation in steady state).
+struct Scratch {
+  void *d = nullptr;
+  size_t cap = 0;
+  int reserve(size_t n) {
+    if (n <= cap) return SBB_OK;
+    if (d) SBB_CUDA(cudaFree(d));
+    d = nullptr;
+    cap = 0;
+    SBB_CUDA(cudaMalloc(&d, n));
+    cap = n;
+    return SBB_OK;
+  }
+  void release() {
+    if (d) cudaFree(d);
+    d = nullptr;
+    cap = 0;
+  }
+};
+
+#define ARG(cond, ...) \
+  do {                 \
+    if (!(cond)) return fail(SBB_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+}  // namespace
+
+struct sbb_layer {
+  sbb_layer_desc desc;
+  long N, H, Mc, M;
+  int device;
+  void *state[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t state_bytes[7] = {0, 0, 0, 0, 0, 0, 0};
+  Scratch fwd_partial;   // k-split partial sums of the forward product
+  Scratch score;         // N REALs
+  Scratch csum;          // N ints
+  Scratch hx, hy, ht;    // staging for the host-buffer entry points
+  cudaStream_t own_stream = nullptr;
+};
+
+namespace {
+
+template <typename T>
+int layer_forward(sbb_layer *L, const T *x, long B, T *y, cudaStream_t st) {
+  const int splits = sbb::forward_splits<T>(B, L->N, L->M);
+  T *partial = y;
+  if (splits > 1) {
+    SBB_TRY(L->fwd_partial.reserve((size_t)splits * B * L->M * sizeof(T)));
+    partial = static_cast<T *>(L->fwd_partial.d);
+  }
+  SBB_CUDA(sbb::launch_forward_product<T>(x, static_cast<const T *>(L->state[SBB_STATE_WEIGHTS]), partial, B, L->N,
+                                          L->M, splits, st));
+  SBB_CUDA(sbb::launch_reduce_bias_softmax<T>(partial, splits, static_cast<const T *>(L->state[SBB_STATE_BIAS]), y, B,
+                                              L->H, L->Mc, 1, st));
+  return SBB_OK;
+}
+
+template <typename T>
+int layer_finish(sbb_layer *L, long h, cudaStream_t st) {
+  if (L->desc.kind != SBB_LAYER_PLASTIC) return SBB_OK;
+  const double cthr = L->desc.taupdt / 2;
+  T *W = static_cast<T *>(L->state[SBB_STATE_WEIGHTS]);
+  T *Ci = static_cast<T *>(L->state[SBB_STATE_CI]);
+  T *Cj = static_cast<T *>(L->state[SBB_STATE_CJ]);
+  T *Cij = static_cast<T *>(L->state[SBB_STATE_CIJ]);
+  uint8_t *wmask = static_cast<uint8_t *>(L->state[SBB_STATE_WMASK]);
+  SBB_CUDA(sbb::launch_update_bias_regularized<T>(static_cast<T *>(L->state[SBB_STATE_BIAS]),
+                                                  static_cast<T *>(L->state[SBB_STATE_KBI]), Cj, (T)cthr,
+                                                  (T)L->desc.khalf, (T)L->desc.pmin, (T)L->desc.taubdt, L->M, st));
+  if (h >= 0) {
+    // The score uses the freshly recomputed, un-masked weight of every connection,
+    // which is a function of the traces alone; the masked weights already written
+    // for hypercolumn h are then rewritten under the updated mask.
+    SBB_CUDA(sbb::launch_mask_update<T>(wmask, nullptr, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h,
+                                        L->desc.mask_iterations, static_cast<T *>(L->score.d),
+                                        static_cast<int *>(L->csum.d), st));
+    SBB_CUDA(sbb::launch_rewrite_hypercolumn<T>(W, wmask, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, st));
+  }
+  return SBB_OK;
+}
+
+template <typename T>
+int layer_train_step(sbb_layer *L, const T *x, const T *y, long B, long h, cudaStream_t st) {
+  const sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, B);
+  T *Ci = static_cast<T *>(L->state[SBB_STATE_CI]);
+  T *Cj = static_cast<T *>(L->state[SBB_STATE_CJ]);
+  SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, nullptr, Ci, p, 1, st));
+  SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, nullptr, Cj, p, 1, st));
+  SBB_CUDA(sbb::launch_trace_update_fused<T>(x, y, B, L->N, L->M, L->H, L->Mc, Ci, Cj,
+                                             static_cast<T *>(L->state[SBB_STATE_CIJ]),
+                                             static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
+                                             static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 0, L->N, st));
+  return layer_finish<T>(L, h, st);
+}
+
+template <typename T>
+int layer_dp_local(sbb_layer *L, const T *x, const T *y, long B, T *delta, long rb, long re, cudaStream_t st) {
+  sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, B);
+  if (rb == 0) {
+    SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, delta, nullptr, p, 0, st));
+    SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, delta + L->N, nullptr, p, 0, st));
+  }
+  SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, L->N, L->M, delta + L->N + L->M, rb, re, st));
+  return SBB_OK;
+}
+
+template <typename T>
+int layer_dp_apply_vectors(sbb_layer *L, const T *delta, long Bg, cudaStream_t st) {
+  const sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, Bg);
+  SBB_CUDA(sbb::launch_vector_ema<T>(static_cast<T *>(L->state[SBB_STATE_CI]), delta, L->N, p, st));
+  SBB_CUDA(sbb::launch_vector_ema<T>(static_cast<T *>(L->state[SBB_STATE_CJ]), delta + L->N, L->M, p, st));
+  return SBB_OK;
+}
+
+template <typename T>
+int layer_dp_apply_rows(sbb_layer *L, const T *delta, long Bg, long rb, long re, cudaStream_t st) {
+  const sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, Bg);
+  SBB_CUDA(sbb::launch_trace_apply<T>(delta + L->N + L->M, L->N, L->M, L->H, L->Mc,
+                                      static_cast<const T *>(L->state[SBB_STATE_CI]),
+                                      static_cast<const T *>(L->state[SBB_STATE_CJ]),
+                                      static_cast<T *>(L->state[SBB_STATE_CIJ]),
+                                      static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
+                                      static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 1, rb, re, st));
+  return SBB_OK;
+}
+
+int check_layer(const sbb_layer *L) {
+  if (!L) return fail(SBB_ERR_INVALID, "null layer handle");
+  int dev = -1;
+  SBB_CUDA(cudaGetDevice(&dev));
+  if (dev != L->device)
+    return fail(SBB_ERR_INVALID, "layer lives on device %d but device %d is current", L->device, dev);
+  return SBB_OK;
+}
+
+int check_batch(const sbb_layer *L, long B) {
+  ARG(B > 0, "batch must be positive, got %ld", B);
+  ARG(B <= 2147483647L / 2 && L->N <= 2147483647L / 2, "batch %ld or in_features %ld out of range", B, L->N);
+  return SBB_OK;
+}
+
+#define DISPATCH(dtype, expr_f32, expr_f64) ((dtype) == SBB_F32 ? (expr_f32) : (expr_f64))
+
+}  // namespace
+
+extern "C" {
+
+int sbb_version(void) { return 100; }
+const char *sbb_last_error(void) { return g_error.c_str(); }
+int sbb_device_count(void) { return device_count(); }
+unsigned long long sbb_kernel_launches(void) { return sbb::kernel_launches(); }
+
+int sbb_stream_sync(void *stream) {
+  SBB_TRY(need_device());
+  SBB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return SBB_OK;
+}
+
+// ---------------------------------------------------------------- stateless
+int sbb_update_state(int dtype, void *activation, const void *inputs, const void *weights, const void *bias, long B,
+                     long N, long M) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(activation && inputs && weights && bias, "update_state: null pointer");
+  ARG(B > 0 && N > 0 && M > 0, "update_state: non-positive shape B=%ld N=%ld M=%ld", B, N, M);
+  SBB_TRY(need_device());
+  const size_t s = esize(dtype);
+  Staged x, w, b, out, part;
+  SBB_TRY(x.upload(inputs, B * N * s));
+  SBB_TRY(w.upload(weights, N * M * s));
+  SBB_TRY(b.upload(bias, M * s));
+  SBB_TRY(out.alloc(B * M * s));
+  const int splits = DISPATCH(dtype, sbb::forward_splits<float>(B, N, M), sbb::forward_splits<double>(B, N, M));
+  void *partial = out.d;
+  if (splits > 1) {
+    SBB_TRY(part.alloc((size_t)splits * B * M * s));
+    partial = part.d;
+  }
+  if (dtype == SBB_F32) {
+    SBB_CUDA(sbb::launch_forward_product<float>(x.as<float>(), w.as<float>(), (float *)partial, B, N, M, splits, 0));
+    SBB_CUDA(sbb::launch_reduce_bias_softmax<float>((float *)partial, splits, b.as<float>(), out.as<float>(), B, 1, M,
+                                                    0, 0));
+  } else {
+    SBB_CUDA(sbb::launch_forward_product<double>(x.as<double>(), w.as<double>(), (double *)partial, B, N, M, splits, 0));
+    SBB_CUDA(sbb::launch_reduce_bias_softmax<double>((double *)partial, splits, b.as<double>(), out.as<double>(), B, 1,
+                                                     M, 0, 0));
+  }
+  SBB_CUDA(cudaDeviceSynchronize());
+  return out.download(activation);
+}
+
+int sbb_add_bias(int dtype, void *a, const void *bias, long rows, long M) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(a && bias, "add_bias: null pointer");
+  ARG(rows > 0 && M > 0, "add_bias: non-positive shape");
+  SBB_TRY(need_device());
+  const size_t s = esize(dtype);
+  Staged da, db;
+  SBB_TRY(da.upload(a, rows * M * s));
+  SBB_TRY(db.upload(bias, M * s));
+  if (dtype == SBB_F32) SBB_CUDA(sbb::launch_add_bias<float>(da.as<float>(), db.as<float>(), rows, M, 0));
+  else SBB_CUDA(sbb::launch_add_bias<double>(da.as<double>(), db.as<double>(), rows, M, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  return da.download(a);
+}
+
+int sbb_softmax_minicolumns(int dtype, void *a, long rows, long H, long Mc) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(a, "softmax_minicolumns: null pointer");
+  ARG(rows > 0 && H > 0 && Mc > 0, "softmax_minicolumns: non-positive shape");
+  SBB_TRY(need_device());
+  Staged da;
+  SBB_TRY(da.upload(a, rows * H * Mc * esize(dtype)));
+  if (dtype == SBB_F32)
+    SBB_CUDA(sbb::launch_reduce_bias_softmax<float>(da.as<float>(), 1, nullptr, da.as<float>(), rows, H, Mc, 1, 0));
+  else
+    SBB_CUDA(sbb::launch_reduce_bias_softmax<double>(da.as<double>(), 1, nullptr, da.as<double>(), rows, H, Mc, 1, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  return da.download(a);
+}
+
+}  // extern "C"
+
+namespace {
+template <typename T>
+int update_counters_t(void *Ci, void *Cj, void *Cij, const void *a_i, const void *a_o, double taupdt, long B, long N,
+                      long M) {
+  const size_t s = sizeof(T);
+  Staged dci, dcj, dcij, dx, dy, sums;
+  SBB_TRY(dci.upload(Ci, N * s));
+  SBB_TRY(dcj.upload(Cj, M * s));
+  SBB_TRY(dcij.upload(Cij, N * M * s));
+  SBB_TRY(dx.upload(a_i, B * N * s));
+  SBB_TRY(dy.upload(a_o, B * M * s));
+  SBB_TRY(sums.alloc((size_t)(N + M + N * M + 4) * s));
+  const sbb::TraceParams<T> p = sbb::make_trace_params<T>(taupdt, taupdt / 2, B);
+  T *sx = sums.as<T>();
+  T *sy = sx + N;
+  // keep the [N, M] block 16-byte aligned whatever N + M is
+  T *sxy = sx + ((N + M + 3) / 4) * 4;
+  SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, sx, nullptr, p, 0, 0));
+  SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, sy, nullptr, p, 0, 0));
+  SBB_CUDA(sbb::launch_outer_product<T>(dx.as<T>(), dy.as<T>(), B, N, M, sxy, 0, N, 0));
+  SBB_CUDA(sbb::launch_counters_apply<T>(dci.as<T>(), sx, N, (T)taupdt, (T)B, 0));
+  SBB_CUDA(sbb::launch_counters_apply<T>(dcj.as<T>(), sy, M, (T)taupdt, (T)B, 0));
+  SBB_CUDA(sbb::launch_counters_apply<T>(dcij.as<T>(), sxy, N * M, (T)taupdt, (T)B, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_TRY(dci.download(Ci));
+  SBB_TRY(dcj.download(Cj));
+  return dcij.download(Cij);
+}
+
+template <typename T>
+int update_weights_t(void *Ci, void *Cj, void *Cij, const void *a_i, const void *a_o, double taupdt, long B, long N,
+                     long M, void *weights, double cthr) {
+  const size_t s = sizeof(T);
+  Staged dci, dcj, dcij, dx, dy, dw;
+  SBB_TRY(dci.upload(Ci, N * s));
+  SBB_TRY(dcj.upload(Cj, M * s));
+  SBB_TRY(dcij.upload(Cij, N * M * s));
+  SBB_TRY(dx.upload(a_i, B * N * s));
+  SBB_TRY(dy.upload(a_o, B * M * s));
+  SBB_TRY(dw.alloc(N * M * s));
+  const sbb::TraceParams<T> p = sbb::make_trace_params<T>(taupdt, cthr, B);
+  SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, nullptr, dci.as<T>(), p, 1, 0));
+  SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, nullptr, dcj.as<T>(), p, 1, 0));
+  SBB_CUDA(sbb::launch_trace_update_fused<T>(dx.as<T>(), dy.as<T>(), B, N, M, 1, M, dci.as<T>(), dcj.as<T>(),
+                                             dcij.as<T>(), dw.as<T>(), nullptr, p, 0, N, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_TRY(dci.download(Ci));
+  SBB_TRY(dcj.download(Cj));
+  SBB_TRY(dcij.download(Cij));
+  return dw.download(weights);
+}
+
+template <typename T>
+int recompute_weights_t(void *weights, const void *Ci, const void *Cj, const void *Cij, double cthr, long N, long M) {
+  const size_t s = sizeof(T);
+  Staged dci, dcj, dcij, dw;
+  SBB_TRY(dci.upload(Ci, N * s));
+  SBB_TRY(dcj.upload(Cj, M * s));
+  SBB_TRY(dcij.upload(Cij, N * M * s));
+  SBB_TRY(dw.alloc(N * M * s));
+  sbb::TraceParams<T> p = sbb::make_trace_params<T>(2 * cthr, cthr, 1);
+  SBB_CUDA(sbb::launch_trace_apply<T>(nullptr, N, M, 1, M, dci.as<T>(), dcj.as<T>(), dcij.as<T>(), dw.as<T>(), nullptr,
+                                      p, 0, 0, N, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  return dw.download(weights);
+}
+
+template <typename T>
+int update_mask_t(uint8_t *wmask, const void *weights, const void *Ci, const void *Cj, const void *Cij, double cthr,
+                  long N, long M, long H, long Mc, long h, long iterations) {
+  const size_t s = sizeof(T);
+  Staged dm, dw, dci, dcj, dcij, score, csum;
+  SBB_TRY(dm.upload(wmask, N * H));
+  SBB_TRY(dw.upload(weights, N * M * s));
+  SBB_TRY(dci.upload(Ci, N * s));
+  SBB_TRY(dcj.upload(Cj, M * s));
+  SBB_TRY(dcij.upload(Cij, N * M * s));
+  SBB_TRY(score.alloc(N * s));
+  SBB_TRY(csum.alloc(N * sizeof(int)));
+  SBB_CUDA(sbb::launch_mask_update<T>(dm.as<uint8_t>(), dw.as<T>(), dci.as<T>(), dcj.as<T>(), dcij.as<T>(), (T)cthr, N,
+                                      M, H, Mc, h, iterations, score.as<T>(), csum.as<int>(), 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  return dm.download(wmask);
+}
+}  // namespace
+
+extern "C" {
+
+int sbb_update_counters(int dtype, void *Ci, void *Cj, void *Cij, const void *a_i, const void *a_o, double taupdt,
+                        long B, long N, long M) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(Ci && Cj && Cij && a_i && a_o, "update_counters: null pointer");
+  ARG(B > 0 && N > 0 && M > 0, "update_counters: non-positive shape");
+  SBB_TRY(need_device());
+  return DISPATCH(dtype, update_counters_t<float>(Ci, Cj, Cij, a_i, a_o, taupdt, B, N, M),
+                  update_counters_t<double>(Ci, Cj, Cij, a_i, a_o, taupdt, B, N, M));
+}
+
+int sbb_update_weights(int dtype, void *Ci, void *Cj, void *Cij, const void *a_i, const void *a_o, double taupdt,
+                       long B, long N, long M, void *weights, double cthr) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(Ci && Cj && Cij && a_i && a_o && weights, "update_weights: null pointer");
+  ARG(B > 0 && N > 0 && M > 0, "update_weights: non-positive shape");
+  SBB_TRY(need_device());
+  return DISPATCH(dtype, update_weights_t<float>(Ci, Cj, Cij, a_i, a_o, taupdt, B, N, M, weights, cthr),
+                  update_weights_t<double>(Ci, Cj, Cij, a_i, a_o, taupdt, B, N, M, weights, cthr));
+}
+
+int sbb_recompute_weights(int dtype, void *weights, const void *Ci, const void *Cj, const void *Cij, double cthr,
+                          long N, long M) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(weights && Ci && Cj && Cij, "recompute_weights: null pointer");
+  ARG(N > 0 && M > 0, "recompute_weights: non-positive shape");
+  SBB_TRY(need_device());
+  return DISPATCH(dtype, recompute_weights_t<float>(weights, Ci, Cj, Cij, cthr, N, M),
+                  recompute_weights_t<double>(weights, Ci, Cj, Cij, cthr, N, M));
+}
+
+int sbb_update_bias(int dtype, void *bias, const void *Cj, double cthr, long M) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(bias && Cj, "update_bias: null pointer");
+  ARG(M > 0, "update_bias: non-positive size");
+  SBB_TRY(need_device());
+  const size_t s = esize(dtype);
+  Staged db, dc;
+  SBB_TRY(db.alloc(M * s));
+  SBB_TRY(dc.upload(Cj, M * s));
+  if (dtype == SBB_F32) SBB_CUDA(sbb::launch_update_bias<float>(db.as<float>(), dc.as<float>(), (float)cthr, M, 0));
+  else SBB_CUDA(sbb::launch_update_bias<double>(db.as<double>(), dc.as<double>(), cthr, M, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  return db.download(bias);
+}
+
+int sbb_update_bias_regularized(int dtype, void *bias, void *kbi, const void *Cj, double cthr, double khalf,
+                                double pmin, double taubdt, long M) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(bias && kbi && Cj, "update_bias_regularized: null pointer");
+  ARG(M > 0, "update_bias_regularized: non-positive size");
+  SBB_TRY(need_device());
+  const size_t s = esize(dtype);
+  Staged db, dk, dc;
+  SBB_TRY(db.alloc(M * s));
+  SBB_TRY(dk.upload(kbi, M * s));
+  SBB_TRY(dc.upload(Cj, M * s));
+  if (dtype == SBB_F32)
+    SBB_CUDA(sbb::launch_update_bias_regularized<float>(db.as<float>(), dk.as<float>(), dc.as<float>(), (float)cthr,
+                                                        (float)khalf, (float)pmin, (float)taubdt, M, 0));
+  else
+    SBB_CUDA(sbb::launch_update_bias_regularized<double>(db.as<double>(), dk.as<double>(), dc.as<double>(), cthr, khalf,
+                                                         pmin, taubdt, M, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_TRY(db.download(bias));
+  return dk.download(kbi);
+}
+
+int sbb_update_mask(int dtype, uint8_t *wmask, const void *weights, const void *Ci, const void *Cj, const void *Cij,
+                    double cthr, long N, long M, long H, long Mc, long h, long iterations) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(wmask && weights && Ci && Cj && Cij, "update_mask: null pointer");
+  ARG(N > 0 && H > 0 && Mc > 0 && M == H * Mc, "update_mask: shape mismatch N=%ld M=%ld H=%ld Mc=%ld", N, M, H, Mc);
+  ARG(h >= 0 && h < H, "update_mask: hypercolumn %ld outside [0,%ld)", h, H);
+  ARG(iterations >= 0, "update_mask: negative iteration count");
+  SBB_TRY(need_device());
+  return DISPATCH(dtype, update_mask_t<float>(wmask, weights, Ci, Cj, Cij, cthr, N, M, H, Mc, h, iterations),
+                  update_mask_t<double>(wmask, weights, Ci, Cj, Cij, cthr, N, M, H, Mc, h, iterations));
+}
+
+int sbb_apply_mask(int dtype, void *weights, const uint8_t *wmask, long N, long M, long H, long Mc) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(weights && wmask, "apply_mask: null pointer");
+  ARG(N > 0 && H > 0 && Mc > 0 && M == H * Mc, "apply_mask: shape mismatch N=%ld M=%ld H=%ld Mc=%ld", N, M, H, Mc);
+  SBB_TRY(need_device());
+  Staged dw, dm;
+  SBB_TRY(dw.upload(weights, N * M * esize(dtype)));
+  SBB_TRY(dm.upload(wmask, N * H));
+  if (dtype == SBB_F32) SBB_CUDA(sbb::launch_apply_mask<float>(dw.as<float>(), dm.as<uint8_t>(), N, M, H, Mc, 0));
+  else SBB_CUDA(sbb::launch_apply_mask<double>(dw.as<double>(), dm.as<uint8_t>(), N, M, H, Mc, 0));
+  SBB_CUDA(cudaDeviceSynchronize());
+  return dw.download(weights);
+}
+
+// -------------------------------------------------------------------- layer
+int sbb_layer_create(const sbb_layer_desc *desc, sbb_layer **out) {
+  ARG(desc && out, "layer_create: null pointer");
+  *out = nullptr;
+  SBB_TRY(check_dtype(desc->dtype));
+  ARG(desc->kind == SBB_LAYER_DENSE || desc->kind == SBB_LAYER_PLASTIC, "layer_create: invalid kind %d", desc->kind);
+  ARG(desc->in_features > 0 && desc->hypercolumns > 0 && desc->minicolumns > 0,
+      "layer_create: non-positive shape N=%ld H=%ld Mc=%ld", desc->in_features, desc->hypercolumns, desc->minicolumns);
+  ARG(desc->mask_iterations >= 0, "layer_create: negative mask_iterations");
+  SBB_TRY(need_device());
+  sbb_layer *L = new sbb_layer();
+  L->desc = *desc;
+  L->N = desc->in_features;
+  L->H = desc->hypercolumns;
+  L->Mc = desc->minicolumns;
+  L->M = L->H * L->Mc;
+  const size_t s = esize(desc->dtype);
+  L->state_bytes[SBB_STATE_WEIGHTS] = (size_t)L->N * L->M * s;
+  L->state_bytes[SBB_STATE_BIAS] = (size_t)L->M * s;
+  L->state_bytes[SBB_STATE_CI] = (size_t)L->N * s;
+  L->state_bytes[SBB_STATE_CJ] = (size_t)L->M * s;
+  L->state_bytes[SBB_STATE_CIJ] = (size_t)L->N * L->M * s;
+  if (desc->kind == SBB_LAYER_PLASTIC) {
+    L->state_bytes[SBB_STATE_KBI] = (size_t)L->M * s;
+    L->state_bytes[SBB_STATE_WMASK] = (size_t)L->N * L->H;
+  }
+  int rc = SBB_OK;
+  cudaError_t e = cudaGetDevice(&L->device);
+  for (int k = 0; k < 7 && e == cudaSuccess; ++k)
+    if (L->state_bytes[k]) {
+      e = cudaMalloc(&L->state[k], L->state_bytes[k]);
+      if (e == cudaSuccess) e = cudaMemset(L->state[k], 0, L->state_bytes[k]);
+    }
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) rc = cuda_fail(e, "layer_create");
+  if (rc == SBB_OK && desc->kind == SBB_LAYER_PLASTIC) {
+    rc = L->score.reserve((size_t)L->N * s);
+    if (rc == SBB_OK) rc = L->csum.reserve((size_t)L->N * sizeof(int));
+  }
+  if (rc != SBB_OK) {
+    std::string keep = g_error;
+    sbb_layer_destroy(L);
+    g_error = keep;
+    return rc;
+  }
+  *out = L;
+  return SBB_OK;
+}
+
+int sbb_layer_destroy(sbb_layer *L) {
+  if (!L) return SBB_OK;
+  for (int k = 0; k < 7; ++k)
+    if (L->state[k]) cudaFree(L->state[k]);
+  L->fwd_partial.release();
+  L->score.release();
+  L->csum.release();
+  L->hx.release();
+  L->hy.release();
+  L->ht.release();
+  if (L->own_stream) cudaStreamDestroy(L->own_stream);
+  delete L;
+  return SBB_OK;
+}
+
+static int state_slot(const sbb_layer *L, int which, size_t bytes, bool check_bytes) {
+  if (!L) return fail(SBB_ERR_INVALID, "null layer handle");
+  ARG(which >= 0 && which < 7, "invalid state index %d", which);
+  ARG(L->state_bytes[which] != 0, "state %d does not exist for this layer kind", which);
+  if (check_bytes)
+    ARG(bytes == L->state_bytes[which], "state %d holds %zu bytes, caller passed %zu", which, L->state_bytes[which],
+        bytes);
+  return SBB_OK;
+}
+
+int sbb_layer_set_state(sbb_layer *L, int which, const void *host, size_t bytes) {
+  SBB_TRY(state_slot(L, which, bytes, true));
+  ARG(host, "set_state: null pointer");
+  SBB_TRY(check_layer(L));
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_CUDA(cudaMemcpy(L->state[which], host, bytes, cudaMemcpyHostToDevice));
+  return SBB_OK;
+}
+
+int sbb_layer_get_state(sbb_layer *L, int which, void *host, size_t bytes) {
+  SBB_TRY(state_slot(L, which, bytes, true));
+  ARG(host, "get_state: null pointer");
+  SBB_TRY(check_layer(L));
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_CUDA(cudaMemcpy(host, L->state[which], bytes, cudaMemcpyDeviceToHost));
+  return SBB_OK;
+}
+
+int sbb_layer_state_ptr(sbb_layer *L, int which, void **device_ptr) {
+  SBB_TRY(state_slot(L, which, 0, false));
+  ARG(device_ptr, "state_ptr: null pointer");
+  *device_ptr = L->state[which];
+  return SBB_OK;
+}
+
+int sbb_layer_forward(sbb_layer *L, const void *x_dev, long B, void *y_dev, void *stream) {
+  SBB_TRY(check_layer(L));
+  ARG(x_dev && y_dev, "layer_forward: null pointer");
+  SBB_TRY(check_batch(L, B));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, layer_forward<float>(L, (const float *)x_dev, B, (float *)y_dev, st),
+                  layer_forward<double>(L, (const double *)x_dev, B, (double *)y_dev, st));
+}
+
+int sbb_layer_train_step(sbb_layer *L, const void *x_dev, const void *y_dev, long B, long hypercolumn, void *stream) {
+  SBB_TRY(check_layer(L));
+  ARG(x_dev && y_dev, "layer_train_step: null pointer");
+  SBB_TRY(check_batch(L, B));
+  ARG(hypercolumn < L->H, "layer_train_step: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+  if (L->desc.kind != SBB_LAYER_PLASTIC) hypercolumn = -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype,
+                  layer_train_step<float>(L, (const float *)x_dev, (const float *)y_dev, B, hypercolumn, st),
+                  layer_train_step<double>(L, (const double *)x_dev, (const double *)y_dev, B, hypercolumn, st));
+}
+
+int sbb_layer_train_finalize(sbb_layer *L, void *stream) {
+  SBB_TRY(check_layer(L));
+  if (L->desc.kind != SBB_LAYER_DENSE) return SBB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const double cthr = L->desc.taupdt / 2;
+  if (L->desc.dtype == SBB_F32)
+    SBB_CUDA(sbb::launch_update_bias<float>((float *)L->state[SBB_STATE_BIAS], (const float *)L->state[SBB_STATE_CJ],
+                                            (float)cthr, L->M, st));
+  else
+    SBB_CUDA(sbb::launch_update_bias<double>((double *)L->state[SBB_STATE_BIAS],
+                                             (const double *)L->state[SBB_STATE_CJ], cthr, L->M, st));
+  return SBB_OK;
+}
+
+int sbb_layer_forward_host(sbb_layer *L, const void *x_host, long B, void *y_host) {
+  SBB_TRY(check_layer(L));
+  ARG(x_host && y_host, "layer_forward_host: null pointer");
+  SBB_TRY(check_batch(L, B));
+  const size_t s = esize(L->desc.dtype);
+  SBB_TRY(L->hx.reserve((size_t)B * L->N * s));
+  SBB_TRY(L->hy.reserve((size_t)B * L->M * s));
+  cudaStream_t st = L->own_stream;
+  // Work queued earlier on other streams (a device-buffer call) must have landed
+  // before this call reads or rewrites the layer state on its own stream.
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_CUDA(cudaMemcpyAsync(L->hx.d, x_host, (size_t)B * L->N * s, cudaMemcpyHostToDevice, st));
+  SBB_TRY(DISPATCH(L->desc.dtype, layer_forward<float>(L, (const float *)L->hx.d, B, (float *)L->hy.d, st),
+                   layer_forward<double>(L, (const double *)L->hx.d, B, (double *)L->hy.d, st)));
+  SBB_CUDA(cudaMemcpyAsync(y_host, L->hy.d, (size_t)B * L->M * s, cudaMemcpyDeviceToHost, st));
+  SBB_CUDA(cudaStreamSynchronize(st));
+  return SBB_OK;
+}
+
+int sbb_layer_train_step_host(sbb_layer *L, const void *x_host, const void *y_host, long B, long hypercolumn) {
+  SBB_TRY(check_layer(L));
+  ARG(x_host && y_host, "layer_train_step_host: null pointer");
+  SBB_TRY(check_batch(L, B));
+  ARG(hypercolumn < L->H, "layer_train_step_host: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+  if (L->desc.kind != SBB_LAYER_PLASTIC) hypercolumn = -1;
+  const size_t s = esize(L->desc.dtype);
+  SBB_TRY(L->hx.reserve((size_t)B * L->N * s));
+  SBB_TRY(L->ht.reserve((size_t)B * L->M * s));
+  cudaStream_t st = L->own_stream;
+  // Work queued earlier on other streams (a device-buffer call) must have landed
+  // before this call reads or rewrites the layer state on its own stream.
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_CUDA(cudaMemcpyAsync(L->hx.d, x_host, (size_t)B * L->N * s, cudaMemcpyHostToDevice, st));
+  SBB_CUDA(cudaMemcpyAsync(L->ht.d, y_host, (size_t)B * L->M * s, cudaMemcpyHostToDevice, st));
+  SBB_TRY(DISPATCH(L->desc.dtype,
+                   layer_train_step<float>(L, (const float *)L->hx.d, (const float *)L->ht.d, B, hypercolumn, st),
+                   layer_train_step<double>(L, (const double *)L->hx.d, (const double *)L->ht.d, B, hypercolumn, st)));
+  SBB_CUDA(cudaStreamSynchronize(st));
+  return SBB_OK;
+}
+
+int sbb_layer_step_host(sbb_layer *L, const void *x_host, const void *target_host, long B, long hypercolumn,
+                        void *y_host) {
+  SBB_TRY(check_layer(L));
+  ARG(x_host, "layer_step_host: null pointer");
+  SBB_TRY(check_batch(L, B));
+  ARG(hypercolumn < L->H, "layer_step_host: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+  if (L->desc.kind != SBB_LAYER_PLASTIC) hypercolumn = -1;
+  const size_t s = esize(L->desc.dtype);
+  SBB_TRY(L->hx.reserve((size_t)B * L->N * s));
+  SBB_TRY(L->hy.reserve((size_t)B * L->M * s));
+  if (target_host) SBB_TRY(L->ht.reserve((size_t)B * L->M * s));
+  cudaStream_t st = L->own_stream;
+  // Work queued earlier on other streams (a device-buffer call) must have landed
+  // before this call reads or rewrites the layer state on its own stream.
+  SBB_CUDA(cudaDeviceSynchronize());
+  SBB_CUDA(cudaMemcpyAsync(L->hx.d, x_host, (size_t)B * L->N * s, cudaMemcpyHostToDevice, st));
+  if (target_host)
+    SBB_CUDA(cudaMemcpyAsync(L->ht.d, target_host, (size_t)B * L->M * s, cudaMemcpyHostToDevice, st));
+  const void *train_on = target_host ? L->ht.d : L->hy.d;
+  if (L->desc.dtype == SBB_F32) {
+    SBB_TRY(layer_forward<float>(L, (const float *)L->hx.d, B, (float *)L->hy.d, st));
+    SBB_TRY(layer_train_step<float>(L, (const float *)L->hx.d, (const float *)train_on, B, hypercolumn, st));
+  } else {
+    SBB_TRY(layer_forward<double>(L, (const double *)L->hx.d, B, (double *)L->hy.d, st));
+    SBB_TRY(layer_train_step<double>(L, (const double *)L->hx.d, (const double *)train_on, B, hypercolumn, st));
+  }
+  if (y_host) SBB_CUDA(cudaMemcpyAsync(y_host, L->hy.d, (size_t)B * L->M * s, cudaMemcpyDeviceToHost, st));
+  SBB_CUDA(cudaStreamSynchronize(st));
+  return SBB_OK;
+}
+
+// ------------------------------------------------------------ data parallel
+size_t sbb_layer_delta_elems(const sbb_layer *L) {
+  if (!L) return 0;
+  return (size_t)L->N + (size_t)L->M + (size_t)L->N * L->M;
+}
+
+static int check_rows(const sbb_layer *L, long rb, long re) {
+  ARG(rb >= 0 && re <= L->N && rb <= re, "row range [%ld,%ld) outside [0,%ld)", rb, re, L->N);
+  ARG(rb % 128 == 0, "row_begin %ld is not a multiple of 128", rb);
+  return SBB_OK;
+}
+
+int sbb_layer_dp_local(sbb_layer *L, const void *x_dev, const void *y_dev, long B_local, void *delta_dev,
+                       long row_begin, long row_end, void *stream) {
+  SBB_TRY(check_layer(L));
+  ARG(x_dev && y_dev && delta_dev, "dp_local: null pointer");
+  SBB_TRY(check_batch(L, B_local));
+  SBB_TRY(check_rows(L, row_begin, row_end));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype,
+                  layer_dp_local<float>(L, (const float *)x_dev, (const float *)y_dev, B_local, (float *)delta_dev,
+                                        row_begin, row_end, st),
+                  layer_dp_local<double>(L, (const double *)x_dev, (const double *)y_dev, B_local,
+                                         (double *)delta_dev, row_begin, row_end, st));
+}
+
+int sbb_layer_dp_apply_vectors(sbb_layer *L, const void *delta_dev, long B_global, void *stream) {
+  SBB_TRY(check_layer(L));
+  ARG(delta_dev, "dp_apply_vectors: null pointer");
+  ARG(B_global > 0, "dp_apply_vectors: non-positive global batch");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, layer_dp_apply_vectors<float>(L, (const float *)delta_dev, B_global, st),
+                  layer_dp_apply_vectors<double>(L, (const double *)delta_dev, B_global, st));
+}
+
+int sbb_layer_dp_apply_rows(sbb_layer *L, const void *delta_dev, long B_global, long row_begin, long row_end,
+                            void *stream) {
+  SBB_TRY(check_layer(L));
+  ARG(delta_dev, "dp_apply_rows: null pointer");
+  ARG(B_global > 0, "dp_apply_rows: non-positive global batch");
+  SBB_TRY(check_rows(L, row_begin, row_end));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype,
+                  layer_dp_apply_rows<float>(L, (const float *)delta_dev, B_global, row_begin, row_end, st),
+                  layer_dp_apply_rows<double>(L, (const double *)delta_dev, B_global, row_begin, row_end, st));
+}
+
+int sbb_layer_dp_finish(sbb_layer *L, long hypercolumn, void *stream) {
+  SBB_TRY(check_layer(L));
+  ARG(hypercolumn < L->H, "dp_finish: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, layer_finish<float>(L, hypercolumn, st), layer_finish<double>(L, hypercolumn, st));
+}
+
+int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, long rows, long classes,
+                      long *correct_host, void *stream) {
+  SBB_TRY(check_dtype(dtype));
+  ARG(pred_dev && labels_dev && correct_host, "count_correct: null pointer");
+  ARG(rows >= 0 && classes > 0, "count_correct: bad shape");
+  SBB_TRY(need_device());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Staged cnt;
+  SBB_TRY(cnt.alloc(sizeof(unsigned long long)));
+  SBB_CUDA(cudaMemsetAsync(cnt.d, 0, sizeof(unsigned long long), st));
+  if (dtype == SBB_F32)
+    SBB_CUDA(sbb::launch_count_correct<float>((const float *)pred_dev, (const float *)labels_dev, rows, classes,
+                                              cnt.as<unsigned long long>(), st));
+  else
+    SBB_CUDA(sbb::launch_count_correct<double>((const double *)pred_dev, (const double *)labels_dev, rows, classes,
+                                               cnt.as<unsigned long long>(), st));
+  unsigned long long h = 0;
+  SBB_CUDA(cudaMemcpyAsync(&h, cnt.d, sizeof(h), cudaMemcpyDeviceToHost, st));
+  SBB_CUDA(cudaStreamSynchronize(st));
+  *correct_host = (long)h;
+  return SBB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,1051 @@
+// General-shape CUDA kernels of the BCPNN layer train step (float and double).
+//
+// These are the kernels that accept any N, M, B (odd sizes, unaligned rows, the
+// 10-column classifier) and the float64 path; the tcgen05 tile kernels for
+// aligned float32 shapes live in their own translation unit and share the
+// arithmetic helpers below.
+//
+// Data layout: every matrix is row-major and contiguous.  x[B,N], y[B,M],
+// weights/Cij[N,M], wmask[N,H] bytes.  Both contractions of the step read their
+// operands "MN-major" (contiguous along the output dimension) except the forward
+// product's x, which is contiguous along the reduction dimension and is
+// transposed on its way into shared memory.
+#include "sbb_kernels.cuh"
+
+#include <atomic>
+#include <math.h>
+
+namespace sbb {
+
+static std::atomic<unsigned long long> g_launches{0};
+unsigned long long kernel_launches() { return g_launches.load(); }
+static inline cudaError_t launched(int n = 1) {
+  g_launches += (unsigned long long)n;
+  return cudaGetLastError();
+}
+
+template <typename T>
+TraceParams<T> make_trace_params(double taupdt, double cthr, long batch) {
+  TraceParams<T> p;
+  p.taupdt = (T)taupdt;
+  // The reference forms (1.0 - taupdt) in double from the REAL-rounded taupdt and
+  // rounds the result to REAL (kernels_openmp_internal.cc:101).
+  p.one_minus = (T)(1.0 - (double)p.taupdt);
+  p.batch = (T)batch;
+  p.cthr = (T)cthr;
+  p.cthr4 = p.cthr * p.cthr * p.cthr * p.cthr;
+  return p;
+}
+template TraceParams<float> make_trace_params<float>(double, double, long);
+template TraceParams<double> make_trace_params<double>(double, double, long);
+
+// ----------------------------------------------------------------------------
+// Arithmetic shared by every kernel that touches a trace or a weight.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ float sbb_log(float x) { return logf(x); }
+__device__ __forceinline__ double sbb_log(double x) { return log(x); }
+__device__ __forceinline__ float sbb_exp(float x) { return expf(x); }
+__device__ __forceinline__ double sbb_exp(double x) { return exp(x); }
+
+// One moving-average step from a batch sum: sum/B, *taupdt, old*(1-taupdt), add,
+// clamp at zero (a NaN clamps to zero, as std::max(0, NaN) does).
+template <typename T>
+__device__ __forceinline__ T trace_ema(T old, T sum, const TraceParams<T> &p) {
+  T tmp = sum / p.batch;
+  tmp = tmp * p.taupdt;
+  T c = old * p.one_minus;
+  c = c + tmp;
+  return c > (T)0 ? c : (T)0;
+}
+
+template <typename T>
+__device__ __forceinline__ T log_ratio(T cij, T ci, T cj, T cthr4) {
+  const T num = cij < cthr4 ? cthr4 : cij;
+  return sbb_log(num / (ci * cj));
+}
+
+// ----------------------------------------------------------------------------
+// 16-byte vector helpers.
+// ----------------------------------------------------------------------------
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+  using type = float4;
+  static constexpr int N = 4;
+};
+template <>
+struct Vec16<double> {
+  using type = double2;
+  static constexpr int N = 2;
+};
+
+__device__ __forceinline__ void unpack(const float4 &v, float *r) {
+  r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+}
+__device__ __forceinline__ void unpack(const double2 &v, double *r) {
+  r[0] = v.x; r[1] = v.y;
+}
+__device__ __forceinline__ float4 pack(const float *r) { return make_float4(r[0], r[1], r[2], r[3]); }
+__device__ __forceinline__ double2 pack(const double *r) { return make_double2(r[0], r[1]); }
+
+// Four consecutive elements from / to memory.  `vec` says the address is 16-byte
+// aligned and all four are in range; otherwise `valid` (1..4) elements are touched.
+__device__ __forceinline__ void load4(const float *p, float *r, bool vec, int valid) {
+  if (vec && valid == 4) {
+    unpack(*reinterpret_cast<const float4 *>(p), r);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) r[c] = c < valid ? p[c] : 0.f;
+  }
+}
+__device__ __forceinline__ void load4(const double *p, double *r, bool vec, int valid) {
+  if (vec && valid == 4) {
+    unpack(*reinterpret_cast<const double2 *>(p), r);
+    unpack(*reinterpret_cast<const double2 *>(p + 2), r + 2);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) r[c] = c < valid ? p[c] : 0.0;
+  }
+}
+__device__ __forceinline__ void store4(float *p, const float *r, bool vec, int valid) {
+  if (vec && valid == 4) {
+    *reinterpret_cast<float4 *>(p) = pack(r);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (c < valid) p[c] = r[c];
+  }
+}
+__device__ __forceinline__ void store4(double *p, const double *r, bool vec, int valid) {
+  if (vec && valid == 4) {
+    *reinterpret_cast<double2 *>(p) = pack(r);
+    *reinterpret_cast<double2 *>(p + 2) = pack(r + 2);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (c < valid) p[c] = r[c];
+  }
+}
+
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ----------------------------------------------------------------------------
+// Tiled contraction core: C[Mdim, Ndim] (+)= A^T-or-A * B over k in [k0, k1).
+// 128x128 output tile per 256-thread CTA, 8x8 micro-tile per thread split into
+// two 4-wide halves in each dimension (rows ty*4+r and 64+ty*4+r; columns
+// tx*4+c and 64+tx*4+c) so shared-memory reads are conflict-free 16-byte loads
+// and global stores are 16 bytes per thread, 256 contiguous bytes per half-warp.
+// The next k-slab is fetched into registers while the current one is multiplied.
+// ----------------------------------------------------------------------------
+template <typename T>
+struct Tile {
+  static constexpr int BM = 128, BN = 128, THREADS = 256;
+  static constexpr int BK = sizeof(T) == 4 ? 16 : 8;
+  static constexpr int LD = 128 + 4;                // shared row stride, elements
+  static constexpr int EPT = BK * 128 / THREADS;    // elements per thread per operand slab
+};
+
+// Operand stored "MN-major": element (k, m) at p[k*ld + m].
+template <typename T, int VEC>
+__device__ __forceinline__ void load_mn(T (&r)[Tile<T>::EPT], const T *__restrict__ p, long ld, int k0, int k1,
+                                        long m0, long mn) {
+  constexpr int VPR = 128 / VEC;
+#pragma unroll
+  for (int t = 0; t < Tile<T>::EPT / VEC; ++t) {
+    const int v = threadIdx.x + t * Tile<T>::THREADS;
+    const int k = k0 + v / VPR;
+    const long m = m0 + (long)(v % VPR) * VEC;
+    const bool ok = k < k1 && m < mn;
+    if constexpr (VEC == 1) {
+      r[t] = ok ? __ldg(p + (long)k * ld + m) : (T)0;
+    } else {
+      using V = typename Vec16<T>::type;
+      if (ok) {
+        unpack(__ldg(reinterpret_cast<const V *>(p + (long)k * ld + m)), &r[t * VEC]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) r[t * VEC + e] = (T)0;
+      }
+    }
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_mn(T *s, const T (&r)[Tile<T>::EPT]) {
+  constexpr int VPR = 128 / VEC;
+#pragma unroll
+  for (int t = 0; t < Tile<T>::EPT / VEC; ++t) {
+    const int v = threadIdx.x + t * Tile<T>::THREADS;
+    const int k = v / VPR;
+    const int m = (v % VPR) * VEC;
+    if constexpr (VEC == 1) {
+      s[k * Tile<T>::LD + m] = r[t];
+    } else {
+      using V = typename Vec16<T>::type;
+      *reinterpret_cast<V *>(s + k * Tile<T>::LD + m) = pack(&r[t * VEC]);
+    }
+  }
+}
+
+// Operand stored "K-major": element (k, m) at p[m*ld + k]; transposed into shared.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_km(T (&r)[Tile<T>::EPT], const T *__restrict__ p, long ld, int k0, int k1,
+                                        long m0, long mn) {
+  constexpr int VPR = Tile<T>::BK / VEC;
+#pragma unroll
+  for (int t = 0; t < Tile<T>::EPT / VEC; ++t) {
+    const int v = threadIdx.x + t * Tile<T>::THREADS;
+    const long m = m0 + v / VPR;
+    const int k = k0 + (v % VPR) * VEC;
+    const bool ok = m < mn && k < k1;
+    if constexpr (VEC == 1) {
+      r[t] = ok ? __ldg(p + m * ld + k) : (T)0;
+    } else {
+      using V = typename Vec16<T>::type;
+      if (ok) {
+        unpack(__ldg(reinterpret_cast<const V *>(p + m * ld + k)), &r[t * VEC]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) r[t * VEC + e] = (T)0;
+      }
+    }
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_km(T *s, const T (&r)[Tile<T>::EPT]) {
+  constexpr int VPR = Tile<T>::BK / VEC;
+#pragma unroll
+  for (int t = 0; t < Tile<T>::EPT / VEC; ++t) {
+    const int v = threadIdx.x + t * Tile<T>::THREADS;
+    const int m = v / VPR;
+    const int k = (v % VPR) * VEC;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) s[(k + e) * Tile<T>::LD + m] = r[t * VEC + e];
+  }
+}
+
+__device__ __forceinline__ void lds4(const float *p, float *r) { unpack(*reinterpret_cast<const float4 *>(p), r); }
+__device__ __forceinline__ void lds4(const double *p, double *r) {
+  unpack(*reinterpret_cast<const double2 *>(p), r);
+  unpack(*reinterpret_cast<const double2 *>(p + 2), r + 2);
+}
+
+template <typename T>
+__device__ __forceinline__ void multiply_slab(const T *As, const T *Bs, T (&acc)[8][8], int ty, int tx) {
+#pragma unroll
+  for (int k = 0; k < Tile<T>::BK; ++k) {
+    T a[8], b[8];
+    lds4(As + k * Tile<T>::LD + ty * 4, a);
+    lds4(As + k * Tile<T>::LD + 64 + ty * 4, a + 4);
+    lds4(Bs + k * Tile<T>::LD + tx * 4, b);
+    lds4(Bs + k * Tile<T>::LD + 64 + tx * 4, b + 4);
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[r][c] = fma(a[r], b[c], acc[r][c]);
+  }
+}
+
+// Row / column of micro-tile entry e (0..7) inside the 128-wide tile.
+__device__ __forceinline__ int micro_index(int t, int e) { return (e < 4 ? 0 : 64) + t * 4 + (e & 3); }
+
+// grid.x = row tiles of the output, grid.y = column tiles, grid.z = k-splits.
+// A is [K x Mdim] MN-major (A_KMAJOR=false) or [Mdim x K] K-major (true); B is
+// [K x Ndim] MN-major.  k-split z covers [z*kper, min(K,(z+1)*kper)), kper a
+// multiple of the slab depth.
+template <typename T, bool A_KMAJOR, int VEC, class Epilogue>
+__global__ void __launch_bounds__(256, sizeof(T) == 4 ? 2 : 1)
+    contraction_kernel(const T *__restrict__ A, long lda, const T *__restrict__ Bm, long ldb, long Mdim, long Ndim,
+                       int K, int kper, Epilogue ep) {
+  using TL = Tile<T>;
+  __shared__ __align__(16) T As[2][TL::BK * TL::LD];
+  __shared__ __align__(16) T Bs[2][TL::BK * TL::LD];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const long m0 = (long)blockIdx.x * TL::BM, n0 = (long)blockIdx.y * TL::BN;
+  const int kbeg = blockIdx.z * kper;
+  const int kend = min(K, kbeg + kper);
+
+  T acc[8][8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[r][c] = (T)0;
+
+  T ra[TL::EPT], rb[TL::EPT];
+  if (kbeg < kend) {
+    if constexpr (A_KMAJOR) load_km<T, VEC>(ra, A, lda, kbeg, kend, m0, Mdim);
+    else load_mn<T, VEC>(ra, A, lda, kbeg, kend, m0, Mdim);
+    load_mn<T, VEC>(rb, Bm, ldb, kbeg, kend, n0, Ndim);
+    if constexpr (A_KMAJOR) store_km<T, VEC>(As[0], ra);
+    else store_mn<T, VEC>(As[0], ra);
+    store_mn<T, VEC>(Bs[0], rb);
+  }
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = kbeg; k0 < kend; k0 += TL::BK) {
+    const int kn = k0 + TL::BK;
+    const bool more = kn < kend;
+    if (more) {
+      if constexpr (A_KMAJOR) load_km<T, VEC>(ra, A, lda, kn, kend, m0, Mdim);
+      else load_mn<T, VEC>(ra, A, lda, kn, kend, m0, Mdim);
+      load_mn<T, VEC>(rb, Bm, ldb, kn, kend, n0, Ndim);
+    }
+    multiply_slab<T>(As[buf], Bs[buf], acc, ty, tx);
+    if (more) {
+      if constexpr (A_KMAJOR) store_km<T, VEC>(As[buf ^ 1], ra);
+      else store_mn<T, VEC>(As[buf ^ 1], ra);
+      store_mn<T, VEC>(Bs[buf ^ 1], rb);
+    }
+    __syncthreads();
+    buf ^= 1;
+  }
+  ep(acc, m0, n0, ty, tx, (int)blockIdx.z);
+}
+
+// Epilogue: partial[z, m, n] = acc  (forward product) or delta[m, n] = acc.
+template <typename T>
+struct StoreEpilogue {
+  T *out;
+  long rows, cols;   // logical extent of one [rows, cols] slice
+  long ld;           // row stride of out
+  long zstride;      // elements between k-split slices
+  bool vec;
+  __device__ __forceinline__ void operator()(T (&acc)[8][8], long m0, long n0, int ty, int tx, int z) const {
+    T *base = out + (long)z * zstride;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const long m = m0 + micro_index(ty, r);
+      if (m >= rows) continue;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const long n = n0 + g * 64 + tx * 4;
+        const long left = cols - n;
+        if (left <= 0) continue;
+        store4(base + m * ld + n, &acc[r][g * 4], vec, left >= 4 ? 4 : (int)left);
+      }
+    }
+  }
+};
+
+// Epilogue of the fused trace step: moving average of Cij, log-ratio weight,
+// threshold and mask zeroing.  Each Cij element is read once and written once.
+template <typename T>
+struct TraceEpilogue {
+  const T *Ci;
+  const T *Cj;
+  T *Cij;
+  T *W;
+  const uint8_t *wmask;  // [N, H] or null
+  long row0;             // global row of tile row 0
+  long row_end;          // global row limit
+  long M, H, Mc;
+  TraceParams<T> p;
+  bool vec;
+  __device__ __forceinline__ void operator()(T (&acc)[8][8], long m0, long n0, int ty, int tx, int) const {
+    T cj[8];
+    int hc[8];
+    bool cj_low[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const long j = n0 + micro_index(tx, c);
+      const bool in = j < M;
+      cj[c] = in ? Cj[j] : (T)1;
+      cj_low[c] = cj[c] < p.cthr;
+      hc[c] = in ? (int)(j / Mc) : 0;
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const long i = row0 + m0 + micro_index(ty, r);
+      if (i >= row_end) continue;
+      const T ci = Ci[i];
+      const bool skip = ci < p.cthr;
+      const uint8_t *mrow = wmask ? wmask + i * H : nullptr;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const long j = n0 + g * 64 + tx * 4;
+        const long left = M - j;
+        if (left <= 0) continue;
+        const int valid = left >= 4 ? 4 : (int)left;
+        T c4[4], w4[4];
+        load4(Cij + i * M + j, c4, vec, valid);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (c < valid) {
+            const T cij = trace_ema(c4[c], acc[r][g * 4 + c], p);
+            c4[c] = cij;
+            T w = (T)0;
+            if (!skip && !cj_low[g * 4 + c] && (mrow == nullptr || mrow[hc[g * 4 + c]] != 0))
+              w = log_ratio(cij, ci, cj[g * 4 + c], p.cthr4);
+            w4[c] = w;
+          }
+        }
+        store4(Cij + i * M + j, c4, vec, valid);
+        store4(W + i * M + j, w4, vec, valid);
+      }
+    }
+  }
+};
+
+template <typename T, bool A_KMAJOR, class Ep>
+static cudaError_t launch_contraction(const T *A, long lda, const T *Bm, long ldb, long Mdim, long Ndim, int K,
+                                      int splits, int kper, bool vec, Ep ep, cudaStream_t st) {
+  dim3 grid((unsigned)((Mdim + 127) / 128), (unsigned)((Ndim + 127) / 128), (unsigned)splits);
+  if (grid.x == 0 || grid.y == 0 || K <= 0) return cudaSuccess;
+  if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidConfiguration;
+  constexpr int V = Vec16<T>::N;
+  if (vec)
+    contraction_kernel<T, A_KMAJOR, V, Ep><<<grid, 256, 0, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, ep);
+  else
+    contraction_kernel<T, A_KMAJOR, 1, Ep><<<grid, 256, 0, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, ep);
+  return launched();
+}
+
+// ----------------------------------------------------------------------------
+// Forward product (split over k so that small batches still fill the GPU).
+// ----------------------------------------------------------------------------
+static int g_sm_count = 0;
+static int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      g_sm_count = n;
+    else
+      g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+template <typename T>
+int forward_splits(long B, long N, long M) {
+  const long tiles = ((B + 127) / 128) * ((M + 127) / 128);
+  const long want = 2L * sm_count();           // two resident CTAs per SM
+  long s = tiles >= want ? 1 : want / (tiles > 0 ? tiles : 1);
+  const long slabs = (N + Tile<T>::BK - 1) / Tile<T>::BK;
+  const long max_s = slabs / 8 > 0 ? slabs / 8 : 1;  // at least 8 slabs per split
+  if (s > max_s) s = max_s;
+  if (s > 64) s = 64;
+  if (s < 1) s = 1;
+  return (int)s;
+}
+template int forward_splits<float>(long, long, long);
+template int forward_splits<double>(long, long, long);
+
+template <typename T>
+cudaError_t launch_forward_product(const T *x, const T *w, T *partial, long B, long N, long M, int splits,
+                                   cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  const long slabs = (N + Tile<T>::BK - 1) / Tile<T>::BK;
+  const int kper = (int)((slabs + splits - 1) / splits) * Tile<T>::BK;
+  const bool vec = (N % V == 0) && (M % V == 0) && aligned16(x) && aligned16(w);
+  StoreEpilogue<T> ep{partial, B, M, M, B * M, (M % V == 0) && aligned16(partial)};
+  return launch_contraction<T, true>(x, N, w, M, B, M, (int)N, splits, kper, vec, ep, st);
+}
+template cudaError_t launch_forward_product<float>(const float *, const float *, float *, long, long, long, int,
+                                                   cudaStream_t);
+template cudaError_t launch_forward_product<double>(const double *, const double *, double *, long, long, long, int,
+                                                    cudaStream_t);
+
+// ----------------------------------------------------------------------------
+// out = sum_s partial[s] + bias, then softmax per hypercolumn.
+// One sub-warp of `width` lanes per (row, hypercolumn) group.  A lane owns the
+// entries sub, sub+width, ... of its group; with CACHE > 0 they stay in registers
+// (Mc <= CACHE*width), otherwise they are re-read from `out`.
+// ----------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ T subwarp_max(T v, int width) {
+  for (int off = width >> 1; off > 0; off >>= 1) {
+    const T o = __shfl_xor_sync(0xffffffffu, v, off, width);
+    v = o > v ? o : v;
+  }
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ T subwarp_sum(T v, int width) {
+  for (int off = width >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off, width);
+  return v;
+}
+
+template <typename T, int CACHE>
+__global__ void __launch_bounds__(256)
+    reduce_bias_softmax_kernel(const T *partial, int splits, long slice, const T *__restrict__ bias, T *out,
+                               long groups, long H, long Mc, int width) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % width;
+  const long warp = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long g = warp * (32 / width) + lane / width;
+  const bool live = g < groups;
+  const long base = g * Mc;            // offset of the group inside [rows, H*Mc]
+  const long col0 = (g % H) * Mc;      // first column of the group
+  constexpr int NC = CACHE > 0 ? CACHE : 1;
+  T v[NC];
+  T mx = -INFINITY;
+  if (CACHE > 0) {
+#pragma unroll
+    for (int e = 0; e < NC; ++e) {
+      const long j = sub + (long)e * width;
+      T s = -INFINITY;
+      if (live && j < Mc) {
+        s = partial[base + j];
+        for (int z = 1; z < splits; ++z) s += partial[(long)z * slice + base + j];
+        if (bias) s += bias[col0 + j];
+      }
+      v[e] = s;
+      mx = s > mx ? s : mx;
+    }
+    mx = subwarp_max(mx, width);
+    T sum = (T)0;
+#pragma unroll
+    for (int e = 0; e < NC; ++e) {
+      const long j = sub + (long)e * width;
+      if (live && j < Mc) {
+        v[e] = sbb_exp(v[e] - mx);
+        sum += v[e];
+      }
+    }
+    sum = subwarp_sum(sum, width);
+#pragma unroll
+    for (int e = 0; e < NC; ++e) {
+      const long j = sub + (long)e * width;
+      if (live && j < Mc) out[base + j] = v[e] / sum;
+    }
+  } else {
+    if (live)
+      for (long j = sub; j < Mc; j += width) {
+        T s = partial[base + j];
+        for (int z = 1; z < splits; ++z) s += partial[(long)z * slice + base + j];
+        if (bias) s += bias[col0 + j];
+        out[base + j] = s;
+        mx = s > mx ? s : mx;
+      }
+    mx = subwarp_max(mx, width);
+    T sum = (T)0;
+    if (live)
+      for (long j = sub; j < Mc; j += width) {
+        const T e = sbb_exp(out[base + j] - mx);
+        out[base + j] = e;
+        sum += e;
+      }
+    sum = subwarp_sum(sum, width);
+    if (live)
+      for (long j = sub; j < Mc; j += width) out[base + j] = out[base + j] / sum;
+  }
+}
+
+// out[r, j] = sum_s partial[s, r, j] + bias[j]   (no softmax)
+template <typename T>
+__global__ void __launch_bounds__(256)
+    reduce_bias_kernel(const T *partial, int splits, long slice, const T *__restrict__ bias, T *out, long total,
+                       long M) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  T s = partial[idx];
+  for (int z = 1; z < splits; ++z) s += partial[(long)z * slice + idx];
+  if (bias) s += bias[idx % M];
+  out[idx] = s;
+}
+
+template <typename T>
+cudaError_t launch_reduce_bias_softmax(const T *partial, int splits, const T *bias, T *out, long rows, long H,
+                                       long Mc, int softmax, cudaStream_t st) {
+  const long M = H * Mc;
+  const long total = rows * M;
+  if (total == 0) return cudaSuccess;
+  if (!softmax) {
+    if (splits == 1 && bias == nullptr && partial == out) return cudaSuccess;
+    reduce_bias_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial, splits, total, bias, out, total, M);
+    return launched();
+  }
+  int width = 32;
+  while (width > 1 && (width >> 1) >= Mc) width >>= 1;
+  const long groups = rows * H;
+  const long per_warp = 32 / width;
+  const long warps = (groups + per_warp - 1) / per_warp;
+  const unsigned blocks = (unsigned)((warps + 7) / 8);
+  const long per_lane = (Mc + width - 1) / width;
+  if (per_lane <= 4)
+    reduce_bias_softmax_kernel<T, 4><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
+  else if (per_lane <= 16)
+    reduce_bias_softmax_kernel<T, 16><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
+  else
+    reduce_bias_softmax_kernel<T, 0><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
+  return launched();
+}
+template cudaError_t launch_reduce_bias_softmax<float>(const float *, int, const float *, float *, long, long, long,
+                                                       int, cudaStream_t);
+template cudaError_t launch_reduce_bias_softmax<double>(const double *, int, const double *, double *, long, long,
+                                                        long, int, cudaStream_t);
+
+// ----------------------------------------------------------------------------
+// Column sums over the batch (and, fused, the Ci / Cj moving averages).
+// Block = 32 columns x 8 row lanes; rows are summed in a fixed order.
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+    colsum_kernel(const T *__restrict__ a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema) {
+  __shared__ T part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long col = (long)blockIdx.x * 32 + tx;
+  T s = (T)0;
+  if (col < cols) {
+    long b = ty;
+    for (; b + 24 < B; b += 32) {
+      const T v0 = __ldg(a + b * cols + col), v1 = __ldg(a + (b + 8) * cols + col);
+      const T v2 = __ldg(a + (b + 16) * cols + col), v3 = __ldg(a + (b + 24) * cols + col);
+      s += v0; s += v1; s += v2; s += v3;
+    }
+    for (; b < B; b += 8) s += __ldg(a + b * cols + col);
+  }
+  part[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && col < cols) {
+    T t = part[0][tx];
+#pragma unroll
+    for (int r = 1; r < 8; ++r) t += part[r][tx];
+    if (ema) c[col] = trace_ema(c[col], t, p);
+    else sums[col] = t;
+  }
+}
+
+template <typename T>
+cudaError_t launch_colsum(const T *a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema, cudaStream_t st) {
+  if (cols == 0) return cudaSuccess;
+  colsum_kernel<T><<<(unsigned)((cols + 31) / 32), 256, 0, st>>>(a, B, cols, sums, c, p, ema);
+  return launched();
+}
+template cudaError_t launch_colsum<float>(const float *, long, long, float *, float *, TraceParams<float>, int,
+                                          cudaStream_t);
+template cudaError_t launch_colsum<double>(const double *, long, long, double *, double *, TraceParams<double>, int,
+                                           cudaStream_t);
+
+template <typename T>
+__global__ void vector_ema_kernel(T *c, const T *__restrict__ sums, long n, TraceParams<T> p) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) c[i] = trace_ema(c[i], sums[i], p);
+}
+template <typename T>
+cudaError_t launch_vector_ema(T *c, const T *sums, long n, TraceParams<T> p, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  vector_ema_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(c, sums, n, p);
+  return launched();
+}
+template cudaError_t launch_vector_ema<float>(float *, const float *, long, TraceParams<float>, cudaStream_t);
+template cudaError_t launch_vector_ema<double>(double *, const double *, long, TraceParams<double>, cudaStream_t);
+
+// ----------------------------------------------------------------------------
+// Trace step: fused (x^T y in the contraction, traces and weights in its
+// epilogue) and split (raw x^T y, then an element-wise tail).
+// ----------------------------------------------------------------------------
+template <typename T>
+cudaError_t launch_trace_update_fused(const T *x, const T *y, long B, long N, long M, long H, long Mc, const T *Ci,
+                                      const T *Cj, T *Cij, T *w, const uint8_t *wmask, TraceParams<T> p,
+                                      long row_begin, long row_end, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  if (row_end <= row_begin) return cudaSuccess;
+  const bool vec = (N % V == 0) && (M % V == 0) && (row_begin % V == 0) && ((row_end - row_begin) % V == 0) &&
+                   aligned16(x) && aligned16(y);
+  TraceEpilogue<T> ep{Ci, Cj, Cij, w, wmask, row_begin, row_end, M, H, Mc, p,
+                      (M % V == 0) && aligned16(Cij) && aligned16(w)};
+  const int kper = (int)((B + Tile<T>::BK - 1) / Tile<T>::BK) * Tile<T>::BK;
+  return launch_contraction<T, false>(x + row_begin, N, y, M, row_end - row_begin, M, (int)B, 1, kper, vec, ep, st);
+}
+template cudaError_t launch_trace_update_fused<float>(const float *, const float *, long, long, long, long, long,
+                                                      const float *, const float *, float *, float *,
+                                                      const uint8_t *, TraceParams<float>, long, long, cudaStream_t);
+template cudaError_t launch_trace_update_fused<double>(const double *, const double *, long, long, long, long, long,
+                                                       const double *, const double *, double *, double *,
+                                                       const uint8_t *, TraceParams<double>, long, long,
+                                                       cudaStream_t);
+
+template <typename T>
+cudaError_t launch_outer_product(const T *x, const T *y, long B, long N, long M, T *delta, long row_begin,
+                                 long row_end, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  if (row_end <= row_begin) return cudaSuccess;
+  const bool vec = (N % V == 0) && (M % V == 0) && (row_begin % V == 0) && ((row_end - row_begin) % V == 0) &&
+                   aligned16(x) && aligned16(y);
+  StoreEpilogue<T> ep{delta + row_begin * M, row_end - row_begin, M, M, 0, (M % V == 0) && aligned16(delta)};
+  const int kper = (int)((B + Tile<T>::BK - 1) / Tile<T>::BK) * Tile<T>::BK;
+  return launch_contraction<T, false>(x + row_begin, N, y, M, row_end - row_begin, M, (int)B, 1, kper, vec, ep, st);
+}
+template cudaError_t launch_outer_product<float>(const float *, const float *, long, long, long, float *, long, long,
+                                                 cudaStream_t);
+template cudaError_t launch_outer_product<double>(const double *, const double *, long, long, long, double *, long,
+                                                  long, cudaStream_t);
+
+// One thread per four consecutive columns of one row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    trace_apply_kernel(const T *__restrict__ delta, long M, long H, long Mc, const T *__restrict__ Ci,
+                       const T *__restrict__ Cj, T *Cij, T *W, const uint8_t *__restrict__ wmask, TraceParams<T> p,
+                       int ema, long row_begin, long row_end, long quads_per_row, bool vec) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long i = row_begin + idx / quads_per_row;
+  if (i >= row_end) return;
+  const long j = (idx % quads_per_row) * 4;
+  const long left = M - j;
+  const int valid = left >= 4 ? 4 : (int)left;
+  const T ci = Ci[i];
+  const bool skip = ci < p.cthr;
+  T c4[4], d4[4], w4[4];
+  load4(Cij + i * M + j, c4, vec, valid);
+  if (ema) load4(delta + i * M + j, d4, vec, valid);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    if (c < valid) {
+      const T cij = ema ? trace_ema(c4[c], d4[c], p) : c4[c];
+      c4[c] = cij;
+      const T cj = Cj[j + c];
+      T w = (T)0;
+      if (!skip && !(cj < p.cthr) && (wmask == nullptr || wmask[i * H + (j + c) / Mc] != 0))
+        w = log_ratio(cij, ci, cj, p.cthr4);
+      w4[c] = w;
+    }
+  }
+  if (ema) store4(Cij + i * M + j, c4, vec, valid);
+  store4(W + i * M + j, w4, vec, valid);
+}
+
+template <typename T>
+cudaError_t launch_trace_apply(const T *delta, long N, long M, long H, long Mc, const T *Ci, const T *Cj, T *Cij,
+                               T *w, const uint8_t *wmask, TraceParams<T> p, int ema, long row_begin, long row_end,
+                               cudaStream_t st) {
+  (void)N;
+  constexpr int V = Vec16<T>::N;
+  if (row_end <= row_begin || M == 0) return cudaSuccess;
+  const long qpr = (M + 3) / 4;
+  const long total = (row_end - row_begin) * qpr;
+  const bool vec = (M % V == 0) && aligned16(Cij) && aligned16(w) && (!ema || aligned16(delta));
+  trace_apply_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(delta, M, H, Mc, Ci, Cj, Cij, w, wmask, p,
+                                                                          ema, row_begin, row_end, qpr, vec);
+  return launched();
+}
+template cudaError_t launch_trace_apply<float>(const float *, long, long, long, long, const float *, const float *,
+                                               float *, float *, const uint8_t *, TraceParams<float>, int, long, long,
+                                               cudaStream_t);
+template cudaError_t launch_trace_apply<double>(const double *, long, long, long, long, const double *,
+                                                const double *, double *, double *, const uint8_t *,
+                                                TraceParams<double>, int, long, long, cudaStream_t);
+
+// Un-fused trace update in the NumPy operation order: (1-t)*C + t*(sum/B).
+template <typename T>
+__global__ void counters_apply_kernel(T *c, const T *__restrict__ sums, long n, T taupdt, T batch) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const T v = ((T)1 - taupdt) * c[i] + taupdt * (sums[i] / batch);
+  c[i] = v > (T)0 ? v : (T)0;
+}
+template <typename T>
+cudaError_t launch_counters_apply(T *c, const T *sums, long n, T taupdt, T batch, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  counters_apply_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(c, sums, n, taupdt, batch);
+  return launched();
+}
+template cudaError_t launch_counters_apply<float>(float *, const float *, long, float, float, cudaStream_t);
+template cudaError_t launch_counters_apply<double>(double *, const double *, long, double, double, cudaStream_t);
+
+// ----------------------------------------------------------------------------
+// Bias kernels and small element-wise helpers.
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void update_bias_kernel(T *bias, const T *__restrict__ Cj, T cthr, long M) {
+  const long j = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j < M) bias[j] = Cj[j] < cthr ? sbb_log((T)2 * cthr) : sbb_log(Cj[j]);
+}
+template <typename T>
+cudaError_t launch_update_bias(T *bias, const T *Cj, T cthr, long M, cudaStream_t st) {
+  if (M == 0) return cudaSuccess;
+  update_bias_kernel<T><<<(unsigned)((M + 255) / 256), 256, 0, st>>>(bias, Cj, cthr, M);
+  return launched();
+}
+template cudaError_t launch_update_bias<float>(float *, const float *, float, long, cudaStream_t);
+template cudaError_t launch_update_bias<double>(double *, const double *, double, long, cudaStream_t);
+
+template <typename T>
+__global__ void update_bias_regularized_kernel(T *bias, T *kbi, const T *__restrict__ Cj, T cthr, T khalf, T pmin4,
+                                               T k, T taubdt, long M) {
+  const long j = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= M) return;
+  const T pj = Cj[j];
+  T kb = (T)1 + k / ((pj - pmin4) * (pj - pmin4));
+  if (pj < pmin4 || kb < khalf) kb = khalf;
+  const T g = ((T)1 - taubdt) * kbi[j] + taubdt * kb;
+  kbi[j] = g;
+  bias[j] = pj < cthr ? g * sbb_log((T)2 * cthr) : g * sbb_log(pj);
+}
+template <typename T>
+cudaError_t launch_update_bias_regularized(T *bias, T *kbi, const T *Cj, T cthr, T khalf, T pmin, T taubdt, long M,
+                                           cudaStream_t st) {
+  if (M == 0) return cudaSuccess;
+  const T pmin4 = pmin / (T)4;
+  const T k = (khalf - (T)1) * (pmin4 * pmin4);
+  update_bias_regularized_kernel<T><<<(unsigned)((M + 255) / 256), 256, 0, st>>>(bias, kbi, Cj, cthr, khalf, pmin4, k,
+                                                                                  taubdt, M);
+  return launched();
+}
+template cudaError_t launch_update_bias_regularized<float>(float *, float *, const float *, float, float, float,
+                                                           float, long, cudaStream_t);
+template cudaError_t launch_update_bias_regularized<double>(double *, double *, const double *, double, double,
+                                                            double, double, long, cudaStream_t);
+
+template <typename T>
+__global__ void add_bias_kernel(T *a, const T *__restrict__ bias, long total, long M) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < total) a[idx] += bias[idx % M];
+}
+template <typename T>
+cudaError_t launch_add_bias(T *a, const T *bias, long rows, long M, cudaStream_t st) {
+  const long total = rows * M;
+  if (total == 0) return cudaSuccess;
+  add_bias_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, bias, total, M);
+  return launched();
+}
+template cudaError_t launch_add_bias<float>(float *, const float *, long, long, cudaStream_t);
+template cudaError_t launch_add_bias<double>(double *, const double *, long, long, cudaStream_t);
+
+template <typename T>
+__global__ void apply_mask_kernel(T *w, const uint8_t *__restrict__ wmask, long total, long M, long H, long Mc) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long i = idx / M, j = idx % M;
+  if (!wmask[i * H + j / Mc]) w[idx] = (T)0;
+}
+template <typename T>
+cudaError_t launch_apply_mask(T *w, const uint8_t *wmask, long N, long M, long H, long Mc, cudaStream_t st) {
+  const long total = N * M;
+  if (total == 0) return cudaSuccess;
+  apply_mask_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(w, wmask, total, M, H, Mc);
+  return launched();
+}
+template cudaError_t launch_apply_mask<float>(float *, const uint8_t *, long, long, long, long, cudaStream_t);
+template cudaError_t launch_apply_mask<double>(double *, const uint8_t *, long, long, long, long, cudaStream_t);
+
+// ----------------------------------------------------------------------------
+// Structural plasticity: score, swap, rewrite.
+// ----------------------------------------------------------------------------
+// One warp per input row: the mutual-information score numerator over the
+// minicolumns of hypercolumn h (terms in REAL, accumulated in double) and the
+// row's count of active connections.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    mask_score_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ weights, const T *__restrict__ Ci,
+                      const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr, T cthr4, long N, long M, long H,
+                      long Mc, long h, T *score, int *csum) {
+  const int lane = threadIdx.x & 31;
+  const long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= N) return;  // whole warp leaves together
+  const T pi = Ci[i];
+  double s = 0.0;
+  if (pi >= cthr) {
+    for (long jj = lane; jj < Mc; jj += 32) {
+      const long col = h * Mc + jj;
+      const T pj = Cj[col];
+      if (pj >= cthr) {
+        const T pij = Cij[i * M + col];
+        const T w = weights ? weights[i * M + col] : log_ratio(pij, pi, pj, cthr4);
+        const T x = ((T)1 - pi) * pj;
+        const T y = (pj - pij) / x;
+        s += (double)(pij * w + (pj - pij) * sbb_log(y));
+      }
+    }
+  }
+  int cnt = 0;
+  for (long k = lane; k < H; k += 32) cnt += wmask[i * H + k];
+  for (int off = 16; off > 0; off >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, off);
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+  }
+  if (lane == 0) {
+    score[i] = (T)s;
+    csum[i] = cnt;
+  }
+}
+
+template <typename T>
+struct Pick {
+  T v;
+  long i;  // -1 = empty
+};
+// Maximum with ties to the larger index / minimum with ties to the larger index:
+// the outcome of a front-to-back scan that replaces on >= (resp. <=).
+template <typename T>
+__device__ __forceinline__ Pick<T> pick_max(Pick<T> a, Pick<T> b) {
+  if (b.i < 0) return a;
+  if (a.i < 0) return b;
+  return (b.v > a.v || (b.v == a.v && b.i > a.i)) ? b : a;
+}
+template <typename T>
+__device__ __forceinline__ Pick<T> pick_min(Pick<T> a, Pick<T> b) {
+  if (b.i < 0) return a;
+  if (a.i < 0) return b;
+  return (b.v < a.v || (b.v == a.v && b.i > a.i)) ? b : a;
+}
+template <typename T>
+__device__ __forceinline__ Pick<T> shfl_pick(Pick<T> p, int off) {
+  Pick<T> o;
+  o.v = __shfl_xor_sync(0xffffffffu, p.v, off);
+  o.i = __shfl_xor_sync(0xffffffffu, p.i, off);
+  return o;
+}
+
+// Single CTA.  Every iteration scans all rows: among silent connections
+// (mask 0) the highest score, among active ones (mask 1) the lowest, both with
+// the reference's sequential-scan semantics: ties go to the last index, and a
+// NaN score can only be selected when it belongs to the first candidate of its
+// class (a scan never replaces its holder with a NaN, nor a NaN holder at all).
+template <typename T>
+__global__ void __launch_bounds__(1024)
+    mask_swap_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long H, long h, long iterations) {
+  __shared__ Pick<T> s_max[32], s_min[32];
+  __shared__ long s_first0[32], s_first1[32];
+  __shared__ int s_done;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x == 0) s_done = 0;
+  __syncthreads();
+  for (long it = 0; it < iterations; ++it) {
+    Pick<T> bmax{(T)0, -1}, bmin{(T)0, -1};
+    long first0 = N, first1 = N;
+    for (long j = threadIdx.x; j < N; j += blockDim.x) {
+      const uint8_t m = wmask[j * H + h];
+      const T sc = (T)((double)nom[j] / (1.0 + (double)csum[j]));
+      if (m == 0) {
+        first0 = j < first0 ? j : first0;
+        if (sc == sc) bmax = pick_max(bmax, Pick<T>{sc, j});
+      } else if (m == 1) {
+        first1 = j < first1 ? j : first1;
+        if (sc == sc) bmin = pick_min(bmin, Pick<T>{sc, j});
+      }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      bmax = pick_max(bmax, shfl_pick(bmax, off));
+      bmin = pick_min(bmin, shfl_pick(bmin, off));
+      const long f0 = __shfl_xor_sync(0xffffffffu, first0, off);
+      const long f1 = __shfl_xor_sync(0xffffffffu, first1, off);
+      first0 = f0 < first0 ? f0 : first0;
+      first1 = f1 < first1 ? f1 : first1;
+    }
+    if (lane == 0) {
+      s_max[wid] = bmax;
+      s_min[wid] = bmin;
+      s_first0[wid] = first0;
+      s_first1[wid] = first1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < nwarps; ++w) {
+        bmax = pick_max(bmax, s_max[w]);
+        bmin = pick_min(bmin, s_min[w]);
+        first0 = s_first0[w] < first0 ? s_first0[w] : first0;
+        first1 = s_first1[w] < first1 ? s_first1[w] : first1;
+      }
+      long imax0 = N, imin1 = N;
+      T vmax0 = (T)0, vmin1 = (T)0;
+      if (first0 < N) {
+        const T sf = (T)((double)nom[first0] / (1.0 + (double)csum[first0]));
+        if (sf != sf) { imax0 = first0; vmax0 = sf; }
+        else { imax0 = bmax.i; vmax0 = bmax.v; }
+      }
+      if (first1 < N) {
+        const T sf = (T)((double)nom[first1] / (1.0 + (double)csum[first1]));
+        if (sf != sf) { imin1 = first1; vmin1 = sf; }
+        else { imin1 = bmin.i; vmin1 = bmin.v; }
+      }
+      if (imax0 == N || imin1 == N || vmax0 < vmin1) {
+        s_done = 1;
+      } else {
+        wmask[imax0 * H + h] = 1;
+        wmask[imin1 * H + h] = 0;
+        csum[imax0] += 1;
+        csum[imin1] -= 1;
+      }
+    }
+    __syncthreads();
+    if (s_done) break;
+  }
+}
+
+template <typename T>
+cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
+                               long N, long M, long H, long Mc, long h, long iterations, T *score, int *csum,
+                               cudaStream_t st) {
+  if (N == 0) return cudaSuccess;
+  const T cthr4 = cthr * cthr * cthr * cthr;
+  mask_score_kernel<T><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wmask, weights, Ci, Cj, Cij, cthr, cthr4, N, M, H, Mc,
+                                                                 h, score, csum);
+  cudaError_t e = launched();
+  if (e != cudaSuccess) return e;
+  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, iterations);
+  return launched();
+}
+template cudaError_t launch_mask_update<float>(uint8_t *, const float *, const float *, const float *, const float *,
+                                               float, long, long, long, long, long, long, float *, int *,
+                                               cudaStream_t);
+template cudaError_t launch_mask_update<double>(uint8_t *, const double *, const double *, const double *,
+                                                const double *, double, long, long, long, long, long, long, double *,
+                                                int *, cudaStream_t);
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+    rewrite_hypercolumn_kernel(T *w, const uint8_t *__restrict__ wmask, const T *__restrict__ Ci,
+                               const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr, T cthr4, long N, long M,
+                               long H, long Mc, long h) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= N * Mc) return;
+  const long i = idx / Mc, col = h * Mc + idx % Mc;
+  const T ci = Ci[i], cj = Cj[col];
+  T v = (T)0;
+  if (wmask[i * H + h] != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[i * M + col], ci, cj, cthr4);
+  w[i * M + col] = v;
+}
+template <typename T>
+cudaError_t launch_rewrite_hypercolumn(T *w, const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr,
+                                       long N, long M, long H, long Mc, long h, cudaStream_t st) {
+  const long total = N * Mc;
+  if (total == 0) return cudaSuccess;
+  const T cthr4 = cthr * cthr * cthr * cthr;
+  rewrite_hypercolumn_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(w, wmask, Ci, Cj, Cij, cthr, cthr4, N,
+                                                                                  M, H, Mc, h);
+  return launched();
+}
+template cudaError_t launch_rewrite_hypercolumn<float>(float *, const uint8_t *, const float *, const float *,
+                                                       const float *, float, long, long, long, long, long,
+                                                       cudaStream_t);
+template cudaError_t launch_rewrite_hypercolumn<double>(double *, const uint8_t *, const double *, const double *,
+                                                        const double *, double, long, long, long, long, long,
+                                                        cudaStream_t);
+
+// ----------------------------------------------------------------------------
+// Evaluation helper: rows whose predicted class equals the labelled class
+// (first maximum wins, as numpy.argmax).
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void count_correct_kernel(const T *__restrict__ pred, const T *__restrict__ labels, long rows, long classes,
+                                     unsigned long long *count) {
+  const long r = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  bool hit = false;
+  if (r < rows) {
+    long ap = 0, al = 0;
+    T vp = pred[r * classes], vl = labels[r * classes];
+    for (long c = 1; c < classes; ++c) {
+      const T p = pred[r * classes + c], l = labels[r * classes + c];
+      if (p > vp) { vp = p; ap = c; }
+      if (l > vl) { vl = l; al = c; }
+    }
+    hit = ap == al;
+  }
+  const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+  if ((threadIdx.x & 31) == 0 && ballot) atomicAdd(count, (unsigned long long)__popc(ballot));
+}
+template <typename T>
+cudaError_t launch_count_correct(const T *pred, const T *labels, long rows, long classes, unsigned long long *count,
+                                 cudaStream_t st) {
+  if (rows == 0) return cudaSuccess;
+  count_correct_kernel<T><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(pred, labels, rows, classes, count);
+  return launched();
+}
+template cudaError_t launch_count_correct<float>(const float *, const float *, long, long, unsigned long long *,
+                                                 cudaStream_t);
+template cudaError_t launch_count_correct<double>(const double *, const double *, long, long, unsigned long long *,
+                                                  cudaStream_t);
+
+}  // namespace sbb

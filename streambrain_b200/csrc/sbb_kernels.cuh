@@ -1,0 +1,103 @@
+// Launch interface of the BCPNN layer kernels (device pointers, asynchronous on
+// the given stream).  Every launcher returns cudaSuccess or the launch error and
+// bumps the process-wide launch counter once per kernel launched.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sbb {
+
+// Scalars of the trace / weight arithmetic, already rounded to REAL.
+template <typename T>
+struct TraceParams {
+  T taupdt;     // trace time constant
+  T one_minus;  // (REAL)(1.0 - (double)taupdt)
+  T batch;      // divisor of the batch sums (global batch under data parallelism)
+  T cthr;       // taupdt / 2
+  T cthr4;      // cthr^4, floor of Cij inside the logarithm
+};
+
+template <typename T>
+TraceParams<T> make_trace_params(double taupdt, double cthr, long batch);
+
+unsigned long long kernel_launches();
+
+// Number of K-splits the forward product uses for a [B,N]x[N,M] problem and the
+// number of REALs of scratch (splits*B*M) it needs.
+template <typename T>
+int forward_splits(long B, long N, long M);
+
+// partial[s, B, M] = x[B, N(k-range s)] * w[N, M]   (s = 0..splits-1)
+template <typename T>
+cudaError_t launch_forward_product(const T *x, const T *w, T *partial, long B, long N, long M, int splits,
+                                   cudaStream_t st);
+
+// out[r, :] = sum_s partial[s, r, :] + bias, then (softmax != 0) the softmax over
+// every group of Mc entries.  partial may alias out when splits == 1; bias may be null.
+template <typename T>
+cudaError_t launch_reduce_bias_softmax(const T *partial, int splits, const T *bias, T *out, long rows, long H,
+                                       long Mc, int softmax, cudaStream_t st);
+
+// sums[j] = sum_b a[b, j]                       (ema == 0)
+// c[j]    = EMA(c[j], sum_b a[b, j])            (ema != 0; sums unused)
+template <typename T>
+cudaError_t launch_colsum(const T *a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema, cudaStream_t st);
+
+// c[j] = EMA(c[j], sums[j])
+template <typename T>
+cudaError_t launch_vector_ema(T *c, const T *sums, long n, TraceParams<T> p, cudaStream_t st);
+
+// Fused trace step for rows [row_begin,row_end) of Cij: acc = x^T y over the batch,
+// Cij = EMA(Cij, acc), w = log-ratio(Cij, Ci, Cj) with rows/columns below cthr and
+// masked connections (wmask may be null) set to zero.  Ci, Cj hold the NEW values.
+template <typename T>
+cudaError_t launch_trace_update_fused(const T *x, const T *y, long B, long N, long M, long H, long Mc, const T *Ci,
+                                      const T *Cj, T *Cij, T *w, const uint8_t *wmask, TraceParams<T> p,
+                                      long row_begin, long row_end, cudaStream_t st);
+
+// delta[i, j] = sum_b x[b, i] y[b, j] for rows [row_begin,row_end)  (delta is [N, M])
+template <typename T>
+cudaError_t launch_outer_product(const T *x, const T *y, long B, long N, long M, T *delta, long row_begin,
+                                 long row_end, cudaStream_t st);
+
+// Element-wise tail of the trace step from precomputed sums (delta may be null when
+// only the weights are to be recomputed from the current traces: ema == 0).
+template <typename T>
+cudaError_t launch_trace_apply(const T *delta, long N, long M, long H, long Mc, const T *Ci, const T *Cj, T *Cij,
+                               T *w, const uint8_t *wmask, TraceParams<T> p, int ema, long row_begin, long row_end,
+                               cudaStream_t st);
+
+// Un-fused Cij update with the numpy operation order: (1-t)*C + t*(sum/B).
+template <typename T>
+cudaError_t launch_counters_apply(T *c, const T *sums, long n, T taupdt, T batch, cudaStream_t st);
+
+template <typename T>
+cudaError_t launch_update_bias(T *bias, const T *Cj, T cthr, long M, cudaStream_t st);
+
+template <typename T>
+cudaError_t launch_update_bias_regularized(T *bias, T *kbi, const T *Cj, T cthr, T khalf, T pmin, T taubdt, long M,
+                                           cudaStream_t st);
+
+template <typename T>
+cudaError_t launch_add_bias(T *a, const T *bias, long rows, long M, cudaStream_t st);
+
+template <typename T>
+cudaError_t launch_apply_mask(T *w, const uint8_t *wmask, long N, long M, long H, long Mc, cudaStream_t st);
+
+// Mask update for hypercolumn h.  `weights` null => the un-masked weight is
+// recomputed from the traces.  score/csum are scratch of N REALs / N ints.
+template <typename T>
+cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
+                               long N, long M, long H, long Mc, long h, long iterations, T *score, int *csum,
+                               cudaStream_t st);
+
+// Rewrites the weights of hypercolumn h's columns from the traces under wmask.
+template <typename T>
+cudaError_t launch_rewrite_hypercolumn(T *w, const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr,
+                                       long N, long M, long H, long Mc, long h, cudaStream_t st);
+
+template <typename T>
+cudaError_t launch_count_correct(const T *pred, const T *labels, long rows, long classes, unsigned long long *count,
+                                 cudaStream_t st);
+
+}  // namespace sbb

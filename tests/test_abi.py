@@ -1,0 +1,81 @@
+"""The C-ABI library loads, exports every symbol the header declares, and refuses
+to compute without a CUDA device.  No GPU needed."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import REPO
+
+
+def _declared_symbols():
+    text = open(os.path.join(REPO, "include", "sbb200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sbb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    from streambrain_b200 import _lib
+    declared = _declared_symbols()
+    assert len(declared) >= 30
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), "libsbb200.so does not export %s" % name
+        assert name in _lib.SIGNATURES, "no ctypes signature for %s" % name
+    assert sorted(_lib.SIGNATURES) == declared
+
+
+def test_version_and_error_string():
+    from streambrain_b200 import _lib
+    assert _lib.lib.sbb_version() >= 100
+    assert isinstance(_lib.lib.sbb_last_error(), bytes)
+
+
+def test_invalid_arguments_are_rejected_before_any_device_work():
+    from streambrain_b200 import _lib
+    a = np.zeros((2, 4), dtype=np.float32)
+    rc = _lib.lib.sbb_softmax_minicolumns(7, _lib.host_ptr(a), 2, 2, 2)
+    assert rc == 1 and b"dtype" in _lib.lib.sbb_last_error()
+    rc = _lib.lib.sbb_softmax_minicolumns(0, None, 2, 2, 2)
+    assert rc == 1
+    rc = _lib.lib.sbb_apply_mask(0, _lib.host_ptr(a), _lib.host_ptr(np.zeros((2, 2), dtype=np.uint8)), 2, 4, 2, 3)
+    assert rc == 1 and b"shape" in _lib.lib.sbb_last_error()
+    desc = _lib.LayerDesc(0, 5, 4, 2, 2, 0.01, 0, 0, 0, 16)
+    h = ctypes.c_void_p()
+    assert _lib.lib.sbb_layer_create(ctypes.byref(desc), ctypes.byref(h)) == 1
+    assert not h.value
+
+
+def test_wrapper_rejects_silent_conversions():
+    from streambrain_b200 import kernels_b200 as k
+    a64 = np.zeros((2, 4))
+    with pytest.raises(TypeError):
+        k.add_bias(a64, np.zeros(4, dtype=np.float32))
+    with pytest.raises(TypeError):
+        k.softmax_minicolumns(np.zeros((4, 4), dtype=np.float32)[:, ::2], 1, 2)
+    with pytest.raises(Exception, match="Invalid dtype"):
+        k.softmax_minicolumns(np.zeros((2, 4), dtype=np.int32), 2, 2)
+
+
+def test_no_cpu_fallback_without_a_device():
+    from streambrain_b200 import _lib
+    if _lib.lib.sbb_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    from streambrain_b200 import kernels_b200 as k
+    with pytest.raises(_lib.SbbError) as e:
+        k.softmax_minicolumns(np.zeros((2, 4), dtype=np.float32), 2, 2)
+    assert e.value.code == 3
+    import streambrain_b200 as B
+    with pytest.raises(_lib.SbbError):
+        B.DenseLayer(8, 1, 4, 0.01, (0.1, 0.1, 0.01), np.float32)
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(REPO, "streambrain_b200")
+    for root, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                src = open(os.path.join(root, f)).read()
+                assert "oracle" not in src.lower() or f == "synthetic.py" and False, os.path.join(root, f)
