@@ -1,0 +1,360 @@
+"""Benchmark of the BCPNN hidden-layer train step (forward + softmax + trace/weight/
+bias/mask update) on synthetic STL-10-shaped data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload stl10_f32|mnist_f32|mnist_f64|wide_f32|stl10_dp_f32]
+
+One "step" is one pass of the layer over one batch: ``compute_activation`` then
+``train_step`` with a mask update (every step: the worst case of the reference's
+schedule).  Default workload: 55296 -> 30x100 units, float32, batch 256 per GPU
+(``stl10_f32``); with N > 1 every rank takes its own 256 samples of a 256*N global
+batch and one sum-allreduce of the batch deltas precedes the trace update (weak
+scaling).  ``stl10_dp_f32`` is the fixed global batch 8192 split over the ranks.
+
+Prints ONE JSON line (rank 0).  ``value`` is samples/s with the batches resident in
+HBM, ``e2e`` the same metric through the host-buffer C-ABI call (pinned host input
+copied in, activations copied out, every step).  ``--impl reference`` times the
+reference's own CPU implementation (compiled OpenMP module under oracle/_ref, else
+the C restatement) on the host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+from streambrain_b200 import synthetic  # noqa: E402
+
+POOL = 8  # distinct resident batches cycled through (8 x 56.6 MB of inputs > 126 MB of L2)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-mask", action="store_true", help="skip the per-step mask update")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def algorithmic_work(N, M, H, B, s):
+    """Bytes and flops one step must move / do, per phase ("Roofline")."""
+    fwd_bytes = (N * M + B * N + B * M + M) * s
+    upd_bytes = (3 * N * M + B * N + B * M) * s + N * H
+    flops = 2.0 * B * N * M
+    return fwd_bytes, upd_bytes, flops
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region (read only)."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.mktemp(prefix="sbb_clocks_", suffix=".csv")
+        self.proc = None
+        self.gpu = gpu_index
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return res
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, reasons, mx = [], set(), None
+        try:
+            for line in open(self.path):
+                f = [t.strip() for t in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx = float(f[2])
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                   f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            res.update(sm_mhz=statistics.median(sm), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+        return res
+
+
+def make_batches(p, batch, count, seed):
+    xs = []
+    for k in range(count):
+        x, _ = synthetic.make_inputs(batch, p["n_pixels"], p["sparsity"], p["dtype"], seed=seed + k)
+        xs.append(x)
+    return xs
+
+
+# --------------------------------------------------------------------------- CPU
+def cpu_layer(p, kernels, seed=0):
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import oracle
+    hp = p["hidden"]
+    np.random.seed(seed)
+    return oracle.OracleLayer(kernels, "plastic", hp["in_features"], hp["hypercolumns"], hp["minicolumns"],
+                              hp["taupdt"], hp["initial_counters"], p["dtype"], khalf=hp["khalf"], pmin=hp["pmin"],
+                              taubdt=hp["taubdt"], density=hp["density"])
+
+
+def cpu_time_steps(p, batch, steps, warmup, budget_s, mask=True):
+    """Time the reference CPU implementation of the same step.  Returns
+    (samples_per_s, median_s, steps_timed, kind, cores)."""
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import oracle
+    kernels = oracle.best_kernels()
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    layer = cpu_layer(p, kernels)
+    xs = make_batches(p, batch, 2, synthetic.DATA_SEED)
+    H = p["hidden"]["hypercolumns"]
+    times = []
+    t_start = time.perf_counter()
+    total = warmup + steps
+    for s in range(total):
+        x = xs[s % len(xs)]
+        t0 = time.perf_counter()
+        act = layer.compute_activation(x)
+        layer.train_step(x, act, (s % H) if mask else None)
+        dt = time.perf_counter() - t0
+        if s >= warmup:
+            times.append(dt)
+        if times and time.perf_counter() - t_start + dt > budget_s:
+            break
+    med = statistics.median(times)
+    return batch / med, med, len(times), kernels.kind, cores
+
+
+def run_reference(args, wl, p, batch):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sps, med, done, kind, cores = cpu_time_steps(p, batch, args.steps, min(args.warmup, 1), budget_s=150.0,
+                                                 mask=not args.no_mask)
+    sample = "%d full steps (forward + train_step%s) of %s at batch %d on the host cores" % (
+        done, "" if args.no_mask else " + mask update", wl, batch)
+    line = {
+        "impl": "reference", "metric": "training samples/sec per layer", "value": sps, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": done, "warmup": min(args.warmup, 1), "ms_per_step": med * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32" if p["dtype"] == np.float32
+        else "f64", "data": "synthetic",
+        "config": {"workload": wl, "batch_per_gpu": batch, "layer": "%d->%dx%d" % (
+            p["hidden"]["in_features"], p["hidden"]["hypercolumns"], p["hidden"]["minicolumns"])},
+        "cpu_baseline": {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": sps, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU
+def run_b200(args, wl, p, batch):
+    import torch
+    import torch.distributed as dist
+    import streambrain_b200 as B200
+    from streambrain_b200._lib import check, lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl b200 needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    hp = p["hidden"]
+    N, H, Mc = hp["in_features"], hp["hypercolumns"], hp["minicolumns"]
+    M = H * Mc
+    np_dtype = p["dtype"]
+    s = np.dtype(np_dtype).itemsize
+    np.random.seed(0)  # identical replicas on every rank
+    layer = B200.StructuralPlasticityLayer(N, H, Mc, hp["taupdt"], hp["khalf"], hp["pmin"], hp["taubdt"],
+                                           hp["density"], 16, hp["initial_counters"], dtype=np_dtype)
+    xs_host = make_batches(p, batch, POOL, synthetic.DATA_SEED + 1000 * rank)
+    xs = [torch.from_numpy(x).cuda() for x in xs_host]
+    ys = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    all_reduce = (lambda t: dist.all_reduce(t, async_op=True)) if world > 1 else None
+    mask = not args.no_mask
+
+    def step(k):
+        x, y = xs[k % POOL], ys[k % 2]
+        check(lib.sbb_layer_forward(layer._handle, x.data_ptr(), batch, y.data_ptr(), stream))
+        h = (k % H) if mask else None
+        if world > 1:
+            layer.dp_train_step(x, y, h, world, all_reduce)
+        else:
+            check(lib.sbb_layer_train_step(layer._handle, x.data_ptr(), y.data_ptr(), batch, -1 if h is None else h,
+                                           stream))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for k in range(args.warmup):
+        step(k)
+    barrier()
+    check(lib.sbb_layer_profile(layer._handle, 1))
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = int(lib.sbb_kernel_launches())
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for k in range(args.steps):
+        step(args.warmup + k)
+    ev1.record()
+    barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    launches = int(lib.sbb_kernel_launches()) - launches0
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+
+    # per-kernel durations recorded inside the timed region
+    def phase_ms(phase):
+        n = ctypes.c_long(0)
+        check(lib.sbb_layer_phase_calls(layer._handle, phase, ctypes.byref(n)))
+        out = []
+        for i in range(max(0, n.value - 64), n.value):
+            ms = ctypes.c_float(0)
+            check(lib.sbb_layer_phase_ms(layer._handle, phase, i, ctypes.byref(ms)))
+            out.append(ms.value)
+        return out, n.value
+    fwd_ms, _ = phase_ms(0)
+    trace_ms, trace_calls = phase_ms(1)
+    check(lib.sbb_layer_profile(layer._handle, 0))
+
+    # end to end through the host-buffer C-ABI call (N = 1 semantics per rank; under
+    # data parallelism the exchange needs device buffers, so e2e is measured at N = 1).
+    e2e = None
+    if world == 1:
+        pinned = [torch.from_numpy(x).pin_memory() for x in xs_host[:4]]
+        y_host = torch.empty((batch, M), dtype=xs[0].dtype).pin_memory()
+        yp = ctypes.c_void_p(y_host.data_ptr())
+        for k in range(2):
+            check(lib.sbb_layer_step_host(layer._handle, ctypes.c_void_p(pinned[k % 4].data_ptr()), None, batch,
+                                          (k % H) if mask else -1, yp))
+        e_steps = max(3, min(args.steps, 20))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for k in range(e_steps):
+            check(lib.sbb_layer_step_host(layer._handle, ctypes.c_void_p(pinned[k % 4].data_ptr()), None, batch,
+                                          (k % H) if mask else -1, yp))
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        e2e = {"value": batch * e_steps / dt, "unit": "samples/s", "h2d_bytes_per_step": batch * N * s,
+               "d2h_bytes_per_step": batch * M * s, "ms_per_step": dt / e_steps * 1e3}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    fwd_b, upd_b, flops = algorithmic_work(N, M, H, batch, s)
+    ms_per_step = elapsed_ms / args.steps
+    value = world * batch * args.steps / (elapsed_ms * 1e-3)
+    # one launch per step on one GPU; under data parallelism the product is cut into row blocks,
+    # so the per-step time is the sum over its launches
+    per_step_trace = (sum(trace_ms) / len(trace_ms)) * (trace_calls / args.steps) if trace_ms else None
+    hbm = float(peaks["hbm_gbs"])
+    roofline = None
+    if per_step_trace:
+        achieved = upd_b / (per_step_trace * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "trace update (x^T y + EMA + log-ratio weights + mask)",
+                    "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                    "traffic": None, "peak_source": peak_kind, "algorithmic_bytes": upd_b,
+                    "ms_per_launch": per_step_trace,
+                    "forward_ms": (sum(fwd_ms) / len(fwd_ms)) if fwd_ms else None}
+    # whole-step roofline: each phase bounded by the larger of its memory and compute time
+    p32 = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) / 6.0 * 1e12  # fp32 via 3xTF32
+    t_roof = max(fwd_b / (hbm * 1e9), flops / p32) + max(upd_b / (hbm * 1e9), flops / p32)
+    step_roofline = {"t_roof_ms": t_roof * 1e3, "frac": t_roof * 1e3 / ms_per_step,
+                     "compute_peak_tflops": p32 / 1e12,
+                     "note": "peak = measured bf16 sustained / 6 (fp32 by three TF32 products)"}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            sps, med, done, kind, cores = cpu_time_steps(p, batch, 3, 1, budget_s=40.0, mask=mask)
+            cpu = {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "ms_per_step": med * 1e3,
+                   "sample": "%d full steps of the same workload (batch %d) after 1 warm-up" % (done, batch)}
+        except Exception as e:  # the CPU leg must never take the GPU line down
+            cpu = {"value": None, "unit": "samples/s", "cores": 0, "kind": "unavailable", "sample": str(e)[:200]}
+
+    line = {
+        "metric": "training samples/sec per layer", "value": value, "unit": "samples/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if wl == "stl10_dp_f32" else "weak", "vs_baseline": None,
+        "dtype": "f32" if np_dtype == np.float32 else "f64", "data": "synthetic",
+        "config": {"workload": wl, "layer": "%d->%dx%d" % (N, H, Mc), "batch_per_gpu": batch,
+                   "global_batch": batch * world, "mask_update": "every step" if mask else "none",
+                   "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
+                       POOL, 2 * N * M * s / 1e6),
+                   "parallelism": "dp%d" % world},
+        "roofline": roofline, "step_roofline": step_roofline, "cpu_baseline": cpu, "e2e": e2e,
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    wl = args.workload or "stl10_f32"
+    p = synthetic.layer_params(wl)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    batch = p["batch"] // world if wl == "stl10_dp_f32" else p["batch"]
+    if args.impl == "reference":
+        run_reference(args, wl, p, batch)
+    else:
+        run_b200(args, wl, p, batch)
+
+
+if __name__ == "__main__":
+    main()

@@ -199,6 +199,20 @@ int sbb_layer_dp_finish(sbb_layer *layer, long hypercolumn, void *stream);
 int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, long rows, long classes,
                       long *correct_host, void *stream);
 
+/* Per-phase device timing of a layer.  With profiling enabled every forward and
+ * every train step brackets its dominant kernel (phase 0: forward product,
+ * phase 1: trace update) with CUDA events on the launching stream, in a ring of
+ * SBB_PROFILE_SLOTS slots per phase.  sbb_layer_phase_ms returns the duration of
+ * call number `index` (0 = first call after enabling) once that work has
+ * finished; it synchronises on the slot's end event.  No counterpart in the
+ * reference, which only takes wall-clock times around fit/evaluate (train.py:181-193). */
+#define SBB_PROFILE_SLOTS 64
+#define SBB_PHASE_FORWARD 0
+#define SBB_PHASE_TRACE 1
+int sbb_layer_profile(sbb_layer *layer, int enable);
+int sbb_layer_phase_calls(sbb_layer *layer, int phase, long *calls);
+int sbb_layer_phase_ms(sbb_layer *layer, int phase, long index, float *ms);
+
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long sbb_kernel_launches(void);
 

@@ -126,9 +126,36 @@ struct sbb_layer {
   Scratch csum;          // N ints
   Scratch hx, hy, ht;    // staging for the host-buffer entry points
   cudaStream_t own_stream = nullptr;
+  // optional per-phase event ring (sbb_layer_profile)
+  bool profiling = false;
+  cudaEvent_t ev_begin[2][SBB_PROFILE_SLOTS];
+  cudaEvent_t ev_end[2][SBB_PROFILE_SLOTS];
+  bool ev_created = false;
+  long phase_calls[2] = {0, 0};
 };
 
 namespace {
+
+// Brackets one kernel launch with events when profiling is on.
+struct PhaseTimer {
+  sbb_layer *L;
+  int phase;
+  cudaStream_t st;
+  long slot = -1;
+  PhaseTimer(sbb_layer *l, int ph, cudaStream_t s) : L(l), phase(ph), st(s) {
+    if (L->profiling) {
+      slot = L->phase_calls[phase] % SBB_PROFILE_SLOTS;
+      cudaEventRecord(L->ev_begin[phase][slot], st);
+    }
+  }
+  void stop() {
+    if (slot >= 0) {
+      cudaEventRecord(L->ev_end[phase][slot], st);
+      L->phase_calls[phase] += 1;
+      slot = -1;
+    }
+  }
+};
 
 template <typename T>
 int layer_forward(sbb_layer *L, const T *x, long B, T *y, cudaStream_t st) {
@@ -138,8 +165,10 @@ int layer_forward(sbb_layer *L, const T *x, long B, T *y, cudaStream_t st) {
     SBB_TRY(L->fwd_partial.reserve((size_t)splits * B * L->M * sizeof(T)));
     partial = static_cast<T *>(L->fwd_partial.d);
   }
+  PhaseTimer timer(L, SBB_PHASE_FORWARD, st);
   SBB_CUDA(sbb::launch_forward_product<T>(x, static_cast<const T *>(L->state[SBB_STATE_WEIGHTS]), partial, B, L->N,
                                           L->M, splits, st));
+  timer.stop();
   SBB_CUDA(sbb::launch_reduce_bias_softmax<T>(partial, splits, static_cast<const T *>(L->state[SBB_STATE_BIAS]), y, B,
                                               L->H, L->Mc, 1, st));
   return SBB_OK;
@@ -176,10 +205,12 @@ int layer_train_step(sbb_layer *L, const T *x, const T *y, long B, long h, cudaS
   T *Cj = static_cast<T *>(L->state[SBB_STATE_CJ]);
   SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, nullptr, Ci, p, 1, st));
   SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, nullptr, Cj, p, 1, st));
+  PhaseTimer timer(L, SBB_PHASE_TRACE, st);
   SBB_CUDA(sbb::launch_trace_update_fused<T>(x, y, B, L->N, L->M, L->H, L->Mc, Ci, Cj,
                                              static_cast<T *>(L->state[SBB_STATE_CIJ]),
                                              static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
                                              static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 0, L->N, st));
+  timer.stop();
   return layer_finish<T>(L, h, st);
 }
 
@@ -190,7 +221,9 @@ int layer_dp_local(sbb_layer *L, const T *x, const T *y, long B, T *delta, long 
     SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, delta, nullptr, p, 0, st));
     SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, delta + L->N, nullptr, p, 0, st));
   }
+  PhaseTimer timer(L, SBB_PHASE_TRACE, st);
   SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, L->N, L->M, delta + L->N + L->M, rb, re, st));
+  timer.stop();
   return SBB_OK;
 }
 
@@ -551,6 +584,12 @@ int sbb_layer_destroy(sbb_layer *L) {
   L->hy.release();
   L->ht.release();
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
+  if (L->ev_created)
+    for (int ph = 0; ph < 2; ++ph)
+      for (int k = 0; k < SBB_PROFILE_SLOTS; ++k) {
+        cudaEventDestroy(L->ev_begin[ph][k]);
+        cudaEventDestroy(L->ev_end[ph][k]);
+      }
   delete L;
   return SBB_OK;
 }
@@ -587,6 +626,42 @@ int sbb_layer_state_ptr(sbb_layer *L, int which, void **device_ptr) {
   SBB_TRY(state_slot(L, which, 0, false));
   ARG(device_ptr, "state_ptr: null pointer");
   *device_ptr = L->state[which];
+  return SBB_OK;
+}
+
+int sbb_layer_profile(sbb_layer *L, int enable) {
+  SBB_TRY(check_layer(L));
+  if (enable && !L->ev_created) {
+    for (int ph = 0; ph < 2; ++ph)
+      for (int k = 0; k < SBB_PROFILE_SLOTS; ++k) {
+        SBB_CUDA(cudaEventCreate(&L->ev_begin[ph][k]));
+        SBB_CUDA(cudaEventCreate(&L->ev_end[ph][k]));
+      }
+    L->ev_created = true;
+  }
+  L->profiling = enable != 0;
+  L->phase_calls[0] = L->phase_calls[1] = 0;
+  return SBB_OK;
+}
+
+int sbb_layer_phase_calls(sbb_layer *L, int phase, long *calls) {
+  SBB_TRY(check_layer(L));
+  ARG(phase == SBB_PHASE_FORWARD || phase == SBB_PHASE_TRACE, "invalid phase %d", phase);
+  ARG(calls, "phase_calls: null pointer");
+  *calls = L->phase_calls[phase];
+  return SBB_OK;
+}
+
+int sbb_layer_phase_ms(sbb_layer *L, int phase, long index, float *ms) {
+  SBB_TRY(check_layer(L));
+  ARG(phase == SBB_PHASE_FORWARD || phase == SBB_PHASE_TRACE, "invalid phase %d", phase);
+  ARG(ms, "phase_ms: null pointer");
+  ARG(L->ev_created, "profiling was never enabled on this layer");
+  ARG(index >= 0 && index < L->phase_calls[phase] && index >= L->phase_calls[phase] - SBB_PROFILE_SLOTS,
+      "call %ld is not in the ring (calls so far: %ld)", index, L->phase_calls[phase]);
+  const long slot = index % SBB_PROFILE_SLOTS;
+  SBB_CUDA(cudaEventSynchronize(L->ev_end[phase][slot]));
+  SBB_CUDA(cudaEventElapsedTime(ms, L->ev_begin[phase][slot], L->ev_end[phase][slot]));
   return SBB_OK;
 }
 
