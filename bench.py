@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mask", action="store_true", help="skip the per-step mask update")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     return ap.parse_args()
 
 
@@ -271,7 +272,7 @@ def run_b200(args, wl, p, batch):
     # end to end through the host-buffer C-ABI call (N = 1 semantics per rank; under
     # data parallelism the exchange needs device buffers, so e2e is measured at N = 1).
     e2e = None
-    if world == 1:
+    if world == 1 and not args.no_e2e:
         pinned = [torch.from_numpy(x).pin_memory() for x in xs_host[:4]]
         y_host = torch.empty((batch, M), dtype=xs[0].dtype).pin_memory()
         yp = ctypes.c_void_p(y_host.data_ptr())

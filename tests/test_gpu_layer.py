@@ -312,7 +312,13 @@ def test_stl10_shaped_layer_full_size_properties(B200, port_kernels):
     rows = [0, 1, 100, 255]
     s = port_kernels.update_state(np.zeros((len(rows), M), dtype=np.float32), W0, b0, np.ascontiguousarray(x[rows]))
     want = port_kernels.softmax_minicolumns(s, H, Mc)
-    assert rel_inf(y[rows], want) < 1e-4   # K = 55296 float32 accumulations in a different order
+    # K = 55296 float32 accumulations: the oracle's own rounding (sequential sums) is of the
+    # order of 1e-4 here, so both are measured against a float64 evaluation of the same rows.
+    s64 = x[rows].astype(np.float64) @ W0.astype(np.float64) + b0.astype(np.float64)
+    y64 = oracle.numpy_softmax_minicolumns(s64, H, Mc)
+    err_dev, err_ref = rel_inf(y[rows], y64), rel_inf(want, y64)
+    assert err_dev < max(2 * err_ref, 1e-5), (err_dev, err_ref)
+    assert rel_inf(y[rows], want) < 1e-3
     assert np.allclose(y.reshape(B, H, Mc).sum(axis=2), 1.0, atol=1e-5)
 
     Ci0, Cj0, Cij0 = dev.Ci, dev.Cj, dev.Cij
@@ -327,8 +333,7 @@ def test_stl10_shaped_layer_full_size_properties(B200, port_kernels):
     assert rel_inf(Cij1[pick], sub[2]) < 1e-5
     masked = np.repeat(mask1[pick], Mc, axis=1).astype(bool)
     assert rel_inf(W1[pick], np.where(masked, cw, 0)) < 1e-4
-    assert np.array_equal(W1 == 0, np.repeat(mask1, Mc, axis=1) == 0) or (Ci1 < taupdt / 2).any() \
-        or (Cj1 < taupdt / 2).any()
+    assert (W1[np.repeat(mask1, Mc, axis=1) == 0] == 0).all()   # silent connections carry no weight
     # (c) identities over ALL rows
     t = np.float64(np.float32(taupdt))
     row_sum = Cij1.astype(np.float64).reshape(N, H, Mc).sum(axis=2)
