@@ -199,6 +199,27 @@ int sbb_layer_dp_finish(sbb_layer *layer, long hypercolumn, void *stream);
 int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, long rows, long classes,
                       long *correct_host, void *stream);
 
+/* Mask update that allocates nothing: for hosts that own all device memory
+ * themselves (one pre-sized arena) or cannot accept the device-wide stall of
+ * cudaMalloc/cudaFree inside their step loop.  Same arithmetic and result as
+ * sbb_update_mask, but every array is a DEVICE pointer supplied by the caller
+ * (wmask is updated in place; weights_dev may be NULL, the un-masked weights are
+ * then recomputed from the traces) and the two per-row work arrays live in a
+ * fixed 1.5 MiB array inside the library, resident on every GPU that loads it
+ * until the process exits.  More than SBB_NOALLOC_MAX_ROWS input rows returns
+ * SBB_ERR_UNSUPPORTED without launching.  All calls on a device share that
+ * array: calls that overlap in time on one GPU race and must be serialised by
+ * the caller.  The first call on each device looks up the array's address
+ * (cudaGetSymbolAddress) and should be made outside any stream capture.  The
+ * work is enqueued on `stream`; the call does not synchronise.  Errors of this
+ * entry point are reported by sbb_noalloc_last_error().
+ * This entry point has no counterpart in the reference. */
+#define SBB_NOALLOC_MAX_ROWS 131072
+int sbb_update_mask_noalloc(int dtype, uint8_t *wmask_dev, const void *weights_dev, const void *Ci_dev,
+                            const void *Cj_dev, const void *Cij_dev, double cthr, long N, long M, long H,
+                            long Mc, long h, long iterations, void *stream);
+const char *sbb_noalloc_last_error(void);
+
 /* Per-phase device timing of a layer.  With profiling enabled every forward and
  * every train step brackets its dominant kernel (phase 0: forward product,
  * phase 1: trace update) with CUDA events on the launching stream, in a ring of

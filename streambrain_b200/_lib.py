@@ -71,6 +71,9 @@ SIGNATURES = {
     "sbb_layer_dp_apply_rows": (c_int, [c_void_p, c_void_p, c_long, c_long, c_long, c_void_p]),
     "sbb_layer_dp_finish": (c_int, [c_void_p, c_long, c_void_p]),
     "sbb_count_correct": (c_int, [c_int, c_void_p, c_void_p, c_long, c_long, POINTER(c_long), c_void_p]),
+    "sbb_update_mask_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_double, c_long,
+                                        c_long, c_long, c_long, c_long, c_long, c_void_p]),
+    "sbb_noalloc_last_error": (c_char_p, []),
     "sbb_layer_profile": (c_int, [c_void_p, c_int]),
     "sbb_layer_phase_calls": (c_int, [c_void_p, c_int, POINTER(c_long)]),
     "sbb_layer_phase_ms": (c_int, [c_void_p, c_int, c_long, POINTER(ctypes.c_float)]),
