@@ -11,6 +11,7 @@
 // product's x, which is contiguous along the reduction dimension and is
 // transposed on its way into shared memory.
 #include "sbb_kernels.cuh"
+#include "sbb_math.cuh"
 
 #include <atomic>
 #include <math.h>
@@ -38,31 +39,6 @@ TraceParams<T> make_trace_params(double taupdt, double cthr, long batch) {
 }
 template TraceParams<float> make_trace_params<float>(double, double, long);
 template TraceParams<double> make_trace_params<double>(double, double, long);
-
-// ----------------------------------------------------------------------------
-// Arithmetic shared by every kernel that touches a trace or a weight.
-// ----------------------------------------------------------------------------
-__device__ __forceinline__ float sbb_log(float x) { return logf(x); }
-__device__ __forceinline__ double sbb_log(double x) { return log(x); }
-__device__ __forceinline__ float sbb_exp(float x) { return expf(x); }
-__device__ __forceinline__ double sbb_exp(double x) { return exp(x); }
-
-// One moving-average step from a batch sum: sum/B, *taupdt, old*(1-taupdt), add,
-// clamp at zero (a NaN clamps to zero, as std::max(0, NaN) does).
-template <typename T>
-__device__ __forceinline__ T trace_ema(T old, T sum, const TraceParams<T> &p) {
-  T tmp = sum / p.batch;
-  tmp = tmp * p.taupdt;
-  T c = old * p.one_minus;
-  c = c + tmp;
-  return c > (T)0 ? c : (T)0;
-}
-
-template <typename T>
-__device__ __forceinline__ T log_ratio(T cij, T ci, T cj, T cthr4) {
-  const T num = cij < cthr4 ? cthr4 : cij;
-  return sbb_log(num / (ci * cj));
-}
 
 // ----------------------------------------------------------------------------
 // 16-byte vector helpers.
@@ -249,19 +225,21 @@ __device__ __forceinline__ void multiply_slab(const T *As, const T *Bs, T (&acc)
 // Row / column of micro-tile entry e (0..7) inside the 128-wide tile.
 __device__ __forceinline__ int micro_index(int t, int e) { return (e < 4 ? 0 : 64) + t * 4 + (e & 3); }
 
-// grid.x = row tiles of the output, grid.y = column tiles, grid.z = k-splits.
+// grid.x = row tiles of the output, grid.y = column tiles (swapped when cols_fastest), grid.z = k-splits.
 // A is [K x Mdim] MN-major (A_KMAJOR=false) or [Mdim x K] K-major (true); B is
 // [K x Ndim] MN-major.  k-split z covers [z*kper, min(K,(z+1)*kper)), kper a
 // multiple of the slab depth.
 template <typename T, bool A_KMAJOR, int VEC, class Epilogue>
 __global__ void __launch_bounds__(256, sizeof(T) == 4 ? 2 : 1)
     contraction_kernel(const T *__restrict__ A, long lda, const T *__restrict__ Bm, long ldb, long Mdim, long Ndim,
-                       int K, int kper, Epilogue ep) {
+                       int K, int kper, bool cols_fastest, Epilogue ep) {
   using TL = Tile<T>;
   __shared__ __align__(16) T As[2][TL::BK * TL::LD];
   __shared__ __align__(16) T Bs[2][TL::BK * TL::LD];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  const long m0 = (long)blockIdx.x * TL::BM, n0 = (long)blockIdx.y * TL::BN;
+  // Rasterisation: the fastest grid dimension walks the tiles that share the larger re-used operand.
+  const long m0 = (long)(cols_fastest ? blockIdx.y : blockIdx.x) * TL::BM;
+  const long n0 = (long)(cols_fastest ? blockIdx.x : blockIdx.y) * TL::BN;
   const int kbeg = blockIdx.z * kper;
   const int kend = min(K, kbeg + kper);
 
@@ -388,15 +366,17 @@ struct TraceEpilogue {
 
 template <typename T, bool A_KMAJOR, class Ep>
 static cudaError_t launch_contraction(const T *A, long lda, const T *Bm, long ldb, long Mdim, long Ndim, int K,
-                                      int splits, int kper, bool vec, Ep ep, cudaStream_t st) {
-  dim3 grid((unsigned)((Mdim + 127) / 128), (unsigned)((Ndim + 127) / 128), (unsigned)splits);
-  if (grid.x == 0 || grid.y == 0 || K <= 0) return cudaSuccess;
+                                      int splits, int kper, bool vec, bool cols_fastest, Ep ep, cudaStream_t st) {
+  const unsigned mt = (unsigned)((Mdim + 127) / 128), nt = (unsigned)((Ndim + 127) / 128);
+  if (mt == 0 || nt == 0 || K <= 0) return cudaSuccess;
+  if (cols_fastest && mt > 65535u) cols_fastest = false;
+  dim3 grid(cols_fastest ? nt : mt, cols_fastest ? mt : nt, (unsigned)splits);
   if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidConfiguration;
   constexpr int V = Vec16<T>::N;
   if (vec)
-    contraction_kernel<T, A_KMAJOR, V, Ep><<<grid, 256, 0, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, ep);
+    contraction_kernel<T, A_KMAJOR, V, Ep><<<grid, 256, 0, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, cols_fastest, ep);
   else
-    contraction_kernel<T, A_KMAJOR, 1, Ep><<<grid, 256, 0, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, ep);
+    contraction_kernel<T, A_KMAJOR, 1, Ep><<<grid, 256, 0, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, cols_fastest, ep);
   return launched();
 }
 
@@ -439,7 +419,7 @@ cudaError_t launch_forward_product(const T *x, const T *w, T *partial, long B, l
   const int kper = (int)((slabs + splits - 1) / splits) * Tile<T>::BK;
   const bool vec = (N % V == 0) && (M % V == 0) && aligned16(x) && aligned16(w);
   StoreEpilogue<T> ep{partial, B, M, M, B * M, (M % V == 0) && aligned16(partial)};
-  return launch_contraction<T, true>(x, N, w, M, B, M, (int)N, splits, kper, vec, ep, st);
+  return launch_contraction<T, true>(x, N, w, M, B, M, (int)N, splits, kper, vec, false, ep, st);
 }
 template cudaError_t launch_forward_product<float>(const float *, const float *, float *, long, long, long, int,
                                                    cudaStream_t);
@@ -647,7 +627,7 @@ cudaError_t launch_trace_update_fused(const T *x, const T *y, long B, long N, lo
   TraceEpilogue<T> ep{Ci, Cj, Cij, w, wmask, row_begin, row_end, M, H, Mc, p,
                       (M % V == 0) && aligned16(Cij) && aligned16(w)};
   const int kper = (int)((B + Tile<T>::BK - 1) / Tile<T>::BK) * Tile<T>::BK;
-  return launch_contraction<T, false>(x + row_begin, N, y, M, row_end - row_begin, M, (int)B, 1, kper, vec, ep, st);
+  return launch_contraction<T, false>(x + row_begin, N, y, M, row_end - row_begin, M, (int)B, 1, kper, vec, true, ep, st);
 }
 template cudaError_t launch_trace_update_fused<float>(const float *, const float *, long, long, long, long, long,
                                                       const float *, const float *, float *, float *,
@@ -666,7 +646,7 @@ cudaError_t launch_outer_product(const T *x, const T *y, long B, long N, long M,
                    aligned16(x) && aligned16(y);
   StoreEpilogue<T> ep{delta + row_begin * M, row_end - row_begin, M, M, 0, (M % V == 0) && aligned16(delta)};
   const int kper = (int)((B + Tile<T>::BK - 1) / Tile<T>::BK) * Tile<T>::BK;
-  return launch_contraction<T, false>(x + row_begin, N, y, M, row_end - row_begin, M, (int)B, 1, kper, vec, ep, st);
+  return launch_contraction<T, false>(x + row_begin, N, y, M, row_end - row_begin, M, (int)B, 1, kper, vec, true, ep, st);
 }
 template cudaError_t launch_outer_product<float>(const float *, const float *, long, long, long, float *, long, long,
                                                  cudaStream_t);
