@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mask", action="store_true", help="skip the per-step mask update")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--contraction", default="tensor", choices=["tensor", "general"],
+                    help="tcgen05 tensor-core kernels (default) or the general-shape FFMA kernels")
     return ap.parse_args()
 
 
@@ -202,6 +204,8 @@ def run_b200(args, wl, p, batch):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --impl b200 needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
+    check(lib.sbb_set_contraction_path(1 if args.contraction == "tensor" else 0))
+    tensor_path = args.contraction == "tensor" and bool(lib.sbb_tensor_path_available()) and p["dtype"] == np.float32
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     hp = p["hidden"]
@@ -268,6 +272,8 @@ def run_b200(args, wl, p, batch):
     fwd_ms, _ = phase_ms(0)
     trace_ms, trace_calls = phase_ms(1)
     check(lib.sbb_layer_profile(layer._handle, 0))
+    wait_status = ctypes.c_int(0)
+    check(lib.sbb_device_wait_status(ctypes.byref(wait_status)))
 
     # end to end through the host-buffer C-ABI call (N = 1 semantics per rank; under
     # data parallelism the exchange needs device buffers, so e2e is measured at N = 1).
@@ -336,7 +342,7 @@ def run_b200(args, wl, p, batch):
                    "global_batch": batch * world, "mask_update": "every step" if mask else "none",
                    "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
                        POOL, 2 * N * M * s / 1e6),
-                   "parallelism": "dp%d" % world},
+                   "contraction": "tcgen05 3xTF32" if tensor_path else "FFMA", "parallelism": "dp%d" % world},
         "roofline": roofline, "step_roofline": step_roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,
     }

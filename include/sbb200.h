@@ -234,6 +234,26 @@ int sbb_layer_profile(sbb_layer *layer, int enable);
 int sbb_layer_phase_calls(sbb_layer *layer, int phase, long *calls);
 int sbb_layer_phase_ms(sbb_layer *layer, int phase, long index, float *ms);
 
+/* Which kernels carry the two contractions (forward product, x^T y) of float32
+ * layers: SBB_PATH_GENERAL = the general-shape FFMA kernels, SBB_PATH_TENSOR =
+ * the tcgen05 tensor-core kernels (three TF32 products per float32 product)
+ * wherever the shape is eligible (row pitches multiples of 16 bytes, device of
+ * compute capability 10.x), the general-shape kernels otherwise.  float64 and
+ * ineligible shapes always take the general-shape kernels.  The initial value is
+ * SBB_PATH_TENSOR unless the environment variable SBB_CONTRACTION is "general".
+ * Process-wide. */
+#define SBB_PATH_GENERAL 0
+#define SBB_PATH_TENSOR 1
+int sbb_set_contraction_path(int path);
+int sbb_get_contraction_path(void);
+/* 1 when the tensor-core kernels can run on the current device. */
+int sbb_tensor_path_available(void);
+/* Status of the bounded device-side waits of the tensor-core kernels on the
+ * current device: *status = 0 when every wait completed, else the code of the
+ * first wait that gave up (SBB_ERR_TIMEOUT is returned as well).  Synchronises
+ * the device. */
+int sbb_device_wait_status(int *status);
+
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long sbb_kernel_launches(void);
 

@@ -13,7 +13,8 @@ from ctypes import POINTER, c_char_p, c_double, c_int, c_long, c_size_t, c_ulong
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libsbb200.so")
+# SBB_LIBRARY points at an alternative build of the same library (e.g. one with extra diagnostics).
+LIB_PATH = os.environ.get("SBB_LIBRARY") or os.path.join(HERE, "libsbb200.so")
 
 SBB_OK = 0
 ERR_NAMES = {1: "SBB_ERR_INVALID", 2: "SBB_ERR_CUDA", 3: "SBB_ERR_NO_DEVICE", 4: "SBB_ERR_UNSUPPORTED",
@@ -77,6 +78,10 @@ SIGNATURES = {
     "sbb_layer_profile": (c_int, [c_void_p, c_int]),
     "sbb_layer_phase_calls": (c_int, [c_void_p, c_int, POINTER(c_long)]),
     "sbb_layer_phase_ms": (c_int, [c_void_p, c_int, c_long, POINTER(ctypes.c_float)]),
+    "sbb_set_contraction_path": (c_int, [c_int]),
+    "sbb_get_contraction_path": (c_int, []),
+    "sbb_tensor_path_available": (c_int, []),
+    "sbb_device_wait_status": (c_int, [POINTER(c_int)]),
     "sbb_kernel_launches": (c_ulonglong, []),
     "sbb_stream_sync": (c_int, [c_void_p]),
 }

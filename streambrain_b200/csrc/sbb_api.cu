@@ -3,8 +3,12 @@
 // include/sbb200.h for the contract of every entry point.
 #include "../../include/sbb200.h"
 #include "sbb_kernels.cuh"
+#include "sbb_tc.cuh"
 
 #include <cstdarg>
+#include <cstdlib>
+#include <type_traits>
+#include <vector>
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -54,6 +58,20 @@ int need_device() {
 }
 
 size_t esize(int dtype) { return dtype == SBB_F32 ? 4 : 8; }
+
+// Process-wide choice of contraction kernels (see sbb_set_contraction_path).
+int initial_path() {
+  const char *e = std::getenv("SBB_CONTRACTION");
+  if (e && std::strcmp(e, "general") == 0) return SBB_PATH_GENERAL;
+  return SBB_PATH_TENSOR;
+}
+int g_path = initial_path();
+
+template <typename T>
+bool tensor_path(const void *x, const void *other, long N, long M) {
+  if (!std::is_same<T, float>::value || g_path != SBB_PATH_TENSOR) return false;
+  return sbb::tc_shape_ok(x, other, N, M) && sbb::tc_available();
+}
 
 int check_dtype(int dtype) {
   if (dtype != SBB_F32 && dtype != SBB_F64) return fail(SBB_ERR_INVALID, "invalid dtype %d", dtype);
@@ -125,6 +143,7 @@ struct sbb_layer {
   Scratch score;         // N REALs
   Scratch csum;          // N ints
   Scratch hx, hy, ht;    // staging for the host-buffer entry points
+  Scratch col_hc;        // M ints: hypercolumn of every output column (j / Mc)
   cudaStream_t own_stream = nullptr;
   // optional per-phase event ring (sbb_layer_profile)
   bool profiling = false;
@@ -159,15 +178,21 @@ struct PhaseTimer {
 
 template <typename T>
 int layer_forward(sbb_layer *L, const T *x, long B, T *y, cudaStream_t st) {
-  const int splits = sbb::forward_splits<T>(B, L->N, L->M);
+  const T *W = static_cast<const T *>(L->state[SBB_STATE_WEIGHTS]);
+  const bool tc = tensor_path<T>(x, W, L->N, L->M);
+  const int splits = tc ? sbb::forward_splits_tc(B, L->N, L->M) : sbb::forward_splits<T>(B, L->N, L->M);
   T *partial = y;
   if (splits > 1) {
     SBB_TRY(L->fwd_partial.reserve((size_t)splits * B * L->M * sizeof(T)));
     partial = static_cast<T *>(L->fwd_partial.d);
   }
   PhaseTimer timer(L, SBB_PHASE_FORWARD, st);
-  SBB_CUDA(sbb::launch_forward_product<T>(x, static_cast<const T *>(L->state[SBB_STATE_WEIGHTS]), partial, B, L->N,
-                                          L->M, splits, st));
+  if (tc) {
+    if constexpr (std::is_same<T, float>::value)
+      SBB_CUDA(sbb::launch_forward_product_tc(x, W, partial, B, L->N, L->M, splits, st));
+  } else {
+    SBB_CUDA(sbb::launch_forward_product<T>(x, W, partial, B, L->N, L->M, splits, st));
+  }
   timer.stop();
   SBB_CUDA(sbb::launch_reduce_bias_softmax<T>(partial, splits, static_cast<const T *>(L->state[SBB_STATE_BIAS]), y, B,
                                               L->H, L->Mc, 1, st));
@@ -206,10 +231,19 @@ int layer_train_step(sbb_layer *L, const T *x, const T *y, long B, long h, cudaS
   SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, nullptr, Ci, p, 1, st));
   SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, nullptr, Cj, p, 1, st));
   PhaseTimer timer(L, SBB_PHASE_TRACE, st);
-  SBB_CUDA(sbb::launch_trace_update_fused<T>(x, y, B, L->N, L->M, L->H, L->Mc, Ci, Cj,
-                                             static_cast<T *>(L->state[SBB_STATE_CIJ]),
-                                             static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
-                                             static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 0, L->N, st));
+  if (tensor_path<T>(x, y, L->N, L->M)) {
+    if constexpr (std::is_same<T, float>::value)
+      SBB_CUDA(sbb::launch_trace_update_tc(x, y, B, L->N, L->M, L->H, Ci, Cj, static_cast<T *>(L->state[SBB_STATE_CIJ]),
+                                           static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
+                                           static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]),
+                                           static_cast<const int *>(L->col_hc.d), p, 0, L->N, st));
+  } else {
+    SBB_CUDA(sbb::launch_trace_update_fused<T>(x, y, B, L->N, L->M, L->H, L->Mc, Ci, Cj,
+                                               static_cast<T *>(L->state[SBB_STATE_CIJ]),
+                                               static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
+                                               static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 0, L->N,
+                                               st));
+  }
   timer.stop();
   return layer_finish<T>(L, h, st);
 }
@@ -222,7 +256,13 @@ int layer_dp_local(sbb_layer *L, const T *x, const T *y, long B, T *delta, long 
     SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, delta + L->N, nullptr, p, 0, st));
   }
   PhaseTimer timer(L, SBB_PHASE_TRACE, st);
-  SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, L->N, L->M, delta + L->N + L->M, rb, re, st));
+  T *xty = delta + L->N + L->M;
+  if (tensor_path<T>(x, y, L->N, L->M) && (reinterpret_cast<uintptr_t>(xty) & 7u) == 0) {
+    if constexpr (std::is_same<T, float>::value)
+      SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, L->N, L->M, xty, rb, re, st));
+  } else {
+    SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, L->N, L->M, xty, rb, re, st));
+  }
   timer.stop();
   return SBB_OK;
 }
@@ -273,6 +313,21 @@ const char *sbb_last_error(void) { return g_error.c_str(); }
 int sbb_device_count(void) { return device_count(); }
 unsigned long long sbb_kernel_launches(void) { return sbb::kernel_launches(); }
 
+int sbb_set_contraction_path(int path) {
+  ARG(path == SBB_PATH_GENERAL || path == SBB_PATH_TENSOR, "invalid contraction path %d", path);
+  g_path = path;
+  return SBB_OK;
+}
+int sbb_get_contraction_path(void) { return g_path; }
+int sbb_tensor_path_available(void) { return device_count() > 0 && sbb::tc_available() ? 1 : 0; }
+int sbb_device_wait_status(int *status) {
+  ARG(status, "device_wait_status: null pointer");
+  SBB_TRY(need_device());
+  SBB_CUDA(sbb::tc_read_status(status));
+  if (*status != 0) return fail(SBB_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", *status);
+  return SBB_OK;
+}
+
 int sbb_stream_sync(void *stream) {
   SBB_TRY(need_device());
   SBB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
@@ -292,14 +347,19 @@ int sbb_update_state(int dtype, void *activation, const void *inputs, const void
   SBB_TRY(w.upload(weights, N * M * s));
   SBB_TRY(b.upload(bias, M * s));
   SBB_TRY(out.alloc(B * M * s));
-  const int splits = DISPATCH(dtype, sbb::forward_splits<float>(B, N, M), sbb::forward_splits<double>(B, N, M));
+  const bool tc = dtype == SBB_F32 && tensor_path<float>(x.d, w.d, N, M);
+  const int splits = tc ? sbb::forward_splits_tc(B, N, M)
+                        : DISPATCH(dtype, sbb::forward_splits<float>(B, N, M), sbb::forward_splits<double>(B, N, M));
   void *partial = out.d;
   if (splits > 1) {
     SBB_TRY(part.alloc((size_t)splits * B * M * s));
     partial = part.d;
   }
   if (dtype == SBB_F32) {
-    SBB_CUDA(sbb::launch_forward_product<float>(x.as<float>(), w.as<float>(), (float *)partial, B, N, M, splits, 0));
+    if (tc)
+      SBB_CUDA(sbb::launch_forward_product_tc(x.as<float>(), w.as<float>(), (float *)partial, B, N, M, splits, 0));
+    else
+      SBB_CUDA(sbb::launch_forward_product<float>(x.as<float>(), w.as<float>(), (float *)partial, B, N, M, splits, 0));
     SBB_CUDA(sbb::launch_reduce_bias_softmax<float>((float *)partial, splits, b.as<float>(), out.as<float>(), B, 1, M,
                                                     0, 0));
   } else {
@@ -362,7 +422,12 @@ int update_counters_t(void *Ci, void *Cj, void *Cij, const void *a_i, const void
   T *sxy = sx + ((N + M + 3) / 4) * 4;
   SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, sx, nullptr, p, 0, 0));
   SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, sy, nullptr, p, 0, 0));
-  SBB_CUDA(sbb::launch_outer_product<T>(dx.as<T>(), dy.as<T>(), B, N, M, sxy, 0, N, 0));
+  if (tensor_path<T>(dx.d, dy.d, N, M)) {
+    if constexpr (std::is_same<T, float>::value)
+      SBB_CUDA(sbb::launch_outer_product_tc(dx.as<T>(), dy.as<T>(), B, N, M, sxy, 0, N, 0));
+  } else {
+    SBB_CUDA(sbb::launch_outer_product<T>(dx.as<T>(), dy.as<T>(), B, N, M, sxy, 0, N, 0));
+  }
   SBB_CUDA(sbb::launch_counters_apply<T>(dci.as<T>(), sx, N, (T)taupdt, (T)B, 0));
   SBB_CUDA(sbb::launch_counters_apply<T>(dcj.as<T>(), sy, M, (T)taupdt, (T)B, 0));
   SBB_CUDA(sbb::launch_counters_apply<T>(dcij.as<T>(), sxy, N * M, (T)taupdt, (T)B, 0));
@@ -386,8 +451,14 @@ int update_weights_t(void *Ci, void *Cj, void *Cij, const void *a_i, const void 
   const sbb::TraceParams<T> p = sbb::make_trace_params<T>(taupdt, cthr, B);
   SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, nullptr, dci.as<T>(), p, 1, 0));
   SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, nullptr, dcj.as<T>(), p, 1, 0));
-  SBB_CUDA(sbb::launch_trace_update_fused<T>(dx.as<T>(), dy.as<T>(), B, N, M, 1, M, dci.as<T>(), dcj.as<T>(),
-                                             dcij.as<T>(), dw.as<T>(), nullptr, p, 0, N, 0));
+  if (tensor_path<T>(dx.d, dy.d, N, M)) {
+    if constexpr (std::is_same<T, float>::value)
+      SBB_CUDA(sbb::launch_trace_update_tc(dx.as<T>(), dy.as<T>(), B, N, M, 1, dci.as<T>(), dcj.as<T>(), dcij.as<T>(),
+                                           dw.as<T>(), nullptr, nullptr, p, 0, N, 0));
+  } else {
+    SBB_CUDA(sbb::launch_trace_update_fused<T>(dx.as<T>(), dy.as<T>(), B, N, M, 1, M, dci.as<T>(), dcj.as<T>(),
+                                               dcij.as<T>(), dw.as<T>(), nullptr, p, 0, N, 0));
+  }
   SBB_CUDA(cudaDeviceSynchronize());
   SBB_TRY(dci.download(Ci));
   SBB_TRY(dcj.download(Cj));
@@ -562,6 +633,13 @@ int sbb_layer_create(const sbb_layer_desc *desc, sbb_layer **out) {
   if (rc == SBB_OK && desc->kind == SBB_LAYER_PLASTIC) {
     rc = L->score.reserve((size_t)L->N * s);
     if (rc == SBB_OK) rc = L->csum.reserve((size_t)L->N * sizeof(int));
+    if (rc == SBB_OK) rc = L->col_hc.reserve((size_t)(L->M + 4) * sizeof(int));
+    if (rc == SBB_OK) {
+      std::vector<int> hc((size_t)L->M);
+      for (long j = 0; j < L->M; ++j) hc[(size_t)j] = (int)(j / L->Mc);
+      e = cudaMemcpy(L->col_hc.d, hc.data(), hc.size() * sizeof(int), cudaMemcpyHostToDevice);
+      if (e != cudaSuccess) rc = cuda_fail(e, "layer_create");
+    }
   }
   if (rc != SBB_OK) {
     std::string keep = g_error;
@@ -583,6 +661,7 @@ int sbb_layer_destroy(sbb_layer *L) {
   L->hx.release();
   L->hy.release();
   L->ht.release();
+  L->col_hc.release();
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
   if (L->ev_created)
     for (int ph = 0; ph < 2; ++ph)

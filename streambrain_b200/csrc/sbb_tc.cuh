@@ -1,0 +1,44 @@
+// Launch interface of the tcgen05 (5th-generation tensor core) contraction
+// kernels: float32 operands multiplied as three TF32 products with float32
+// accumulation in tensor memory, operands fetched by TMA.  Only shapes whose
+// row pitches are multiples of 16 bytes are eligible; callers fall back to the
+// general-shape kernels otherwise.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sbb_kernels.cuh"
+
+namespace sbb {
+
+// True when the current device is compute capability 10.x and the driver's
+// tensor-map encoder could be resolved.
+bool tc_available();
+
+// Row pitches of x[B,N], y[B,M] / w[N,M] must be multiples of 16 bytes and the
+// base pointers 16-byte aligned.
+bool tc_shape_ok(const void *x, const void *y_or_w, long N, long M);
+
+// Number of k-splits the tensor-core forward product uses (scratch = splits*B*M floats).
+int forward_splits_tc(long B, long N, long M);
+
+// partial[s, B, M] = x[B, k-range s] * w[N, M]
+cudaError_t launch_forward_product_tc(const float *x, const float *w, float *partial, long B, long N, long M,
+                                      int splits, cudaStream_t st);
+
+// Fused trace step (same contract as launch_trace_update_fused); col_hc[j] = j / Mc.
+cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long N, long M, long H,
+                                   const float *Ci, const float *Cj, float *Cij, float *w, const uint8_t *wmask,
+                                   const int *col_hc, TraceParams<float> p, long row_begin, long row_end,
+                                   cudaStream_t st);
+
+// delta[i, j] = sum_b x[b, i] y[b, j] for rows [row_begin,row_end)
+cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long N, long M, float *delta,
+                                    long row_begin, long row_end, cudaStream_t st);
+
+// Status word of the bounded device-side waits on the current device: 0 = all
+// waits completed, otherwise the code of the first wait that gave up.
+// Synchronises the device.
+cudaError_t tc_read_status(int *status);
+
+}  // namespace sbb

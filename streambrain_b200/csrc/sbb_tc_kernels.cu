@@ -1,0 +1,826 @@
+// tcgen05 / TMEM / TMA contraction kernels for sm_100a.
+//
+// One persistent, warp-specialised kernel template serves both contractions of
+// the layer step:
+//
+//   trace update   D[i, j] = sum_b x[b, i] * y[b, j]   A = x  (MN-major), B = y (MN-major), K = batch
+//   forward        D[b, j] = sum_k x[b, k] * w[k, j]   A = x  (K-major),  B = w (MN-major), K = in_features
+//
+// float32 accuracy on TF32 tensor cores: every operand value v is split in
+// shared memory into hi = tf32(v) (round to nearest) and lo = v - hi, and each
+// k-step issues three MMAs  hi*hi + hi*lo + lo*hi  into one float32 accumulator
+// in tensor memory (the dropped lo*lo term is below 2^-22 relative).
+//
+// Roles inside a CTA (448 threads, one CTA per SM, tiles walked persistently):
+//   warps 0-3   converters: wait for a TMA stage, write hi in place and lo beside it
+//   warps 4-11  epilogue: tcgen05.ld the accumulator (16x256b shape, so that four
+//               lanes cover 32 contiguous bytes of a row) and either store it or run
+//               the trace / weight arithmetic against Cij in global memory
+//   warp 12     TMA producer (one lane): cp.async.bulk.tensor loads, no multicast
+//   warp 13     MMA issuer (one lane) and owner of the TMEM allocation
+// Hand-offs use mbarriers; every wait is bounded by wall time (%globaltimer):
+// a wait that gives up records a code in a global status word, raises the CTA's
+// abort flag, and every role falls through to the common tear-down (drain the
+// tensor pipe, free TMEM) instead of spinning.
+#include "sbb_tc.cuh"
+
+#include <cuda.h>
+
+#include <atomic>
+#include <cstdlib>
+#include <mutex>
+
+#include "sbb_math.cuh"
+
+namespace sbb {
+namespace {
+
+constexpr int kConvWarps = 4;
+constexpr int kEpiWarps = 8;
+constexpr int kTmaWarp = kConvWarps + kEpiWarps;
+constexpr int kMmaWarp = kTmaWarp + 1;
+constexpr int kThreads = (kMmaWarp + 1) * 32;  // 448
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+
+enum WaitCode { kWaitEmpty = 1, kWaitFull = 2, kWaitConv = 3, kWaitAccEmpty = 4, kWaitAccFull = 5, kWaitDrain = 6 };
+
+struct TcWork {
+  int m_tiles, n_tiles, splits;
+  int k_total;      // extent of the reduction dimension
+  int k_per_split;  // multiple of the stage depth
+  int m_fastest;    // tile order: row tiles fastest (1) or column tiles fastest (0)
+  int a_row0;       // offset added to the A row coordinate (first output row of this launch)
+};
+
+struct TcEpilogue {
+  // raw store: out[(split*rows + m)*ld + n]
+  float *out;
+  long rows, cols, ld;
+  // fused trace step (rows = row_end - row_begin, global row = row0 + m)
+  const float *Ci;
+  const float *Cj;
+  float *Cij;
+  float *W;
+  const uint8_t *wmask;
+  const int *col_hc;
+  long H, row0;
+  TraceParams<float> p;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting or the time limit passed
+// (in which case it raises the abort flag and records `code`).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                            int code) {
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 TMEM lanes x 32 columns: thread t gets, for rep = 0..3, registers
+//   r[4*rep+0..1] = lane t/4,     columns 8*rep + 2*(t%4) + {0,1}
+//   r[4*rep+2..3] = lane t/4 + 8, same columns.
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&r)[16]) {
+  uint32_t u[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int k = 0; k < 16; ++k) r[k] = __uint_as_float(u[k]);
+}
+
+// Shared-memory matrix descriptor (sm_100 version field set).
+//   K-major operand:  rows of 128 bytes along k, 128-byte swizzle with 16-byte base (layout type 2);
+//                     SBO = 1024 (eight rows), LBO unused.
+//   MN-major 32-bit operand: the only layout the tensor core accepts is the 128-byte swizzle with
+//                     32-byte base (layout type 1): atoms of 4 k-rows x 128 bytes (32 elements along
+//                     MN); SBO = distance between consecutive 4-row atoms along k, LBO = distance
+//                     between 32-element groups along MN.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return smem_desc(saddr, lbo_bytes, sbo_bytes, 2u);  // K-major, SWIZZLE_128B
+}
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr, uint32_t lbo_bytes) {
+  return smem_desc(saddr, lbo_bytes, 512u, 1u);       // MN-major, SWIZZLE_128B_BASE32B
+}
+
+__device__ __forceinline__ float tf32_rn(float v) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+  return __uint_as_float(u);
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int BN, int BK, int STAGES>
+struct TcSmem {
+  static constexpr int A_BYTES = 128 * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // TMA landing zone (becomes "hi" in place)
+  static constexpr int STAGE_BYTES = 2 * RAW_BYTES;    // + the "lo" copy
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 3 * STAGES + 5;      // full, conv, empty per stage; acc_full[2], acc_empty[2], drain
+  static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr, abort flag, alignment slack
+};
+
+__device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// Two 16-lane halves of a warp's TMEM lane quarter, 32 columns each, one wait.
+__device__ __forceinline__ void tmem_ld_pair(uint32_t taddr_lo, uint32_t taddr_hi, float (&a)[16], float (&b)[16]) {
+  uint32_t u[16], v[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+      : "r"(taddr_lo)
+      : "memory");
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr_hi)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    a[k] = __uint_as_float(u[k]);
+    b[k] = __uint_as_float(v[k]);
+  }
+}
+
+// CHAIN = number of k-blocks accumulated in tensor memory before the running sum
+// is taken over by float32 registers (0 = the whole k-range in tensor memory).
+// The tensor core adds each MMA into its accumulator with less than IEEE
+// rounding, so the error of a chain grows with its length; long reductions
+// (the forward pass sums over in_features) are cut into short chains whose
+// results the epilogue warps add in full float32.
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
+__global__ void __launch_bounds__(kThreads, 1)
+    tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcWork wk,
+                          TcEpilogue ep, int *status) {
+  using SM = TcSmem<BN, BK, STAGES>;
+  static_assert(!A_KMAJOR || BK == 32, "a K-major operand is loaded as one 128-byte-wide box");
+  static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0, "tile shape");
+  static_assert(!(FUSED && CHAIN > 0), "the fused epilogue consumes a whole-range accumulator");
+  static_assert(CHAIN == 0 || BN <= 128, "register-resident running sums are sized for 128 columns");
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t dyn_base = smem_u32(smem_dyn);
+  const uint32_t base = (dyn_base + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+  uint8_t *smem = smem_dyn + (base - dyn_base);
+  const uint32_t bars = base + SM::BAR_OFFSET;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_conv = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+  const uint32_t bar_drain = bars + 8u * (3 * STAGES + 4);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + SM::BAR_OFFSET + SM::NUM_BARS * 8);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_conv(s), kConvWarps * 32);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), kEpiWarps * 32);
+    }
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
+  // Decode a work index into (m_tile, n_tile, split) and its k-block range.
+  auto decode = [&](long w, int &mt, int &nt, int &sp, int &kbeg, int &nkb) {
+    if (wk.m_fastest) {
+      mt = (int)(w % wk.m_tiles);
+      const long r = w / wk.m_tiles;
+      nt = (int)(r % wk.n_tiles);
+      sp = (int)(r / wk.n_tiles);
+    } else {
+      nt = (int)(w % wk.n_tiles);
+      const long r = w / wk.n_tiles;
+      mt = (int)(r % wk.m_tiles);
+      sp = (int)(r / wk.m_tiles);
+    }
+    kbeg = sp * wk.k_per_split;
+    const int kend = min(wk.k_total, kbeg + wk.k_per_split);
+    nkb = (kend - kbeg + BK - 1) / BK;
+  };
+
+  if (warp == kTmaWarp) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        int mt, nt, sp, kbeg, nkb;
+        decode(w, mt, nt, sp, kbeg, nkb);
+        if (FUSED) {
+          // Pull this tile's block of the trace matrix towards L2 while its products run;
+          // the epilogue reads it one tile-time from now.
+          const long n0 = (long)nt * BN;
+          const long ncols = ep.cols - n0 < BN ? ep.cols - n0 : BN;
+          const long r1 = ep.rows - (long)mt * 128 < 128 ? ep.rows - (long)mt * 128 : 128;
+          const float *blk = ep.Cij + (ep.row0 + (long)mt * 128) * ep.cols + n0;
+          for (long r = 0; r < r1; ++r) prefetch_l2(blk + r * ep.cols, (uint32_t)(ncols * 4));
+        }
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status, kWaitEmpty)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_full(s), SM::RAW_BYTES);
+          const uint32_t a_dst = base + s * SM::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + SM::A_BYTES;
+          const int k0 = kbeg + kb * BK;
+          if (A_KMAJOR) {
+            tma_load_2d(a_dst, &tmA, k0, wk.a_row0 + mt * 128, bar_full(s));
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              tma_load_2d(a_dst + c * (BK * 128), &tmA, wk.a_row0 + mt * 128 + 32 * c, k0, bar_full(s));
+          }
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) tma_load_2d(b_dst + c * (BK * 128), &tmB, nt * BN + 32 * c, k0, bar_full(s));
+        }
+      }
+      if (!ok) {
+        // Loads already issued still land in this CTA's shared memory: give them
+        // a bounded moment before the CTA retires.
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_KMAJOR ? 0u : 1u) << 15) | (1u << 16) |
+                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      uint32_t it = 0, chain = 0;
+      bool ok = true;
+      for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        int mt, nt, sp, kbeg, nkb;
+        decode(w, mt, nt, sp, kbeg, nkb);
+        int kb = 0;
+        while (kb < nkb && ok) {
+          const uint32_t buf = chain & 1u, aph = (chain >> 1) & 1u;
+          if (!mbar_wait(bar_acc_empty(buf), aph ^ 1u, abort_flag, status, kWaitAccEmpty)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          const int kb_end = CHAIN > 0 ? min(nkb, kb + CHAIN) : nkb;
+          for (bool first = true; kb < kb_end; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1u;
+            if (!mbar_wait(bar_conv(s), ph, abort_flag, status, kWaitConv)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_hi = base + s * SM::STAGE_BYTES;
+            const uint32_t b_hi = a_hi + SM::A_BYTES;
+            const uint32_t a_lo = a_hi + SM::RAW_BYTES;
+            const uint32_t b_lo = b_hi + SM::RAW_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < BK / 8; ++kk) {
+              // One MMA consumes 8 k-values: 32 bytes along a K-major row, or eight
+              // 128-byte rows (two 4-row swizzle atoms) of an MN-major operand.
+              const uint64_t da_hi =
+                  A_KMAJOR ? smem_desc_sw128(a_hi + kk * 32, 16, 1024) : smem_desc_mn(a_hi + kk * 1024, BK * 128);
+              const uint64_t da_lo =
+                  A_KMAJOR ? smem_desc_sw128(a_lo + kk * 32, 16, 1024) : smem_desc_mn(a_lo + kk * 1024, BK * 128);
+              const uint64_t db_hi = smem_desc_mn(b_hi + kk * 1024, BK * 128);
+              const uint64_t db_lo = smem_desc_mn(b_lo + kk * 1024, BK * 128);
+              mma_tf32(d_tmem, da_lo, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
+              mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+              mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            }
+            first = false;
+            mma_commit(bar_empty(s));  // the stage may be refilled once these MMAs have read it
+          }
+          if (ok) {
+            mma_commit(bar_acc_full(buf));
+            ++chain;
+          }
+        }
+      }
+      // Drain: nothing of this CTA may still be running in the tensor pipe when TMEM is freed.
+      mma_commit(bar_drain);
+      mbar_wait(bar_drain, 0, abort_flag, status, kWaitDrain);
+    }
+  } else if (warp < kConvWarps) {
+    // ------------------------------------------------------------ hi / lo converters
+    uint32_t it = 0;
+    bool ok = true;
+    for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      int mt, nt, sp, kbeg, nkb;
+      decode(w, mt, nt, sp, kbeg, nkb);
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        if (!mbar_wait(bar_full(s), ph, abort_flag, status, kWaitFull)) { ok = false; break; }
+        float4 *raw = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES);
+        float4 *lo = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
+#pragma unroll 4
+        for (int c = threadIdx.x; c < SM::RAW_BYTES / 16; c += kConvWarps * 32) {
+          const float4 v = raw[c];
+          float4 h, l;
+          h.x = tf32_rn(v.x); h.y = tf32_rn(v.y); h.z = tf32_rn(v.z); h.w = tf32_rn(v.w);
+          l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+          raw[c] = h;
+          lo[c] = l;
+        }
+        fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
+        mbar_arrive(bar_conv(s));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    // Thread (lane) owns four tile rows (16*hh + lane/4 + 8*rr) of its warp's TMEM lane
+    // quarter and, per 32-column group, the column pairs 8*rep + 2*(lane%4) + {0,1}:
+    // four lanes cover 32 contiguous bytes of a row, so global accesses fill whole sectors.
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int ch = (warp - kConvWarps) >> 2;     // which half of the tile's columns
+    const int lr = lane >> 2, lc = (lane & 3) * 2;
+    constexpr int NG = BN / 64;                  // 32-column groups per warp
+    uint32_t chain = 0;
+    bool ok = true;
+    for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      int mt, nt, sp, kbeg, nkb;
+      decode(w, mt, nt, sp, kbeg, nkb);
+      const long m_base = (long)mt * 128 + 32 * q;   // first tile row of this warp's lane quarter
+      const long n_base = (long)nt * BN + ch * (BN / 2);
+      bool rv[4];
+      long grow[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long m = m_base + 16 * (j >> 1) + lr + 8 * (j & 1);
+        rv[j] = m < ep.rows;
+        grow[j] = m;
+      }
+      if constexpr (CHAIN > 0) {
+        // ---- running sums in registers, one TMEM chain at a time (forward product)
+        float sum[NG][2][16];
+#pragma unroll
+        for (int g = 0; g < NG; ++g)
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+            for (int k = 0; k < 16; ++k) sum[g][hh][k] = 0.f;
+        const int nchains = (nkb + CHAIN - 1) / CHAIN;
+        for (int c = 0; c < nchains && ok; ++c, ++chain) {
+          const uint32_t buf = chain & 1u, aph = (chain >> 1) & 1u;
+          if (!mbar_wait(bar_acc_full(buf), aph, abort_flag, status, kWaitAccFull)) { ok = false; break; }
+          __syncwarp();
+          tc_fence_after();
+#pragma unroll
+          for (int g = 0; g < NG; ++g) {
+            float a0[16], a1[16];
+            const uint32_t t0 = tmem_base + buf * BN + ch * (BN / 2) + g * 32 + ((uint32_t)(32 * q) << 16);
+            tmem_ld_pair(t0, t0 + (16u << 16), a0, a1);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              sum[g][0][k] += a0[k];
+              sum[g][1][k] += a1[k];
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(bar_acc_empty(buf));
+        }
+        if (ok) {
+#pragma unroll
+          for (int g = 0; g < NG; ++g)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (!rv[j]) continue;
+              float *orow = ep.out + ((long)sp * ep.rows + grow[j]) * ep.ld;
+#pragma unroll
+              for (int rep = 0; rep < 4; ++rep) {
+                const long n = n_base + g * 32 + rep * 8 + lc;
+                if (n < ep.cols)
+                  __stcs(reinterpret_cast<float2 *>(orow + n),
+                         make_float2(sum[g][j >> 1][rep * 4 + (j & 1) * 2], sum[g][j >> 1][rep * 4 + (j & 1) * 2 + 1]));
+              }
+            }
+        }
+      } else {
+        const uint32_t buf = chain & 1u, aph = (chain >> 1) & 1u;
+        if (!mbar_wait(bar_acc_full(buf), aph, abort_flag, status, kWaitAccFull)) { ok = false; break; }
+        __syncwarp();
+        tc_fence_after();
+        float ci[4];
+        bool skip[4];
+        const uint8_t *mrow[4];
+        if (FUSED) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const long i = ep.row0 + grow[j];
+            ci[j] = rv[j] ? ep.Ci[i] : 1.f;
+            skip[j] = ci[j] < ep.p.cthr;
+            mrow[j] = (rv[j] && ep.wmask) ? ep.wmask + i * ep.H : nullptr;
+          }
+        }
+#pragma unroll 1
+        for (int g = 0; g < NG; ++g) {
+          float a0[16], a1[16];
+          const uint32_t t0 = tmem_base + buf * BN + ch * (BN / 2) + g * 32 + ((uint32_t)(32 * q) << 16);
+          __syncwarp();  // tcgen05.ld is warp-collective
+          tmem_ld_pair(t0, t0 + (16u << 16), a0, a1);
+          const long n0 = n_base + g * 32 + lc;
+          bool cv[4];
+#pragma unroll
+          for (int rep = 0; rep < 4; ++rep) cv[rep] = n0 + rep * 8 < ep.cols;  // cols is even: n+1 is in range too
+          if (FUSED) {
+            // Issue every global load of this 32-column group before the first use, so each
+            // thread keeps 16 eight-byte loads of the trace matrix in flight.
+            float2 c[4][4], cj[4];
+            int2 hc[4];
+#pragma unroll
+            for (int rep = 0; rep < 4; ++rep) {
+              cj[rep] = cv[rep] ? __ldg(reinterpret_cast<const float2 *>(ep.Cj + n0 + rep * 8)) : make_float2(1.f, 1.f);
+              hc[rep] = (cv[rep] && ep.wmask) ? __ldg(reinterpret_cast<const int2 *>(ep.col_hc + n0 + rep * 8))
+                                              : make_int2(0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+              for (int rep = 0; rep < 4; ++rep)
+                c[j][rep] = (rv[j] && cv[rep])
+                                ? __ldcs(reinterpret_cast<const float2 *>(ep.Cij + (ep.row0 + grow[j]) * ep.cols + n0 + rep * 8))
+                                : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float *acc = (j >> 1) ? a1 : a0;
+#pragma unroll
+              for (int rep = 0; rep < 4; ++rep) {
+                if (!(rv[j] && cv[rep])) continue;
+                float2 c2 = c[j][rep], w2 = make_float2(0.f, 0.f);
+                c2.x = trace_ema(c2.x, acc[rep * 4 + (j & 1) * 2 + 0], ep.p);
+                c2.y = trace_ema(c2.y, acc[rep * 4 + (j & 1) * 2 + 1], ep.p);
+                if (!skip[j]) {
+                  bool on0 = !(cj[rep].x < ep.p.cthr), on1 = !(cj[rep].y < ep.p.cthr);
+                  if (mrow[j]) {
+                    on0 = on0 && mrow[j][hc[rep].x] != 0;
+                    on1 = on1 && mrow[j][hc[rep].y] != 0;
+                  }
+                  if (on0) w2.x = log_ratio(c2.x, ci[j], cj[rep].x, ep.p.cthr4);
+                  if (on1) w2.y = log_ratio(c2.y, ci[j], cj[rep].y, ep.p.cthr4);
+                }
+                const long off = (ep.row0 + grow[j]) * ep.cols + n0 + rep * 8;
+                __stcs(reinterpret_cast<float2 *>(ep.Cij + off), c2);
+                __stcs(reinterpret_cast<float2 *>(ep.W + off), w2);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (!rv[j]) continue;
+              const float *acc = (j >> 1) ? a1 : a0;
+              float *orow = ep.out + ((long)sp * ep.rows + grow[j]) * ep.ld;
+#pragma unroll
+              for (int rep = 0; rep < 4; ++rep)
+                if (cv[rep])
+                  __stcs(reinterpret_cast<float2 *>(orow + n0 + rep * 8),
+                         make_float2(acc[rep * 4 + (j & 1) * 2], acc[rep * 4 + (j & 1) * 2 + 1]));
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar_acc_empty(buf));  // the accumulator buffer may be overwritten
+        ++chain;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+std::mutex g_mutex;
+EncodeTiledFn g_encode = nullptr;
+int g_available = -1;           // -1 unknown, 0 no, 1 yes
+int *g_status[64] = {nullptr};  // per-device status word
+int g_sm_count_tc[64] = {0};
+
+int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev < 0 || dev >= 64 ? 0 : dev;
+}
+
+bool init_once() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_available < 0) {
+    g_available = 0;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess && fn != nullptr) {
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+      g_available = 1;
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  return g_available == 1;
+}
+
+int *status_word() {
+  const int dev = current_device();
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_status[dev] == nullptr) {
+    int *p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+    g_status[dev] = p;
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    g_sm_count_tc[dev] = n > 0 ? n : 148;
+  }
+  return g_status[dev];
+}
+
+// 2-D float32 tensor map over a row-major [outer, inner] matrix, zero fill.  `mn_major` selects the
+// 32-byte-base flavour of the 128-byte swizzle that MN-major 32-bit operands need.
+bool make_map(CUtensorMap *map, const float *base, long inner, long outer, int box_inner, int box_outer,
+              bool mn_major) {
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)inner * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
+cudaError_t launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, const TcWork &wk, const TcEpilogue &ep,
+                      cudaStream_t st) {
+  using SM = TcSmem<BN, BK, STAGES>;
+  int *status = status_word();
+  if (status == nullptr) return cudaErrorMemoryAllocation;
+  auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN>;
+  static bool configured[64] = {false};
+  const int dev = current_device();
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
+  if (total <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)(total < g_sm_count_tc[dev] ? total : g_sm_count_tc[dev]);
+  kernel<<<grid, kThreads, SM::TOTAL, st>>>(tmA, tmB, wk, ep, status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// Launch counter shared with the general-shape kernels (defined in sbb_kernels.cu).
+void count_launches(int n);
+
+bool tc_available() {
+  if (!init_once()) return false;
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
+  return major == 10;
+}
+
+bool tc_shape_ok(const void *x, const void *y_or_w, long N, long M) {
+  return N % 4 == 0 && M % 4 == 0 && N >= 4 && M >= 4 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(y_or_w) & 15u) == 0 && N < 2147483647L && M < 2147483647L;
+}
+
+namespace {
+constexpr int kFwdBN = 128, kFwdBK = 32, kFwdStages = 3;
+constexpr int kFwdChain = 4;  // 4 k-blocks of 32 = 128 k-values (48 MMAs) per tensor-memory accumulation chain
+constexpr int kTrBN = 256, kTrBK = 16, kTrStages = 4;
+
+// k-blocks per split and the number of (non-empty) splits for the forward product.
+void forward_split_plan(long B, long N, long M, int &splits, int &k_per_split) {
+  const long tiles = ((B + 127) / 128) * ((M + kFwdBN - 1) / kFwdBN);
+  const long kblocks = (N + kFwdBK - 1) / kFwdBK;
+  const int dev = current_device();
+  const long sms = g_sm_count_tc[dev] > 0 ? g_sm_count_tc[dev] : 148;
+  long want = tiles >= sms ? 1 : sms / tiles;
+  if (want > kblocks / 8) want = kblocks / 8 > 0 ? kblocks / 8 : 1;  // at least 8 k-blocks per split
+  if (want > 64) want = 64;
+  const long per = (kblocks + want - 1) / want;
+  splits = (int)((kblocks + per - 1) / per);
+  k_per_split = (int)per * kFwdBK;
+}
+}  // namespace
+
+int forward_splits_tc(long B, long N, long M) {
+  status_word();  // fills the SM count
+  int s, k;
+  forward_split_plan(B, N, M, s, k);
+  return s;
+}
+
+cudaError_t launch_forward_product_tc(const float *x, const float *w, float *partial, long B, long N, long M,
+                                      int splits, cudaStream_t st) {
+  if (!tc_available() || !tc_shape_ok(x, w, N, M) || (reinterpret_cast<uintptr_t>(partial) & 7u)) return cudaErrorNotSupported;
+  int plan_splits, k_per_split;
+  status_word();
+  forward_split_plan(B, N, M, plan_splits, k_per_split);
+  if (plan_splits != splits) return cudaErrorInvalidValue;
+  CUtensorMap tmA, tmB;
+  if (!make_map(&tmA, x, N, B, 32, 128, false) || !make_map(&tmB, w, M, N, 32, kFwdBK, true)) return cudaErrorInvalidValue;
+  TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0};
+  TcEpilogue ep{};
+  ep.out = partial;
+  ep.rows = B;
+  ep.cols = M;
+  ep.ld = M;
+  cudaError_t e = launch_tc<true, kFwdBN, kFwdBK, kFwdStages, false, kFwdChain>(tmA, tmB, wk, ep, st);
+  if (e == cudaSuccess) count_launches(1);
+  return e;
+}
+
+cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long N, long M, long H, const float *Ci,
+                                   const float *Cj, float *Cij, float *w, const uint8_t *wmask, const int *col_hc,
+                                   TraceParams<float> p, long row_begin, long row_end, cudaStream_t st) {
+  if (!tc_available() || !tc_shape_ok(x, y, N, M) || row_begin % 128 != 0) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(Cij) & 7u) || (reinterpret_cast<uintptr_t>(w) & 7u) ||
+      (reinterpret_cast<uintptr_t>(Cj) & 7u) || (wmask && (col_hc == nullptr || (reinterpret_cast<uintptr_t>(col_hc) & 7u))))
+    return cudaErrorNotSupported;
+  if (row_end <= row_begin) return cudaSuccess;
+  CUtensorMap tmA, tmB;
+  if (!make_map(&tmA, x, N, B, 32, kTrBK, true) || !make_map(&tmB, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  const long rows = row_end - row_begin;
+  const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
+  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin};
+  TcEpilogue ep{};
+  ep.rows = rows;
+  ep.cols = M;
+  ep.Ci = Ci;
+  ep.Cj = Cj;
+  ep.Cij = Cij;
+  ep.W = w;
+  ep.wmask = wmask;
+  ep.col_hc = col_hc;
+  ep.H = H;
+  ep.row0 = row_begin;
+  ep.p = p;
+  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tmA, tmB, wk, ep, st);
+  if (e == cudaSuccess) count_launches(1);
+  return e;
+}
+
+cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long N, long M, float *delta,
+                                    long row_begin, long row_end, cudaStream_t st) {
+  if (!tc_available() || !tc_shape_ok(x, y, N, M) || row_begin % 128 != 0 ||
+      (reinterpret_cast<uintptr_t>(delta) & 7u))
+    return cudaErrorNotSupported;
+  if (row_end <= row_begin) return cudaSuccess;
+  CUtensorMap tmA, tmB;
+  if (!make_map(&tmA, x, N, B, 32, kTrBK, true) || !make_map(&tmB, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  const long rows = row_end - row_begin;
+  const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
+  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin};
+  TcEpilogue ep{};
+  ep.out = delta + row_begin * M;
+  ep.rows = rows;
+  ep.cols = M;
+  ep.ld = M;
+  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0>(tmA, tmB, wk, ep, st);
+  if (e == cudaSuccess) count_launches(1);
+  return e;
+}
+
+
+cudaError_t tc_read_status(int *status) {
+  *status = 0;
+  const int dev = current_device();
+  int *p = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    p = g_status[dev];
+  }
+  if (p == nullptr) return cudaSuccess;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return e;
+  return cudaMemcpy(status, p, sizeof(int), cudaMemcpyDeviceToHost);
+}
+
+}  // namespace sbb

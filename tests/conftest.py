@@ -39,3 +39,22 @@ TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}
 def port_kernels():
     import oracle
     return oracle.PortKernels()
+
+
+@pytest.fixture(params=["general", "tensor"])
+def contraction_path(request):
+    """Runs a GPU test once per contraction path: the general-shape FFMA kernels and the
+    tcgen05 tensor-core kernels (which fall back to the former for float64 and for shapes
+    whose rows are not 16-byte multiples).  After the test the status word of the bounded
+    device-side waits must be clear."""
+    import ctypes
+    from streambrain_b200._lib import lib
+    if request.param == "tensor" and not lib.sbb_tensor_path_available():
+        pytest.skip("tensor-core path not available on this device")
+    before = lib.sbb_get_contraction_path()
+    assert lib.sbb_set_contraction_path(1 if request.param == "tensor" else 0) == 0
+    yield request.param
+    status = ctypes.c_int(0)
+    rc = lib.sbb_device_wait_status(ctypes.byref(status))
+    lib.sbb_set_contraction_path(before)
+    assert rc == 0 and status.value == 0, "a bounded device-side wait gave up (code %d)" % status.value

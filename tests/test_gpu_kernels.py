@@ -7,7 +7,7 @@ import pytest
 
 from conftest import TOL, load_golden, rel_inf
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("contraction_path")]
 
 DTYPES = [("f32", np.float32), ("f64", np.float64)]
 
@@ -65,7 +65,9 @@ def test_kernels_match_reference_golden(k, tag, dtype):
 
 
 SHAPES = [(1, 1, 1, 1), (3, 5, 1, 2), (7, 129, 3, 43), (33, 257, 5, 13), (100, 1000, 30, 10), (128, 64, 2, 300),
-          (65, 130, 1, 1024), (17, 520, 7, 19)]
+          (65, 130, 1, 1024), (17, 520, 7, 19),
+          # rows that are 16-byte multiples: eligible for the tensor-core kernels
+          (5, 4, 1, 4), (77, 388, 3, 44), (300, 260, 2, 130), (16, 2048, 1, 260), (130, 132, 4, 65)]
 
 
 @pytest.mark.parametrize("tag,dtype", DTYPES)

@@ -13,7 +13,7 @@ from conftest import TOL, load_golden, rel_inf
 
 import oracle
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("contraction_path")]
 
 DTYPES = [("f32", np.float32), ("f64", np.float64)]
 PLASTIC_STATE = ("weights", "bias", "Ci", "Cj", "Cij", "kbi", "wmask")
