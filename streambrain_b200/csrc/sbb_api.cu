@@ -140,8 +140,7 @@ struct sbb_layer {
   void *state[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   size_t state_bytes[7] = {0, 0, 0, 0, 0, 0, 0};
   Scratch fwd_partial;   // k-split partial sums of the forward product
-  Scratch score;         // N REALs
-  Scratch csum;          // N ints
+  Scratch score;         // mask-update scratch: per-row score, active count, candidate lists
   Scratch hx, hy, ht;    // staging for the host-buffer entry points
   Scratch col_hc;        // M ints: hypercolumn of every output column (j / Mc)
   cudaStream_t own_stream = nullptr;
@@ -216,8 +215,7 @@ int layer_finish(sbb_layer *L, long h, cudaStream_t st) {
     // which is a function of the traces alone; the masked weights already written
     // for hypercolumn h are then rewritten under the updated mask.
     SBB_CUDA(sbb::launch_mask_update<T>(wmask, nullptr, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h,
-                                        L->desc.mask_iterations, static_cast<T *>(L->score.d),
-                                        static_cast<int *>(L->csum.d), st));
+                                        L->desc.mask_iterations, L->score.d, st));
     SBB_CUDA(sbb::launch_rewrite_hypercolumn<T>(W, wmask, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, st));
   }
   return SBB_OK;
@@ -485,16 +483,15 @@ template <typename T>
 int update_mask_t(uint8_t *wmask, const void *weights, const void *Ci, const void *Cj, const void *Cij, double cthr,
                   long N, long M, long H, long Mc, long h, long iterations) {
   const size_t s = sizeof(T);
-  Staged dm, dw, dci, dcj, dcij, score, csum;
+  Staged dm, dw, dci, dcj, dcij, score;
   SBB_TRY(dm.upload(wmask, N * H));
   SBB_TRY(dw.upload(weights, N * M * s));
   SBB_TRY(dci.upload(Ci, N * s));
   SBB_TRY(dcj.upload(Cj, M * s));
   SBB_TRY(dcij.upload(Cij, N * M * s));
-  SBB_TRY(score.alloc(N * s));
-  SBB_TRY(csum.alloc(N * sizeof(int)));
+  SBB_TRY(score.alloc(sbb::mask_scratch_bytes(N, s)));
   SBB_CUDA(sbb::launch_mask_update<T>(dm.as<uint8_t>(), dw.as<T>(), dci.as<T>(), dcj.as<T>(), dcij.as<T>(), (T)cthr, N,
-                                      M, H, Mc, h, iterations, score.as<T>(), csum.as<int>(), 0));
+                                      M, H, Mc, h, iterations, score.d, 0));
   SBB_CUDA(cudaDeviceSynchronize());
   return dm.download(wmask);
 }
@@ -631,8 +628,7 @@ int sbb_layer_create(const sbb_layer_desc *desc, sbb_layer **out) {
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) rc = cuda_fail(e, "layer_create");
   if (rc == SBB_OK && desc->kind == SBB_LAYER_PLASTIC) {
-    rc = L->score.reserve((size_t)L->N * s);
-    if (rc == SBB_OK) rc = L->csum.reserve((size_t)L->N * sizeof(int));
+    rc = L->score.reserve(sbb::mask_scratch_bytes(L->N, s));
     if (rc == SBB_OK) rc = L->col_hc.reserve((size_t)(L->M + 4) * sizeof(int));
     if (rc == SBB_OK) {
       std::vector<int> hc((size_t)L->M);
@@ -657,7 +653,6 @@ int sbb_layer_destroy(sbb_layer *L) {
     if (L->state[k]) cudaFree(L->state[k]);
   L->fwd_partial.release();
   L->score.release();
-  L->csum.release();
   L->hx.release();
   L->hy.release();
   L->ht.release();

@@ -876,8 +876,10 @@ __device__ __forceinline__ Pick<T> shfl_pick(Pick<T> p, int off) {
 // class (a scan never replaces its holder with a NaN, nor a NaN holder at all).
 template <typename T>
 __global__ void __launch_bounds__(1024)
-    mask_swap_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long H, long h, long iterations) {
+    mask_swap_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long H, long h, long iterations,
+                     const int *__restrict__ run_flag) {
   __shared__ Pick<T> s_max[32], s_min[32];
+  if (run_flag != nullptr && *run_flag == 0) return;   // the candidate-list path already did this update
   __shared__ long s_first0[32], s_first1[32];
   __shared__ int s_done;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -945,25 +947,193 @@ __global__ void __launch_bounds__(1024)
   }
 }
 
+// ---- fast swap: per-chunk candidate lists, then a short exact simulation -------------------
+// Only the two rows of a swap change their score, so the row chosen in iteration t is always
+// among the t+1 best of its class in the initial ordering or a row moved by an earlier swap.
+// Phase A extracts, per chunk of rows, the `iterations` best silent rows (highest score, ties
+// to the larger index) and the `iterations` worst active rows (lowest score, ties to the
+// larger index); phase B merges them and replays the swaps exactly.  A NaN score makes the
+// reference's scan order-dependent; phase A then raises a flag and the one-CTA full scan
+// (mask_swap_kernel) runs instead.
+constexpr int kSwapMaxIter = 32;
+constexpr int kSwapMaxChunks = 24;   // kSwapMaxChunks * kSwapMaxIter + kSwapMaxIter <= 1024 list slots
+
+template <typename T>
+__device__ __forceinline__ T swap_score(const T *nom, const int *csum, long j) {
+  return (T)((double)nom[j] / (1.0 + (double)csum[j]));
+}
+
+// lists: [class][chunk][iterations] of (value, index); index -1 = empty.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    mask_candidates_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ nom, const int *__restrict__ csum,
+                           long N, long H, long h, int iterations, long rows_per_chunk, T *cand_v, long *cand_i,
+                           int *nan_flag) {
+  __shared__ Pick<T> s_pick[8];
+  __shared__ Pick<T> s_prev;
+  const long r0 = (long)blockIdx.x * rows_per_chunk;
+  const long r1 = r0 + rows_per_chunk < N ? r0 + rows_per_chunk : N;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  bool saw_nan = false;
+  for (int cls = 0; cls < 2; ++cls) {
+    Pick<T> prev{(T)0, -1};
+    for (int k = 0; k < iterations; ++k) {
+      Pick<T> best{(T)0, -1};
+      for (long j = r0 + threadIdx.x; j < r1; j += blockDim.x) {
+        if (wmask[j * H + h] != cls) continue;
+        const T sc = swap_score(nom, csum, j);
+        if (sc != sc) { saw_nan = true; continue; }
+        // eligible: strictly after the previous pick in this class's order
+        bool after = prev.i < 0;
+        if (!after) after = cls == 0 ? (sc < prev.v || (sc == prev.v && j < prev.i)) : (sc > prev.v || (sc == prev.v && j < prev.i));
+        if (!after) continue;
+        best = cls == 0 ? pick_max(best, Pick<T>{sc, j}) : pick_min(best, Pick<T>{sc, j});
+      }
+      for (int off = 16; off > 0; off >>= 1)
+        best = cls == 0 ? pick_max(best, shfl_pick(best, off)) : pick_min(best, shfl_pick(best, off));
+      if (lane == 0) s_pick[wid] = best;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) best = cls == 0 ? pick_max(best, s_pick[w]) : pick_min(best, s_pick[w]);
+        s_prev = best;
+        const long slot = ((long)cls * gridDim.x + blockIdx.x) * iterations + k;
+        cand_v[slot] = best.v;
+        cand_i[slot] = best.i;
+      }
+      __syncthreads();
+      prev = s_prev;
+      if (prev.i < 0) {   // class exhausted in this chunk: the remaining slots are empty
+        for (int kk = k + 1 + threadIdx.x; kk < iterations; kk += blockDim.x)
+          cand_i[((long)cls * gridDim.x + blockIdx.x) * iterations + kk] = -1;
+        break;
+      }
+    }
+    __syncthreads();
+  }
+  if (saw_nan) atomicOr(nan_flag, 1);
+}
+
+template <typename T>
+struct Slot {
+  T v;
+  long i;
+  int s;  // list slot, -1 = empty
+};
+template <typename T>
+__device__ __forceinline__ Slot<T> slot_best(Slot<T> a, Slot<T> b, bool want_max) {
+  if (b.s < 0) return a;
+  if (a.s < 0) return b;
+  const bool take = want_max ? (b.v > a.v || (b.v == a.v && b.i > a.i)) : (b.v < a.v || (b.v == a.v && b.i > a.i));
+  return take ? b : a;
+}
+template <typename T>
+__device__ __forceinline__ Slot<T> block_best(Slot<T> mine, bool want_max, Slot<T> *s_red) {
+  for (int off = 16; off > 0; off >>= 1) {
+    Slot<T> o;
+    o.v = __shfl_xor_sync(0xffffffffu, mine.v, off);
+    o.i = __shfl_xor_sync(0xffffffffu, mine.i, off);
+    o.s = __shfl_xor_sync(0xffffffffu, mine.s, off);
+    mine = slot_best(mine, o, want_max);
+  }
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) s_red[wid] = mine;
+  __syncthreads();
+  Slot<T> r = s_red[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) r = slot_best(r, s_red[w], want_max);
+  return r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+    mask_replay_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long H, long h, int iterations,
+                       int chunks, const T *__restrict__ cand_v, const long *__restrict__ cand_i,
+                       const int *__restrict__ nan_flag) {
+  __shared__ T lv[2][1024];
+  __shared__ long li[2][1024];
+  __shared__ Slot<T> s_red[32];
+  if (*nan_flag) return;   // the full scan handles this update
+  const int base = chunks * iterations;   // first slot for rows moved by a swap
+  const int t = threadIdx.x;
+  for (int cls = 0; cls < 2; ++cls) {
+    li[cls][t] = t < base ? cand_i[(long)cls * base + t] : -1;
+    lv[cls][t] = (t < base && li[cls][t] >= 0) ? cand_v[(long)cls * base + t] : (T)0;
+  }
+  __syncthreads();
+  for (int it = 0; it < iterations; ++it) {
+    const Slot<T> s0 = block_best(Slot<T>{lv[0][t], li[0][t], li[0][t] >= 0 ? t : -1}, true, s_red);
+    const Slot<T> a1 = block_best(Slot<T>{lv[1][t], li[1][t], li[1][t] >= 0 ? t : -1}, false, s_red);
+    if (s0.s < 0 || a1.s < 0 || s0.v < a1.v) break;   // uniform: every thread holds the same picks
+    __syncthreads();
+    if (t == 0) {
+      wmask[s0.i * H + h] = 1;
+      wmask[a1.i * H + h] = 0;
+      csum[s0.i] += 1;
+      csum[a1.i] -= 1;
+      li[0][s0.s] = -1;
+      li[1][a1.s] = -1;
+      // the moved rows join the other class with their new counts
+      li[1][base + it] = s0.i;
+      lv[1][base + it] = swap_score(nom, csum, s0.i);
+      li[0][base + it] = a1.i;
+      lv[0][base + it] = swap_score(nom, csum, a1.i);
+    }
+    __syncthreads();
+  }
+}
+
+size_t mask_scratch_bytes(long N, size_t elem) {
+  const size_t a = ((size_t)N * elem + 255) & ~(size_t)255;
+  const size_t b = ((size_t)N * sizeof(int) + 255) & ~(size_t)255;
+  const size_t cand = (size_t)2 * kSwapMaxChunks * kSwapMaxIter * (sizeof(double) + sizeof(long)) + 256;
+  return a + b + cand;
+}
+
 template <typename T>
 cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
-                               long N, long M, long H, long Mc, long h, long iterations, T *score, int *csum,
+                               long N, long M, long H, long Mc, long h, long iterations, void *scratch,
                                cudaStream_t st) {
   if (N == 0) return cudaSuccess;
+  unsigned char *base = static_cast<unsigned char *>(scratch);
+  const size_t a = ((size_t)N * sizeof(T) + 255) & ~(size_t)255;
+  const size_t b = ((size_t)N * sizeof(int) + 255) & ~(size_t)255;
+  T *score = reinterpret_cast<T *>(base);
+  int *csum = reinterpret_cast<int *>(base + a);
+  unsigned char *cand = base + a + b;
   const T cthr4 = cthr * cthr * cthr * cthr;
   mask_score_kernel<T><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wmask, weights, Ci, Cj, Cij, cthr, cthr4, N, M, H, Mc,
                                                                  h, score, csum);
   cudaError_t e = launched();
   if (e != cudaSuccess) return e;
-  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, iterations);
+  if (iterations >= 1 && iterations <= kSwapMaxIter && N >= 4096) {
+    int chunks = (int)((N + 1023) / 1024);
+    if (chunks > kSwapMaxChunks) chunks = kSwapMaxChunks;
+    const long rows_per_chunk = (N + chunks - 1) / chunks;
+    chunks = (int)((N + rows_per_chunk - 1) / rows_per_chunk);
+    int *nan_flag = reinterpret_cast<int *>(cand);
+    long *cand_i = reinterpret_cast<long *>(cand + 256);
+    T *cand_v = reinterpret_cast<T *>(cand + 256 + (size_t)2 * kSwapMaxChunks * kSwapMaxIter * sizeof(long));
+    e = cudaMemsetAsync(nan_flag, 0, sizeof(int), st);
+    if (e != cudaSuccess) return e;
+    mask_candidates_kernel<T><<<chunks, 256, 0, st>>>(wmask, score, csum, N, H, h, (int)iterations, rows_per_chunk,
+                                                      cand_v, cand_i, nan_flag);
+    e = launched();
+    if (e != cudaSuccess) return e;
+    mask_replay_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, (int)iterations, chunks, cand_v, cand_i,
+                                              nan_flag);
+    e = launched();
+    if (e != cudaSuccess) return e;
+    mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, iterations, nan_flag);
+    return launched();
+  }
+  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, iterations, nullptr);
   return launched();
 }
 template cudaError_t launch_mask_update<float>(uint8_t *, const float *, const float *, const float *, const float *,
-                                               float, long, long, long, long, long, long, float *, int *,
-                                               cudaStream_t);
+                                               float, long, long, long, long, long, long, void *, cudaStream_t);
 template cudaError_t launch_mask_update<double>(uint8_t *, const double *, const double *, const double *,
-                                                const double *, double, long, long, long, long, long, long, double *,
-                                                int *, cudaStream_t);
+                                                const double *, double, long, long, long, long, long, long, void *,
+                                                cudaStream_t);
 
 template <typename T>
 __global__ void __launch_bounds__(256)

@@ -85,10 +85,12 @@ template <typename T>
 cudaError_t launch_apply_mask(T *w, const uint8_t *wmask, long N, long M, long H, long Mc, cudaStream_t st);
 
 // Mask update for hypercolumn h.  `weights` null => the un-masked weight is
-// recomputed from the traces.  score/csum are scratch of N REALs / N ints.
+// recomputed from the traces.  `scratch` holds mask_scratch_bytes(N, sizeof(T))
+// bytes (256-byte aligned): per-row score and active count plus candidate lists.
+size_t mask_scratch_bytes(long N, size_t elem);
 template <typename T>
 cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
-                               long N, long M, long H, long Mc, long h, long iterations, T *score, int *csum,
+                               long N, long M, long H, long Mc, long h, long iterations, void *scratch,
                                cudaStream_t st);
 
 // Rewrites the weights of hypercolumn h's columns from the traces under wmask.

@@ -9,7 +9,7 @@
 // no cudaMalloc, no cudaFree, no library routine that allocates.
 //
 // Cost and limits
-//   * The array is SBB_NOALLOC_MAX_ROWS * 12 bytes (1.5 MiB) and is resident on
+//   * The array is SBB_NOALLOC_MAX_ROWS * 12 bytes plus 32 KiB (1.5 MiB) and is resident on
 //     every GPU that loads the library, from load until the process exits.
 //   * Layers with more than SBB_NOALLOC_MAX_ROWS input rows are refused with
 //     SBB_ERR_UNSUPPORTED; nothing is launched in that case.
@@ -31,11 +31,12 @@ namespace {
 constexpr long kMaxRows = SBB_NOALLOC_MAX_ROWS;
 constexpr size_t kScoreBytes = (size_t)kMaxRows * sizeof(double);  // REAL score per row, sized for double
 constexpr size_t kCountBytes = (size_t)kMaxRows * sizeof(int);     // active connections per row
+constexpr size_t kListBytes = 32 * 1024;                           // candidate lists of the swap search
 
 // In host code this name is only a handle for the runtime; it is NOT a device
 // address and must never be passed to a kernel.  The address a kernel can use
 // comes from cudaGetSymbolAddress, once per device.
-static __device__ __align__(256) unsigned char g_mask_scratch[kScoreBytes + kCountBytes];
+static __device__ __align__(256) unsigned char g_mask_scratch[kScoreBytes + kCountBytes + kListBytes];
 
 constexpr int kMaxDevices = 64;
 void *g_scratch_ptr[kMaxDevices] = {nullptr};
@@ -98,17 +99,20 @@ int sbb_update_mask_noalloc(int dtype, uint8_t *wmask_dev, const void *weights_d
   void *scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc != SBB_OK) return rc;
-  int *csum = reinterpret_cast<int *>(static_cast<unsigned char *>(scratch) + kScoreBytes);
+  if (sbb::mask_scratch_bytes(N, dtype == SBB_F32 ? 4 : 8) > kScoreBytes + kCountBytes + kListBytes) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "update_mask_noalloc: built-in work area too small");
+    return SBB_ERR_UNSUPPORTED;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (dtype == SBB_F32)
     e = sbb::launch_mask_update<float>(wmask_dev, (const float *)weights_dev, (const float *)Ci_dev,
                                        (const float *)Cj_dev, (const float *)Cij_dev, (float)cthr, N, M, H, Mc, h,
-                                       iterations, static_cast<float *>(scratch), csum, st);
+                                       iterations, scratch, st);
   else
     e = sbb::launch_mask_update<double>(wmask_dev, (const double *)weights_dev, (const double *)Ci_dev,
                                         (const double *)Cj_dev, (const double *)Cij_dev, cthr, N, M, H, Mc, h,
-                                        iterations, static_cast<double *>(scratch), csum, st);
+                                        iterations, scratch, st);
   if (e != cudaSuccess) {
     snprintf(g_noalloc_error, sizeof(g_noalloc_error), "update_mask_noalloc: launch failed (%s)",
              cudaGetErrorString(e));

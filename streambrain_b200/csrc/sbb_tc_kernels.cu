@@ -50,6 +50,8 @@ struct TcWork {
   int k_per_split;  // multiple of the stage depth
   int m_fastest;    // tile order: row tiles fastest (1) or column tiles fastest (0)
   int a_row0;       // offset added to the A row coordinate (first output row of this launch)
+  int a_box3;       // A stage fetched by one 3-D box (MN-major A whose row length is a multiple of 32)
+  int b_box3_tiles; // column tiles [0, b_box3_tiles) fetch their B stage by one 3-D box
 };
 
 struct TcEpilogue {
@@ -65,6 +67,7 @@ struct TcEpilogue {
   const int *col_hc;
   long H, row0;
   TraceParams<float> p;
+  float inv_batch;  // 1 / batch
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -126,6 +129,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+
+// One box over the 3-D view [chunk][row][32] of an MN-major matrix: a whole stage of an operand
+// (every 32-element group along MN, all k-rows) in a single instruction.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -214,10 +231,6 @@ struct TcSmem {
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr, abort flag, alignment slack
 };
 
-__device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
 // Two 16-lane halves of a warp's TMEM lane quarter, 32 columns each, one wait.
 __device__ __forceinline__ void tmem_ld_pair(uint32_t taddr_lo, uint32_t taddr_hi, float (&a)[16], float (&b)[16]) {
   uint32_t u[16], v[16];
@@ -251,8 +264,9 @@ __device__ __forceinline__ void tmem_ld_pair(uint32_t taddr_lo, uint32_t taddr_h
 // results the epilogue warps add in full float32.
 template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
 __global__ void __launch_bounds__(kThreads, 1)
-    tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcWork wk,
-                          TcEpilogue ep, int *status) {
+    tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                          const __grid_constant__ CUtensorMap tmA3, const __grid_constant__ CUtensorMap tmB3,
+                          const __grid_constant__ CUtensorMap tmC, TcWork wk, TcEpilogue ep, int *status) {
   using SM = TcSmem<BN, BK, STAGES>;
   static_assert(!A_KMAJOR || BK == 32, "a K-major operand is loaded as one 128-byte-wide box");
   static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0, "tile shape");
@@ -327,11 +341,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (FUSED) {
           // Pull this tile's block of the trace matrix towards L2 while its products run;
           // the epilogue reads it one tile-time from now.
-          const long n0 = (long)nt * BN;
-          const long ncols = ep.cols - n0 < BN ? ep.cols - n0 : BN;
-          const long r1 = ep.rows - (long)mt * 128 < 128 ? ep.rows - (long)mt * 128 : 128;
-          const float *blk = ep.Cij + (ep.row0 + (long)mt * 128) * ep.cols + n0;
-          for (long r = 0; r < r1; ++r) prefetch_l2(blk + r * ep.cols, (uint32_t)(ncols * 4));
+          tma_prefetch_2d(&tmC, nt * BN, (int)ep.row0 + mt * 128);
         }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % STAGES;
@@ -343,13 +353,20 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int k0 = kbeg + kb * BK;
           if (A_KMAJOR) {
             tma_load_2d(a_dst, &tmA, k0, wk.a_row0 + mt * 128, bar_full(s));
+          } else if (wk.a_box3) {
+            tma_load_3d(a_dst, &tmA3, 0, k0, (wk.a_row0 + mt * 128) / 32, bar_full(s));
           } else {
 #pragma unroll
             for (int c = 0; c < 4; ++c)
               tma_load_2d(a_dst + c * (BK * 128), &tmA, wk.a_row0 + mt * 128 + 32 * c, k0, bar_full(s));
           }
+          if (nt < wk.b_box3_tiles) {
+            tma_load_3d(b_dst, &tmB3, 0, k0, nt * (BN / 32), bar_full(s));
+          } else {
 #pragma unroll
-          for (int c = 0; c < BN / 32; ++c) tma_load_2d(b_dst + c * (BK * 128), &tmB, nt * BN + 32 * c, k0, bar_full(s));
+            for (int c = 0; c < BN / 32; ++c)
+              tma_load_2d(b_dst + c * (BK * 128), &tmB, nt * BN + 32 * c, k0, bar_full(s));
+          }
         }
       }
       if (!ok) {
@@ -553,23 +570,34 @@ __global__ void __launch_bounds__(kThreads, 1)
                 c[j][rep] = (rv[j] && cv[rep])
                                 ? __ldcs(reinterpret_cast<const float2 *>(ep.Cij + (ep.row0 + grow[j]) * ep.cols + n0 + rep * 8))
                                 : make_float2(0.f, 0.f);
+            // All of this thread's columns in the group usually belong to one hypercolumn
+            // (col_hc is non-decreasing), so one mask byte per row decides them all.
+            int hc_last = hc[0].x;
+#pragma unroll
+            for (int rep = 0; rep < 4; ++rep)
+              if (cv[rep]) hc_last = hc[rep].y;   // columns past the matrix edge carry no hypercolumn
+            const bool one_hc = hc[0].x == hc_last;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float *acc = (j >> 1) ? a1 : a0;
+              bool row_on = !skip[j];
+              if (row_on && mrow[j] && one_hc) row_on = mrow[j][hc[0].x] != 0;
 #pragma unroll
               for (int rep = 0; rep < 4; ++rep) {
                 if (!(rv[j] && cv[rep])) continue;
                 float2 c2 = c[j][rep], w2 = make_float2(0.f, 0.f);
-                c2.x = trace_ema(c2.x, acc[rep * 4 + (j & 1) * 2 + 0], ep.p);
-                c2.y = trace_ema(c2.y, acc[rep * 4 + (j & 1) * 2 + 1], ep.p);
-                if (!skip[j]) {
+                c2.x = trace_ema_fast(c2.x, acc[rep * 4 + (j & 1) * 2 + 0], ep.p, ep.inv_batch);
+                c2.y = trace_ema_fast(c2.y, acc[rep * 4 + (j & 1) * 2 + 1], ep.p, ep.inv_batch);
+                if (row_on) {
                   bool on0 = !(cj[rep].x < ep.p.cthr), on1 = !(cj[rep].y < ep.p.cthr);
-                  if (mrow[j]) {
+                  if (mrow[j] && !one_hc) {
                     on0 = on0 && mrow[j][hc[rep].x] != 0;
                     on1 = on1 && mrow[j][hc[rep].y] != 0;
                   }
-                  if (on0) w2.x = log_ratio(c2.x, ci[j], cj[rep].x, ep.p.cthr4);
-                  if (on1) w2.y = log_ratio(c2.y, ci[j], cj[rep].y, ep.p.cthr4);
+                  const float wx = log_ratio_fast(c2.x, ci[j], cj[rep].x, ep.p.cthr4);
+                  const float wy = log_ratio_fast(c2.y, ci[j], cj[rep].y, ep.p.cthr4);
+                  w2.x = on0 ? wx : 0.f;
+                  w2.y = on1 ? wy : 0.f;
                 }
                 const long off = (ep.row0 + grow[j]) * ep.cols + n0 + rep * 8;
                 __stcs(reinterpret_cast<float2 *>(ep.Cij + off), c2);
@@ -671,9 +699,39 @@ bool make_map(CUtensorMap *map, const float *base, long inner, long outer, int b
   return r == CUDA_SUCCESS;
 }
 
+// 3-D view {32, rows, cols/32} of a row-major [rows, cols] float32 matrix (element (i, r, c) = m[r][32c + i]);
+// a box {32, box_rows, box_chunks} lands in shared memory as [chunk][row][32], the MN-major stage layout.
+bool make_map_chunks(CUtensorMap *map, const float *base, long cols, long rows, int box_rows, int box_chunks) {
+  if (cols < 32) return false;
+  cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(cols / 32)};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * sizeof(float), 128};
+  cuuint32_t box[3] = {32, (cuuint32_t)box_rows, (cuuint32_t)box_chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Un-swizzled 2-D map used only to prefetch a [128 x box_cols] block of the trace matrix into L2.
+bool make_map_plain(CUtensorMap *map, const float *base, long cols, long rows, int box_cols, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Column tiles of width bn whose every 32-column group lies inside the matrix.
+int full_chunk_tiles(long cols, int bn) { return (int)(((cols / 32) * 32) / bn); }
+
+struct TcMaps {
+  CUtensorMap a, b, a3, b3, c;
+};
+
 template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
-cudaError_t launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, const TcWork &wk, const TcEpilogue &ep,
-                      cudaStream_t st) {
+cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st) {
   using SM = TcSmem<BN, BK, STAGES>;
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
@@ -688,7 +746,7 @@ cudaError_t launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, const TcWo
   const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
   if (total <= 0) return cudaSuccess;
   const unsigned grid = (unsigned)(total < g_sm_count_tc[dev] ? total : g_sm_count_tc[dev]);
-  kernel<<<grid, kThreads, SM::TOTAL, st>>>(tmA, tmB, wk, ep, status);
+  kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, wk, ep, status);
   return cudaGetLastError();
 }
 
@@ -744,15 +802,20 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   status_word();
   forward_split_plan(B, N, M, plan_splits, k_per_split);
   if (plan_splits != splits) return cudaErrorInvalidValue;
-  CUtensorMap tmA, tmB;
-  if (!make_map(&tmA, x, N, B, 32, 128, false) || !make_map(&tmB, w, M, N, 32, kFwdBK, true)) return cudaErrorInvalidValue;
-  TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0};
+  TcMaps tm;
+  if (!make_map(&tm.a, x, N, B, 32, 128, false) || !make_map(&tm.b, w, M, N, 32, kFwdBK, true)) return cudaErrorInvalidValue;
+  tm.a3 = tm.a;
+  tm.c = tm.a;
+  const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, kFwdBN / 32);
+  if (!b3) tm.b3 = tm.b;
+  TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
+            b3 ? full_chunk_tiles(M, kFwdBN) : 0};
   TcEpilogue ep{};
   ep.out = partial;
   ep.rows = B;
   ep.cols = M;
   ep.ld = M;
-  cudaError_t e = launch_tc<true, kFwdBN, kFwdBK, kFwdStages, false, kFwdChain>(tmA, tmB, wk, ep, st);
+  cudaError_t e = launch_tc<true, kFwdBN, kFwdBK, kFwdStages, false, kFwdChain>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
@@ -765,11 +828,17 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
       (reinterpret_cast<uintptr_t>(Cj) & 7u) || (wmask && (col_hc == nullptr || (reinterpret_cast<uintptr_t>(col_hc) & 7u))))
     return cudaErrorNotSupported;
   if (row_end <= row_begin) return cudaSuccess;
-  CUtensorMap tmA, tmB;
-  if (!make_map(&tmA, x, N, B, 32, kTrBK, true) || !make_map(&tmB, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  TcMaps tm;
+  if (!make_map(&tm.a, x, N, B, 32, kTrBK, true) || !make_map(&tm.b, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  if (!make_map_plain(&tm.c, Cij, M, N, M < kTrBN ? (int)M : kTrBN, 128)) return cudaErrorInvalidValue;
+  const bool a3 = N % 32 == 0 && make_map_chunks(&tm.a3, x, N, B, kTrBK, 4);
+  if (!a3) tm.a3 = tm.a;
+  const bool b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, kTrBN / 32);
+  if (!b3) tm.b3 = tm.b;
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
-  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin};
+  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
+            b3 ? full_chunk_tiles(M, kTrBN) : 0};
   TcEpilogue ep{};
   ep.rows = rows;
   ep.cols = M;
@@ -782,7 +851,8 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   ep.H = H;
   ep.row0 = row_begin;
   ep.p = p;
-  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tmA, tmB, wk, ep, st);
+  ep.inv_batch = 1.0f / p.batch;
+  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
@@ -793,17 +863,23 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
       (reinterpret_cast<uintptr_t>(delta) & 7u))
     return cudaErrorNotSupported;
   if (row_end <= row_begin) return cudaSuccess;
-  CUtensorMap tmA, tmB;
-  if (!make_map(&tmA, x, N, B, 32, kTrBK, true) || !make_map(&tmB, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  TcMaps tm;
+  if (!make_map(&tm.a, x, N, B, 32, kTrBK, true) || !make_map(&tm.b, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  tm.c = tm.a;
+  const bool a3 = N % 32 == 0 && make_map_chunks(&tm.a3, x, N, B, kTrBK, 4);
+  if (!a3) tm.a3 = tm.a;
+  const bool b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, kTrBN / 32);
+  if (!b3) tm.b3 = tm.b;
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
-  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin};
+  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
+            b3 ? full_chunk_tiles(M, kTrBN) : 0};
   TcEpilogue ep{};
   ep.out = delta + row_begin * M;
   ep.rows = rows;
   ep.cols = M;
   ep.ld = M;
-  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0>(tmA, tmB, wk, ep, st);
+  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }

@@ -146,11 +146,13 @@ def _mask_case(rs, n, hc, mc, dtype, density=0.3):
     return wmask, w, Ci, Cj, Cij
 
 
-@pytest.mark.parametrize("n,hc,mc", [(1, 1, 2), (53, 4, 6), (128, 2, 64), (700, 3, 100), (2500, 30, 10)])
+@pytest.mark.parametrize("n,hc,mc", [(1, 1, 2), (53, 4, 6), (128, 2, 64), (700, 3, 100), (2500, 30, 10),
+                                     # 4096 rows and more take the candidate-list search instead of the full scan
+                                     (4096, 2, 8), (5000, 3, 20), (30011, 2, 10)])
 def test_update_mask_f64_identical_to_oracle(k, port_kernels, n, hc, mc):
     rs = np.random.RandomState(n)
     wmask, w, Ci, Cj, Cij = _mask_case(rs, n, hc, mc, np.float64)
-    for it in (1, 16, 40):
+    for it in (1, 16, 32, 40):
         for h in sorted({0, hc - 1, hc // 2}):
             got = k.update_mask(wmask.copy(), w, Ci, Cj, Cij, 0.01, hc, mc, h, it)
             want = port_kernels.update_mask(wmask.copy(), w, Ci, Cj, Cij, 0.01, hc, mc, h, it)
@@ -173,3 +175,26 @@ def test_update_mask_edge_cases(k, port_kernels):
     assert np.array_equal(got, want)
     # zero iterations leaves the mask alone
     assert np.array_equal(k.update_mask(wmask.copy(), w, Ci, Cj, Cij, 0.01, 2, 5, 0, 0), wmask)
+
+
+@pytest.mark.parametrize("n", [300, 6000])
+def test_update_mask_with_nan_and_inf_scores(k, port_kernels, n):
+    """Rows whose Ci is exactly 1 (an input that is always on) divide by zero in the score:
+    +-inf and NaN scores must be ranked exactly as the reference's front-to-back scan ranks
+    them, in the full scan and (n >= 4096) in the candidate-list search with its fallback."""
+    rs = np.random.RandomState(n)
+    wmask, w, Ci, Cj, Cij = _mask_case(rs, n, 3, 6, np.float64, density=0.4)
+    for variant in range(3):
+        Ci2, Cij2 = Ci.copy(), Cij.copy()
+        hot = rs.choice(n, size=7, replace=False)
+        Ci2[hot] = 1.0
+        if variant == 1:
+            Cij2[hot[:3]] = Cj[None, :]          # pj - pij == 0 -> 0 * log(0/0): NaN
+        if variant == 2:
+            Ci2[0] = 1.0                          # the very first candidate of its class
+            Cij2[0] = Cj
+        with np.errstate(all="ignore"):
+            for h in range(3):
+                got = k.update_mask(wmask.copy(), w, Ci2, Cj, Cij2, 0.01, 3, 6, h, 16)
+                want = port_kernels.update_mask(wmask.copy(), w, Ci2, Cj, Cij2, 0.01, 3, 6, h, 16)
+                assert np.array_equal(got, want), (variant, h)

@@ -49,7 +49,7 @@ def test_noalloc_mask_update_matches_allocating_entry_point(dtype):
     from streambrain_b200._lib import lib
     rs = np.random.RandomState(17)
     # two calls in a row: a large case, then a smaller one on another hypercolumn
-    for n, hc, mc, h, iterations in ((3000, 5, 40, 3, 16), (700, 4, 25, 1, 16)):
+    for n, hc, mc, h, iterations in ((6000, 5, 40, 3, 16), (700, 4, 25, 1, 16)):
         wmask, w, Ci, Cj, Cij = _case(rs, n, hc, mc, dtype)
         want = k.update_mask(wmask.copy(), w, Ci, Cj, Cij, 0.01, hc, mc, h, iterations)
         got = _noalloc(lib, torch, dtype, wmask.copy(), w, Ci, Cj, Cij, 0.01, hc, mc, h, iterations)
