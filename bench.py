@@ -122,6 +122,25 @@ class ClockSampler:
         return res
 
 
+def steady_state_traces(p, x, seed=7):
+    """Traces of a layer that has already seen data, used as the start state of both arms.
+
+    With the constructor's initial traces (Ci = 1, Cij = Cj = 1/Mc) the plasticity score
+    log((pj - pij) / ((1 - pi) pj)) is undefined (0/0), which is why the reference never
+    updates the mask in its first epoch (_cpu_base_backend.py:297).  The timed steps update
+    the mask, so they start where later epochs are: Ci = mean input, Cj = 1/Mc and
+    Cij = Ci*Cj (independent units) with 5 % seeded noise."""
+    hp = p["hidden"]
+    N, M, Mc = hp["in_features"], hp["hypercolumns"] * hp["minicolumns"], hp["minicolumns"]
+    rs = np.random.default_rng(seed)
+    dt = p["dtype"]
+    Ci = np.clip(x.mean(axis=0, dtype=np.float64), 0.02, 0.98).astype(dt)
+    Cj = np.full(M, 1.0 / Mc, dtype=dt)
+    Cij = (Ci[:, None].astype(np.float32) * Cj[None, :].astype(np.float32))
+    Cij *= 1.0 + 0.05 * rs.standard_normal(size=(N, M), dtype=np.float32)
+    return Ci, Cj, np.ascontiguousarray(Cij.astype(dt))
+
+
 def make_batches(p, batch, count, seed):
     xs = []
     for k in range(count):
@@ -151,6 +170,7 @@ def cpu_time_steps(p, batch, steps, warmup, budget_s, mask=True):
     os.environ.setdefault("OMP_NUM_THREADS", str(cores))
     layer = cpu_layer(p, kernels)
     xs = make_batches(p, batch, 2, synthetic.DATA_SEED)
+    layer.Ci, layer.Cj, layer.Cij = steady_state_traces(p, xs[0])
     H = p["hidden"]["hypercolumns"]
     times = []
     t_start = time.perf_counter()
@@ -217,6 +237,8 @@ def run_b200(args, wl, p, batch):
     layer = B200.StructuralPlasticityLayer(N, H, Mc, hp["taupdt"], hp["khalf"], hp["pmin"], hp["taubdt"],
                                            hp["density"], 16, hp["initial_counters"], dtype=np_dtype)
     xs_host = make_batches(p, batch, POOL, synthetic.DATA_SEED + 1000 * rank)
+    ref_batch = xs_host[0] if rank == 0 else make_batches(p, batch, 1, synthetic.DATA_SEED)[0]
+    layer.Ci, layer.Cj, layer.Cij = steady_state_traces(p, ref_batch)   # identical on every rank
     xs = [torch.from_numpy(x).cuda() for x in xs_host]
     ys = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -340,6 +362,7 @@ def run_b200(args, wl, p, batch):
         "dtype": "f32" if np_dtype == np.float32 else "f64", "data": "synthetic",
         "config": {"workload": wl, "layer": "%d->%dx%d" % (N, H, Mc), "batch_per_gpu": batch,
                    "global_batch": batch * world, "mask_update": "every step" if mask else "none",
+                   "start_state": "traces at the independent steady state (mask scores finite, as from epoch 2 on)",
                    "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
                        POOL, 2 * N * M * s / 1e6),
                    "contraction": "tcgen05 3xTF32" if tensor_path else "FFMA", "parallelism": "dp%d" % world},

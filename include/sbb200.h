@@ -205,7 +205,7 @@ int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, l
  * sbb_update_mask, but every array is a DEVICE pointer supplied by the caller
  * (wmask is updated in place; weights_dev may be NULL, the un-masked weights are
  * then recomputed from the traces) and the two per-row work arrays live in a
- * fixed 1.5 MiB array inside the library, resident on every GPU that loads it
+ * fixed 1.7 MiB array inside the library, resident on every GPU that loads it
  * until the process exits.  More than SBB_NOALLOC_MAX_ROWS input rows returns
  * SBB_ERR_UNSUPPORTED without launching.  All calls on a device share that
  * array: calls that overlap in time on one GPU race and must be serialised by

@@ -216,7 +216,8 @@ int layer_finish(sbb_layer *L, long h, cudaStream_t st) {
     // for hypercolumn h are then rewritten under the updated mask.
     SBB_CUDA(sbb::launch_mask_update<T>(wmask, nullptr, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h,
                                         L->desc.mask_iterations, L->score.d, st));
-    SBB_CUDA(sbb::launch_rewrite_hypercolumn<T>(W, wmask, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, st));
+    SBB_CUDA(sbb::launch_rewrite_hypercolumn<T>(W, wmask, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, L->score.d,
+                                                st));
   }
   return SBB_OK;
 }

@@ -811,7 +811,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
     mask_score_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ weights, const T *__restrict__ Ci,
                       const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr, T cthr4, long N, long M, long H,
-                      long Mc, long h, T *score, int *csum) {
+                      long Mc, long h, T *score, int *csum, uint8_t *old_col) {
   const int lane = threadIdx.x & 31;
   const long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= N) return;  // whole warp leaves together
@@ -839,6 +839,7 @@ __global__ void __launch_bounds__(256)
   if (lane == 0) {
     score[i] = (T)s;
     csum[i] = cnt;
+    old_col[i] = wmask[i * H + h];   // the mask column before the swaps, for the weight rewrite
   }
 }
 
@@ -956,36 +957,59 @@ __global__ void __launch_bounds__(1024)
 // reference's scan order-dependent; phase A then raises a flag and the one-CTA full scan
 // (mask_swap_kernel) runs instead.
 constexpr int kSwapMaxIter = 32;
-constexpr int kSwapMaxChunks = 24;   // kSwapMaxChunks * kSwapMaxIter + kSwapMaxIter <= 1024 list slots
+constexpr int kSwapSlots = 768;           // list slots per class in the replay kernel (static shared memory budget)
+constexpr int kSwapCacheRows = 4096;      // rows per chunk whose score and class fit the chunk's shared memory
 
 template <typename T>
-__device__ __forceinline__ T swap_score(const T *nom, const int *csum, long j) {
-  return (T)((double)nom[j] / (1.0 + (double)csum[j]));
+__device__ __forceinline__ T swap_score(T nom, int csum) {
+  return (T)((double)nom / (1.0 + (double)csum));
 }
 
 // lists: [class][chunk][iterations] of (value, index); index -1 = empty.
-template <typename T>
+// CACHED: the chunk's scores and classes are kept in shared memory for the rounds.
+template <typename T, bool CACHED>
 __global__ void __launch_bounds__(256)
     mask_candidates_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ nom, const int *__restrict__ csum,
                            long N, long H, long h, int iterations, long rows_per_chunk, T *cand_v, long *cand_i,
                            int *nan_flag) {
   __shared__ Pick<T> s_pick[8];
   __shared__ Pick<T> s_prev;
+  extern __shared__ __align__(16) unsigned char cand_dyn[];
+  T *s_sc = reinterpret_cast<T *>(cand_dyn);
+  uint8_t *s_cl = cand_dyn + (CACHED ? rows_per_chunk * sizeof(T) : 0);
   const long r0 = (long)blockIdx.x * rows_per_chunk;
   const long r1 = r0 + rows_per_chunk < N ? r0 + rows_per_chunk : N;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   bool saw_nan = false;
+  if (CACHED) {
+    for (long j = r0 + threadIdx.x; j < r1; j += blockDim.x) {
+      const uint8_t m = wmask[j * H + h];
+      const T sc = swap_score(nom[j], csum[j]);
+      uint8_t cl = m <= 1 ? m : 2;
+      if (cl < 2 && sc != sc) { saw_nan = true; cl = 2; }
+      s_sc[j - r0] = sc;
+      s_cl[j - r0] = cl;
+    }
+    __syncthreads();
+  }
   for (int cls = 0; cls < 2; ++cls) {
     Pick<T> prev{(T)0, -1};
     for (int k = 0; k < iterations; ++k) {
       Pick<T> best{(T)0, -1};
       for (long j = r0 + threadIdx.x; j < r1; j += blockDim.x) {
-        if (wmask[j * H + h] != cls) continue;
-        const T sc = swap_score(nom, csum, j);
-        if (sc != sc) { saw_nan = true; continue; }
+        T sc;
+        if (CACHED) {
+          if (s_cl[j - r0] != cls) continue;
+          sc = s_sc[j - r0];
+        } else {
+          if (wmask[j * H + h] != cls) continue;
+          sc = swap_score(nom[j], csum[j]);
+          if (sc != sc) { saw_nan = true; continue; }
+        }
         // eligible: strictly after the previous pick in this class's order
         bool after = prev.i < 0;
-        if (!after) after = cls == 0 ? (sc < prev.v || (sc == prev.v && j < prev.i)) : (sc > prev.v || (sc == prev.v && j < prev.i));
+        if (!after)
+          after = cls == 0 ? (sc < prev.v || (sc == prev.v && j < prev.i)) : (sc > prev.v || (sc == prev.v && j < prev.i));
         if (!after) continue;
         best = cls == 0 ? pick_max(best, Pick<T>{sc, j}) : pick_min(best, Pick<T>{sc, j});
       }
@@ -1027,7 +1051,7 @@ __device__ __forceinline__ Slot<T> slot_best(Slot<T> a, Slot<T> b, bool want_max
   return take ? b : a;
 }
 template <typename T>
-__device__ __forceinline__ Slot<T> block_best(Slot<T> mine, bool want_max, Slot<T> *s_red) {
+__device__ __forceinline__ Slot<T> warp_best(Slot<T> mine, bool want_max) {
   for (int off = 16; off > 0; off >>= 1) {
     Slot<T> o;
     o.v = __shfl_xor_sync(0xffffffffu, mine.v, off);
@@ -1035,98 +1059,137 @@ __device__ __forceinline__ Slot<T> block_best(Slot<T> mine, bool want_max, Slot<
     o.s = __shfl_xor_sync(0xffffffffu, mine.s, off);
     mine = slot_best(mine, o, want_max);
   }
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  return mine;
+}
+// Best entry over the whole block (all threads get it); s_red holds 33 entries.
+template <typename T>
+__device__ __forceinline__ Slot<T> block_best(Slot<T> mine, bool want_max, Slot<T> *s_red) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  mine = warp_best(mine, want_max);
   __syncthreads();
   if (lane == 0) s_red[wid] = mine;
   __syncthreads();
-  Slot<T> r = s_red[0];
-  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) r = slot_best(r, s_red[w], want_max);
-  return r;
+  if (wid == 0) {
+    Slot<T> x = lane < nw ? s_red[lane] : Slot<T>{(T)0, -1, -1};
+    x = warp_best(x, want_max);
+    if (lane == 0) s_red[32] = x;
+  }
+  __syncthreads();
+  return s_red[32];
 }
 
 template <typename T>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(kSwapSlots)
     mask_replay_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long H, long h, int iterations,
                        int chunks, const T *__restrict__ cand_v, const long *__restrict__ cand_i,
                        const int *__restrict__ nan_flag) {
-  __shared__ T lv[2][1024];
-  __shared__ long li[2][1024];
-  __shared__ Slot<T> s_red[32];
+  __shared__ T lv[2][kSwapSlots], lnom[2][kSwapSlots];
+  __shared__ long li[2][kSwapSlots];
+  __shared__ int lcs[2][kSwapSlots];
+  __shared__ Slot<T> s_red[33];
   if (*nan_flag) return;   // the full scan handles this update
   const int base = chunks * iterations;   // first slot for rows moved by a swap
   const int t = threadIdx.x;
   for (int cls = 0; cls < 2; ++cls) {
-    li[cls][t] = t < base ? cand_i[(long)cls * base + t] : -1;
-    lv[cls][t] = (t < base && li[cls][t] >= 0) ? cand_v[(long)cls * base + t] : (T)0;
+    const long i = t < base ? cand_i[(long)cls * base + t] : -1;
+    li[cls][t] = i;
+    lv[cls][t] = i >= 0 ? cand_v[(long)cls * base + t] : (T)0;
+    lnom[cls][t] = i >= 0 ? nom[i] : (T)0;
+    lcs[cls][t] = i >= 0 ? csum[i] : 0;
   }
   __syncthreads();
   for (int it = 0; it < iterations; ++it) {
     const Slot<T> s0 = block_best(Slot<T>{lv[0][t], li[0][t], li[0][t] >= 0 ? t : -1}, true, s_red);
     const Slot<T> a1 = block_best(Slot<T>{lv[1][t], li[1][t], li[1][t] >= 0 ? t : -1}, false, s_red);
     if (s0.s < 0 || a1.s < 0 || s0.v < a1.v) break;   // uniform: every thread holds the same picks
-    __syncthreads();
     if (t == 0) {
+      // the moved rows join the other class with their new counts
+      const int cs_up = lcs[0][s0.s] + 1, cs_down = lcs[1][a1.s] - 1;
+      const T nom_up = lnom[0][s0.s], nom_down = lnom[1][a1.s];
       wmask[s0.i * H + h] = 1;
       wmask[a1.i * H + h] = 0;
-      csum[s0.i] += 1;
-      csum[a1.i] -= 1;
+      csum[s0.i] = cs_up;
+      csum[a1.i] = cs_down;
       li[0][s0.s] = -1;
       li[1][a1.s] = -1;
-      // the moved rows join the other class with their new counts
       li[1][base + it] = s0.i;
-      lv[1][base + it] = swap_score(nom, csum, s0.i);
+      lnom[1][base + it] = nom_up;
+      lcs[1][base + it] = cs_up;
+      lv[1][base + it] = swap_score(nom_up, cs_up);
       li[0][base + it] = a1.i;
-      lv[0][base + it] = swap_score(nom, csum, a1.i);
+      lnom[0][base + it] = nom_down;
+      lcs[0][base + it] = cs_down;
+      lv[0][base + it] = swap_score(nom_down, cs_down);
     }
     __syncthreads();
   }
 }
 
+static inline size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+static constexpr size_t kSwapListBytes = 256 + (size_t)2 * kSwapSlots * (sizeof(double) + sizeof(long));
+
 size_t mask_scratch_bytes(long N, size_t elem) {
-  const size_t a = ((size_t)N * elem + 255) & ~(size_t)255;
-  const size_t b = ((size_t)N * sizeof(int) + 255) & ~(size_t)255;
-  const size_t cand = (size_t)2 * kSwapMaxChunks * kSwapMaxIter * (sizeof(double) + sizeof(long)) + 256;
-  return a + b + cand;
+  return align256((size_t)N * elem) + align256((size_t)N * sizeof(int)) + align256((size_t)N) + kSwapListBytes;
 }
+
+// Scratch layout: [score N x T][active count N x int][old mask column N bytes][nan flag, candidate lists].
+template <typename T>
+struct MaskScratch {
+  T *score;
+  int *csum;
+  uint8_t *old_col;
+  int *nan_flag;
+  long *cand_i;
+  T *cand_v;
+  MaskScratch(void *scratch, long N) {
+    unsigned char *p = static_cast<unsigned char *>(scratch);
+    score = reinterpret_cast<T *>(p);
+    p += align256((size_t)N * sizeof(T));
+    csum = reinterpret_cast<int *>(p);
+    p += align256((size_t)N * sizeof(int));
+    old_col = p;
+    p += align256((size_t)N);
+    nan_flag = reinterpret_cast<int *>(p);
+    cand_i = reinterpret_cast<long *>(p + 256);
+    cand_v = reinterpret_cast<T *>(p + 256 + (size_t)2 * kSwapSlots * sizeof(long));
+  }
+};
 
 template <typename T>
 cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
                                long N, long M, long H, long Mc, long h, long iterations, void *scratch,
                                cudaStream_t st) {
   if (N == 0) return cudaSuccess;
-  unsigned char *base = static_cast<unsigned char *>(scratch);
-  const size_t a = ((size_t)N * sizeof(T) + 255) & ~(size_t)255;
-  const size_t b = ((size_t)N * sizeof(int) + 255) & ~(size_t)255;
-  T *score = reinterpret_cast<T *>(base);
-  int *csum = reinterpret_cast<int *>(base + a);
-  unsigned char *cand = base + a + b;
+  MaskScratch<T> ms(scratch, N);
   const T cthr4 = cthr * cthr * cthr * cthr;
   mask_score_kernel<T><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wmask, weights, Ci, Cj, Cij, cthr, cthr4, N, M, H, Mc,
-                                                                 h, score, csum);
+                                                                 h, ms.score, ms.csum, ms.old_col);
   cudaError_t e = launched();
   if (e != cudaSuccess) return e;
   if (iterations >= 1 && iterations <= kSwapMaxIter && N >= 4096) {
+    const int max_chunks = (kSwapSlots - (int)iterations) / (int)iterations;
     int chunks = (int)((N + 1023) / 1024);
-    if (chunks > kSwapMaxChunks) chunks = kSwapMaxChunks;
+    if (chunks > max_chunks) chunks = max_chunks;
     const long rows_per_chunk = (N + chunks - 1) / chunks;
     chunks = (int)((N + rows_per_chunk - 1) / rows_per_chunk);
-    int *nan_flag = reinterpret_cast<int *>(cand);
-    long *cand_i = reinterpret_cast<long *>(cand + 256);
-    T *cand_v = reinterpret_cast<T *>(cand + 256 + (size_t)2 * kSwapMaxChunks * kSwapMaxIter * sizeof(long));
-    e = cudaMemsetAsync(nan_flag, 0, sizeof(int), st);
+    e = cudaMemsetAsync(ms.nan_flag, 0, sizeof(int), st);
     if (e != cudaSuccess) return e;
-    mask_candidates_kernel<T><<<chunks, 256, 0, st>>>(wmask, score, csum, N, H, h, (int)iterations, rows_per_chunk,
-                                                      cand_v, cand_i, nan_flag);
+    if (rows_per_chunk <= kSwapCacheRows)
+      mask_candidates_kernel<T, true><<<chunks, 256, (size_t)rows_per_chunk * (sizeof(T) + 1), st>>>(
+          wmask, ms.score, ms.csum, N, H, h, (int)iterations, rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag);
+    else
+      mask_candidates_kernel<T, false><<<chunks, 256, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, (int)iterations,
+                                                               rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag);
     e = launched();
     if (e != cudaSuccess) return e;
-    mask_replay_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, (int)iterations, chunks, cand_v, cand_i,
-                                              nan_flag);
+    mask_replay_kernel<T><<<1, kSwapSlots, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, (int)iterations, chunks,
+                                                    ms.cand_v, ms.cand_i, ms.nan_flag);
     e = launched();
     if (e != cudaSuccess) return e;
-    mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, iterations, nan_flag);
+    mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, iterations, ms.nan_flag);
     return launched();
   }
-  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, score, csum, N, H, h, iterations, nullptr);
+  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, iterations, nullptr);
   return launched();
 }
 template cudaError_t launch_mask_update<float>(uint8_t *, const float *, const float *, const float *, const float *,
@@ -1135,35 +1198,45 @@ template cudaError_t launch_mask_update<double>(uint8_t *, const double *, const
                                                 const double *, double, long, long, long, long, long, long, void *,
                                                 cudaStream_t);
 
+// After the swaps only the rows whose mask bit changed need new weights in hypercolumn h:
+// the trace step already wrote every other row of the block under the (unchanged) old mask.
+// One warp per row compares the row's old and new mask bit.
 template <typename T>
 __global__ void __launch_bounds__(256)
-    rewrite_hypercolumn_kernel(T *w, const uint8_t *__restrict__ wmask, const T *__restrict__ Ci,
-                               const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr, T cthr4, long N, long M,
-                               long H, long Mc, long h) {
-  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= N * Mc) return;
-  const long i = idx / Mc, col = h * Mc + idx % Mc;
-  const T ci = Ci[i], cj = Cj[col];
-  T v = (T)0;
-  if (wmask[i * H + h] != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[i * M + col], ci, cj, cthr4);
-  w[i * M + col] = v;
+    rewrite_changed_rows_kernel(T *w, const uint8_t *__restrict__ wmask, const uint8_t *__restrict__ old_col,
+                                const T *__restrict__ Ci, const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr,
+                                T cthr4, long N, long M, long H, long Mc, long h) {
+  const int lane = threadIdx.x & 31;
+  const long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= N) return;
+  const uint8_t now = wmask[i * H + h];
+  if (now == old_col[i]) return;
+  const T ci = Ci[i];
+  for (long jj = lane; jj < Mc; jj += 32) {
+    const long col = h * Mc + jj;
+    const T cj = Cj[col];
+    T v = (T)0;
+    if (now != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[i * M + col], ci, cj, cthr4);
+    w[i * M + col] = v;
+  }
 }
 template <typename T>
 cudaError_t launch_rewrite_hypercolumn(T *w, const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr,
-                                       long N, long M, long H, long Mc, long h, cudaStream_t st) {
-  const long total = N * Mc;
-  if (total == 0) return cudaSuccess;
+                                       long N, long M, long H, long Mc, long h, const void *mask_scratch,
+                                       cudaStream_t st) {
+  if (N == 0 || Mc == 0) return cudaSuccess;
+  MaskScratch<T> ms(const_cast<void *>(mask_scratch), N);
   const T cthr4 = cthr * cthr * cthr * cthr;
-  rewrite_hypercolumn_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(w, wmask, Ci, Cj, Cij, cthr, cthr4, N,
-                                                                                  M, H, Mc, h);
+  rewrite_changed_rows_kernel<T><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(w, wmask, ms.old_col, Ci, Cj, Cij, cthr, cthr4,
+                                                                          N, M, H, Mc, h);
   return launched();
 }
 template cudaError_t launch_rewrite_hypercolumn<float>(float *, const uint8_t *, const float *, const float *,
                                                        const float *, float, long, long, long, long, long,
-                                                       cudaStream_t);
+                                                       const void *, cudaStream_t);
 template cudaError_t launch_rewrite_hypercolumn<double>(double *, const uint8_t *, const double *, const double *,
                                                         const double *, double, long, long, long, long, long,
-                                                        cudaStream_t);
+                                                        const void *, cudaStream_t);
 
 // ----------------------------------------------------------------------------
 // Evaluation helper: rows whose predicted class equals the labelled class

@@ -86,17 +86,19 @@ cudaError_t launch_apply_mask(T *w, const uint8_t *wmask, long N, long M, long H
 
 // Mask update for hypercolumn h.  `weights` null => the un-masked weight is
 // recomputed from the traces.  `scratch` holds mask_scratch_bytes(N, sizeof(T))
-// bytes (256-byte aligned): per-row score and active count plus candidate lists.
+// bytes (256-byte aligned): per-row score, active count and previous mask bit, candidate lists.
 size_t mask_scratch_bytes(long N, size_t elem);
 template <typename T>
 cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
                                long N, long M, long H, long Mc, long h, long iterations, void *scratch,
                                cudaStream_t st);
 
-// Rewrites the weights of hypercolumn h's columns from the traces under wmask.
+// Rewrites the weights of hypercolumn h's columns from the traces for the rows whose mask
+// bit the preceding launch_mask_update (same scratch) changed.
 template <typename T>
 cudaError_t launch_rewrite_hypercolumn(T *w, const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr,
-                                       long N, long M, long H, long Mc, long h, cudaStream_t st);
+                                       long N, long M, long H, long Mc, long h, const void *mask_scratch,
+                                       cudaStream_t st);
 
 template <typename T>
 cudaError_t launch_count_correct(const T *pred, const T *labels, long rows, long classes, unsigned long long *count,

@@ -9,7 +9,7 @@
 // no cudaMalloc, no cudaFree, no library routine that allocates.
 //
 // Cost and limits
-//   * The array is SBB_NOALLOC_MAX_ROWS * 12 bytes plus 32 KiB (1.5 MiB) and is resident on
+//   * The array is SBB_NOALLOC_MAX_ROWS * 13 bytes plus 40 KiB (1.7 MiB) and is resident on
 //     every GPU that loads the library, from load until the process exits.
 //   * Layers with more than SBB_NOALLOC_MAX_ROWS input rows are refused with
 //     SBB_ERR_UNSUPPORTED; nothing is launched in that case.
@@ -31,12 +31,13 @@ namespace {
 constexpr long kMaxRows = SBB_NOALLOC_MAX_ROWS;
 constexpr size_t kScoreBytes = (size_t)kMaxRows * sizeof(double);  // REAL score per row, sized for double
 constexpr size_t kCountBytes = (size_t)kMaxRows * sizeof(int);     // active connections per row
-constexpr size_t kListBytes = 32 * 1024;                           // candidate lists of the swap search
+constexpr size_t kColBytes = (size_t)kMaxRows;                     // previous mask bit per row
+constexpr size_t kListBytes = 40 * 1024;                           // candidate lists of the swap search
 
 // In host code this name is only a handle for the runtime; it is NOT a device
 // address and must never be passed to a kernel.  The address a kernel can use
 // comes from cudaGetSymbolAddress, once per device.
-static __device__ __align__(256) unsigned char g_mask_scratch[kScoreBytes + kCountBytes + kListBytes];
+static __device__ __align__(256) unsigned char g_mask_scratch[kScoreBytes + kCountBytes + kColBytes + kListBytes];
 
 constexpr int kMaxDevices = 64;
 void *g_scratch_ptr[kMaxDevices] = {nullptr};
@@ -99,7 +100,7 @@ int sbb_update_mask_noalloc(int dtype, uint8_t *wmask_dev, const void *weights_d
   void *scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc != SBB_OK) return rc;
-  if (sbb::mask_scratch_bytes(N, dtype == SBB_F32 ? 4 : 8) > kScoreBytes + kCountBytes + kListBytes) {
+  if (sbb::mask_scratch_bytes(N, dtype == SBB_F32 ? 4 : 8) > kScoreBytes + kCountBytes + kColBytes + kListBytes) {
     snprintf(g_noalloc_error, sizeof(g_noalloc_error), "update_mask_noalloc: built-in work area too small");
     return SBB_ERR_UNSUPPORTED;
   }

@@ -40,9 +40,9 @@ constexpr int kEpiWarps = 8;
 constexpr int kTmaWarp = kConvWarps + kEpiWarps;
 constexpr int kMmaWarp = kTmaWarp + 1;
 constexpr int kThreads = (kMmaWarp + 1) * 32;  // 448
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock per wait
 
-enum WaitCode { kWaitEmpty = 1, kWaitFull = 2, kWaitConv = 3, kWaitAccEmpty = 4, kWaitAccFull = 5, kWaitDrain = 6 };
+enum WaitCode { kWaitEmpty = 1, kWaitFull = 2, kWaitConv = 3, kWaitAccEmpty = 4, kWaitAccFull = 5, kWaitDrain = 6, kWaitSlab = 7 };
 
 struct TcWork {
   int m_tiles, n_tiles, splits;
@@ -52,6 +52,7 @@ struct TcWork {
   int a_row0;       // offset added to the A row coordinate (first output row of this launch)
   int a_box3;       // A stage fetched by one 3-D box (MN-major A whose row length is a multiple of 32)
   int b_box3_tiles; // column tiles [0, b_box3_tiles) fetch their B stage by one 3-D box
+  int variant;      // timing experiments in trace builds only
 };
 
 struct TcEpilogue {
@@ -65,9 +66,10 @@ struct TcEpilogue {
   float *W;
   const uint8_t *wmask;
   const int *col_hc;
+  uint32_t hc_magic;   // ceil(2^32 / Mc) when floor(n * magic / 2^32) == n / Mc for every column, else 0
   long H, row0;
   TraceParams<float> p;
-  float inv_batch;  // 1 / batch
+  float ema_scale;  // taupdt / batch: weight of the batch sum in the moving average
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -101,16 +103,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false when the CTA is aborting or the time limit passed
-// (in which case it raises the abort flag and records `code`).
+// (in which case it raises the abort flag and records `code`).  The limit is
+// counted on the SM's own cycle counter: %globaltimer is read through the memory
+// system and costs microseconds per read on a busy GPU, which a wait taken
+// thousands of times per launch cannot afford.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
                                             int code) {
-  const unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
   unsigned spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0) {
+    if ((++spins & 1023u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -139,12 +144,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
-               "r"(x), "r"(y)
-               : "memory");
-}
-
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
                : "memory");
@@ -219,16 +218,33 @@ __device__ __forceinline__ float tf32_rn(float v) {
   return __uint_as_float(u);
 }
 
+#ifdef SBB_TC_TRACE
+__device__ unsigned long long g_tc_trace[64 * 16];
+#define TC_TRACE(tile, ev) do { if (blockIdx.x == 0 && (tile) < 64) g_tc_trace[(tile) * 16 + (ev)] = (unsigned long long)clock64(); } while (0)
+__device__ unsigned long long g_tc_trace2[16 * 4 * 8];
+#define TC_TRACE2(tile, g, ev)
+#else
+#define TC_TRACE(tile, ev)
+#define TC_TRACE2(tile, g, ev)
+#endif
+
 // ------------------------------------------------------------------ the kernel
-template <int BN, int BK, int STAGES>
+constexpr int kSlabBytes = 32 * 32 * 4;  // one epilogue warp's 32-row x 32-column block of the trace matrix
+
+template <int BN, int BK, int STAGES, bool FUSED>
 struct TcSmem {
   static constexpr int A_BYTES = 128 * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // TMA landing zone (becomes "hi" in place)
   static constexpr int STAGE_BYTES = 2 * RAW_BYTES;    // + the "lo" copy
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int NUM_BARS = 3 * STAGES + 5;      // full, conv, empty per stage; acc_full[2], acc_empty[2], drain
+  static constexpr int SLAB_OFFSET = STAGES * STAGE_BYTES;
+  // fused epilogue: two landing buffers per epilogue warp for blocks of the trace matrix
+  static constexpr int SLAB_TOTAL = FUSED ? kEpiWarps * 2 * kSlabBytes : 0;
+  static constexpr int BAR_OFFSET = SLAB_OFFSET + SLAB_TOTAL;
+  // full, conv, empty per stage; acc_full[2], acc_empty[2], drain; slab[warp][2]
+  static constexpr int NUM_BARS = 3 * STAGES + 5 + 2 * kEpiWarps;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr, abort flag, alignment slack
+  static_assert(TOTAL <= 232448, "shared memory budget");
 };
 
 // Two 16-lane halves of a warp's TMEM lane quarter, 32 columns each, one wait.
@@ -263,11 +279,12 @@ __device__ __forceinline__ void tmem_ld_pair(uint32_t taddr_lo, uint32_t taddr_h
 // (the forward pass sums over in_features) are cut into short chains whose
 // results the epilogue warps add in full float32.
 template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
+// 14 warps are allocated registers as 16: 128 registers per thread is the most that fits one CTA per SM.
 __global__ void __launch_bounds__(kThreads, 1)
     tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA3, const __grid_constant__ CUtensorMap tmB3,
                           const __grid_constant__ CUtensorMap tmC, TcWork wk, TcEpilogue ep, int *status) {
-  using SM = TcSmem<BN, BK, STAGES>;
+  using SM = TcSmem<BN, BK, STAGES, FUSED>;
   static_assert(!A_KMAJOR || BK == 32, "a K-major operand is loaded as one 128-byte-wide box");
   static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0, "tile shape");
   static_assert(!(FUSED && CHAIN > 0), "the fused epilogue consumes a whole-range accumulator");
@@ -283,6 +300,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
   auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
   const uint32_t bar_drain = bars + 8u * (3 * STAGES + 4);
+  auto bar_slab = [&](int e, int b) { return bars + 8u * (3 * STAGES + 5 + 2 * e + b); };
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + SM::BAR_OFFSET + SM::NUM_BARS * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -299,6 +317,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_acc_empty(b), kEpiWarps * 32);
     }
     mbar_init(bar_drain, 1);
+    for (int e = 0; e < kEpiWarps; ++e) {
+      mbar_init(bar_slab(e, 0), 1);
+      mbar_init(bar_slab(e, 1), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -338,15 +360,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
         int mt, nt, sp, kbeg, nkb;
         decode(w, mt, nt, sp, kbeg, nkb);
-        if (FUSED) {
-          // Pull this tile's block of the trace matrix towards L2 while its products run;
-          // the epilogue reads it one tile-time from now.
-          tma_prefetch_2d(&tmC, nt * BN, (int)ep.row0 + mt * 128);
-        }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status, kWaitEmpty)) { ok = false; break; }
+          if (kb == 0) TC_TRACE((w - blockIdx.x) / gridDim.x, 0);
+          if (kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 8);
           mbar_arrive_expect_tx(bar_full(s), SM::RAW_BYTES);
           const uint32_t a_dst = base + s * SM::STAGE_BYTES;
           const uint32_t b_dst = a_dst + SM::A_BYTES;
@@ -372,8 +391,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!ok) {
         // Loads already issued still land in this CTA's shared memory: give them
         // a bounded moment before the CTA retires.
-        const unsigned long long t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 200000ull) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000ll) {
         }
       }
     }
@@ -391,6 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         while (kb < nkb && ok) {
           const uint32_t buf = chain & 1u, aph = (chain >> 1) & 1u;
           if (!mbar_wait(bar_acc_empty(buf), aph ^ 1u, abort_flag, status, kWaitAccEmpty)) { ok = false; break; }
+          TC_TRACE(chain, 7);
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
           const int kb_end = CHAIN > 0 ? min(nkb, kb + CHAIN) : nkb;
@@ -398,6 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
             if (!mbar_wait(bar_conv(s), ph, abort_flag, status, kWaitConv)) { ok = false; break; }
+            if (first) TC_TRACE(chain, 1);
             tc_fence_after();
             const uint32_t a_hi = base + s * SM::STAGE_BYTES;
             const uint32_t b_hi = a_hi + SM::A_BYTES;
@@ -421,6 +442,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mma_commit(bar_empty(s));  // the stage may be refilled once these MMAs have read it
           }
           if (ok) {
+            TC_TRACE(chain, 2);
             mma_commit(bar_acc_full(buf));
             ++chain;
           }
@@ -441,6 +463,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         if (!mbar_wait(bar_full(s), ph, abort_flag, status, kWaitFull)) { ok = false; break; }
+        if (threadIdx.x == 0 && kb == 0) TC_TRACE((w - blockIdx.x) / gridDim.x, 5);
+        if (threadIdx.x == 0 && kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 9);
         float4 *raw = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES);
         float4 *lo = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
 #pragma unroll 4
@@ -467,9 +491,39 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr int NG = BN / 64;                  // 32-column groups per warp
     uint32_t chain = 0;
     bool ok = true;
+    const int ew = warp - kConvWarps;            // epilogue warp index
+    uint32_t swz[4];                             // byte offset of column pair `rep` inside a swizzled 128-byte row
+#pragma unroll
+    for (int rep = 0; rep < 4; ++rep) swz[rep] = ((uint32_t)((2 * rep + (lc >> 2)) ^ lr) << 4) + (uint32_t)(lc & 3) * 4u;
+    uint32_t slab = 0;                           // blocks of the trace matrix consumed so far (fused epilogue)
+    // Hypercolumn of a column: exact multiply-shift division when the host verified it, else the table.
+    auto hc_of = [&](long n) -> int {
+      return ep.hc_magic ? (int)__umulhi((uint32_t)n, ep.hc_magic) : __ldg(ep.col_hc + n);
+    };
+    // Block number s of this warp (buffer s % 2): column group g of tile (mt, nt).
+    auto issue_slab_at = [&](uint32_t s, int mt, int nt, int g) {
+      const uint32_t b = s & 1u;
+      mbar_arrive_expect_tx(bar_slab(ew, b), kSlabBytes);
+      tma_load_2d(base + SM::SLAB_OFFSET + (ew * 2 + b) * kSlabBytes, &tmC, nt * BN + ch * (BN / 2) + g * 32,
+                  (int)ep.row0 + mt * 128 + 32 * q, bar_slab(ew, b));
+    };
+#ifdef SBB_TC_TRACE
+    if (!(wk.variant & 8))
+#endif
+    if (FUSED && lane == 0 && (long)blockIdx.x < total) {
+      int mt, nt, sp, kbeg, nkb;
+      decode(blockIdx.x, mt, nt, sp, kbeg, nkb);
+      issue_slab_at(0, mt, nt, 0);
+      issue_slab_at(1, mt, nt, 1);
+    }
     for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
       int mt, nt, sp, kbeg, nkb;
       decode(w, mt, nt, sp, kbeg, nkb);
+      int mt_next = 0, nt_next = 0;
+      if (FUSED && w + gridDim.x < total) {
+        int sp2, kb2, nk2;
+        decode(w + gridDim.x, mt_next, nt_next, sp2, kb2, nk2);
+      }
       const long m_base = (long)mt * 128 + 32 * q;   // first tile row of this warp's lane quarter
       const long n_base = (long)nt * BN + ch * (BN / 2);
       bool rv[4];
@@ -528,83 +582,155 @@ __global__ void __launch_bounds__(kThreads, 1)
       } else {
         const uint32_t buf = chain & 1u, aph = (chain >> 1) & 1u;
         if (!mbar_wait(bar_acc_full(buf), aph, abort_flag, status, kWaitAccFull)) { ok = false; break; }
+        if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 3);
         __syncwarp();
         tc_fence_after();
-        float ci[4];
-        bool skip[4];
-        const uint8_t *mrow[4];
+        float rci[4];           // 1 / Ci of the thread's four rows
+        bool row_live[4];       // Ci >= cthr
+        uint32_t mbits[4];      // bit k: connection of the row to hypercolumn hc_first + k is active
+        float *crow[4];         // the row's trace elements at this thread's first column
+        int hc_first = 0;       // hypercolumn of the first column of this warp's half tile
+        bool mask_fast = true;  // the half tile spans at most four hypercolumns (bits in mbits)
+        float2 cj_next[4];
+#ifdef SBB_TC_TRACE
+        if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 10);
+#endif
         if (FUSED) {
+          if (ep.wmask) {
+            const long c_first = n_base < ep.cols ? n_base : ep.cols - 1;
+            const long c_last = n_base + BN / 2 - 1 < ep.cols ? n_base + BN / 2 - 1 : ep.cols - 1;
+            hc_first = hc_of(c_first);
+            mask_fast = hc_of(c_last) - hc_first <= 3;
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const long i = ep.row0 + grow[j];
-            ci[j] = rv[j] ? ep.Ci[i] : 1.f;
-            skip[j] = ci[j] < ep.p.cthr;
-            mrow[j] = (rv[j] && ep.wmask) ? ep.wmask + i * ep.H : nullptr;
+#ifdef SBB_TC_TRACE
+            const float ci = (wk.variant & 256) ? 0.5f : (rv[j] ? __ldg(ep.Ci + i) : 1.f);
+#else
+            const float ci = rv[j] ? __ldg(ep.Ci + i) : 1.f;
+#endif
+            rci[j] = 1.f / ci;   // correctly rounded: computed once per row
+            row_live[j] = !(ci < ep.p.cthr);
+            crow[j] = ep.Cij + i * ep.cols + n_base + lc;
+            mbits[j] = 0xFu;
+#ifdef SBB_TC_TRACE
+            if (!(wk.variant & 64))
+#endif
+            if (ep.wmask && rv[j] && mask_fast) {
+              // all mask bytes this row can need in this tile, fetched together up front
+              const uint8_t *mr = ep.wmask + i * ep.H + hc_first;
+              uint32_t bits = 0;
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                if (hc_first + k < ep.H && __ldg(mr + k) != 0) bits |= 1u << k;
+              mbits[j] = bits;
+            }
+          }
+#pragma unroll
+          for (int rep = 0; rep < 4; ++rep) {
+            const long n = n_base + lc + rep * 8;
+            cj_next[rep] = n < ep.cols ? __ldg(reinterpret_cast<const float2 *>(ep.Cj + n)) : make_float2(1.f, 1.f);
+#ifdef SBB_TC_TRACE
+            if (wk.variant & 256) cj_next[rep] = make_float2(0.5f, 0.5f);
+#endif
           }
         }
+#ifdef SBB_TC_TRACE
+        if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 11);
+#endif
+        // Whole tile inside the matrix (the common case): no per-element range checks.
+        const bool interior = (long)mt * 128 + 128 <= ep.rows && n_base + BN / 2 <= ep.cols;
+        if (FUSED) {
+          const long w_minus_c = ep.W - ep.Cij;   // the weight of an element sits this far from its trace
 #pragma unroll 1
-        for (int g = 0; g < NG; ++g) {
-          float a0[16], a1[16];
-          const uint32_t t0 = tmem_base + buf * BN + ch * (BN / 2) + g * 32 + ((uint32_t)(32 * q) << 16);
-          __syncwarp();  // tcgen05.ld is warp-collective
-          tmem_ld_pair(t0, t0 + (16u << 16), a0, a1);
-          const long n0 = n_base + g * 32 + lc;
-          bool cv[4];
-#pragma unroll
-          for (int rep = 0; rep < 4; ++rep) cv[rep] = n0 + rep * 8 < ep.cols;  // cols is even: n+1 is in range too
-          if (FUSED) {
-            // Issue every global load of this 32-column group before the first use, so each
-            // thread keeps 16 eight-byte loads of the trace matrix in flight.
-            float2 c[4][4], cj[4];
-            int2 hc[4];
+          for (int g = 0; g < NG; ++g) {
+            // This warp's 32 x 32 block of the trace matrix was fetched by TMA two blocks ago
+            // (128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8); every row
+            // of this thread has r % 8 == lane / 4).
+            const uint32_t sb = slab & 1u;
+            if (!mbar_wait(bar_slab(ew, sb), (slab >> 1) & 1u, abort_flag, status, kWaitSlab)) { ok = false; break; }
+            const uint8_t *sl = smem + SM::SLAB_OFFSET + (ew * 2 + sb) * kSlabBytes + lr * 128;
+            const long n0 = n_base + g * 32 + lc;
+            // per-column data of this group: 1/Cj, threshold flags, mask bit position of each column
+            float2 rcj[4];
+            uint32_t colbits = 0;   // bits 2*rep, 2*rep+1: Cj >= cthr; bits 8+4*rep..: hypercolumn offsets (2 bits each)
 #pragma unroll
             for (int rep = 0; rep < 4; ++rep) {
-              cj[rep] = cv[rep] ? __ldg(reinterpret_cast<const float2 *>(ep.Cj + n0 + rep * 8)) : make_float2(1.f, 1.f);
-              hc[rep] = (cv[rep] && ep.wmask) ? __ldg(reinterpret_cast<const int2 *>(ep.col_hc + n0 + rep * 8))
-                                              : make_int2(0, 0);
+              const float2 cj = cj_next[rep];
+              rcj[rep] = make_float2(1.f / cj.x, 1.f / cj.y);   // correctly rounded, once per column pair and group
+              if (!(cj.x < ep.p.cthr)) colbits |= 1u << (2 * rep);
+              if (!(cj.y < ep.p.cthr)) colbits |= 2u << (2 * rep);
+              const long n = n0 + rep * 8;
+              if (ep.wmask && mask_fast && (interior || n < ep.cols)) {
+                colbits |= (uint32_t)(hc_of(n) - hc_first) << (8 + 4 * rep);
+                colbits |= (uint32_t)(hc_of(n + 1) - hc_first) << (10 + 4 * rep);
+              }
+              // the next group's Cj, in flight while this group is processed
+              const long nn = n + 32;
+              cj_next[rep] = (g + 1 < NG && nn < ep.cols) ? __ldg(reinterpret_cast<const float2 *>(ep.Cj + nn)) : make_float2(1.f, 1.f);
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int hh = 0; hh < 2; ++hh) {
+              // 16 of the warp's 32 TMEM lanes at a time keeps the live registers within budget
+              float a[16];
+              __syncwarp();  // tcgen05.ld is warp-collective
+              tmem_ld_16x256b_x4(tmem_base + buf * BN + ch * (BN / 2) + g * 32 + ((uint32_t)(32 * q + 16 * hh) << 16), a);
+              float2 c[2][4];
 #pragma unroll
-              for (int rep = 0; rep < 4; ++rep)
-                c[j][rep] = (rv[j] && cv[rep])
-                                ? __ldcs(reinterpret_cast<const float2 *>(ep.Cij + (ep.row0 + grow[j]) * ep.cols + n0 + rep * 8))
-                                : make_float2(0.f, 0.f);
-            // All of this thread's columns in the group usually belong to one hypercolumn
-            // (col_hc is non-decreasing), so one mask byte per row decides them all.
-            int hc_last = hc[0].x;
+              for (int rr = 0; rr < 2; ++rr)
 #pragma unroll
-            for (int rep = 0; rep < 4; ++rep)
-              if (cv[rep]) hc_last = hc[rep].y;   // columns past the matrix edge carry no hypercolumn
-            const bool one_hc = hc[0].x == hc_last;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float *acc = (j >> 1) ? a1 : a0;
-              bool row_on = !skip[j];
-              if (row_on && mrow[j] && one_hc) row_on = mrow[j][hc[0].x] != 0;
-#pragma unroll
-              for (int rep = 0; rep < 4; ++rep) {
-                if (!(rv[j] && cv[rep])) continue;
-                float2 c2 = c[j][rep], w2 = make_float2(0.f, 0.f);
-                c2.x = trace_ema_fast(c2.x, acc[rep * 4 + (j & 1) * 2 + 0], ep.p, ep.inv_batch);
-                c2.y = trace_ema_fast(c2.y, acc[rep * 4 + (j & 1) * 2 + 1], ep.p, ep.inv_batch);
-                if (row_on) {
-                  bool on0 = !(cj[rep].x < ep.p.cthr), on1 = !(cj[rep].y < ep.p.cthr);
-                  if (mrow[j] && !one_hc) {
-                    on0 = on0 && mrow[j][hc[rep].x] != 0;
-                    on1 = on1 && mrow[j][hc[rep].y] != 0;
-                  }
-                  const float wx = log_ratio_fast(c2.x, ci[j], cj[rep].x, ep.p.cthr4);
-                  const float wy = log_ratio_fast(c2.y, ci[j], cj[rep].y, ep.p.cthr4);
-                  w2.x = on0 ? wx : 0.f;
-                  w2.y = on1 ? wy : 0.f;
+                for (int rep = 0; rep < 4; ++rep)
+                  c[rr][rep] = *reinterpret_cast<const float2 *>(sl + (16 * hh + 8 * rr) * 128 + swz[rep]);
+              if (hh == 1) {
+                // The buffer is about to be overwritten by the async proxy (TMA): every lane's
+                // reads above must have been performed first, not merely issued.
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  // block slab+2: two column groups ahead in this tile, or the next tile's first groups
+                  if (g + 2 < NG) issue_slab_at(slab + 2, mt, nt, g + 2);
+                  else if (w + gridDim.x < total) issue_slab_at(slab + 2, mt_next, nt_next, g + 2 - NG);
                 }
-                const long off = (ep.row0 + grow[j]) * ep.cols + n0 + rep * 8;
-                __stcs(reinterpret_cast<float2 *>(ep.Cij + off), c2);
-                __stcs(reinterpret_cast<float2 *>(ep.W + off), w2);
+              }
+#pragma unroll
+              for (int rr = 0; rr < 2; ++rr) {
+                const int j = 2 * hh + rr;
+                if (!interior && !rv[j]) continue;
+                const bool row_on = row_live[j];
+                float *cp = crow[j] + g * 32;
+#pragma unroll
+                for (int rep = 0; rep < 4; ++rep) {
+                  if (!interior && !(n0 + rep * 8 < ep.cols)) continue;
+                  float2 c2 = c[rr][rep];
+                  c2.x = fmaxf(fmaf(c2.x, ep.p.one_minus, a[rep * 4 + rr * 2 + 0] * ep.ema_scale), 0.f);
+                  c2.y = fmaxf(fmaf(c2.y, ep.p.one_minus, a[rep * 4 + rr * 2 + 1] * ep.ema_scale), 0.f);
+                  bool on0 = row_on && ((colbits >> (2 * rep)) & 1u), on1 = row_on && ((colbits >> (2 * rep + 1)) & 1u);
+                  if (mask_fast) {
+                    on0 = on0 && ((mbits[j] >> ((colbits >> (8 + 4 * rep)) & 3u)) & 1u);
+                    on1 = on1 && ((mbits[j] >> ((colbits >> (10 + 4 * rep)) & 3u)) & 1u);
+                  } else if (row_on) {
+                    const uint8_t *mr = ep.wmask + (ep.row0 + grow[j]) * ep.H;
+                    on0 = on0 && __ldg(mr + hc_of(n0 + rep * 8)) != 0;
+                    on1 = on1 && __ldg(mr + hc_of(n0 + rep * 8 + 1)) != 0;
+                  }
+                  const float wx = __logf(fmaxf(c2.x, ep.p.cthr4) * (rci[j] * rcj[rep].x));
+                  const float wy = __logf(fmaxf(c2.y, ep.p.cthr4) * (rci[j] * rcj[rep].y));
+                  __stcs(reinterpret_cast<float2 *>(cp + rep * 8), c2);
+                  __stcs(reinterpret_cast<float2 *>(cp + w_minus_c + rep * 8), make_float2(on0 ? wx : 0.f, on1 ? wy : 0.f));
+                }
               }
             }
-          } else {
+            ++slab;
+          }
+        } else {
+#pragma unroll 1
+          for (int g = 0; g < NG; ++g) {
+            float a0[16], a1[16];
+            const uint32_t t0 = tmem_base + buf * BN + ch * (BN / 2) + g * 32 + ((uint32_t)(32 * q) << 16);
+            __syncwarp();  // tcgen05.ld is warp-collective
+            tmem_ld_pair(t0, t0 + (16u << 16), a0, a1);
+            const long n0 = n_base + g * 32 + lc;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (!rv[j]) continue;
@@ -612,12 +738,14 @@ __global__ void __launch_bounds__(kThreads, 1)
               float *orow = ep.out + ((long)sp * ep.rows + grow[j]) * ep.ld;
 #pragma unroll
               for (int rep = 0; rep < 4; ++rep)
-                if (cv[rep])
+                if (n0 + rep * 8 < ep.cols)   // cols is even: n+1 is in range too
                   __stcs(reinterpret_cast<float2 *>(orow + n0 + rep * 8),
                          make_float2(acc[rep * 4 + (j & 1) * 2], acc[rep * 4 + (j & 1) * 2 + 1]));
             }
           }
         }
+        if (!ok) break;
+        if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 4);
         tc_fence_before();
         mbar_arrive(bar_acc_empty(buf));  // the accumulator buffer may be overwritten
         ++chain;
@@ -712,17 +840,6 @@ bool make_map_chunks(CUtensorMap *map, const float *base, long cols, long rows, 
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Un-swizzled 2-D map used only to prefetch a [128 x box_cols] block of the trace matrix into L2.
-bool make_map_plain(CUtensorMap *map, const float *base, long cols, long rows, int box_cols, int box_rows) {
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // Column tiles of width bn whose every 32-column group lies inside the matrix.
 int full_chunk_tiles(long cols, int bn) { return (int)(((cols / 32) * 32) / bn); }
 
@@ -732,7 +849,7 @@ struct TcMaps {
 
 template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
 cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st) {
-  using SM = TcSmem<BN, BK, STAGES>;
+  using SM = TcSmem<BN, BK, STAGES, FUSED>;
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
   auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN>;
@@ -746,6 +863,12 @@ cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, 
   const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
   if (total <= 0) return cudaSuccess;
   const unsigned grid = (unsigned)(total < g_sm_count_tc[dev] ? total : g_sm_count_tc[dev]);
+#ifdef SBB_TC_TRACE
+  TcWork wk2 = wk;
+  if (const char *v = getenv("SBB_TC_VARIANT")) wk2.variant = atoi(v);
+  kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, wk2, ep, status);
+  return cudaGetLastError();
+#endif
   kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, wk, ep, status);
   return cudaGetLastError();
 }
@@ -771,7 +894,7 @@ bool tc_shape_ok(const void *x, const void *y_or_w, long N, long M) {
 namespace {
 constexpr int kFwdBN = 128, kFwdBK = 32, kFwdStages = 3;
 constexpr int kFwdChain = 4;  // 4 k-blocks of 32 = 128 k-values (48 MMAs) per tensor-memory accumulation chain
-constexpr int kTrBN = 256, kTrBK = 16, kTrStages = 4;
+constexpr int kTrBN = 256, kTrBK = 16, kTrStages = 3;
 
 // k-blocks per split and the number of (non-empty) splits for the forward product.
 void forward_split_plan(long B, long N, long M, int &splits, int &k_per_split) {
@@ -809,7 +932,7 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, kFwdBN / 32);
   if (!b3) tm.b3 = tm.b;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
-            b3 ? full_chunk_tiles(M, kFwdBN) : 0};
+            b3 ? full_chunk_tiles(M, kFwdBN) : 0, 0};
   TcEpilogue ep{};
   ep.out = partial;
   ep.rows = B;
@@ -820,9 +943,31 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   return e;
 }
 
+// Multiplier for n / d by multiply-high, or 0 if it is not exact for every n < limit.
+static uint32_t exact_division_magic(long d, long limit) {
+  if (d <= 1 || d >= (1L << 31) || limit >= (1L << 31)) return 0;
+  const uint64_t magic = ((1ull << 32) + (uint64_t)d - 1) / (uint64_t)d;
+  if (magic >> 32) return 0;
+  for (long n = 0; n < limit; ++n)
+    if ((long)(((uint64_t)n * magic) >> 32) != n / d) return 0;
+  return (uint32_t)magic;
+}
+
 cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long N, long M, long H, const float *Ci,
                                    const float *Cj, float *Cij, float *w, const uint8_t *wmask, const int *col_hc,
                                    TraceParams<float> p, long row_begin, long row_end, cudaStream_t st) {
+  static long magic_for_mc = -1, magic_for_m = -1;
+  static uint32_t magic_value = 0;
+  uint32_t hc_magic = 0;
+  if (wmask != nullptr && H > 0) {
+    const long Mc = M / H;
+    if (magic_for_mc != Mc || magic_for_m != M) {   // verified once per layer shape
+      magic_value = exact_division_magic(Mc, M + 2);
+      magic_for_mc = Mc;
+      magic_for_m = M;
+    }
+    hc_magic = magic_value;
+  }
   if (!tc_available() || !tc_shape_ok(x, y, N, M) || row_begin % 128 != 0) return cudaErrorNotSupported;
   if ((reinterpret_cast<uintptr_t>(Cij) & 7u) || (reinterpret_cast<uintptr_t>(w) & 7u) ||
       (reinterpret_cast<uintptr_t>(Cj) & 7u) || (wmask && (col_hc == nullptr || (reinterpret_cast<uintptr_t>(col_hc) & 7u))))
@@ -830,7 +975,7 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   if (row_end <= row_begin) return cudaSuccess;
   TcMaps tm;
   if (!make_map(&tm.a, x, N, B, 32, kTrBK, true) || !make_map(&tm.b, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
-  if (!make_map_plain(&tm.c, Cij, M, N, M < kTrBN ? (int)M : kTrBN, 128)) return cudaErrorInvalidValue;
+  if (!make_map(&tm.c, Cij, M, N, 32, 32, false)) return cudaErrorInvalidValue;   // 32 x 32 blocks, 128-byte swizzle
   const bool a3 = N % 32 == 0 && make_map_chunks(&tm.a3, x, N, B, kTrBK, 4);
   if (!a3) tm.a3 = tm.a;
   const bool b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, kTrBN / 32);
@@ -838,7 +983,7 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0};
+            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
   TcEpilogue ep{};
   ep.rows = rows;
   ep.cols = M;
@@ -848,10 +993,11 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   ep.W = w;
   ep.wmask = wmask;
   ep.col_hc = col_hc;
+  ep.hc_magic = hc_magic;
   ep.H = H;
   ep.row0 = row_begin;
   ep.p = p;
-  ep.inv_batch = 1.0f / p.batch;
+  ep.ema_scale = p.taupdt / p.batch;
   cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
@@ -873,7 +1019,7 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0};
+            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
   TcEpilogue ep{};
   ep.out = delta + row_begin * M;
   ep.rows = rows;
@@ -884,6 +1030,17 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   return e;
 }
 
+
+#ifdef SBB_TC_TRACE
+extern "C" int sbb_tc_trace_read(unsigned long long *out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 64 * 16);
+}
+extern "C" int sbb_tc_trace2_read(unsigned long long *out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace2, sizeof(unsigned long long) * 16 * 4 * 8);
+}
+#endif
 
 cudaError_t tc_read_status(int *status) {
   *status = 0;

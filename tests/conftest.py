@@ -30,6 +30,15 @@ def rel_inf(a, b):
     return 0.0 if num == 0.0 else num / max(den, 1e-300)
 
 
+def weight_err(w, ref):
+    """Error of a weight matrix relative to max(1, max|ref|).  Weights are logarithms of trace
+    ratios and enter the forward sum next to biases of order one, so an absolute scale of one
+    is the meaningful floor when every weight happens to be tiny (independent units)."""
+    w = np.asarray(w, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    return np.abs(w - ref).max() / max(1.0, np.abs(ref).max())
+
+
 # Parity tolerances of the path (relative, norm-wise): activations and traces within
 # 1e-5 in float32 and 1e-12 in float64 of the reference `cpu` backend.
 TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}

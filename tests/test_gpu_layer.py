@@ -9,7 +9,7 @@ import random
 import numpy as np
 import pytest
 
-from conftest import TOL, load_golden, rel_inf
+from conftest import TOL, load_golden, rel_inf, weight_err
 
 import oracle
 
@@ -89,11 +89,11 @@ def test_layer_steps_teacher_forced_vs_golden(B200, tag, dtype):
                                           float(g["hp_taupdt"]) / 2, Mc, 1e-5), s
         if np.array_equal(got_mask, want["wmask"]):
             W = layer.weights
-            assert rel_inf(W, want["weights"]) < 10 * tol, s
+            assert weight_err(W, want["weights"]) < 10 * tol, s
             assert np.array_equal(W == 0, want["weights"] == 0), s
         for name in ("Ci", "Cj", "Cij"):
             assert rel_inf(getattr(dense, name), g["d%d_%s" % (s, name)]) < tol, (s, name)
-        assert rel_inf(dense.weights, g["d%d_weights" % s]) < 10 * tol, s
+        assert weight_err(dense.weights, g["d%d_weights" % s]) < 10 * tol, s
         for name in PLASTIC_STATE:
             setattr(layer, name, want[name])
         for name in ("weights", "Ci", "Cj", "Cij"):
@@ -218,7 +218,7 @@ def test_mnist_shaped_layer_teacher_forced_vs_oracle(B200, port_kernels, tag, dt
             assert mask_mismatch_is_a_tie(got, ref.wmask, h or 0, before, ref.state(), p["hidden"]["taupdt"] / 2, Mc,
                                           1e-5), s
         if np.array_equal(got, ref.wmask):
-            assert rel_inf(dev.weights, ref.weights) < 10 * tol, s
+            assert weight_err(dev.weights, ref.weights) < 10 * tol, s
         for name in PLASTIC_STATE:
             setattr(dev, name, getattr(ref, name))
 
