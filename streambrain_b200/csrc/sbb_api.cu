@@ -143,6 +143,7 @@ struct sbb_layer {
   Scratch score;         // mask-update scratch: per-row score, active count, candidate lists
   Scratch hx, hy, ht;    // staging for the host-buffer entry points
   Scratch col_hc;        // M ints: hypercolumn of every output column (j / Mc)
+  Scratch rc;            // threshold-gated reciprocals of Ci and Cj for the tensor-core trace update
   cudaStream_t own_stream = nullptr;
   // optional per-phase event ring (sbb_layer_profile)
   bool profiling = false;
@@ -235,7 +236,8 @@ int layer_train_step(sbb_layer *L, const T *x, const T *y, long B, long h, cudaS
       SBB_CUDA(sbb::launch_trace_update_tc(x, y, B, L->N, L->M, L->H, Ci, Cj, static_cast<T *>(L->state[SBB_STATE_CIJ]),
                                            static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
                                            static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]),
-                                           static_cast<const int *>(L->col_hc.d), p, 0, L->N, st));
+                                           static_cast<const int *>(L->col_hc.d), static_cast<float *>(L->rc.d), p,
+                                           0, L->N, st));
   } else {
     SBB_CUDA(sbb::launch_trace_update_fused<T>(x, y, B, L->N, L->M, L->H, L->Mc, Ci, Cj,
                                                static_cast<T *>(L->state[SBB_STATE_CIJ]),
@@ -447,13 +449,15 @@ int update_weights_t(void *Ci, void *Cj, void *Cij, const void *a_i, const void 
   SBB_TRY(dx.upload(a_i, B * N * s));
   SBB_TRY(dy.upload(a_o, B * M * s));
   SBB_TRY(dw.alloc(N * M * s));
+  Staged drc;
+  SBB_TRY(drc.alloc(sbb::tc_trace_scratch_bytes(N, M)));
   const sbb::TraceParams<T> p = sbb::make_trace_params<T>(taupdt, cthr, B);
   SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, nullptr, dci.as<T>(), p, 1, 0));
   SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, nullptr, dcj.as<T>(), p, 1, 0));
   if (tensor_path<T>(dx.d, dy.d, N, M)) {
     if constexpr (std::is_same<T, float>::value)
       SBB_CUDA(sbb::launch_trace_update_tc(dx.as<T>(), dy.as<T>(), B, N, M, 1, dci.as<T>(), dcj.as<T>(), dcij.as<T>(),
-                                           dw.as<T>(), nullptr, nullptr, p, 0, N, 0));
+                                           dw.as<T>(), nullptr, nullptr, drc.as<float>(), p, 0, N, 0));
   } else {
     SBB_CUDA(sbb::launch_trace_update_fused<T>(dx.as<T>(), dy.as<T>(), B, N, M, 1, M, dci.as<T>(), dcj.as<T>(),
                                                dcij.as<T>(), dw.as<T>(), nullptr, p, 0, N, 0));
@@ -628,6 +632,7 @@ int sbb_layer_create(const sbb_layer_desc *desc, sbb_layer **out) {
     }
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) rc = cuda_fail(e, "layer_create");
+  if (rc == SBB_OK) rc = L->rc.reserve(sbb::tc_trace_scratch_bytes(L->N, L->M));
   if (rc == SBB_OK && desc->kind == SBB_LAYER_PLASTIC) {
     rc = L->score.reserve(sbb::mask_scratch_bytes(L->N, s));
     if (rc == SBB_OK) rc = L->col_hc.reserve((size_t)(L->M + 4) * sizeof(int));
@@ -658,6 +663,7 @@ int sbb_layer_destroy(sbb_layer *L) {
   L->hy.release();
   L->ht.release();
   L->col_hc.release();
+  L->rc.release();
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
   if (L->ev_created)
     for (int ph = 0; ph < 2; ++ph)

@@ -27,10 +27,13 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
                                       int splits, cudaStream_t st);
 
 // Fused trace step (same contract as launch_trace_update_fused); col_hc[j] = j / Mc.
+// `scratch` holds tc_trace_scratch_bytes(N, M) bytes, 16-byte aligned (threshold-gated
+// reciprocals of Ci and Cj, written by a small kernel ahead of the contraction).
+size_t tc_trace_scratch_bytes(long N, long M);
 cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long N, long M, long H,
                                    const float *Ci, const float *Cj, float *Cij, float *w, const uint8_t *wmask,
-                                   const int *col_hc, TraceParams<float> p, long row_begin, long row_end,
-                                   cudaStream_t st);
+                                   const int *col_hc, float *scratch, TraceParams<float> p, long row_begin,
+                                   long row_end, cudaStream_t st);
 
 // delta[i, j] = sum_b x[b, i] y[b, j] for rows [row_begin,row_end)
 cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long N, long M, float *delta,

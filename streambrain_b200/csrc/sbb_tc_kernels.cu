@@ -15,10 +15,11 @@
 //   warps 0-3   converters: wait for a TMA stage, write hi in place and lo beside it
 //   warps 4-11  epilogue: tcgen05.ld the accumulator (16x256b shape, so that four
 //               lanes cover 32 contiguous bytes of a row) and either store it or run
-//               the trace / weight arithmetic against Cij in global memory
+//               the trace / weight arithmetic against 32 x 32 blocks of Cij that TMA
+//               stages in shared memory two blocks ahead
 //   warp 12     TMA producer (one lane): cp.async.bulk.tensor loads, no multicast
 //   warp 13     MMA issuer (one lane) and owner of the TMEM allocation
-// Hand-offs use mbarriers; every wait is bounded by wall time (%globaltimer):
+// Hand-offs use mbarriers; every wait is bounded by a count of SM clock cycles:
 // a wait that gives up records a code in a global status word, raises the CTA's
 // abort flag, and every role falls through to the common tear-down (drain the
 // tensor pipe, free TMEM) instead of spinning.
@@ -52,7 +53,6 @@ struct TcWork {
   int a_row0;       // offset added to the A row coordinate (first output row of this launch)
   int a_box3;       // A stage fetched by one 3-D box (MN-major A whose row length is a multiple of 32)
   int b_box3_tiles; // column tiles [0, b_box3_tiles) fetch their B stage by one 3-D box
-  int variant;      // timing experiments in trace builds only
 };
 
 struct TcEpilogue {
@@ -60,14 +60,15 @@ struct TcEpilogue {
   float *out;
   long rows, cols, ld;
   // fused trace step (rows = row_end - row_begin, global row = row0 + m)
-  const float *Ci;
-  const float *Cj;
+  const float *rci;    // per global row: 1 / Ci, or 0 when Ci < cthr
+  const float *rcj;    // per column: 1 / Cj, or 0 when Cj < cthr
   float *Cij;
   float *W;
   const uint8_t *wmask;
   const int *col_hc;
   uint32_t hc_magic;   // ceil(2^32 / Mc) when floor(n * magic / 2^32) == n / Mc for every column, else 0
-  long H, row0;
+  long H, Mc, row0;
+  int fast_ok;         // select-word epilogue usable: Mc >= 32 (or no mask) and cthr^4 a normal float
   TraceParams<float> p;
   float ema_scale;  // taupdt / batch: weight of the batch sum in the moving average
 };
@@ -75,10 +76,12 @@ struct TcEpilogue {
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
+constexpr float kLn2 = 0.693147180559945309f;
+// log2 by the special-function unit alone (subnormal arguments read as zero).
+__device__ __forceinline__ float lg2_ftz(float v) {
+  float r;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -212,10 +215,12 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr, uint32_t lbo_by
   return smem_desc(saddr, lbo_bytes, 512u, 1u);       // MN-major, SWIZZLE_128B_BASE32B
 }
 
+// Rounds v to the 11 significant bits of TF32 (Veltkamp split with 2^13 + 1; ties to even) on the
+// FMA pipe: the conversion instruction runs on the quarter-rate pipe the logarithms need.  The
+// low 13 bits of the result are zero and v - tf32_rn(v) is exact.  |v| >= 2^114 overflows to NaN.
 __device__ __forceinline__ float tf32_rn(float v) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
-  return __uint_as_float(u);
+  const float c = __fmul_rn(v, 8193.f);
+  return __fsub_rn(c, __fsub_rn(c, v));
 }
 
 #ifdef SBB_TC_TRACE
@@ -472,7 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const float4 v = raw[c];
           float4 h, l;
           h.x = tf32_rn(v.x); h.y = tf32_rn(v.y); h.z = tf32_rn(v.z); h.w = tf32_rn(v.w);
-          l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+          l.x = __fsub_rn(v.x, h.x); l.y = __fsub_rn(v.y, h.y); l.z = __fsub_rn(v.z, h.z); l.w = __fsub_rn(v.w, h.w);
           raw[c] = h;
           lo[c] = l;
         }
@@ -507,9 +512,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       tma_load_2d(base + SM::SLAB_OFFSET + (ew * 2 + b) * kSlabBytes, &tmC, nt * BN + ch * (BN / 2) + g * 32,
                   (int)ep.row0 + mt * 128 + 32 * q, bar_slab(ew, b));
     };
-#ifdef SBB_TC_TRACE
-    if (!(wk.variant & 8))
-#endif
     if (FUSED && lane == 0 && (long)blockIdx.x < total) {
       int mt, nt, sp, kbeg, nkb;
       decode(blockIdx.x, mt, nt, sp, kbeg, nkb);
@@ -585,64 +587,47 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 3);
         __syncwarp();
         tc_fence_after();
-        float rci[4];           // 1 / Ci of the thread's four rows
-        bool row_live[4];       // Ci >= cthr
-        uint32_t mbits[4];      // bit k: connection of the row to hypercolumn hc_first + k is active
-        float *crow[4];         // the row's trace elements at this thread's first column
-        int hc_first = 0;       // hypercolumn of the first column of this warp's half tile
-        bool mask_fast = true;  // the half tile spans at most four hypercolumns (bits in mbits)
-        float2 cj_next[4];
-#ifdef SBB_TC_TRACE
-        if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 10);
-#endif
-        if (FUSED) {
-          if (ep.wmask) {
-            const long c_first = n_base < ep.cols ? n_base : ep.cols - 1;
-            const long c_last = n_base + BN / 2 - 1 < ep.cols ? n_base + BN / 2 - 1 : ep.cols - 1;
-            hc_first = hc_of(c_first);
-            mask_fast = hc_of(c_last) - hc_first <= 3;
+        // this warp's accumulator block: TMEM lanes 32q.., columns of its half tile
+        const uint32_t tacc = tmem_base + buf * BN + ch * (BN / 2) + ((uint32_t)(32 * q) << 16);
+        if constexpr (FUSED) {
+          // ---- per tile: reciprocal of Ci (0 = row below threshold), trace row pointers and the
+          // row's mask bytes for every hypercolumn this half tile touches (bit k: hc_first + k)
+          const bool has_mask = ep.wmask != nullptr;
+          int hc_first = 0, hc_last = 0;
+          if (has_mask) {
+            hc_first = hc_of(n_base < ep.cols ? n_base : ep.cols - 1);
+            hc_last = hc_of(n_base + BN / 2 - 1 < ep.cols ? n_base + BN / 2 - 1 : ep.cols - 1);
           }
+          const bool bits_ok = hc_last - hc_first <= 7;
+          float rci[4];
+          uint32_t mbits[4];
+          float *crow[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const long i = ep.row0 + grow[j];
-#ifdef SBB_TC_TRACE
-            const float ci = (wk.variant & 256) ? 0.5f : (rv[j] ? __ldg(ep.Ci + i) : 1.f);
-#else
-            const float ci = rv[j] ? __ldg(ep.Ci + i) : 1.f;
-#endif
-            rci[j] = 1.f / ci;   // correctly rounded: computed once per row
-            row_live[j] = !(ci < ep.p.cthr);
+            rci[j] = rv[j] ? __ldg(ep.rci + i) : 0.f;
             crow[j] = ep.Cij + i * ep.cols + n_base + lc;
-            mbits[j] = 0xFu;
-#ifdef SBB_TC_TRACE
-            if (!(wk.variant & 64))
-#endif
-            if (ep.wmask && rv[j] && mask_fast) {
-              // all mask bytes this row can need in this tile, fetched together up front
+            mbits[j] = 0xFFu;
+            if (has_mask && rv[j] && bits_ok) {
               const uint8_t *mr = ep.wmask + i * ep.H + hc_first;
               uint32_t bits = 0;
 #pragma unroll
-              for (int k = 0; k < 4; ++k)
-                if (hc_first + k < ep.H && __ldg(mr + k) != 0) bits |= 1u << k;
+              for (int k = 0; k < 8; ++k)
+                if (hc_first + k <= hc_last && __ldg(mr + k) != 0) bits |= 1u << k;
               mbits[j] = bits;
             }
           }
+          // reciprocals of Cj for the first column group: this thread's pairs and, one per lane, the whole group
+          float2 rcj_next[4];
 #pragma unroll
           for (int rep = 0; rep < 4; ++rep) {
             const long n = n_base + lc + rep * 8;
-            cj_next[rep] = n < ep.cols ? __ldg(reinterpret_cast<const float2 *>(ep.Cj + n)) : make_float2(1.f, 1.f);
-#ifdef SBB_TC_TRACE
-            if (wk.variant & 256) cj_next[rep] = make_float2(0.5f, 0.5f);
-#endif
+            rcj_next[rep] = n < ep.cols ? __ldg(reinterpret_cast<const float2 *>(ep.rcj + n)) : make_float2(0.f, 0.f);
           }
-        }
-#ifdef SBB_TC_TRACE
-        if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 11);
-#endif
-        // Whole tile inside the matrix (the common case): no per-element range checks.
-        const bool interior = (long)mt * 128 + 128 <= ep.rows && n_base + BN / 2 <= ep.cols;
-        if (FUSED) {
+          float lane_rcj_next = n_base + lane < ep.cols ? __ldg(ep.rcj + n_base + lane) : 0.f;
+          const bool tile_fast = ep.fast_ok && bits_ok && (long)mt * 128 + 128 <= ep.rows;
           const long w_minus_c = ep.W - ep.Cij;   // the weight of an element sits this far from its trace
+          if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 10);
 #pragma unroll 1
           for (int g = 0; g < NG; ++g) {
             // This warp's 32 x 32 block of the trace matrix was fetched by TMA two blocks ago
@@ -651,31 +636,46 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t sb = slab & 1u;
             if (!mbar_wait(bar_slab(ew, sb), (slab >> 1) & 1u, abort_flag, status, kWaitSlab)) { ok = false; break; }
             const uint8_t *sl = smem + SM::SLAB_OFFSET + (ew * 2 + sb) * kSlabBytes + lr * 128;
-            const long n0 = n_base + g * 32 + lc;
-            // per-column data of this group: 1/Cj, threshold flags, mask bit position of each column
+            const long gs = n_base + g * 32;   // first column of the group
             float2 rcj[4];
-            uint32_t colbits = 0;   // bits 2*rep, 2*rep+1: Cj >= cthr; bits 8+4*rep..: hypercolumn offsets (2 bits each)
 #pragma unroll
-            for (int rep = 0; rep < 4; ++rep) {
-              const float2 cj = cj_next[rep];
-              rcj[rep] = make_float2(1.f / cj.x, 1.f / cj.y);   // correctly rounded, once per column pair and group
-              if (!(cj.x < ep.p.cthr)) colbits |= 1u << (2 * rep);
-              if (!(cj.y < ep.p.cthr)) colbits |= 2u << (2 * rep);
-              const long n = n0 + rep * 8;
-              if (ep.wmask && mask_fast && (interior || n < ep.cols)) {
-                colbits |= (uint32_t)(hc_of(n) - hc_first) << (8 + 4 * rep);
-                colbits |= (uint32_t)(hc_of(n + 1) - hc_first) << (10 + 4 * rep);
+            for (int rep = 0; rep < 4; ++rep) rcj[rep] = rcj_next[rep];
+            const float lane_rcj = lane_rcj_next;
+            if (g + 1 < NG) {   // the next group's values, in flight while this group is processed
+#pragma unroll
+              for (int rep = 0; rep < 4; ++rep) {
+                const long nn = gs + 32 + lc + rep * 8;
+                rcj_next[rep] = nn < ep.cols ? __ldg(reinterpret_cast<const float2 *>(ep.rcj + nn)) : make_float2(0.f, 0.f);
               }
-              // the next group's Cj, in flight while this group is processed
-              const long nn = n + 32;
-              cj_next[rep] = (g + 1 < NG && nn < ep.cols) ? __ldg(reinterpret_cast<const float2 *>(ep.Cj + nn)) : make_float2(1.f, 1.f);
+              lane_rcj_next = gs + 32 + lane < ep.cols ? __ldg(ep.rcj + gs + 32 + lane) : 0.f;
+            }
+            // Fast groups (whole block inside the matrix, at most two hypercolumns per group): one
+            // select word per row, bit 8*rep + e = "element e of column pair rep keeps its weight".
+            const bool g_fast = tile_fast && gs + 32 <= ep.cols;
+            uint32_t sel[4] = {0u, 0u, 0u, 0u};
+            if (g_fast) {
+              const uint32_t live32 = __ballot_sync(0xFFFFFFFFu, lane_rcj != 0.f);   // columns at or above the threshold
+              uint32_t first32 = 0xFFFFFFFFu;   // columns of the group's first hypercolumn
+              int k0 = 0;
+              if (has_mask) {
+                const int hc0 = hc_of(gs);
+                const long bnd = (long)(hc0 + 1) * ep.Mc - gs;
+                if (bnd < 32) first32 = (1u << bnd) - 1u;
+                k0 = hc0 - hc_first;
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t m0 = 0u - ((mbits[j] >> k0) & 1u), m1 = 0u - ((mbits[j] >> (k0 + 1)) & 1u);
+                const uint32_t word = ((m0 & first32) | (m1 & ~first32)) & live32;
+                sel[j] = rci[j] != 0.f ? (word >> lc) & 0x03030303u : 0u;
+              }
             }
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
               // 16 of the warp's 32 TMEM lanes at a time keeps the live registers within budget
               float a[16];
               __syncwarp();  // tcgen05.ld is warp-collective
-              tmem_ld_16x256b_x4(tmem_base + buf * BN + ch * (BN / 2) + g * 32 + ((uint32_t)(32 * q + 16 * hh) << 16), a);
+              tmem_ld_16x256b_x4(tacc + g * 32 + ((uint32_t)(16 * hh) << 16), a);
               float2 c[2][4];
 #pragma unroll
               for (int rr = 0; rr < 2; ++rr)
@@ -693,41 +693,67 @@ __global__ void __launch_bounds__(kThreads, 1)
                   else if (w + gridDim.x < total) issue_slab_at(slab + 2, mt_next, nt_next, g + 2 - NG);
                 }
               }
+              if (g_fast) {
 #pragma unroll
-              for (int rr = 0; rr < 2; ++rr) {
-                const int j = 2 * hh + rr;
-                if (!interior && !rv[j]) continue;
-                const bool row_on = row_live[j];
-                float *cp = crow[j] + g * 32;
+                for (int rr = 0; rr < 2; ++rr) {
+                  const int j = 2 * hh + rr;
+                  float *cp = crow[j] + g * 32;
+                  const float r = rci[j];
+                  const uint32_t sj = sel[j];
 #pragma unroll
-                for (int rep = 0; rep < 4; ++rep) {
-                  if (!interior && !(n0 + rep * 8 < ep.cols)) continue;
-                  float2 c2 = c[rr][rep];
-                  c2.x = fmaxf(fmaf(c2.x, ep.p.one_minus, a[rep * 4 + rr * 2 + 0] * ep.ema_scale), 0.f);
-                  c2.y = fmaxf(fmaf(c2.y, ep.p.one_minus, a[rep * 4 + rr * 2 + 1] * ep.ema_scale), 0.f);
-                  bool on0 = row_on && ((colbits >> (2 * rep)) & 1u), on1 = row_on && ((colbits >> (2 * rep + 1)) & 1u);
-                  if (mask_fast) {
-                    on0 = on0 && ((mbits[j] >> ((colbits >> (8 + 4 * rep)) & 3u)) & 1u);
-                    on1 = on1 && ((mbits[j] >> ((colbits >> (10 + 4 * rep)) & 3u)) & 1u);
-                  } else if (row_on) {
-                    const uint8_t *mr = ep.wmask + (ep.row0 + grow[j]) * ep.H;
-                    on0 = on0 && __ldg(mr + hc_of(n0 + rep * 8)) != 0;
-                    on1 = on1 && __ldg(mr + hc_of(n0 + rep * 8 + 1)) != 0;
+                  for (int rep = 0; rep < 4; ++rep) {
+                    float2 c2 = c[rr][rep];
+                    c2.x = fmaxf(fmaf(c2.x, ep.p.one_minus, a[rep * 4 + rr * 2 + 0] * ep.ema_scale), 0.f);
+                    c2.y = fmaxf(fmaf(c2.y, ep.p.one_minus, a[rep * 4 + rr * 2 + 1] * ep.ema_scale), 0.f);
+                    const float wx = lg2_ftz(fmaxf(c2.x, ep.p.cthr4) * (r * rcj[rep].x)) * kLn2;
+                    const float wy = lg2_ftz(fmaxf(c2.y, ep.p.cthr4) * (r * rcj[rep].y)) * kLn2;
+                    __stcs(reinterpret_cast<float2 *>(cp + rep * 8), c2);
+                    __stcs(reinterpret_cast<float2 *>(cp + w_minus_c + rep * 8),
+                           make_float2((sj & (1u << (8 * rep))) ? wx : 0.f, (sj & (2u << (8 * rep))) ? wy : 0.f));
                   }
-                  const float wx = __logf(fmaxf(c2.x, ep.p.cthr4) * (rci[j] * rcj[rep].x));
-                  const float wy = __logf(fmaxf(c2.y, ep.p.cthr4) * (rci[j] * rcj[rep].y));
-                  __stcs(reinterpret_cast<float2 *>(cp + rep * 8), c2);
-                  __stcs(reinterpret_cast<float2 *>(cp + w_minus_c + rep * 8), make_float2(on0 ? wx : 0.f, on1 ? wy : 0.f));
+                }
+              } else {
+                // edge blocks and layouts the select words do not cover: every element checked
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                  const int j = 2 * hh + rr;
+                  if (!rv[j]) continue;
+                  float *cp = crow[j] + g * 32;
+                  const uint8_t *mr = has_mask ? ep.wmask + (ep.row0 + grow[j]) * ep.H : nullptr;
+#pragma unroll
+                  for (int rep = 0; rep < 4; ++rep) {
+                    const long n = gs + lc + rep * 8;
+                    if (!(n < ep.cols)) continue;   // cols is even: n + 1 is in range too
+                    float2 c2 = c[rr][rep];
+                    c2.x = fmaxf(fmaf(c2.x, ep.p.one_minus, a[rep * 4 + rr * 2 + 0] * ep.ema_scale), 0.f);
+                    c2.y = fmaxf(fmaf(c2.y, ep.p.one_minus, a[rep * 4 + rr * 2 + 1] * ep.ema_scale), 0.f);
+                    bool on0 = rci[j] != 0.f && rcj[rep].x != 0.f, on1 = rci[j] != 0.f && rcj[rep].y != 0.f;
+                    if (has_mask) {
+                      const int h0 = hc_of(n), h1 = hc_of(n + 1);
+                      if (bits_ok) {
+                        on0 = on0 && ((mbits[j] >> (h0 - hc_first)) & 1u);
+                        on1 = on1 && ((mbits[j] >> (h1 - hc_first)) & 1u);
+                      } else {
+                        on0 = on0 && __ldg(mr + h0) != 0;
+                        on1 = on1 && __ldg(mr + h1) != 0;
+                      }
+                    }
+                    const float wx = __logf(fmaxf(c2.x, ep.p.cthr4) * (rci[j] * rcj[rep].x));
+                    const float wy = __logf(fmaxf(c2.y, ep.p.cthr4) * (rci[j] * rcj[rep].y));
+                    __stcs(reinterpret_cast<float2 *>(cp + rep * 8), c2);
+                    __stcs(reinterpret_cast<float2 *>(cp + w_minus_c + rep * 8), make_float2(on0 ? wx : 0.f, on1 ? wy : 0.f));
+                  }
                 }
               }
             }
             ++slab;
+            if (threadIdx.x == kConvWarps * 32 && g < 3) TC_TRACE(chain, 13 + g);
           }
         } else {
 #pragma unroll 1
           for (int g = 0; g < NG; ++g) {
             float a0[16], a1[16];
-            const uint32_t t0 = tmem_base + buf * BN + ch * (BN / 2) + g * 32 + ((uint32_t)(32 * q) << 16);
+            const uint32_t t0 = tacc + g * 32;
             __syncwarp();  // tcgen05.ld is warp-collective
             tmem_ld_pair(t0, t0 + (16u << 16), a0, a1);
             const long n0 = n_base + g * 32 + lc;
@@ -863,12 +889,6 @@ cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, 
   const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
   if (total <= 0) return cudaSuccess;
   const unsigned grid = (unsigned)(total < g_sm_count_tc[dev] ? total : g_sm_count_tc[dev]);
-#ifdef SBB_TC_TRACE
-  TcWork wk2 = wk;
-  if (const char *v = getenv("SBB_TC_VARIANT")) wk2.variant = atoi(v);
-  kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, wk2, ep, status);
-  return cudaGetLastError();
-#endif
   kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, wk, ep, status);
   return cudaGetLastError();
 }
@@ -932,7 +952,7 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, kFwdBN / 32);
   if (!b3) tm.b3 = tm.b;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
-            b3 ? full_chunk_tiles(M, kFwdBN) : 0, 0};
+            b3 ? full_chunk_tiles(M, kFwdBN) : 0};
   TcEpilogue ep{};
   ep.out = partial;
   ep.rows = B;
@@ -953,9 +973,31 @@ static uint32_t exact_division_magic(long d, long limit) {
   return (uint32_t)magic;
 }
 
+namespace {
+// out = C < cthr ? 0 : 1 / C  for rows [row_begin, row_end) of Ci and every column of Cj: the
+// epilogue multiplies by these and reads "below the threshold" off the zero.
+__global__ void trace_reciprocals_kernel(const float *__restrict__ Ci, long row_begin, long row_end,
+                                         const float *__restrict__ Cj, long M, float cthr, float *__restrict__ rci,
+                                         float *__restrict__ rcj) {
+  const long rows = row_end - row_begin;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < rows + M; t += (long)gridDim.x * blockDim.x) {
+    if (t < rows) {
+      const float c = Ci[row_begin + t];
+      rci[row_begin + t] = c < cthr ? 0.f : 1.f / c;
+    } else {
+      const float c = Cj[t - rows];
+      rcj[t - rows] = c < cthr ? 0.f : 1.f / c;
+    }
+  }
+}
+}  // namespace
+
+size_t tc_trace_scratch_bytes(long N, long M) { return (size_t)(((N + 3) / 4) * 4 + M + 4) * sizeof(float); }
+
 cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long N, long M, long H, const float *Ci,
                                    const float *Cj, float *Cij, float *w, const uint8_t *wmask, const int *col_hc,
-                                   TraceParams<float> p, long row_begin, long row_end, cudaStream_t st) {
+                                   float *scratch, TraceParams<float> p, long row_begin, long row_end,
+                                   cudaStream_t st) {
   static long magic_for_mc = -1, magic_for_m = -1;
   static uint32_t magic_value = 0;
   uint32_t hc_magic = 0;
@@ -970,7 +1012,8 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   }
   if (!tc_available() || !tc_shape_ok(x, y, N, M) || row_begin % 128 != 0) return cudaErrorNotSupported;
   if ((reinterpret_cast<uintptr_t>(Cij) & 7u) || (reinterpret_cast<uintptr_t>(w) & 7u) ||
-      (reinterpret_cast<uintptr_t>(Cj) & 7u) || (wmask && (col_hc == nullptr || (reinterpret_cast<uintptr_t>(col_hc) & 7u))))
+      scratch == nullptr || (reinterpret_cast<uintptr_t>(scratch) & 15u) ||
+      (wmask && (col_hc == nullptr || (reinterpret_cast<uintptr_t>(col_hc) & 7u))))
     return cudaErrorNotSupported;
   if (row_end <= row_begin) return cudaSuccess;
   TcMaps tm;
@@ -983,18 +1026,29 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
+            b3 ? full_chunk_tiles(M, kTrBN) : 0};
   TcEpilogue ep{};
   ep.rows = rows;
   ep.cols = M;
-  ep.Ci = Ci;
-  ep.Cj = Cj;
+  float *rci = scratch, *rcj = scratch + ((N + 3) / 4) * 4;
+  {
+    const long n = rows + M;
+    const unsigned blocks = (unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+    trace_reciprocals_kernel<<<blocks, 256, 0, st>>>(Ci, row_begin, row_end, Cj, M, p.cthr, rci, rcj);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    count_launches(1);
+  }
+  ep.rci = rci;
+  ep.rcj = rcj;
   ep.Cij = Cij;
   ep.W = w;
   ep.wmask = wmask;
   ep.col_hc = col_hc;
   ep.hc_magic = hc_magic;
   ep.H = H;
+  ep.Mc = H > 0 ? M / H : M;
+  ep.fast_ok = (wmask == nullptr || ep.Mc >= 32) && p.cthr4 >= 1e-30f;
   ep.row0 = row_begin;
   ep.p = p;
   ep.ema_scale = p.taupdt / p.batch;
@@ -1019,7 +1073,7 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
+            b3 ? full_chunk_tiles(M, kTrBN) : 0};
   TcEpilogue ep{};
   ep.out = delta + row_begin * M;
   ep.rows = rows;
