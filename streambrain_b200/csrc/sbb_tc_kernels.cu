@@ -6,13 +6,14 @@
 //   trace update   D[i, j] = sum_b x[b, i] * y[b, j]   A = x  (MN-major), B = y (MN-major), K = batch
 //   forward        D[b, j] = sum_k x[b, k] * w[k, j]   A = x  (K-major),  B = w (MN-major), K = in_features
 //
-// float32 accuracy on TF32 tensor cores: every operand value v is split in
-// shared memory into hi = tf32(v) (round to nearest) and lo = v - hi, and each
-// k-step issues three MMAs  hi*hi + hi*lo + lo*hi  into one float32 accumulator
-// in tensor memory (the dropped lo*lo term is below 2^-22 relative).
+// float32 accuracy on TF32 tensor cores: every operand value v is used as
+// hi = v truncated to TF32 (what the tensor core reads of the raw float32) and
+// lo = tf32(v - hi), written beside it in shared memory, and each k-step issues
+// three MMAs  hi*hi + hi*lo + lo*hi  into one float32 accumulator in tensor
+// memory (the dropped lo*lo term is below 2^-20 relative).
 //
 // Roles inside a CTA (448 threads, one CTA per SM, tiles walked persistently):
-//   warps 0-3   converters: wait for a TMA stage, write hi in place and lo beside it
+//   warps 0-3   converters: wait for a TMA stage, write the lo parts beside it
 //   warps 4-11  epilogue: tcgen05.ld the accumulator (16x256b shape, so that four
 //               lanes cover 32 contiguous bytes of a row) and either store it or run
 //               the trace / weight arithmetic against 32 x 32 blocks of Cij that TMA
@@ -215,12 +216,16 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr, uint32_t lbo_by
   return smem_desc(saddr, lbo_bytes, 512u, 1u);       // MN-major, SWIZZLE_128B_BASE32B
 }
 
-// Rounds v to the 11 significant bits of TF32 (Veltkamp split with 2^13 + 1; ties to even) on the
-// FMA pipe: the conversion instruction runs on the quarter-rate pipe the logarithms need.  The
-// low 13 bits of the result are zero and v - tf32_rn(v) is exact.  |v| >= 2^114 overflows to NaN.
-__device__ __forceinline__ float tf32_rn(float v) {
-  const float c = __fmul_rn(v, 8193.f);
-  return __fsub_rn(c, __fsub_rn(c, v));
+// The "lo" part of v for the split product.  The tensor core reads only the upper 19 bits of a
+// 32-bit TF32 operand, so the untouched value already acts as hi = v truncated to TF32 and only
+// lo = v - hi (exact) has to be produced; it is rounded to the 11 significant bits of TF32
+// (Veltkamp split with 2^13 + 1, all on the FMA pipe), so that what the tensor core drops of it
+// is zero.  hi + lo then differs from v by at most 2^-22 |v|.  Inf / NaN give a NaN lo.
+__device__ __forceinline__ float tf32_lo(float v) {
+  const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+  const float lo = __fsub_rn(v, hi);
+  const float c = __fmul_rn(lo, 8193.f);
+  return __fsub_rn(c, __fsub_rn(c, lo));
 }
 
 #ifdef SBB_TC_TRACE
@@ -240,7 +245,7 @@ template <int BN, int BK, int STAGES, bool FUSED>
 struct TcSmem {
   static constexpr int A_BYTES = 128 * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
-  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // TMA landing zone (becomes "hi" in place)
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // TMA landing zone: the raw values serve as "hi"
   static constexpr int STAGE_BYTES = 2 * RAW_BYTES;    // + the "lo" copy
   static constexpr int SLAB_OFFSET = STAGES * STAGE_BYTES;
   // fused epilogue: two landing buffers per epilogue warp for blocks of the trace matrix
@@ -472,15 +477,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (threadIdx.x == 0 && kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 9);
         float4 *raw = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES);
         float4 *lo = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
-#pragma unroll 4
-        for (int c = threadIdx.x; c < SM::RAW_BYTES / 16; c += kConvWarps * 32) {
-          const float4 v = raw[c];
-          float4 h, l;
-          h.x = tf32_rn(v.x); h.y = tf32_rn(v.y); h.z = tf32_rn(v.z); h.w = tf32_rn(v.w);
-          l.x = __fsub_rn(v.x, h.x); l.y = __fsub_rn(v.y, h.y); l.z = __fsub_rn(v.z, h.z); l.w = __fsub_rn(v.w, h.w);
-          raw[c] = h;
-          lo[c] = l;
-        }
+        // Every load of the stage is issued before the first store (registers are plentiful
+        // here): the hand-off to the MMA warp costs one shared-memory round trip, not one per piece.
+        constexpr int kPieces = SM::RAW_BYTES / 16 / (kConvWarps * 32);
+        static_assert(SM::RAW_BYTES % (16 * kConvWarps * 32) == 0, "a stage is a whole number of 16-byte pieces per thread");
+        float4 v[kPieces];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) v[i] = raw[threadIdx.x + i * (kConvWarps * 32)];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i)
+          lo[threadIdx.x + i * (kConvWarps * 32)] =
+              make_float4(tf32_lo(v[i].x), tf32_lo(v[i].y), tf32_lo(v[i].z), tf32_lo(v[i].w));
         fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
         mbar_arrive(bar_conv(s));
       }
