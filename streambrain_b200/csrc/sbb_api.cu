@@ -216,9 +216,7 @@ int layer_finish(sbb_layer *L, long h, cudaStream_t st) {
     // which is a function of the traces alone; the masked weights already written
     // for hypercolumn h are then rewritten under the updated mask.
     SBB_CUDA(sbb::launch_mask_update<T>(wmask, nullptr, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h,
-                                        L->desc.mask_iterations, L->score.d, st));
-    SBB_CUDA(sbb::launch_rewrite_hypercolumn<T>(W, wmask, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, L->score.d,
-                                                st));
+                                        L->desc.mask_iterations, L->score.d, st, W));
   }
   return SBB_OK;
 }

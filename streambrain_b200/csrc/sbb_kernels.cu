@@ -818,15 +818,25 @@ __global__ void __launch_bounds__(256)
   const T pi = Ci[i];
   double s = 0.0;
   if (pi >= cthr) {
-    for (long jj = lane; jj < Mc; jj += 32) {
-      const long col = h * Mc + jj;
-      const T pj = Cj[col];
-      if (pj >= cthr) {
-        const T pij = Cij[i * M + col];
-        const T w = weights ? weights[i * M + col] : log_ratio(pij, pi, pj, cthr4);
-        const T x = ((T)1 - pi) * pj;
-        const T y = (pj - pij) / x;
-        s += (double)(pij * w + (pj - pij) * sbb_log(y));
+    // four strided elements per lane at a time, all loads issued before the arithmetic
+    for (long j0 = 0; j0 < Mc; j0 += 128) {
+      T pj[4], pij[4], wv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long jj = j0 + lane + 32 * u, col = h * Mc + jj;
+        const bool in = jj < Mc;
+        pj[u] = in ? Cj[col] : (T)0;
+        pij[u] = in ? Cij[i * M + col] : (T)0;
+        wv[u] = (in && weights) ? weights[i * M + col] : (T)0;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (j0 + lane + 32 * u < Mc && pj[u] >= cthr) {
+          const T w = weights ? wv[u] : log_ratio(pij[u], pi, pj[u], cthr4);
+          const T x = ((T)1 - pi) * pj[u];
+          const T y = (pj[u] - pij[u]) / x;
+          s += (double)(pij[u] * w + (pj[u] - pij[u]) * sbb_log(y));
+        }
       }
     }
   }
@@ -877,8 +887,10 @@ __device__ __forceinline__ Pick<T> shfl_pick(Pick<T> p, int off) {
 // class (a scan never replaces its holder with a NaN, nor a NaN holder at all).
 template <typename T>
 __global__ void __launch_bounds__(1024)
-    mask_swap_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long H, long h, long iterations,
-                     const int *__restrict__ run_flag) {
+    mask_swap_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long M, long H, long Mc, long h,
+                     long iterations, const int *__restrict__ run_flag, T *rewrite_w,
+                     const uint8_t *__restrict__ old_col, const T *__restrict__ Ci, const T *__restrict__ Cj,
+                     const T *__restrict__ Cij, T cthr, T cthr4) {
   __shared__ Pick<T> s_max[32], s_min[32];
   if (run_flag != nullptr && *run_flag == 0) return;   // the candidate-list path already did this update
   __shared__ long s_first0[32], s_first1[32];
@@ -946,6 +958,20 @@ __global__ void __launch_bounds__(1024)
     __syncthreads();
     if (s_done) break;
   }
+  if (rewrite_w == nullptr) return;
+  // rows whose mask bit changed get new weights in hypercolumn h (at most 2 * iterations rows)
+  for (long j = threadIdx.x; j < N; j += blockDim.x) {
+    const uint8_t now = wmask[j * H + h];
+    if (now == old_col[j]) continue;
+    const T ci = Ci[j];
+    for (long jj = 0; jj < Mc; ++jj) {
+      const long col = h * Mc + jj;
+      const T cj = Cj[col];
+      T v = (T)0;
+      if (now != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[j * M + col], ci, cj, cthr4);
+      rewrite_w[j * M + col] = v;
+    }
+  }
 }
 
 // ---- fast swap: per-chunk candidate lists, then a short exact simulation -------------------
@@ -953,27 +979,73 @@ __global__ void __launch_bounds__(1024)
 // among the t+1 best of its class in the initial ordering or a row moved by an earlier swap.
 // Phase A extracts, per chunk of rows, the `iterations` best silent rows (highest score, ties
 // to the larger index) and the `iterations` worst active rows (lowest score, ties to the
-// larger index); phase B merges them and replays the swaps exactly.  A NaN score makes the
-// reference's scan order-dependent; phase A then raises a flag and the one-CTA full scan
-// (mask_swap_kernel) runs instead.
+// larger index); phase B reduces the chunk lists to one list per class and replays the swaps
+// exactly.  A NaN score makes the reference's scan order-dependent; phase A then raises a flag
+// and the one-CTA full scan (mask_swap_kernel) runs instead.
+//
+// Every selection is "K rounds of arg-best over entries that come strictly after the previous
+// pick in the class order", done by single warps with shuffles: no block barrier inside a round.
 constexpr int kSwapMaxIter = 32;
-constexpr int kSwapSlots = 768;           // list slots per class in the replay kernel (static shared memory budget)
+constexpr int kSwapSlots = 768;           // candidate slots per class handed from phase A to phase B
 constexpr int kSwapCacheRows = 4096;      // rows per chunk whose score and class fit the chunk's shared memory
+constexpr int kSwapThreads = 256;         // both phases: 8 warps = 2 classes x 4 slices
 
 template <typename T>
 __device__ __forceinline__ T swap_score(T nom, int csum) {
   return (T)((double)nom / (1.0 + (double)csum));
 }
 
+// Class order: silent rows (cls 0) by score descending, active rows (cls 1) ascending; equal
+// scores by index descending (the reference's scans keep the last of equals).
+template <typename T>
+__device__ __forceinline__ bool comes_after(int cls, T v, long i, const Pick<T> &prev) {
+  if (prev.i < 0) return true;
+  return cls == 0 ? (v < prev.v || (v == prev.v && i < prev.i)) : (v > prev.v || (v == prev.v && i < prev.i));
+}
+template <typename T>
+__device__ __forceinline__ Pick<T> warp_pick(Pick<T> best, int cls) {
+  for (int off = 16; off > 0; off >>= 1)
+    best = cls == 0 ? pick_max(best, shfl_pick(best, off)) : pick_min(best, shfl_pick(best, off));
+  return best;
+}
+// One warp: the first `rounds` entries of (v[e], i[e]), e in [0, n), in class order -> out_v/out_i
+// (index -1 pads the tail).  i[e] < 0 marks an empty entry.
+template <typename T>
+__device__ __forceinline__ void warp_select(int cls, const T *v, const long *i, int n, int rounds, T *out_v,
+                                            long *out_i) {
+  const int lane = threadIdx.x & 31;
+  Pick<T> prev{(T)0, -1};
+  for (int k = 0; k < rounds; ++k) {
+    Pick<T> best{(T)0, -1};
+    for (int e = lane; e < n; e += 32) {
+      const long idx = i[e];
+      if (idx < 0) continue;
+      const T val = v[e];
+      if (!comes_after(cls, val, idx, prev)) continue;
+      best = cls == 0 ? pick_max(best, Pick<T>{val, idx}) : pick_min(best, Pick<T>{val, idx});
+    }
+    best = warp_pick(best, cls);
+    if (lane == 0) {
+      out_v[k] = best.v;
+      out_i[k] = best.i;
+    }
+    if (best.i < 0) {   // exhausted: the remaining slots are empty
+      for (int kk = k + 1 + lane; kk < rounds; kk += 32) out_i[kk] = -1;
+      break;
+    }
+    prev = best;
+  }
+}
+
 // lists: [class][chunk][iterations] of (value, index); index -1 = empty.
 // CACHED: the chunk's scores and classes are kept in shared memory for the rounds.
 template <typename T, bool CACHED>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kSwapThreads)
     mask_candidates_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ nom, const int *__restrict__ csum,
                            long N, long H, long h, int iterations, long rows_per_chunk, T *cand_v, long *cand_i,
                            int *nan_flag) {
-  __shared__ Pick<T> s_pick[8];
-  __shared__ Pick<T> s_prev;
+  __shared__ T s_lv[2][4][kSwapMaxIter];
+  __shared__ long s_li[2][4][kSwapMaxIter];
   extern __shared__ __align__(16) unsigned char cand_dyn[];
   T *s_sc = reinterpret_cast<T *>(cand_dyn);
   uint8_t *s_cl = cand_dyn + (CACHED ? rows_per_chunk * sizeof(T) : 0);
@@ -992,11 +1064,15 @@ __global__ void __launch_bounds__(256)
     }
     __syncthreads();
   }
-  for (int cls = 0; cls < 2; ++cls) {
+  // level 1: warp (cls, slice) lists the first `iterations` rows of its class in its quarter of the chunk
+  const int cls = wid & 1, slice = wid >> 1;
+  {
+    const long len = r1 - r0, q = (len + 3) / 4;
+    const long b = r0 + slice * q, e = b + q < r1 ? b + q : r1;
     Pick<T> prev{(T)0, -1};
     for (int k = 0; k < iterations; ++k) {
       Pick<T> best{(T)0, -1};
-      for (long j = r0 + threadIdx.x; j < r1; j += blockDim.x) {
+      for (long j = b + lane; j < e; j += 32) {
         T sc;
         if (CACHED) {
           if (s_cl[j - r0] != cls) continue;
@@ -1006,122 +1082,131 @@ __global__ void __launch_bounds__(256)
           sc = swap_score(nom[j], csum[j]);
           if (sc != sc) { saw_nan = true; continue; }
         }
-        // eligible: strictly after the previous pick in this class's order
-        bool after = prev.i < 0;
-        if (!after)
-          after = cls == 0 ? (sc < prev.v || (sc == prev.v && j < prev.i)) : (sc > prev.v || (sc == prev.v && j < prev.i));
-        if (!after) continue;
+        if (!comes_after(cls, sc, j, prev)) continue;
         best = cls == 0 ? pick_max(best, Pick<T>{sc, j}) : pick_min(best, Pick<T>{sc, j});
       }
-      for (int off = 16; off > 0; off >>= 1)
-        best = cls == 0 ? pick_max(best, shfl_pick(best, off)) : pick_min(best, shfl_pick(best, off));
-      if (lane == 0) s_pick[wid] = best;
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        for (int w = 1; w < 8; ++w) best = cls == 0 ? pick_max(best, s_pick[w]) : pick_min(best, s_pick[w]);
-        s_prev = best;
-        const long slot = ((long)cls * gridDim.x + blockIdx.x) * iterations + k;
-        cand_v[slot] = best.v;
-        cand_i[slot] = best.i;
+      best = warp_pick(best, cls);
+      if (lane == 0) {
+        s_lv[cls][slice][k] = best.v;
+        s_li[cls][slice][k] = best.i;
       }
-      __syncthreads();
-      prev = s_prev;
-      if (prev.i < 0) {   // class exhausted in this chunk: the remaining slots are empty
-        for (int kk = k + 1 + threadIdx.x; kk < iterations; kk += blockDim.x)
-          cand_i[((long)cls * gridDim.x + blockIdx.x) * iterations + kk] = -1;
+      if (best.i < 0) {
+        for (int kk = k + 1 + lane; kk < iterations; kk += 32) s_li[cls][slice][kk] = -1;
         break;
       }
+      prev = best;
     }
-    __syncthreads();
+  }
+  __syncthreads();
+  // level 2: one warp per class merges the four slice lists into the chunk's list
+  if (wid < 2) {
+    // the four lists are contiguous only when iterations == kSwapMaxIter: compact them first
+    __shared__ T m_v[2][4 * kSwapMaxIter];
+    __shared__ long m_i[2][4 * kSwapMaxIter];
+    for (int e = lane; e < 4 * iterations; e += 32) {
+      m_v[wid][e] = s_lv[wid][e / iterations][e % iterations];
+      m_i[wid][e] = s_li[wid][e / iterations][e % iterations];
+    }
+    __syncwarp();
+    const long slot = ((long)wid * gridDim.x + blockIdx.x) * iterations;
+    warp_select<T>(wid, m_v[wid], m_i[wid], 4 * iterations, iterations, cand_v + slot, cand_i + slot);
   }
   if (saw_nan) atomicOr(nan_flag, 1);
 }
 
+// Phase B, one CTA: reduce the chunk lists to the first `iterations` rows of each class, replay
+// the swaps on them (warp 0; every lane keeps one listed row and one moved row per class), then
+// rewrite the weights of hypercolumn h for the rows a swap touched (rewrite_w != null).
 template <typename T>
-struct Slot {
-  T v;
-  long i;
-  int s;  // list slot, -1 = empty
-};
-template <typename T>
-__device__ __forceinline__ Slot<T> slot_best(Slot<T> a, Slot<T> b, bool want_max) {
-  if (b.s < 0) return a;
-  if (a.s < 0) return b;
-  const bool take = want_max ? (b.v > a.v || (b.v == a.v && b.i > a.i)) : (b.v < a.v || (b.v == a.v && b.i > a.i));
-  return take ? b : a;
-}
-template <typename T>
-__device__ __forceinline__ Slot<T> warp_best(Slot<T> mine, bool want_max) {
-  for (int off = 16; off > 0; off >>= 1) {
-    Slot<T> o;
-    o.v = __shfl_xor_sync(0xffffffffu, mine.v, off);
-    o.i = __shfl_xor_sync(0xffffffffu, mine.i, off);
-    o.s = __shfl_xor_sync(0xffffffffu, mine.s, off);
-    mine = slot_best(mine, o, want_max);
-  }
-  return mine;
-}
-// Best entry over the whole block (all threads get it); s_red holds 33 entries.
-template <typename T>
-__device__ __forceinline__ Slot<T> block_best(Slot<T> mine, bool want_max, Slot<T> *s_red) {
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  mine = warp_best(mine, want_max);
+__global__ void __launch_bounds__(kSwapThreads)
+    mask_replay_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long M, long H, long Mc, long h,
+                       int iterations, int chunks, const T *__restrict__ cand_v, const long *__restrict__ cand_i,
+                       const int *__restrict__ nan_flag, T *rewrite_w, const T *__restrict__ Ci,
+                       const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr, T cthr4) {
+  __shared__ T e_v[2][kSwapSlots];
+  __shared__ long e_i[2][kSwapSlots];
+  __shared__ T l1_v[2][4 * kSwapMaxIter], top_v[2][kSwapMaxIter];
+  __shared__ long l1_i[2][4 * kSwapMaxIter], top_i[2][kSwapMaxIter];
+  __shared__ long touched[2 * kSwapMaxIter];
+  __shared__ int n_touched;
+  if (*nan_flag) return;   // the full scan handles this update
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int total = chunks * iterations;   // entries per class, <= kSwapSlots
+  for (int c = 0; c < 2; ++c)
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+      e_i[c][e] = cand_i[(long)c * total + e];
+      e_v[c][e] = cand_v[(long)c * total + e];
+    }
+  if (threadIdx.x == 0) n_touched = 0;
   __syncthreads();
-  if (lane == 0) s_red[wid] = mine;
+  {
+    const int cls = wid & 1, slice = wid >> 1;
+    const int q = (total + 3) / 4, b = slice * q, n = b + q <= total ? q : (total > b ? total - b : 0);
+    warp_select<T>(cls, e_v[cls] + b, e_i[cls] + b, n, iterations, l1_v[cls] + slice * iterations,
+                   l1_i[cls] + slice * iterations);
+  }
+  __syncthreads();
+  if (wid < 2) warp_select<T>(wid, l1_v[wid], l1_i[wid], 4 * iterations, iterations, top_v[wid], top_i[wid]);
   __syncthreads();
   if (wid == 0) {
-    Slot<T> x = lane < nw ? s_red[lane] : Slot<T>{(T)0, -1, -1};
-    x = warp_best(x, want_max);
-    if (lane == 0) s_red[32] = x;
-  }
-  __syncthreads();
-  return s_red[32];
-}
-
-template <typename T>
-__global__ void __launch_bounds__(kSwapSlots)
-    mask_replay_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long H, long h, int iterations,
-                       int chunks, const T *__restrict__ cand_v, const long *__restrict__ cand_i,
-                       const int *__restrict__ nan_flag) {
-  __shared__ T lv[2][kSwapSlots], lnom[2][kSwapSlots];
-  __shared__ long li[2][kSwapSlots];
-  __shared__ int lcs[2][kSwapSlots];
-  __shared__ Slot<T> s_red[33];
-  if (*nan_flag) return;   // the full scan handles this update
-  const int base = chunks * iterations;   // first slot for rows moved by a swap
-  const int t = threadIdx.x;
-  for (int cls = 0; cls < 2; ++cls) {
-    const long i = t < base ? cand_i[(long)cls * base + t] : -1;
-    li[cls][t] = i;
-    lv[cls][t] = i >= 0 ? cand_v[(long)cls * base + t] : (T)0;
-    lnom[cls][t] = i >= 0 ? nom[i] : (T)0;
-    lcs[cls][t] = i >= 0 ? csum[i] : 0;
-  }
-  __syncthreads();
-  for (int it = 0; it < iterations; ++it) {
-    const Slot<T> s0 = block_best(Slot<T>{lv[0][t], li[0][t], li[0][t] >= 0 ? t : -1}, true, s_red);
-    const Slot<T> a1 = block_best(Slot<T>{lv[1][t], li[1][t], li[1][t] >= 0 ? t : -1}, false, s_red);
-    if (s0.s < 0 || a1.s < 0 || s0.v < a1.v) break;   // uniform: every thread holds the same picks
-    if (t == 0) {
-      // the moved rows join the other class with their new counts
-      const int cs_up = lcs[0][s0.s] + 1, cs_down = lcs[1][a1.s] - 1;
-      const T nom_up = lnom[0][s0.s], nom_down = lnom[1][a1.s];
-      wmask[s0.i * H + h] = 1;
-      wmask[a1.i * H + h] = 0;
-      csum[s0.i] = cs_up;
-      csum[a1.i] = cs_down;
-      li[0][s0.s] = -1;
-      li[1][a1.s] = -1;
-      li[1][base + it] = s0.i;
-      lnom[1][base + it] = nom_up;
-      lcs[1][base + it] = cs_up;
-      lv[1][base + it] = swap_score(nom_up, cs_up);
-      li[0][base + it] = a1.i;
-      lnom[0][base + it] = nom_down;
-      lcs[0][base + it] = cs_down;
-      lv[0][base + it] = swap_score(nom_down, cs_down);
+    // slot A of a lane: listed row number `lane` of the class; slot B: the row moved into the class by swap `lane`
+    long ia[2], ib[2] = {-1, -1};
+    T va[2], vb[2] = {(T)0, (T)0}, na[2], nb[2] = {(T)0, (T)0};
+    int ca[2], cb[2] = {0, 0};
+    for (int c = 0; c < 2; ++c) {
+      ia[c] = lane < iterations ? top_i[c][lane] : -1;
+      va[c] = ia[c] >= 0 ? top_v[c][lane] : (T)0;
+      na[c] = ia[c] >= 0 ? nom[ia[c]] : (T)0;
+      ca[c] = ia[c] >= 0 ? csum[ia[c]] : 0;
     }
-    __syncthreads();
+    for (int it = 0; it < iterations; ++it) {
+      // best silent row (cls 0: maximum) and worst active row (cls 1: minimum) over both slots of every lane
+      Pick<T> p[2];
+      for (int c = 0; c < 2; ++c) {
+        Pick<T> mine{va[c], ia[c]};
+        const Pick<T> other{vb[c], ib[c]};
+        mine = c == 0 ? pick_max(mine, other) : pick_min(mine, other);
+        p[c] = warp_pick(mine, c);
+      }
+      if (p[0].i < 0 || p[1].i < 0 || p[0].v < p[1].v) break;   // uniform across the warp
+      // owners hand over the moved rows' numerators and counts, and drop the rows from their class
+      T mv_nom[2];
+      int mv_cs[2];
+      for (int c = 0; c < 2; ++c) {
+        const bool own_a = ia[c] == p[c].i, own_b = ib[c] == p[c].i;
+        const unsigned who = __ballot_sync(0xffffffffu, own_a || own_b);
+        const int src = __ffs(who) - 1;
+        const T my_nom = own_a ? na[c] : nb[c];
+        const int my_cs = own_a ? ca[c] : cb[c];
+        mv_nom[c] = __shfl_sync(0xffffffffu, my_nom, src);
+        mv_cs[c] = __shfl_sync(0xffffffffu, my_cs, src);
+        if (own_a) ia[c] = -1;
+        if (own_b) ib[c] = -1;
+      }
+      if (lane == it) {
+        // the silent row becomes active with one more connection, the active row silent with one fewer
+        ib[1] = p[0].i; nb[1] = mv_nom[0]; cb[1] = mv_cs[0] + 1; vb[1] = swap_score(nb[1], cb[1]);
+        ib[0] = p[1].i; nb[0] = mv_nom[1]; cb[0] = mv_cs[1] - 1; vb[0] = swap_score(nb[0], cb[0]);
+        wmask[p[0].i * H + h] = 1;
+        wmask[p[1].i * H + h] = 0;
+        csum[p[0].i] = cb[1];
+        csum[p[1].i] = cb[0];
+        touched[2 * it] = p[0].i;
+        touched[2 * it + 1] = p[1].i;
+        n_touched = 2 * it + 2;
+      }
+    }
+  }
+  __syncthreads();
+  if (rewrite_w == nullptr) return;
+  // a touched row's weights in hypercolumn h follow its final mask bit (idempotent when a row was touched twice)
+  const int nt = n_touched;
+  for (long t = threadIdx.x; t < (long)nt * Mc; t += blockDim.x) {
+    const long i = touched[t / Mc], col = h * Mc + t % Mc;
+    const T ci = Ci[i], cj = Cj[col];
+    T v = (T)0;
+    if (wmask[i * H + h] != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[i * M + col], ci, cj, cthr4);
+    rewrite_w[i * M + col] = v;
   }
 }
 
@@ -1158,7 +1243,7 @@ struct MaskScratch {
 template <typename T>
 cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
                                long N, long M, long H, long Mc, long h, long iterations, void *scratch,
-                               cudaStream_t st) {
+                               cudaStream_t st, T *rewrite_w) {
   if (N == 0) return cudaSuccess;
   MaskScratch<T> ms(scratch, N);
   const T cthr4 = cthr * cthr * cthr * cthr;
@@ -1166,8 +1251,9 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
                                                                  h, ms.score, ms.csum, ms.old_col);
   cudaError_t e = launched();
   if (e != cudaSuccess) return e;
+  const int *run_flag = nullptr;
   if (iterations >= 1 && iterations <= kSwapMaxIter && N >= 4096) {
-    const int max_chunks = (kSwapSlots - (int)iterations) / (int)iterations;
+    const int max_chunks = kSwapSlots / (int)iterations;
     int chunks = (int)((N + 1023) / 1024);
     if (chunks > max_chunks) chunks = max_chunks;
     const long rows_per_chunk = (N + chunks - 1) / chunks;
@@ -1175,68 +1261,31 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
     e = cudaMemsetAsync(ms.nan_flag, 0, sizeof(int), st);
     if (e != cudaSuccess) return e;
     if (rows_per_chunk <= kSwapCacheRows)
-      mask_candidates_kernel<T, true><<<chunks, 256, (size_t)rows_per_chunk * (sizeof(T) + 1), st>>>(
+      mask_candidates_kernel<T, true><<<chunks, kSwapThreads, (size_t)rows_per_chunk * (sizeof(T) + 1), st>>>(
           wmask, ms.score, ms.csum, N, H, h, (int)iterations, rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag);
     else
-      mask_candidates_kernel<T, false><<<chunks, 256, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, (int)iterations,
-                                                               rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag);
+      mask_candidates_kernel<T, false><<<chunks, kSwapThreads, 0, st>>>(
+          wmask, ms.score, ms.csum, N, H, h, (int)iterations, rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag);
     e = launched();
     if (e != cudaSuccess) return e;
-    mask_replay_kernel<T><<<1, kSwapSlots, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, (int)iterations, chunks,
-                                                    ms.cand_v, ms.cand_i, ms.nan_flag);
+    mask_replay_kernel<T><<<1, kSwapThreads, 0, st>>>(wmask, ms.score, ms.csum, N, M, H, Mc, h, (int)iterations, chunks,
+                                                     ms.cand_v, ms.cand_i, ms.nan_flag, rewrite_w, Ci, Cj, Cij, cthr,
+                                                     cthr4);
     e = launched();
     if (e != cudaSuccess) return e;
-    mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, iterations, ms.nan_flag);
-    return launched();
+    run_flag = ms.nan_flag;   // the full scan below only runs when a NaN score was seen
   }
-  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, ms.score, ms.csum, N, H, h, iterations, nullptr);
+  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, ms.score, ms.csum, N, M, H, Mc, h, iterations, run_flag, rewrite_w,
+                                          ms.old_col, Ci, Cj, Cij, cthr, cthr4);
   return launched();
 }
 template cudaError_t launch_mask_update<float>(uint8_t *, const float *, const float *, const float *, const float *,
-                                               float, long, long, long, long, long, long, void *, cudaStream_t);
+                                               float, long, long, long, long, long, long, void *, cudaStream_t,
+                                               float *);
 template cudaError_t launch_mask_update<double>(uint8_t *, const double *, const double *, const double *,
                                                 const double *, double, long, long, long, long, long, long, void *,
-                                                cudaStream_t);
+                                                cudaStream_t, double *);
 
-// After the swaps only the rows whose mask bit changed need new weights in hypercolumn h:
-// the trace step already wrote every other row of the block under the (unchanged) old mask.
-// One warp per row compares the row's old and new mask bit.
-template <typename T>
-__global__ void __launch_bounds__(256)
-    rewrite_changed_rows_kernel(T *w, const uint8_t *__restrict__ wmask, const uint8_t *__restrict__ old_col,
-                                const T *__restrict__ Ci, const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr,
-                                T cthr4, long N, long M, long H, long Mc, long h) {
-  const int lane = threadIdx.x & 31;
-  const long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (i >= N) return;
-  const uint8_t now = wmask[i * H + h];
-  if (now == old_col[i]) return;
-  const T ci = Ci[i];
-  for (long jj = lane; jj < Mc; jj += 32) {
-    const long col = h * Mc + jj;
-    const T cj = Cj[col];
-    T v = (T)0;
-    if (now != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[i * M + col], ci, cj, cthr4);
-    w[i * M + col] = v;
-  }
-}
-template <typename T>
-cudaError_t launch_rewrite_hypercolumn(T *w, const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr,
-                                       long N, long M, long H, long Mc, long h, const void *mask_scratch,
-                                       cudaStream_t st) {
-  if (N == 0 || Mc == 0) return cudaSuccess;
-  MaskScratch<T> ms(const_cast<void *>(mask_scratch), N);
-  const T cthr4 = cthr * cthr * cthr * cthr;
-  rewrite_changed_rows_kernel<T><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(w, wmask, ms.old_col, Ci, Cj, Cij, cthr, cthr4,
-                                                                          N, M, H, Mc, h);
-  return launched();
-}
-template cudaError_t launch_rewrite_hypercolumn<float>(float *, const uint8_t *, const float *, const float *,
-                                                       const float *, float, long, long, long, long, long,
-                                                       const void *, cudaStream_t);
-template cudaError_t launch_rewrite_hypercolumn<double>(double *, const uint8_t *, const double *, const double *,
-                                                        const double *, double, long, long, long, long, long,
-                                                        const void *, cudaStream_t);
 
 // ----------------------------------------------------------------------------
 // Evaluation helper: rows whose predicted class equals the labelled class

@@ -87,18 +87,13 @@ cudaError_t launch_apply_mask(T *w, const uint8_t *wmask, long N, long M, long H
 // Mask update for hypercolumn h.  `weights` null => the un-masked weight is
 // recomputed from the traces.  `scratch` holds mask_scratch_bytes(N, sizeof(T))
 // bytes (256-byte aligned): per-row score, active count and previous mask bit, candidate lists.
+// `rewrite_w` non-null => the weights of hypercolumn h are recomputed from the traces, under the
+// new mask, for every row whose mask bit a swap changed.
 size_t mask_scratch_bytes(long N, size_t elem);
 template <typename T>
 cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, const T *Cj, const T *Cij, T cthr,
                                long N, long M, long H, long Mc, long h, long iterations, void *scratch,
-                               cudaStream_t st);
-
-// Rewrites the weights of hypercolumn h's columns from the traces for the rows whose mask
-// bit the preceding launch_mask_update (same scratch) changed.
-template <typename T>
-cudaError_t launch_rewrite_hypercolumn(T *w, const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr,
-                                       long N, long M, long H, long Mc, long h, const void *mask_scratch,
-                                       cudaStream_t st);
+                               cudaStream_t st, T *rewrite_w = nullptr);
 
 template <typename T>
 cudaError_t launch_count_correct(const T *pred, const T *labels, long rows, long classes, unsigned long long *count,
