@@ -42,13 +42,15 @@ POOL = 8  # distinct resident batches cycled through (8 x 56.6 MB of inputs > 12
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mask", action="store_true", help="skip the per-step mask update")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-dp-large", action="store_true",
+                    help="skip the extra leg on the large-batch data-parallel workload (stl10_dp_f32)")
     ap.add_argument("--contraction", default="tensor", choices=["tensor", "general"],
                     help="tcgen05 tensor-core kernels (default) or the general-shape FFMA kernels")
     return ap.parse_args()
@@ -71,55 +73,50 @@ def algorithmic_work(N, M, H, B, s):
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples during the timed region (read only)."""
+    """SM clock and throttle-reason samples during the timed region, read through NVML every few
+    milliseconds on a thread of this process (read only; nothing is set)."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+               (0x4, "sw_power_cap"))
 
-    def __init__(self, gpu_index):
-        self.path = tempfile.mktemp(prefix="sbb_clocks_", suffix=".csv")
-        self.proc = None
-        self.gpu = gpu_index
+    def __init__(self, gpu_index, period_s=0.004):
+        import threading
+        self.sm, self.reasons, self.max_mhz = [], set(), None
+        self.stop_flag = threading.Event()
+        self.thread = None
         try:
-            self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=self.out, stderr=subprocess.DEVNULL)
+            import pynvml
+            pynvml.nvmlInit()
+            try:   # the CUDA ordinal may be remapped by CUDA_VISIBLE_DEVICES: find the board by UUID
+                import torch
+                h = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid))
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
         except Exception:
-            self.proc = None
+            return
+
+        def poll():
+            while not self.stop_flag.is_set():
+                try:
+                    self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                    bits = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                    for bit, name in self.REASONS:
+                        if bits & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+                self.stop_flag.wait(period_s)
+        self.thread = threading.Thread(target=poll, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return res
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.out.close()
-        sm, reasons, mx = [], set(), None
-        try:
-            for line in open(self.path):
-                f = [t.strip() for t in line.split(",")]
-                if len(f) < 9:
-                    continue
-                try:
-                    sm.append(float(f[1]))
-                    mx = float(f[2])
-                except ValueError:
-                    continue
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                   f[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if sm:
-            res.update(sm_mhz=statistics.median(sm), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
-        return res
+        self.stop_flag.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(sm)}
 
 
 def steady_state_traces(p, x, seed=7):
@@ -227,7 +224,10 @@ def run_b200(args, wl, p, batch):
     check(lib.sbb_set_contraction_path(1 if args.contraction == "tensor" else 0))
     tensor_path = args.contraction == "tensor" and bool(lib.sbb_tensor_path_available()) and p["dtype"] == np.float32
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL's kernels on a high-priority stream: their few CTAs are scheduled ahead of the pending
+        # CTAs of the step's own kernels, so the reduction of a row block runs beside the next block
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
     hp = p["hidden"]
     N, H, Mc = hp["in_features"], hp["hypercolumns"], hp["minicolumns"]
     M = H * Mc
@@ -296,6 +296,58 @@ def run_b200(args, wl, p, batch):
     check(lib.sbb_layer_profile(layer._handle, 0))
     wait_status = ctypes.c_int(0)
     check(lib.sbb_device_wait_status(ctypes.byref(wait_status)))
+
+    # The data-parallel workload of the same layer (global batch 8192 cut evenly over the ranks, strong
+    # scaling), timed the same way and reported beside the headline under "dp_large_batch".
+    dp_large = None
+    if wl == "stl10_f32" and not args.no_dp_large:
+        del xs, ys
+        pl = synthetic.layer_params("stl10_dp_f32")
+        gb = pl["batch"]
+        bl = gb // world
+        hl = pl["hidden"]
+        np.random.seed(0)
+        big = B200.StructuralPlasticityLayer(N, H, Mc, hl["taupdt"], hl["khalf"], hl["pmin"], hl["taubdt"],
+                                             hl["density"], 16, hl["initial_counters"], dtype=np_dtype)
+        big.Ci, big.Cj, big.Cij = steady_state_traces(pl, ref_batch)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(synthetic.DATA_SEED + 17 * rank)
+        xl = []
+        for _ in range(2):   # uniform pixels, complementary-coded (p, 1 - p), made on the device: 1.8 GB per batch at N = 1
+            pix = torch.rand((bl, N // 2), device="cuda", generator=gen, dtype=torch.float32)
+            xl.append(torch.stack((pix, 1.0 - pix), dim=2).reshape(bl, N).contiguous())
+            del pix
+        yl = torch.empty((bl, M), dtype=torch.float32, device="cuda")
+
+        def big_step(k):
+            x = xl[k % 2]
+            check(lib.sbb_layer_forward(big._handle, x.data_ptr(), bl, yl.data_ptr(), stream))
+            h = (k % H) if mask else None
+            if world > 1:
+                big.dp_train_step(x, yl, h, world, all_reduce)
+            else:
+                check(lib.sbb_layer_train_step(big._handle, x.data_ptr(), yl.data_ptr(), bl, -1 if h is None else h,
+                                               stream))
+        n_big = max(3, min(args.steps, 8))
+        for k in range(3):
+            big_step(k)
+        barrier()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for k in range(n_big):
+            big_step(3 + k)
+        b1.record()
+        barrier()
+        big_ms = b0.elapsed_time(b1)
+        if world > 1:
+            t = torch.tensor([big_ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            big_ms = float(t.item())
+        dp_large = {"workload": "stl10_dp_f32", "global_batch": gb, "batch_per_gpu": bl, "scaling": "strong",
+                    "value": gb * n_big / (big_ms * 1e-3), "unit": "samples/s", "ms_per_step": big_ms / n_big,
+                    "steps": n_big, "warmup": 3, "data": "synthetic, made on the device"}
+        del xl, yl, big
+        xs = [torch.from_numpy(x).cuda() for x in xs_host[:4]]
 
     # end to end through the host-buffer C-ABI call (N = 1 semantics per rank; under
     # data parallelism the exchange needs device buffers, so e2e is measured at N = 1).
@@ -366,7 +418,8 @@ def run_b200(args, wl, p, batch):
                    "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
                        POOL, 2 * N * M * s / 1e6),
                    "contraction": "tcgen05 3xTF32" if tensor_path else "FFMA", "parallelism": "dp%d" % world},
-        "roofline": roofline, "step_roofline": step_roofline, "cpu_baseline": cpu, "e2e": e2e,
+        "roofline": roofline, "step_roofline": step_roofline, "dp_large_batch": dp_large, "cpu_baseline": cpu,
+        "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -246,6 +246,15 @@ int sbb_layer_phase_ms(sbb_layer *layer, int phase, long index, float *ms);
 #define SBB_PATH_TENSOR 1
 int sbb_set_contraction_path(int path);
 int sbb_get_contraction_path(void);
+/* Multiprocessors the persistent tensor-core kernel of sbb_layer_dp_local (the batch
+ * outer product of one row block) leaves free: it launches one CTA per remaining
+ * multiprocessor.  A data-parallel step sets this so that the kernels of the collective
+ * reducing the previous row block, which run beside it on another stream, find room
+ * at once instead of waiting for a resident CTA to retire.  0 (the initial value, or the
+ * environment variable SBB_COMM_SMS) uses every multiprocessor.  Process-wide.
+ * No counterpart in the reference (its MPI backend reduces on the host). */
+int sbb_set_reserved_sms(int sms);
+int sbb_get_reserved_sms(void);
 /* 1 when the tensor-core kernels can run on the current device. */
 int sbb_tensor_path_available(void);
 /* Status of the bounded device-side waits of the tensor-core kernels on the

@@ -80,6 +80,8 @@ SIGNATURES = {
     "sbb_layer_phase_ms": (c_int, [c_void_p, c_int, c_long, POINTER(ctypes.c_float)]),
     "sbb_set_contraction_path": (c_int, [c_int]),
     "sbb_get_contraction_path": (c_int, []),
+    "sbb_set_reserved_sms": (c_int, [c_int]),
+    "sbb_get_reserved_sms": (c_int, []),
     "sbb_tensor_path_available": (c_int, []),
     "sbb_device_wait_status": (c_int, [POINTER(c_int)]),
     "sbb_kernel_launches": (c_ulonglong, []),

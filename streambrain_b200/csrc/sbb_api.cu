@@ -318,6 +318,13 @@ int sbb_set_contraction_path(int path) {
   return SBB_OK;
 }
 int sbb_get_contraction_path(void) { return g_path; }
+
+int sbb_set_reserved_sms(int sms) {
+  if (sms < 0) return fail(SBB_ERR_INVALID, "sbb_set_reserved_sms: negative count");
+  sbb::tc_set_reserved_sms(sms);
+  return SBB_OK;
+}
+int sbb_get_reserved_sms(void) { return sbb::tc_get_reserved_sms(); }
 int sbb_tensor_path_available(void) { return device_count() > 0 && sbb::tc_available() ? 1 : 0; }
 int sbb_device_wait_status(int *status) {
   ARG(status, "device_wait_status: null pointer");

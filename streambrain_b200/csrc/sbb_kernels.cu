@@ -654,37 +654,59 @@ template cudaError_t launch_outer_product<float>(const float *, const float *, l
 template cudaError_t launch_outer_product<double>(const double *, const double *, long, long, long, double *, long,
                                                   long, cudaStream_t);
 
-// One thread per four consecutive columns of one row.
+// One thread per four consecutive columns, walking kApplyRows rows: the column data (Cj, the
+// hypercolumn of each column) is set up once per thread, rows only add Ci and the mask byte.
+constexpr int kApplyRows = 8;
 template <typename T>
 __global__ void __launch_bounds__(256)
     trace_apply_kernel(const T *__restrict__ delta, long M, long H, long Mc, const T *__restrict__ Ci,
                        const T *__restrict__ Cj, T *Cij, T *W, const uint8_t *__restrict__ wmask, TraceParams<T> p,
-                       int ema, long row_begin, long row_end, long quads_per_row, bool vec) {
-  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long i = row_begin + idx / quads_per_row;
-  if (i >= row_end) return;
-  const long j = (idx % quads_per_row) * 4;
+                       int ema, long row_begin, long row_end, bool vec) {
+  const long j = ((long)blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (j >= M) return;
   const long left = M - j;
   const int valid = left >= 4 ? 4 : (int)left;
-  const T ci = Ci[i];
-  const bool skip = ci < p.cthr;
-  T c4[4], d4[4], w4[4];
-  load4(Cij + i * M + j, c4, vec, valid);
-  if (ema) load4(delta + i * M + j, d4, vec, valid);
+  T cj[4];
+  bool col_on[4];
+  long hc[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    if (c < valid) {
-      const T cij = ema ? trace_ema(c4[c], d4[c], p) : c4[c];
-      c4[c] = cij;
-      const T cj = Cj[j + c];
-      T w = (T)0;
-      if (!skip && !(cj < p.cthr) && (wmask == nullptr || wmask[i * H + (j + c) / Mc] != 0))
-        w = log_ratio(cij, ci, cj, p.cthr4);
-      w4[c] = w;
-    }
+    cj[c] = c < valid ? Cj[j + c] : (T)1;
+    col_on[c] = c < valid && !(cj[c] < p.cthr);
+    hc[c] = wmask ? (j + (c < valid ? c : 0)) / Mc : 0;
   }
-  if (ema) store4(Cij + i * M + j, c4, vec, valid);
-  store4(W + i * M + j, w4, vec, valid);
+  const bool one_hc = hc[0] == hc[3] && hc[0] == hc[1] && hc[0] == hc[2];
+  const long r0 = row_begin + (long)blockIdx.x * kApplyRows;
+  const long r1 = r0 + kApplyRows < row_end ? r0 + kApplyRows : row_end;
+  for (long i = r0; i < r1; ++i) {
+    const T ci = Ci[i];
+    const bool row_on = !(ci < p.cthr);
+    bool on[4];
+    if (wmask == nullptr) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) on[c] = row_on && col_on[c];
+    } else if (one_hc) {
+      const bool m = wmask[i * H + hc[0]] != 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) on[c] = row_on && col_on[c] && m;
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) on[c] = row_on && col_on[c] && wmask[i * H + hc[c]] != 0;
+    }
+    T c4[4], d4[4], w4[4];
+    load4(Cij + i * M + j, c4, vec, valid);
+    if (ema) load4(delta + i * M + j, d4, vec, valid);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (c < valid) {
+        const T cij = ema ? trace_ema(c4[c], d4[c], p) : c4[c];
+        c4[c] = cij;
+        w4[c] = on[c] ? log_ratio(cij, ci, cj[c], p.cthr4) : (T)0;
+      }
+    }
+    if (ema) store4(Cij + i * M + j, c4, vec, valid);
+    store4(W + i * M + j, w4, vec, valid);
+  }
 }
 
 template <typename T>
@@ -695,10 +717,12 @@ cudaError_t launch_trace_apply(const T *delta, long N, long M, long H, long Mc, 
   constexpr int V = Vec16<T>::N;
   if (row_end <= row_begin || M == 0) return cudaSuccess;
   const long qpr = (M + 3) / 4;
-  const long total = (row_end - row_begin) * qpr;
   const bool vec = (M % V == 0) && aligned16(Cij) && aligned16(w) && (!ema || aligned16(delta));
-  trace_apply_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(delta, M, H, Mc, Ci, Cj, Cij, w, wmask, p,
-                                                                          ema, row_begin, row_end, qpr, vec);
+  const long row_groups = (row_end - row_begin + kApplyRows - 1) / kApplyRows;
+  const int threads = qpr >= 256 ? 256 : (int)((qpr + 31) / 32 * 32);
+  const dim3 grid((unsigned)row_groups, (unsigned)((qpr + threads - 1) / threads));
+  trace_apply_kernel<T><<<grid, threads, 0, st>>>(delta, M, H, Mc, Ci, Cj, Cij, w, wmask, p, ema, row_begin, row_end,
+                                                  vec);
   return launched();
 }
 template cudaError_t launch_trace_apply<float>(const float *, long, long, long, long, const float *, const float *,

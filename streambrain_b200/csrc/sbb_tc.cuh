@@ -39,6 +39,10 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
 cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long N, long M, float *delta,
                                     long row_begin, long row_end, cudaStream_t st);
 
+// Multiprocessors launch_outer_product_tc leaves free for kernels of other streams.
+void tc_set_reserved_sms(int sms);
+int tc_get_reserved_sms();
+
 // Status word of the bounded device-side waits on the current device: 0 = all
 // waits completed, otherwise the code of the first wait that gave up.
 // Synchronises the device.

@@ -878,6 +878,7 @@ EncodeTiledFn g_encode = nullptr;
 int g_available = -1;           // -1 unknown, 0 no, 1 yes
 int *g_status[64] = {nullptr};  // per-device status word
 int g_sm_count_tc[64] = {0};
+std::atomic<int> g_reserved_sms{-1};   // -1: not set yet (the environment decides on first use)
 
 int current_device() {
   int dev = 0;
@@ -953,7 +954,8 @@ struct TcMaps {
 };
 
 template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
-cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st) {
+cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st,
+                      bool leave_reserved_sms = false) {
   using SM = TcSmem<BN, BK, STAGES, FUSED, A_KMAJOR>;
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
@@ -967,7 +969,9 @@ cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, 
   }
   const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
   if (total <= 0) return cudaSuccess;
-  const unsigned grid = (unsigned)(total < g_sm_count_tc[dev] ? total : g_sm_count_tc[dev]);
+  int sms = g_sm_count_tc[dev] - (leave_reserved_sms ? tc_get_reserved_sms() : 0);
+  if (sms < 1) sms = 1;
+  const unsigned grid = (unsigned)(total < sms ? total : sms);
   kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, wk, ep, status);
   return cudaGetLastError();
 }
@@ -1158,7 +1162,8 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   ep.rows = rows;
   ep.cols = M;
   ep.ld = M;
-  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0>(tm, wk, ep, st);
+  // the one contraction that runs beside a collective (the reduction of the previous row block)
+  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0>(tm, wk, ep, st, true);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
@@ -1174,6 +1179,18 @@ extern "C" int sbb_tc_trace2_read(unsigned long long *out) {
   return (int)cudaMemcpyFromSymbol(out, g_tc_trace2, sizeof(unsigned long long) * 16 * 4 * 8);
 }
 #endif
+
+void tc_set_reserved_sms(int sms) { g_reserved_sms.store(sms < 0 ? 0 : sms); }
+int tc_get_reserved_sms() {
+  int v = g_reserved_sms.load();
+  if (v < 0) {
+    const char *e = getenv("SBB_COMM_SMS");
+    v = e ? atoi(e) : 0;
+    if (v < 0) v = 0;
+    g_reserved_sms.store(v);
+  }
+  return v;
+}
 
 cudaError_t tc_read_status(int *status) {
   *status = 0;

@@ -1,0 +1,114 @@
+"""The data-parallel train step over NCCL on two GPUs of one node: each rank runs
+the pipelined step (row blocks of the batch outer product all-reduced while the
+next block is computed) on its half of the batch; the replicas must stay
+bit-identical and equal, within float32 summation-order tolerance, a single
+GPU's step on the whole batch -- the equivalence the reference asserts for its
+MPI backend (BCPNN/backend/_kernels/test_mpi.py:48-59).  Skipped with fewer than
+two GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import REPO, TOL, rel_inf, weight_err
+
+pytestmark = pytest.mark.gpu
+
+N, H, MC, B_LOCAL, TAU = 512, 8, 32, 96, 0.02
+M = H * MC
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _make_layer(B200, path):
+    from streambrain_b200._lib import check, lib
+    check(lib.sbb_set_contraction_path(1 if path == "tensor" else 0))
+    np.random.seed(11)
+    layer = B200.StructuralPlasticityLayer(N, H, MC, TAU, -100.0, 0.05, 0.01, 0.5, 16, (1.0, 1.0 / MC, 1.0 / MC),
+                                           dtype=np.float32)
+    rs = np.random.RandomState(5)
+    layer.Ci = (0.2 + 0.6 * rs.rand(N)).astype(np.float32)
+    layer.Cj = (0.2 + 0.6 * rs.rand(M)).astype(np.float32) / MC
+    # near independence: small weights keep the softmax of the second step well conditioned, so
+    # that the two arithmetic orders (fused step / reduced sums) stay within the float32 tolerance
+    layer.Cij = (np.outer(layer.Ci, layer.Cj) * (0.95 + 0.1 * rs.rand(N, M))).astype(np.float32)
+    return layer
+
+
+def _batches(world, steps):
+    rs = np.random.RandomState(7)
+    return [rs.rand(world * B_LOCAL, N).astype(np.float32) for _ in range(steps)]
+
+
+def _worker(rank, world, port, path, out_dir):
+    sys.path.insert(0, REPO)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import streambrain_b200 as B200
+    layer = _make_layer(B200, path)
+    steps = 2
+    for k, xb in enumerate(_batches(world, steps)):
+        x = torch.from_numpy(xb[rank * B_LOCAL:(rank + 1) * B_LOCAL]).cuda()
+        y = layer.compute_activation(x)
+        layer.dp_train_step(x, y, (2 + k) % H, world, lambda t: dist.all_reduce(t, async_op=True), row_blocks=3)
+    torch.cuda.synchronize()
+    np.savez(os.path.join(out_dir, "rank%d.npz" % rank), Ci=layer.Ci, Cj=layer.Cj, Cij=layer.Cij,
+             weights=layer.weights, bias=layer.bias, wmask=layer.wmask)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("path", ["general", "tensor"])
+def test_two_gpu_step_equals_big_batch(tmp_path, path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), path, str(tmp_path)), nprocs=world, join=True)
+    r0 = np.load(tmp_path / "rank0.npz")
+    r1 = np.load(tmp_path / "rank1.npz")
+    for name in r0.files:
+        assert np.array_equal(r0[name], r1[name]), name   # replicas stay identical
+
+    import streambrain_b200 as B200
+    torch.cuda.set_device(0)
+
+    class Done:
+        def wait(self):
+            pass
+
+    # (a) the same kernels on one GPU with the whole batch (world_size 1, nothing to reduce): only the
+    # order of the batch summation differs; (b) the fused single-device step, whose trace arithmetic is
+    # ordered differently (kernels_openmp_internal.cc:361-383 against kernels_mpi_internal.cc:100-250).
+    whole, fused = _make_layer(B200, path), _make_layer(B200, path)
+    for k, xb in enumerate(_batches(world, 2)):
+        for layer in (whole, fused):
+            halves = [xb[r * B_LOCAL:(r + 1) * B_LOCAL] for r in range(world)]
+            y = np.concatenate([layer.compute_activation(h) for h in halves])   # per-rank forward, as the workers do
+            if layer is whole:
+                layer.dp_train_step(torch.from_numpy(xb).cuda(), torch.from_numpy(y).cuda(), (2 + k) % H, 1,
+                                    lambda t: Done(), row_blocks=3)
+            else:
+                layer.train_step(xb, y, (2 + k) % H)
+    torch.cuda.synchronize()
+    tol = TOL[np.dtype(np.float32)]
+    for ref, scale in ((whole, 1), (fused, 10)):
+        errs = {name: rel_inf(r0[name], getattr(ref, name)) for name in ("Ci", "Cj", "Cij", "bias")}
+        errs["weights"] = weight_err(r0["weights"], ref.weights)
+        errs["wmask bits that differ"] = int((r0["wmask"] != ref.wmask).sum())
+        assert errs["wmask bits that differ"] == 0, errs
+        assert all(errs[name] < scale * tol for name in ("Ci", "Cj", "Cij", "bias")), errs
+        assert errs["weights"] < 10 * scale * tol, errs
