@@ -49,6 +49,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mask", action="store_true", help="skip the per-step mask update")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--dp-path", action="store_true",
+                    help="at N = 1, run the data-parallel step (row-block products, reduction, row-block "
+                         "apply) with nothing to reduce: the kernels every rank runs at N > 1")
     ap.add_argument("--no-dp-large", action="store_true",
                     help="skip the extra leg on the large-batch data-parallel workload (stl10_dp_f32)")
     ap.add_argument("--contraction", default="tensor", choices=["tensor", "general"],
@@ -242,14 +245,18 @@ def run_b200(args, wl, p, batch):
     xs = [torch.from_numpy(x).cuda() for x in xs_host]
     ys = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    all_reduce = (lambda t: dist.all_reduce(t, async_op=True)) if world > 1 else None
+    class _Reduced:   # a finished reduction, for --dp-path at N = 1
+        def wait(self):
+            pass
+    dp_path = world > 1 or args.dp_path
+    all_reduce = (lambda t: dist.all_reduce(t, async_op=True)) if world > 1 else (lambda t: _Reduced())
     mask = not args.no_mask
 
     def step(k):
         x, y = xs[k % POOL], ys[k % 2]
         check(lib.sbb_layer_forward(layer._handle, x.data_ptr(), batch, y.data_ptr(), stream))
         h = (k % H) if mask else None
-        if world > 1:
+        if dp_path:
             layer.dp_train_step(x, y, h, world, all_reduce)
         else:
             check(lib.sbb_layer_train_step(layer._handle, x.data_ptr(), y.data_ptr(), batch, -1 if h is None else h,
@@ -323,7 +330,7 @@ def run_b200(args, wl, p, batch):
             x = xl[k % 2]
             check(lib.sbb_layer_forward(big._handle, x.data_ptr(), bl, yl.data_ptr(), stream))
             h = (k % H) if mask else None
-            if world > 1:
+            if dp_path:
                 big.dp_train_step(x, yl, h, world, all_reduce)
             else:
                 check(lib.sbb_layer_train_step(big._handle, x.data_ptr(), yl.data_ptr(), bl, -1 if h is None else h,
@@ -417,7 +424,7 @@ def run_b200(args, wl, p, batch):
                    "start_state": "traces at the independent steady state (mask scores finite, as from epoch 2 on)",
                    "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
                        POOL, 2 * N * M * s / 1e6),
-                   "contraction": "tcgen05 3xTF32" if tensor_path else "FFMA", "parallelism": "dp%d" % world},
+                   "contraction": "tcgen05 3xTF32" if tensor_path else "FFMA", "parallelism": "dp%d" % world + (" (data-parallel step, nothing to reduce)" if args.dp_path and world == 1 else "")},
         "roofline": roofline, "step_roofline": step_roofline, "dp_large_batch": dp_large, "cpu_baseline": cpu,
         "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,

@@ -64,9 +64,9 @@ def _worker(rank, world, port, path, out_dir):
         x = torch.from_numpy(xb[rank * B_LOCAL:(rank + 1) * B_LOCAL]).cuda()
         y = layer.compute_activation(x)
         layer.dp_train_step(x, y, (2 + k) % H, world, lambda t: dist.all_reduce(t, async_op=True), row_blocks=3)
-    torch.cuda.synchronize()
-    np.savez(os.path.join(out_dir, "rank%d.npz" % rank), Ci=layer.Ci, Cj=layer.Cj, Cij=layer.Cij,
-             weights=layer.weights, bias=layer.bias, wmask=layer.wmask)
+        torch.cuda.synchronize()
+        np.savez(os.path.join(out_dir, "rank%d_step%d.npz" % (rank, k)), Ci=layer.Ci, Cj=layer.Cj, Cij=layer.Cij,
+                 weights=layer.weights, bias=layer.bias, wmask=layer.wmask)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -78,10 +78,13 @@ def test_two_gpu_step_equals_big_batch(tmp_path, path):
     import torch.multiprocessing as mp
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), path, str(tmp_path)), nprocs=world, join=True)
-    r0 = np.load(tmp_path / "rank0.npz")
-    r1 = np.load(tmp_path / "rank1.npz")
-    for name in r0.files:
-        assert np.array_equal(r0[name], r1[name]), name   # replicas stay identical
+    got = []
+    for k in range(2):
+        r0 = np.load(tmp_path / ("rank0_step%d.npz" % k))
+        r1 = np.load(tmp_path / ("rank1_step%d.npz" % k))
+        for name in r0.files:
+            assert np.array_equal(r0[name], r1[name]), name   # replicas stay identical
+        got.append(r0)
 
     import streambrain_b200 as B200
     torch.cuda.set_device(0)
@@ -93,9 +96,13 @@ def test_two_gpu_step_equals_big_batch(tmp_path, path):
     # (a) the same kernels on one GPU with the whole batch (world_size 1, nothing to reduce): only the
     # order of the batch summation differs; (b) the fused single-device step, whose trace arithmetic is
     # ordered differently (kernels_openmp_internal.cc:361-383 against kernels_mpi_internal.cc:100-250).
+    # One step is compared at the float32 tolerance.  The second step's forward pass amplifies the
+    # first step's rounding differences in the weights (sums over all inputs, then a softmax), for
+    # the summation orders of two ranks and of one alike, so it is compared ten times looser.
     whole, fused = _make_layer(B200, path), _make_layer(B200, path)
+    tol = TOL[np.dtype(np.float32)]
     for k, xb in enumerate(_batches(world, 2)):
-        for layer in (whole, fused):
+        for layer, scale in ((whole, 1), (fused, 10)):
             halves = [xb[r * B_LOCAL:(r + 1) * B_LOCAL] for r in range(world)]
             y = np.concatenate([layer.compute_activation(h) for h in halves])   # per-rank forward, as the workers do
             if layer is whole:
@@ -103,12 +110,11 @@ def test_two_gpu_step_equals_big_batch(tmp_path, path):
                                     lambda t: Done(), row_blocks=3)
             else:
                 layer.train_step(xb, y, (2 + k) % H)
-    torch.cuda.synchronize()
-    tol = TOL[np.dtype(np.float32)]
-    for ref, scale in ((whole, 1), (fused, 10)):
-        errs = {name: rel_inf(r0[name], getattr(ref, name)) for name in ("Ci", "Cj", "Cij", "bias")}
-        errs["weights"] = weight_err(r0["weights"], ref.weights)
-        errs["wmask bits that differ"] = int((r0["wmask"] != ref.wmask).sum())
-        assert errs["wmask bits that differ"] == 0, errs
-        assert all(errs[name] < scale * tol for name in ("Ci", "Cj", "Cij", "bias")), errs
-        assert errs["weights"] < 10 * scale * tol, errs
+            torch.cuda.synchronize()
+            scale *= 10 ** k
+            errs = {name: rel_inf(got[k][name], getattr(layer, name)) for name in ("Ci", "Cj", "Cij", "bias")}
+            errs["weights"] = weight_err(got[k]["weights"], layer.weights)
+            errs["wmask bits that differ"] = int((got[k]["wmask"] != layer.wmask).sum())
+            assert errs["wmask bits that differ"] == 0, (k, errs)
+            assert all(errs[name] < scale * tol for name in ("Ci", "Cj", "Cij", "bias")), (k, errs)
+            assert errs["weights"] < 10 * scale * tol, (k, errs)
