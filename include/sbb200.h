@@ -168,6 +168,18 @@ int sbb_layer_train_step_host(sbb_layer *layer, const void *x_host, const void *
                               long hypercolumn);
 int sbb_layer_step_host(sbb_layer *layer, const void *x_host, const void *target_host, long B,
                         long hypercolumn, void *y_host);
+/* The same step without waiting for it: the inputs are copied on a copy stream into one of
+ * two staging buffers, the step runs on the layer's own stream behind the copy, the activation
+ * is copied to y_host (may be NULL) on a third stream, and the call returns at once.  The
+ * copy of call k+1 therefore runs beside the step of call k (the loop body of
+ * _cpu_base_backend.py:290-309 with its host-device traffic double-buffered).  Host buffers
+ * should be page-locked, must stay untouched until sbb_layer_wait returns (x_host, target_host)
+ * and hold the result only after it (y_host).  Between the first such call and sbb_layer_wait
+ * no other entry point may be used on this layer. */
+int sbb_layer_step_host_async(sbb_layer *layer, const void *x_host, const void *target_host, long B,
+                              long hypercolumn, void *y_host);
+/* Waits for every sbb_layer_step_host_async issued so far (copies included). */
+int sbb_layer_wait(sbb_layer *layer);
 
 /* ------------------------------------------------------------------------
  * Batch data-parallel step, split around the one exchange the path has.

@@ -80,6 +80,8 @@ SIGNATURES = {
     "sbb_layer_phase_ms": (c_int, [c_void_p, c_int, c_long, POINTER(ctypes.c_float)]),
     "sbb_set_contraction_path": (c_int, [c_int]),
     "sbb_get_contraction_path": (c_int, []),
+    "sbb_layer_step_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_long, c_void_p]),
+    "sbb_layer_wait": (c_int, [c_void_p]),
     "sbb_set_reserved_sms": (c_int, [c_int]),
     "sbb_get_reserved_sms": (c_int, []),
     "sbb_tensor_path_available": (c_int, []),

@@ -159,6 +159,30 @@ class _DeviceLayer:
                                       None if y is None else host_ptr(y)))
         return y
 
+    def step_host_async(self, inputs, targets=None, hypercolumn=None, out=None):
+        """:meth:`step_host` without waiting: the upload of this call's inputs runs beside the
+        previous call's step (two staging slots on the device).  ``inputs`` / ``targets`` /
+        ``out`` must be C-contiguous arrays of the layer's dtype (page-locked memory for a true
+        overlap, e.g. ``torch.empty(...).pin_memory().numpy()``); they may not be touched, and
+        ``out`` does not hold the activation, until :meth:`wait` returns."""
+        for a in (inputs, targets, out):
+            if a is not None and (a.dtype != self.dtype or not a.flags["C_CONTIGUOUS"]):
+                raise TypeError("step_host_async needs C-contiguous %s arrays" % np.dtype(self.dtype))
+        B = inputs.shape[0]
+        if inputs.shape[1] != self.in_features:
+            raise ValueError("inputs must have %d columns" % self.in_features)
+        for a in (targets, out):
+            if a is not None and a.shape != (B, self.out_features):
+                raise ValueError("targets / out must be [%d, %d]" % (B, self.out_features))
+        h = -1 if hypercolumn is None else int(hypercolumn)
+        check(lib.sbb_layer_step_host_async(self._handle, host_ptr(inputs),
+                                            None if targets is None else host_ptr(targets), B, h,
+                                            None if out is None else host_ptr(out)))
+
+    def wait(self):
+        """Block until every :meth:`step_host_async` issued so far has finished."""
+        check(lib.sbb_layer_wait(self._handle))
+
     def train_finalize(self):
         check(lib.sbb_layer_train_finalize(self._handle, _stream_ptr() if torch is not None and
                                            torch.cuda.is_available() else None))

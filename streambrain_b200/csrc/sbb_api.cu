@@ -145,6 +145,14 @@ struct sbb_layer {
   Scratch col_hc;        // M ints: hypercolumn of every output column (j / Mc)
   Scratch rc;            // threshold-gated reciprocals of Ci and Cj for the tensor-core trace update
   cudaStream_t own_stream = nullptr;
+  // sbb_layer_step_host_async: two staging slots, copies on their own streams
+  Scratch ax[2], ay[2], at[2];
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+  cudaEvent_t ev_copied[2] = {nullptr, nullptr};    // slot's inputs have landed
+  cudaEvent_t ev_stepped[2] = {nullptr, nullptr};   // the step that used the slot has finished
+  cudaEvent_t ev_read[2] = {nullptr, nullptr};      // the slot's activation has been copied out
+  unsigned long long async_calls = 0;
+  bool async_open = false;
   // optional per-phase event ring (sbb_layer_profile)
   bool profiling = false;
   cudaEvent_t ev_begin[2][SBB_PROFILE_SLOTS];
@@ -670,6 +678,16 @@ int sbb_layer_destroy(sbb_layer *L) {
   L->col_hc.release();
   L->rc.release();
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
+  if (L->h2d_stream) cudaStreamDestroy(L->h2d_stream);
+  if (L->d2h_stream) cudaStreamDestroy(L->d2h_stream);
+  for (int k = 0; k < 2; ++k) {
+    if (L->ev_copied[k]) cudaEventDestroy(L->ev_copied[k]);
+    if (L->ev_stepped[k]) cudaEventDestroy(L->ev_stepped[k]);
+    if (L->ev_read[k]) cudaEventDestroy(L->ev_read[k]);
+    L->ax[k].release();
+    L->ay[k].release();
+    L->at[k].release();
+  }
   if (L->ev_created)
     for (int ph = 0; ph < 2; ++ph)
       for (int k = 0; k < SBB_PROFILE_SLOTS; ++k) {
@@ -855,6 +873,73 @@ int sbb_layer_step_host(sbb_layer *L, const void *x_host, const void *target_hos
   }
   if (y_host) SBB_CUDA(cudaMemcpyAsync(y_host, L->hy.d, (size_t)B * L->M * s, cudaMemcpyDeviceToHost, st));
   SBB_CUDA(cudaStreamSynchronize(st));
+  return SBB_OK;
+}
+
+int sbb_layer_step_host_async(sbb_layer *L, const void *x_host, const void *target_host, long B, long hypercolumn,
+                              void *y_host) {
+  SBB_TRY(check_layer(L));
+  ARG(x_host, "layer_step_host_async: null pointer");
+  SBB_TRY(check_batch(L, B));
+  ARG(hypercolumn < L->H, "layer_step_host_async: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+  if (L->desc.kind != SBB_LAYER_PLASTIC) hypercolumn = -1;
+  const size_t s = esize(L->desc.dtype);
+  if (!L->h2d_stream) {
+    SBB_CUDA(cudaStreamCreateWithFlags(&L->h2d_stream, cudaStreamNonBlocking));
+    SBB_CUDA(cudaStreamCreateWithFlags(&L->d2h_stream, cudaStreamNonBlocking));
+    for (int k = 0; k < 2; ++k) {
+      SBB_CUDA(cudaEventCreateWithFlags(&L->ev_copied[k], cudaEventDisableTiming));
+      SBB_CUDA(cudaEventCreateWithFlags(&L->ev_stepped[k], cudaEventDisableTiming));
+      SBB_CUDA(cudaEventCreateWithFlags(&L->ev_read[k], cudaEventDisableTiming));
+    }
+  }
+  if (!L->async_open) {
+    // Work queued earlier on other streams must have landed before this pipeline touches the layer.
+    SBB_CUDA(cudaDeviceSynchronize());
+    L->async_open = true;
+  }
+  const int slot = (int)(L->async_calls & 1ull);
+  // growing a staging buffer allocates (and so waits for the device): only the first calls do
+  SBB_TRY(L->ax[slot].reserve((size_t)B * L->N * s));
+  SBB_TRY(L->ay[slot].reserve((size_t)B * L->M * s));
+  if (target_host) SBB_TRY(L->at[slot].reserve((size_t)B * L->M * s));
+  cudaStream_t st = L->own_stream;
+  // inputs: after the step that last read this slot, beside the step now running
+  SBB_CUDA(cudaStreamWaitEvent(L->h2d_stream, L->ev_stepped[slot], 0));
+  SBB_CUDA(cudaMemcpyAsync(L->ax[slot].d, x_host, (size_t)B * L->N * s, cudaMemcpyHostToDevice, L->h2d_stream));
+  if (target_host)
+    SBB_CUDA(cudaMemcpyAsync(L->at[slot].d, target_host, (size_t)B * L->M * s, cudaMemcpyHostToDevice,
+                             L->h2d_stream));
+  SBB_CUDA(cudaEventRecord(L->ev_copied[slot], L->h2d_stream));
+  // the step: behind its inputs and behind the read-out of the activation this slot held two calls ago
+  SBB_CUDA(cudaStreamWaitEvent(st, L->ev_copied[slot], 0));
+  SBB_CUDA(cudaStreamWaitEvent(st, L->ev_read[slot], 0));
+  const void *train_on = target_host ? L->at[slot].d : L->ay[slot].d;
+  if (L->desc.dtype == SBB_F32) {
+    SBB_TRY(layer_forward<float>(L, (const float *)L->ax[slot].d, B, (float *)L->ay[slot].d, st));
+    SBB_TRY(layer_train_step<float>(L, (const float *)L->ax[slot].d, (const float *)train_on, B, hypercolumn, st));
+  } else {
+    SBB_TRY(layer_forward<double>(L, (const double *)L->ax[slot].d, B, (double *)L->ay[slot].d, st));
+    SBB_TRY(layer_train_step<double>(L, (const double *)L->ax[slot].d, (const double *)train_on, B, hypercolumn, st));
+  }
+  SBB_CUDA(cudaEventRecord(L->ev_stepped[slot], st));
+  if (y_host) {
+    SBB_CUDA(cudaStreamWaitEvent(L->d2h_stream, L->ev_stepped[slot], 0));
+    SBB_CUDA(cudaMemcpyAsync(y_host, L->ay[slot].d, (size_t)B * L->M * s, cudaMemcpyDeviceToHost, L->d2h_stream));
+    SBB_CUDA(cudaEventRecord(L->ev_read[slot], L->d2h_stream));
+  }
+  L->async_calls += 1;
+  return SBB_OK;
+}
+
+int sbb_layer_wait(sbb_layer *L) {
+  SBB_TRY(check_layer(L));
+  if (L->h2d_stream) {
+    SBB_CUDA(cudaStreamSynchronize(L->h2d_stream));
+    SBB_CUDA(cudaStreamSynchronize(L->own_stream));
+    SBB_CUDA(cudaStreamSynchronize(L->d2h_stream));
+  }
+  L->async_open = false;
   return SBB_OK;
 }
 

@@ -141,6 +141,28 @@ def test_device_tensor_path_equals_host_path(B200):
     assert t.is_cuda and np.array_equal(t.cpu().numpy(), lb.Cij)
 
 
+def test_async_host_steps_equal_blocking_host_steps(B200):
+    """Five pipelined host-buffer steps (copies double-buffered against the steps, page-locked
+    buffers) leave the same state and return the same activations as five blocking calls."""
+    import torch
+    g = load_golden("layer_f32.npz")
+    B, steps = int(g["B"]), 5
+    blocking, _ = _layers_from_golden(B200, g, np.float32)
+    piped, _ = _layers_from_golden(B200, g, np.float32)
+    xs = [torch.from_numpy(np.ascontiguousarray(g["x"][s * B:(s + 1) * B])).pin_memory() for s in range(steps)]
+    outs = [torch.empty((B, piped.out_features), dtype=torch.float32).pin_memory() for _ in range(steps)]
+    want = [blocking.step_host(xs[s].numpy(), None, s % 3) for s in range(steps)]
+    for s in range(steps):
+        piped.step_host_async(xs[s].numpy(), None, s % 3, out=outs[s].numpy())
+    piped.wait()
+    for s in range(steps):
+        assert np.array_equal(outs[s].numpy(), want[s]), s
+    for name in PLASTIC_STATE:
+        assert np.array_equal(getattr(piped, name), getattr(blocking, name)), name
+    # the blocking entry points work again after wait()
+    assert np.array_equal(piped.step_host(xs[0].numpy(), None, 1), blocking.step_host(xs[0].numpy(), None, 1))
+
+
 @pytest.mark.parametrize("tag,dtype", DTYPES)
 def test_network_fit_and_evaluate_vs_golden(B200, tag, dtype):
     g = load_golden("network_%s.npz" % tag)
