@@ -138,6 +138,9 @@ def steady_state_traces(p, x, seed=7):
     Cj = np.full(M, 1.0 / Mc, dtype=dt)
     Cij = (Ci[:, None].astype(np.float32) * Cj[None, :].astype(np.float32))
     Cij *= 1.0 + 0.05 * rs.standard_normal(size=(N, M), dtype=np.float32)
+    # keep Cij < Cj (and < Ci): the score takes log((pj - pij) / ...), which a joint trace above its
+    # marginal would turn into NaN -- a state the moving averages cannot reach from data
+    np.minimum(Cij, 0.98 * np.minimum(Ci[:, None].astype(np.float32), Cj[None, :].astype(np.float32)), out=Cij)
     return Ci, Cj, np.ascontiguousarray(Cij.astype(dt))
 
 

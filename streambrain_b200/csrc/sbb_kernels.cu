@@ -1007,10 +1007,13 @@ __global__ void __launch_bounds__(1024)
 // exactly.  A NaN score makes the reference's scan order-dependent; phase A then raises a flag
 // and the one-CTA full scan (mask_swap_kernel) runs instead.
 //
-// Every selection is "K rounds of arg-best over entries that come strictly after the previous
-// pick in the class order", done by single warps with shuffles: no block barrier inside a round.
+// Scores are mapped to unsigned keys whose integer order is the class order (silent rows: score
+// descending first = larger key; active rows: the complement), so that one selection round is a
+// register-local maximum, one warp-wide integer maximum (redux) for the key and one for the row
+// index among equal keys (the reference's scans keep the last of equal scores), and a clear of the
+// winner's register: no shuffle trees, no block barrier inside a round.
 constexpr int kSwapMaxIter = 32;
-constexpr int kSwapSlots = 768;           // candidate slots per class handed from phase A to phase B
+constexpr int kSwapSlots = 1024;          // candidate slots per class handed from phase A to phase B
 constexpr int kSwapCacheRows = 4096;      // rows per chunk whose score and class fit the chunk's shared memory
 constexpr int kSwapThreads = 256;         // both phases: 8 warps = 2 classes x 4 slices
 
@@ -1019,121 +1022,136 @@ __device__ __forceinline__ T swap_score(T nom, int csum) {
   return (T)((double)nom / (1.0 + (double)csum));
 }
 
-// Class order: silent rows (cls 0) by score descending, active rows (cls 1) ascending; equal
-// scores by index descending (the reference's scans keep the last of equals).
+// Order-preserving keys: a < b  <=>  key(a) < key(b) for non-NaN scores (-0 counts as +0).
+// Key 0 is never produced by a score and marks an empty slot, also after complementing.
 template <typename T>
-__device__ __forceinline__ bool comes_after(int cls, T v, long i, const Pick<T> &prev) {
-  if (prev.i < 0) return true;
-  return cls == 0 ? (v < prev.v || (v == prev.v && i < prev.i)) : (v > prev.v || (v == prev.v && i < prev.i));
+struct ScoreKey;
+template <>
+struct ScoreKey<float> {
+  typedef uint32_t type;
+  static __device__ __forceinline__ type make(float v) {
+    const uint32_t u = __float_as_uint(v == 0.f ? 0.f : v);
+    return (u >> 31) ? ~u : (u | 0x80000000u);
+  }
+  static __device__ __forceinline__ float value(type k) {
+    return __uint_as_float((k >> 31) ? (k ^ 0x80000000u) : ~k);
+  }
+  static __device__ __forceinline__ type warp_max(type k) { return __reduce_max_sync(0xffffffffu, k); }
+};
+template <>
+struct ScoreKey<double> {
+  typedef unsigned long long type;
+  static __device__ __forceinline__ type make(double v) {
+    const unsigned long long u = (unsigned long long)__double_as_longlong(v == 0.0 ? 0.0 : v);
+    return (u >> 63) ? ~u : (u | 0x8000000000000000ull);
+  }
+  static __device__ __forceinline__ double value(type k) {
+    return __longlong_as_double((long long)((k >> 63) ? (k ^ 0x8000000000000000ull) : ~k));
+  }
+  static __device__ __forceinline__ type warp_max(type k) {
+    const uint32_t hi = __reduce_max_sync(0xffffffffu, (uint32_t)(k >> 32));
+    const uint32_t lo = __reduce_max_sync(0xffffffffu, (uint32_t)(k >> 32) == hi ? (uint32_t)k : 0u);
+    return ((type)hi << 32) | lo;
+  }
+};
+// Class key: maximum = first in the class order.  cls 0 (silent): highest score; cls 1 (active): lowest.
+template <typename T>
+__device__ __forceinline__ typename ScoreKey<T>::type class_key(int cls, T v) {
+  const typename ScoreKey<T>::type k = ScoreKey<T>::make(v);
+  return cls == 0 ? k : ~k;
 }
 template <typename T>
-__device__ __forceinline__ Pick<T> warp_pick(Pick<T> best, int cls) {
-  for (int off = 16; off > 0; off >>= 1)
-    best = cls == 0 ? pick_max(best, shfl_pick(best, off)) : pick_min(best, shfl_pick(best, off));
-  return best;
+__device__ __forceinline__ T class_key_value(int cls, typename ScoreKey<T>::type k) {
+  return ScoreKey<T>::value(cls == 0 ? k : ~k);
 }
-// One warp: the first `rounds` entries of (v[e], i[e]), e in [0, n), in class order -> out_v/out_i
-// (index -1 pads the tail).  i[e] < 0 marks an empty entry.
-template <typename T>
-__device__ __forceinline__ void warp_select(int cls, const T *v, const long *i, int n, int rounds, T *out_v,
-                                            long *out_i) {
+
+// One warp: the first `rounds` of its R x 32 register-resident entries (key 0 = empty) in class
+// order; lane 0 writes round k's (score, row) to out_v[k], out_i[k] (row -1 pads an exhausted list).
+template <typename T, int R>
+__device__ __forceinline__ void warp_select_regs(int cls, typename ScoreKey<T>::type (&key)[R], uint32_t (&row)[R],
+                                                 int rounds, T *out_v, long *out_i) {
+  typedef typename ScoreKey<T>::type K;
   const int lane = threadIdx.x & 31;
-  Pick<T> prev{(T)0, -1};
   for (int k = 0; k < rounds; ++k) {
-    Pick<T> best{(T)0, -1};
-    for (int e = lane; e < n; e += 32) {
-      const long idx = i[e];
-      if (idx < 0) continue;
-      const T val = v[e];
-      if (!comes_after(cls, val, idx, prev)) continue;
-      best = cls == 0 ? pick_max(best, Pick<T>{val, idx}) : pick_min(best, Pick<T>{val, idx});
-    }
-    best = warp_pick(best, cls);
-    if (lane == 0) {
-      out_v[k] = best.v;
-      out_i[k] = best.i;
-    }
-    if (best.i < 0) {   // exhausted: the remaining slots are empty
-      for (int kk = k + 1 + lane; kk < rounds; kk += 32) out_i[kk] = -1;
+    K mine = 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r) mine = key[r] > mine ? key[r] : mine;
+    const K best = ScoreKey<T>::warp_max(mine);
+    if (best == 0) {   // exhausted (uniform)
+      for (int kk = k + lane; kk < rounds; kk += 32) out_i[kk] = -1;
       break;
     }
-    prev = best;
+    uint32_t my_row = 0;   // rows are stored + 1 so that 0 means "not holding the best key"
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (key[r] == best && row[r] + 1u > my_row) my_row = row[r] + 1u;
+    const uint32_t win = __reduce_max_sync(0xffffffffu, my_row);
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (key[r] == best && row[r] + 1u == win) key[r] = 0;
+    if (lane == 0) {
+      out_v[k] = class_key_value<T>(cls, best);
+      out_i[k] = (long)win - 1;
+    }
   }
 }
 
-// lists: [class][chunk][iterations] of (value, index); index -1 = empty.
-// CACHED: the chunk's scores and classes are kept in shared memory for the rounds.
-template <typename T, bool CACHED>
+// Phase A.  lists: [class][chunk][iterations] of (value, row); row -1 = empty.
+// CACHED: the chunk's scores and classes are first gathered into shared memory (coalesced).
+template <typename T, int R>
 __global__ void __launch_bounds__(kSwapThreads)
     mask_candidates_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ nom, const int *__restrict__ csum,
                            long N, long H, long h, int iterations, long rows_per_chunk, T *cand_v, long *cand_i,
                            int *nan_flag) {
-  __shared__ T s_lv[2][4][kSwapMaxIter];
-  __shared__ long s_li[2][4][kSwapMaxIter];
+  typedef typename ScoreKey<T>::type K;
+  __shared__ T s_lv[2][4 * kSwapMaxIter];
+  __shared__ long s_li[2][4 * kSwapMaxIter];
   extern __shared__ __align__(16) unsigned char cand_dyn[];
   T *s_sc = reinterpret_cast<T *>(cand_dyn);
-  uint8_t *s_cl = cand_dyn + (CACHED ? rows_per_chunk * sizeof(T) : 0);
+  uint8_t *s_cl = cand_dyn + rows_per_chunk * sizeof(T);
   const long r0 = (long)blockIdx.x * rows_per_chunk;
   const long r1 = r0 + rows_per_chunk < N ? r0 + rows_per_chunk : N;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   bool saw_nan = false;
-  if (CACHED) {
-    for (long j = r0 + threadIdx.x; j < r1; j += blockDim.x) {
-      const uint8_t m = wmask[j * H + h];
-      const T sc = swap_score(nom[j], csum[j]);
-      uint8_t cl = m <= 1 ? m : 2;
-      if (cl < 2 && sc != sc) { saw_nan = true; cl = 2; }
-      s_sc[j - r0] = sc;
-      s_cl[j - r0] = cl;
-    }
-    __syncthreads();
+  for (long j = r0 + threadIdx.x; j < r1; j += blockDim.x) {
+    const uint8_t m = wmask[j * H + h];
+    const T sc = swap_score(nom[j], csum[j]);
+    uint8_t cl = m <= 1 ? m : 2;
+    if (cl < 2 && sc != sc) { saw_nan = true; cl = 2; }
+    s_sc[j - r0] = sc;
+    s_cl[j - r0] = cl;
   }
+  __syncthreads();
   // level 1: warp (cls, slice) lists the first `iterations` rows of its class in its quarter of the chunk
   const int cls = wid & 1, slice = wid >> 1;
   {
     const long len = r1 - r0, q = (len + 3) / 4;
-    const long b = r0 + slice * q, e = b + q < r1 ? b + q : r1;
-    Pick<T> prev{(T)0, -1};
-    for (int k = 0; k < iterations; ++k) {
-      Pick<T> best{(T)0, -1};
-      for (long j = b + lane; j < e; j += 32) {
-        T sc;
-        if (CACHED) {
-          if (s_cl[j - r0] != cls) continue;
-          sc = s_sc[j - r0];
-        } else {
-          if (wmask[j * H + h] != cls) continue;
-          sc = swap_score(nom[j], csum[j]);
-          if (sc != sc) { saw_nan = true; continue; }
-        }
-        if (!comes_after(cls, sc, j, prev)) continue;
-        best = cls == 0 ? pick_max(best, Pick<T>{sc, j}) : pick_min(best, Pick<T>{sc, j});
-      }
-      best = warp_pick(best, cls);
-      if (lane == 0) {
-        s_lv[cls][slice][k] = best.v;
-        s_li[cls][slice][k] = best.i;
-      }
-      if (best.i < 0) {
-        for (int kk = k + 1 + lane; kk < iterations; kk += 32) s_li[cls][slice][kk] = -1;
-        break;
-      }
-      prev = best;
+    const long b = slice * q, e = b + q < len ? b + q : len;   // chunk-relative
+    K key[R];
+    uint32_t row[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const long j = b + lane + 32 * r;
+      const bool mine = j < e && s_cl[j < e ? j : 0] == cls;
+      key[r] = mine ? class_key<T>(cls, s_sc[j]) : (K)0;
+      row[r] = (uint32_t)(r0 + j);
     }
+    warp_select_regs<T, R>(cls, key, row, iterations, s_lv[cls] + slice * iterations, s_li[cls] + slice * iterations);
   }
   __syncthreads();
-  // level 2: one warp per class merges the four slice lists into the chunk's list
+  // level 2: one warp per class merges the four slice lists (4 * iterations <= 128 entries) into the chunk's list
   if (wid < 2) {
-    // the four lists are contiguous only when iterations == kSwapMaxIter: compact them first
-    __shared__ T m_v[2][4 * kSwapMaxIter];
-    __shared__ long m_i[2][4 * kSwapMaxIter];
-    for (int e = lane; e < 4 * iterations; e += 32) {
-      m_v[wid][e] = s_lv[wid][e / iterations][e % iterations];
-      m_i[wid][e] = s_li[wid][e / iterations][e % iterations];
+    K key[4];
+    uint32_t row[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int e = lane + 32 * r;
+      const long i = e < 4 * iterations ? s_li[wid][e] : -1;
+      key[r] = i >= 0 ? class_key<T>(wid, s_lv[wid][e]) : (K)0;
+      row[r] = i >= 0 ? (uint32_t)i : 0u;
     }
-    __syncwarp();
     const long slot = ((long)wid * gridDim.x + blockIdx.x) * iterations;
-    warp_select<T>(wid, m_v[wid], m_i[wid], 4 * iterations, iterations, cand_v + slot, cand_i + slot);
+    warp_select_regs<T, 4>(wid, key, row, iterations, cand_v + slot, cand_i + slot);
   }
   if (saw_nan) atomicOr(nan_flag, 1);
 }
@@ -1147,8 +1165,8 @@ __global__ void __launch_bounds__(kSwapThreads)
                        int iterations, int chunks, const T *__restrict__ cand_v, const long *__restrict__ cand_i,
                        const int *__restrict__ nan_flag, T *rewrite_w, const T *__restrict__ Ci,
                        const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr, T cthr4) {
-  __shared__ T e_v[2][kSwapSlots];
-  __shared__ long e_i[2][kSwapSlots];
+  typedef typename ScoreKey<T>::type K;
+  constexpr int R1 = kSwapSlots / 4 / 32;   // registers per lane for a quarter of one class's chunk lists
   __shared__ T l1_v[2][4 * kSwapMaxIter], top_v[2][kSwapMaxIter];
   __shared__ long l1_i[2][4 * kSwapMaxIter], top_i[2][kSwapMaxIter];
   __shared__ long touched[2 * kSwapMaxIter];
@@ -1156,67 +1174,88 @@ __global__ void __launch_bounds__(kSwapThreads)
   if (*nan_flag) return;   // the full scan handles this update
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int total = chunks * iterations;   // entries per class, <= kSwapSlots
-  for (int c = 0; c < 2; ++c)
-    for (int e = threadIdx.x; e < total; e += blockDim.x) {
-      e_i[c][e] = cand_i[(long)c * total + e];
-      e_v[c][e] = cand_v[(long)c * total + e];
-    }
   if (threadIdx.x == 0) n_touched = 0;
-  __syncthreads();
   {
     const int cls = wid & 1, slice = wid >> 1;
-    const int q = (total + 3) / 4, b = slice * q, n = b + q <= total ? q : (total > b ? total - b : 0);
-    warp_select<T>(cls, e_v[cls] + b, e_i[cls] + b, n, iterations, l1_v[cls] + slice * iterations,
-                   l1_i[cls] + slice * iterations);
+    const int q = (total + 3) / 4, b = slice * q, e = b + q < total ? b + q : total;
+    K key[R1];
+    uint32_t row[R1];
+#pragma unroll
+    for (int r = 0; r < R1; ++r) {
+      const int t = b + lane + 32 * r;
+      const long i = t < e ? cand_i[(long)cls * total + t] : -1;
+      key[r] = i >= 0 ? class_key<T>(cls, cand_v[(long)cls * total + t]) : (K)0;
+      row[r] = i >= 0 ? (uint32_t)i : 0u;
+    }
+    warp_select_regs<T, R1>(cls, key, row, iterations, l1_v[cls] + slice * iterations, l1_i[cls] + slice * iterations);
   }
   __syncthreads();
-  if (wid < 2) warp_select<T>(wid, l1_v[wid], l1_i[wid], 4 * iterations, iterations, top_v[wid], top_i[wid]);
+  if (wid < 2) {
+    K key[4];
+    uint32_t row[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int e = lane + 32 * r;
+      const long i = e < 4 * iterations ? l1_i[wid][e] : -1;
+      key[r] = i >= 0 ? class_key<T>(wid, l1_v[wid][e]) : (K)0;
+      row[r] = i >= 0 ? (uint32_t)i : 0u;
+    }
+    warp_select_regs<T, 4>(wid, key, row, iterations, top_v[wid], top_i[wid]);
+  }
   __syncthreads();
   if (wid == 0) {
-    // slot A of a lane: listed row number `lane` of the class; slot B: the row moved into the class by swap `lane`
-    long ia[2], ib[2] = {-1, -1};
-    T va[2], vb[2] = {(T)0, (T)0}, na[2], nb[2] = {(T)0, (T)0};
+    // per class c: slot A = listed row number `lane`, slot B = the row moved into the class by swap `lane`
+    K ka[2], kb[2] = {0, 0};
+    uint32_t ra[2], rb[2] = {0u, 0u};
+    T na[2], nb[2] = {(T)0, (T)0};
     int ca[2], cb[2] = {0, 0};
+#pragma unroll
     for (int c = 0; c < 2; ++c) {
-      ia[c] = lane < iterations ? top_i[c][lane] : -1;
-      va[c] = ia[c] >= 0 ? top_v[c][lane] : (T)0;
-      na[c] = ia[c] >= 0 ? nom[ia[c]] : (T)0;
-      ca[c] = ia[c] >= 0 ? csum[ia[c]] : 0;
+      const long i = lane < iterations ? top_i[c][lane] : -1;
+      ka[c] = i >= 0 ? class_key<T>(c, top_v[c][lane]) : (K)0;
+      ra[c] = i >= 0 ? (uint32_t)i : 0u;
+      na[c] = i >= 0 ? nom[i] : (T)0;
+      ca[c] = i >= 0 ? csum[i] : 0;
     }
     for (int it = 0; it < iterations; ++it) {
-      // best silent row (cls 0: maximum) and worst active row (cls 1: minimum) over both slots of every lane
-      Pick<T> p[2];
-      for (int c = 0; c < 2; ++c) {
-        Pick<T> mine{va[c], ia[c]};
-        const Pick<T> other{vb[c], ib[c]};
-        mine = c == 0 ? pick_max(mine, other) : pick_min(mine, other);
-        p[c] = warp_pick(mine, c);
-      }
-      if (p[0].i < 0 || p[1].i < 0 || p[0].v < p[1].v) break;   // uniform across the warp
-      // owners hand over the moved rows' numerators and counts, and drop the rows from their class
+      K best[2];
+      uint32_t win[2];
       T mv_nom[2];
       int mv_cs[2];
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const bool own_a = ia[c] == p[c].i, own_b = ib[c] == p[c].i;
+        best[c] = ScoreKey<T>::warp_max(ka[c] > kb[c] ? ka[c] : kb[c]);
+        uint32_t mine = 0;
+        if (best[c] != 0 && ka[c] == best[c]) mine = ra[c] + 1u;
+        if (best[c] != 0 && kb[c] == best[c] && rb[c] + 1u > mine) mine = rb[c] + 1u;
+        win[c] = __reduce_max_sync(0xffffffffu, mine);
+      }
+      // no silent or no active row left, or the best silent row scores below the worst active one
+      if (best[0] == 0 || best[1] == 0 ||
+          class_key_value<T>(0, best[0]) < class_key_value<T>(1, best[1]))
+        break;   // uniform across the warp
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const bool own_a = ka[c] == best[c] && ra[c] + 1u == win[c];
+        const bool own_b = !own_a && kb[c] == best[c] && rb[c] + 1u == win[c];
         const unsigned who = __ballot_sync(0xffffffffu, own_a || own_b);
         const int src = __ffs(who) - 1;
-        const T my_nom = own_a ? na[c] : nb[c];
-        const int my_cs = own_a ? ca[c] : cb[c];
-        mv_nom[c] = __shfl_sync(0xffffffffu, my_nom, src);
-        mv_cs[c] = __shfl_sync(0xffffffffu, my_cs, src);
-        if (own_a) ia[c] = -1;
-        if (own_b) ib[c] = -1;
+        mv_nom[c] = __shfl_sync(0xffffffffu, own_a ? na[c] : nb[c], src);
+        mv_cs[c] = __shfl_sync(0xffffffffu, own_a ? ca[c] : cb[c], src);
+        if (own_a) ka[c] = 0;
+        if (own_b) kb[c] = 0;
       }
       if (lane == it) {
         // the silent row becomes active with one more connection, the active row silent with one fewer
-        ib[1] = p[0].i; nb[1] = mv_nom[0]; cb[1] = mv_cs[0] + 1; vb[1] = swap_score(nb[1], cb[1]);
-        ib[0] = p[1].i; nb[0] = mv_nom[1]; cb[0] = mv_cs[1] - 1; vb[0] = swap_score(nb[0], cb[0]);
-        wmask[p[0].i * H + h] = 1;
-        wmask[p[1].i * H + h] = 0;
-        csum[p[0].i] = cb[1];
-        csum[p[1].i] = cb[0];
-        touched[2 * it] = p[0].i;
-        touched[2 * it + 1] = p[1].i;
+        const long up = (long)win[0] - 1, down = (long)win[1] - 1;
+        rb[1] = (uint32_t)up;   nb[1] = mv_nom[0]; cb[1] = mv_cs[0] + 1; kb[1] = class_key<T>(1, swap_score(nb[1], cb[1]));
+        rb[0] = (uint32_t)down; nb[0] = mv_nom[1]; cb[0] = mv_cs[1] - 1; kb[0] = class_key<T>(0, swap_score(nb[0], cb[0]));
+        wmask[up * H + h] = 1;
+        wmask[down * H + h] = 0;
+        csum[up] = cb[1];
+        csum[down] = cb[0];
+        touched[2 * it] = up;
+        touched[2 * it + 1] = down;
         n_touched = 2 * it + 2;
       }
     }
@@ -1276,20 +1315,25 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
   cudaError_t e = launched();
   if (e != cudaSuccess) return e;
   const int *run_flag = nullptr;
-  if (iterations >= 1 && iterations <= kSwapMaxIter && N >= 4096) {
-    const int max_chunks = kSwapSlots / (int)iterations;
-    int chunks = (int)((N + 1023) / 1024);
+  // candidate lists: rows fit 32-bit indices and a chunk (<= kSwapCacheRows rows) fits shared memory
+  const int max_chunks = iterations >= 1 && iterations <= kSwapMaxIter ? kSwapSlots / (int)iterations : 0;
+  if (max_chunks > 0 && N >= 1024 && N < (1l << 31) && (N + max_chunks - 1) / max_chunks <= kSwapCacheRows) {
+    int chunks = (int)((N + 767) / 768);
     if (chunks > max_chunks) chunks = max_chunks;
     const long rows_per_chunk = (N + chunks - 1) / chunks;
     chunks = (int)((N + rows_per_chunk - 1) / rows_per_chunk);
     e = cudaMemsetAsync(ms.nan_flag, 0, sizeof(int), st);
     if (e != cudaSuccess) return e;
-    if (rows_per_chunk <= kSwapCacheRows)
-      mask_candidates_kernel<T, true><<<chunks, kSwapThreads, (size_t)rows_per_chunk * (sizeof(T) + 1), st>>>(
-          wmask, ms.score, ms.csum, N, H, h, (int)iterations, rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag);
-    else
-      mask_candidates_kernel<T, false><<<chunks, kSwapThreads, 0, st>>>(
-          wmask, ms.score, ms.csum, N, H, h, (int)iterations, rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag);
+    const size_t dyn = (size_t)rows_per_chunk * (sizeof(T) + 1);
+    const long slice = (rows_per_chunk + 3) / 4;   // rows one warp keeps in registers, 32 per register
+#define SBB_CAND(R)                                                                                              \
+  mask_candidates_kernel<T, R><<<chunks, kSwapThreads, dyn, st>>>(wmask, ms.score, ms.csum, N, H, h, (int)iterations, \
+                                                                  rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag)
+    if (slice <= 4 * 32) SBB_CAND(4);
+    else if (slice <= 8 * 32) SBB_CAND(8);
+    else if (slice <= 16 * 32) SBB_CAND(16);
+    else SBB_CAND(32);
+#undef SBB_CAND
     e = launched();
     if (e != cudaSuccess) return e;
     mask_replay_kernel<T><<<1, kSwapThreads, 0, st>>>(wmask, ms.score, ms.csum, N, M, H, Mc, h, (int)iterations, chunks,
