@@ -162,16 +162,8 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Same with the A operand read from tensor memory (128 lanes x 8 columns of 32-bit values at a_tmem).
+// D[128 x N] (+)= A[128 x 8] * B[8 x N]: A read from tensor memory (128 lanes x 8 columns of 32-bit
+// values at a_tmem), B through a shared-memory descriptor, TF32 inputs, float32 accumulation.
 __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                             uint32_t accumulate) {
   asm volatile(
@@ -181,16 +173,26 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Each lane writes 32 consecutive 32-bit columns of its own tensor-memory lane.
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
+// Each lane writes NCOL (16 or 32) consecutive 32-bit columns of its own tensor-memory lane.
+template <int NCOL>
+__device__ __forceinline__ void tmem_st_32x32b(uint32_t taddr, const uint32_t (&r)[NCOL]) {
+  static_assert(NCOL == 16 || NCOL == 32, "column count");
+  if constexpr (NCOL == 32) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+  }
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -231,9 +233,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= (uint64_t)layout_type << 61;
   return d;
 }
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return smem_desc(saddr, lbo_bytes, sbo_bytes, 2u);  // K-major, SWIZZLE_128B
-}
 __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr, uint32_t lbo_bytes) {
   return smem_desc(saddr, lbo_bytes, 512u, 1u);       // MN-major, SWIZZLE_128B_BASE32B
 }
@@ -263,19 +262,18 @@ __device__ unsigned long long g_tc_trace2[16 * 4 * 8];
 // ------------------------------------------------------------------ the kernel
 constexpr int kSlabBytes = 32 * 32 * 4;  // one epilogue warp's 32-row x 32-column block of the trace matrix
 
-// A_TMEM: the A operand's hi / lo parts live in tensor memory (written by the converters), so
-// only B has a "lo" copy in shared memory and the tensor core fetches only B from there.
-template <int BN, int BK, int STAGES, bool FUSED, bool A_TMEM>
+// The A operand's hi / lo parts live in tensor memory (written by the converters), so only B
+// has a "lo" copy in shared memory and the tensor core fetches only B from there.
+template <int BN, int BK, int STAGES, bool FUSED>
 struct TcSmem {
   static constexpr int A_BYTES = 128 * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // TMA landing zone: the raw values serve as "hi"
-  static constexpr int LO_BYTES = A_TMEM ? B_BYTES : RAW_BYTES;
-  static constexpr int STAGE_BYTES = RAW_BYTES + LO_BYTES;
-  // tensor memory: two accumulators, then (A_TMEM) per stage BK columns of A hi and BK of A lo
+  static constexpr int STAGE_BYTES = RAW_BYTES + B_BYTES;   // + B's lo parts
+  // tensor memory: two accumulators, then per stage BK columns of A hi and BK of A lo
   static constexpr int TMEM_A_COL = 2 * BN;
-  static constexpr int TMEM_COLS = A_TMEM ? 512 : 2 * BN;
-  static_assert(!A_TMEM || 2 * BN + STAGES * 2 * BK <= 512, "tensor memory budget");
+  static constexpr int TMEM_COLS = 512;
+  static_assert(2 * BN + STAGES * 2 * BK <= TMEM_COLS, "tensor memory budget");
   static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte swizzle alignment");
   static constexpr int SLAB_OFFSET = STAGES * STAGE_BYTES;
   // fused epilogue: two landing buffers per epilogue warp for blocks of the trace matrix
@@ -324,10 +322,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA3, const __grid_constant__ CUtensorMap tmB3,
                           const __grid_constant__ CUtensorMap tmC, TcWork wk, TcEpilogue ep, int *status) {
-  constexpr bool A_TMEM = A_KMAJOR;   // the K-major A of the forward product is staged through tensor memory
-  using SM = TcSmem<BN, BK, STAGES, FUSED, A_TMEM>;
+  using SM = TcSmem<BN, BK, STAGES, FUSED>;
   static_assert(!A_KMAJOR || BK == 32, "a K-major operand is loaded as one 128-byte-wide box");
-  static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0, "tile shape");
+  static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0 && BK <= 32, "tile shape");
   static_assert(!(FUSED && CHAIN > 0), "the fused epilogue consumes a whole-range accumulator");
   static_assert(CHAIN == 0 || BN <= 128, "register-resident running sums are sized for 128 columns");
   extern __shared__ uint8_t smem_dyn[];
@@ -440,7 +437,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_KMAJOR ? 0u : 1u) << 15) | (1u << 16) |
+      // D float32, A and B TF32; A (tensor memory) K-major, B (shared memory) MN-major
+      constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) |
                                  ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       uint32_t it = 0, chain = 0;
       bool ok = true;
@@ -461,31 +459,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (!mbar_wait(bar_conv(s), ph, abort_flag, status, kWaitConv)) { ok = false; break; }
             if (first) TC_TRACE(chain, 1);
             tc_fence_after();
-            const uint32_t a_hi = base + s * SM::STAGE_BYTES;
-            const uint32_t b_hi = a_hi + SM::A_BYTES;
-            const uint32_t a_lo = a_hi + SM::RAW_BYTES;                              // !A_TMEM only
-            const uint32_t b_lo = a_hi + SM::RAW_BYTES + (A_TMEM ? 0 : SM::A_BYTES);
-            const uint32_t ta_hi = tmem_base + SM::TMEM_A_COL + s * (2 * BK);        // A_TMEM only
+            const uint32_t b_hi = base + s * SM::STAGE_BYTES + SM::A_BYTES;
+            const uint32_t b_lo = base + s * SM::STAGE_BYTES + SM::RAW_BYTES;
+            const uint32_t ta_hi = tmem_base + SM::TMEM_A_COL + s * (2 * BK);
 #pragma unroll
             for (int kk = 0; kk < BK / 8; ++kk) {
-              // One MMA consumes 8 k-values: eight 128-byte rows (two 4-row swizzle atoms) of an
-              // MN-major operand, 32 bytes along a K-major row, or 8 columns of tensor memory.
+              // One MMA consumes 8 k-values: 8 columns of A in tensor memory, eight 128-byte rows
+              // (two 4-row swizzle atoms) of the MN-major B in shared memory.
               const uint64_t db_hi = smem_desc_mn(b_hi + kk * 1024, BK * 128);
               const uint64_t db_lo = smem_desc_mn(b_lo + kk * 1024, BK * 128);
-              const uint32_t acc0 = (first && kk == 0) ? 0u : 1u;
-              if constexpr (A_TMEM) {
-                mma_tf32_ts(d_tmem, ta_hi + BK + kk * 8, db_hi, idesc, acc0);
-                mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_lo, idesc, 1u);
-                mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_hi, idesc, 1u);
-              } else {
-                const uint64_t da_hi =
-                    A_KMAJOR ? smem_desc_sw128(a_hi + kk * 32, 16, 1024) : smem_desc_mn(a_hi + kk * 1024, BK * 128);
-                const uint64_t da_lo =
-                    A_KMAJOR ? smem_desc_sw128(a_lo + kk * 32, 16, 1024) : smem_desc_mn(a_lo + kk * 1024, BK * 128);
-                mma_tf32(d_tmem, da_lo, db_hi, idesc, acc0);
-                mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
-                mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
-              }
+              mma_tf32_ts(d_tmem, ta_hi + BK + kk * 8, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
+              mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_lo, idesc, 1u);
+              mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_hi, idesc, 1u);
             }
             first = false;
             mma_commit(bar_empty(s));  // the stage may be refilled once these MMAs have read it
@@ -514,52 +499,48 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!mbar_wait(bar_full(s), ph, abort_flag, status, kWaitFull)) { ok = false; break; }
         if (threadIdx.x == 0 && kb == 0) TC_TRACE((w - blockIdx.x) / gridDim.x, 5);
         if (threadIdx.x == 0 && kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 9);
-        // Every load of the stage is issued before the first store (registers are plentiful
-        // here): the hand-off to the MMA warp costs one shared-memory round trip, not one per piece.
-        constexpr int kConvThreads = kConvWarps * 32;
-        if constexpr (A_TMEM) {
-          // A: this thread's row of the K-major tile (128 bytes; 16-byte chunk c sits at c ^ (row % 8))
-          // goes to its lane of tensor memory, hi (the raw bits) in BK columns and lo in the next BK.
-          static_assert(BK == 32 && kConvWarps == 4, "one A row of 32 values per converter thread");
+        static_assert(kConvWarps == 4, "one A row (tensor-memory lane) per converter thread");
+        // A: this thread's row of the tile goes to its lane of tensor memory, hi (the raw bits) in BK
+        // columns and lo in the next BK.
+        uint32_t r[BK];
+        if constexpr (A_KMAJOR) {
+          // K-major tile, 128-byte rows: 16-byte chunk c of row m sits at chunk c ^ (m % 8)
+          static_assert(BK == 32, "a K-major row is one 128-byte swizzle span");
           const uint8_t *arow = smem + s * SM::STAGE_BYTES + threadIdx.x * 128;
-          uint32_t r[32];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             const uint4 q4 = *reinterpret_cast<const uint4 *>(arow + ((c ^ (threadIdx.x & 7)) << 4));
             r[4 * c + 0] = q4.x; r[4 * c + 1] = q4.y; r[4 * c + 2] = q4.z; r[4 * c + 3] = q4.w;
           }
-          const uint32_t ta = tmem_base + SM::TMEM_A_COL + s * (2 * BK) + ((uint32_t)(warp * 32) << 16);
-          tmem_st_32x32b_x32(ta, r);
-#pragma unroll
-          for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(tf32_lo(__uint_as_float(r[k])));
-          tmem_st_32x32b_x32(ta + BK, r);
-          // B: lo parts beside the raw tile in shared memory
-          const float4 *rawb = reinterpret_cast<const float4 *>(smem + s * SM::STAGE_BYTES + SM::A_BYTES);
-          float4 *lob = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
-          constexpr int kPieces = SM::B_BYTES / 16 / kConvThreads;
-          static_assert(SM::B_BYTES % (16 * kConvThreads) == 0, "a whole number of 16-byte pieces per thread");
-          float4 v[kPieces];
-#pragma unroll
-          for (int i = 0; i < kPieces; ++i) v[i] = rawb[threadIdx.x + i * kConvThreads];
-#pragma unroll
-          for (int i = 0; i < kPieces; ++i)
-            lob[threadIdx.x + i * kConvThreads] =
-                make_float4(tf32_lo(v[i].x), tf32_lo(v[i].y), tf32_lo(v[i].z), tf32_lo(v[i].w));
-          tmem_wait_st();
-          tc_fence_before();
         } else {
-          const float4 *raw = reinterpret_cast<const float4 *>(smem + s * SM::STAGE_BYTES);
-          float4 *lo = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
-          constexpr int kPieces = SM::RAW_BYTES / 16 / kConvThreads;
-          static_assert(SM::RAW_BYTES % (16 * kConvThreads) == 0, "a whole number of 16-byte pieces per thread");
-          float4 v[kPieces];
+          // MN-major tile [32-row chunk][k][32 rows]: element (k, m) of chunk m / 32 sits in the
+          // 128-byte line k at 32-byte piece ((m % 32) / 8) ^ (k % 4); a warp reads one line per k.
+          const uint8_t *acol = smem + s * SM::STAGE_BYTES + warp * (BK * 128) + ((lane & 7) << 2);
 #pragma unroll
-          for (int i = 0; i < kPieces; ++i) v[i] = raw[threadIdx.x + i * kConvThreads];
-#pragma unroll
-          for (int i = 0; i < kPieces; ++i)
-            lo[threadIdx.x + i * kConvThreads] =
-                make_float4(tf32_lo(v[i].x), tf32_lo(v[i].y), tf32_lo(v[i].z), tf32_lo(v[i].w));
+          for (int k = 0; k < BK; ++k)
+            r[k] = *reinterpret_cast<const uint32_t *>(acol + k * 128 + ((((lane >> 3) ^ (k & 3))) << 5));
         }
+        const uint32_t ta = tmem_base + SM::TMEM_A_COL + s * (2 * BK) + ((uint32_t)(warp * 32) << 16);
+        tmem_st_32x32b<BK>(ta, r);
+#pragma unroll
+        for (int k = 0; k < BK; ++k) r[k] = __float_as_uint(tf32_lo(__uint_as_float(r[k])));
+        tmem_st_32x32b<BK>(ta + BK, r);
+        // B: lo parts beside the raw tile in shared memory.  Every load is issued before the first
+        // store: the hand-off to the MMA warp costs one shared-memory round trip, not one per piece.
+        constexpr int kConvThreads = kConvWarps * 32;
+        const float4 *rawb = reinterpret_cast<const float4 *>(smem + s * SM::STAGE_BYTES + SM::A_BYTES);
+        float4 *lob = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
+        constexpr int kPieces = SM::B_BYTES / 16 / kConvThreads;
+        static_assert(SM::B_BYTES % (16 * kConvThreads) == 0, "a whole number of 16-byte pieces per thread");
+        float4 v[kPieces];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) v[i] = rawb[threadIdx.x + i * kConvThreads];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i)
+          lob[threadIdx.x + i * kConvThreads] =
+              make_float4(tf32_lo(v[i].x), tf32_lo(v[i].y), tf32_lo(v[i].z), tf32_lo(v[i].w));
+        tmem_wait_st();
+        tc_fence_before();
         fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
         mbar_arrive(bar_conv(s));
       }
@@ -956,7 +937,7 @@ struct TcMaps {
 template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
 cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st,
                       bool leave_reserved_sms = false) {
-  using SM = TcSmem<BN, BK, STAGES, FUSED, A_KMAJOR>;
+  using SM = TcSmem<BN, BK, STAGES, FUSED>;
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
   auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN>;
@@ -997,7 +978,7 @@ bool tc_shape_ok(const void *x, const void *y_or_w, long N, long M) {
 namespace {
 constexpr int kFwdBN = 128, kFwdBK = 32, kFwdStages = 4;
 constexpr int kFwdChain = 4;  // 4 k-blocks of 32 = 128 k-values (48 MMAs) per tensor-memory accumulation chain
-constexpr int kTrBN = 256, kTrBK = 16, kTrStages = 3;
+constexpr int kTrBN = 192, kTrBK = 16, kTrStages = 4;
 
 // k-blocks per split and the number of (non-empty) splits for the forward product.
 void forward_split_plan(long B, long N, long M, int &splits, int &k_per_split) {
