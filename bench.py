@@ -68,7 +68,8 @@ def measured_peaks():
 
 
 def algorithmic_work(N, M, H, B, s):
-    """Bytes and flops one step must move / do, per phase ("Roofline")."""
+    """Bytes and flops one step must move / do, per phase: the forward product reads W, x and the
+    bias and writes y; the trace update reads Cij and writes Cij and W (3 N M), reads x, y and the mask."""
     fwd_bytes = (N * M + B * N + B * M + M) * s
     upd_bytes = (3 * N * M + B * N + B * M) * s + N * H
     flops = 2.0 * B * N * M

@@ -54,6 +54,7 @@ struct TcWork {
   int a_row0;       // offset added to the A row coordinate (first output row of this launch)
   int a_box3;       // A stage fetched by one 3-D box (MN-major A whose row length is a multiple of 32)
   int b_box3_tiles; // column tiles [0, b_box3_tiles) fetch their B stage by one 3-D box
+  int b_prefetch;   // B k-blocks requested into L2 ahead of the load into shared memory (0 = none)
 };
 
 struct TcEpilogue {
@@ -147,6 +148,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
+}
+// The same boxes requested into L2 only: takes DRAM latency out of the shared-memory pipeline.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
@@ -398,9 +410,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
         int mt, nt, sp, kbeg, nkb;
         decode(w, mt, nt, sp, kbeg, nkb);
+        auto prefetch_b = [&](int kb) {   // k-block kb of this unit's B operand -> L2
+          const int k0 = kbeg + kb * BK;
+          if (nt < wk.b_box3_tiles) {
+            tma_prefetch_3d(&tmB3, 0, k0, nt * (BN / 32));
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) tma_prefetch_2d(&tmB, nt * BN + 32 * c, k0);
+          }
+        };
+        for (int kb = 0; kb < wk.b_prefetch && kb < nkb; ++kb) prefetch_b(kb);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
+          if (wk.b_prefetch > 0 && kb + wk.b_prefetch < nkb) prefetch_b(kb + wk.b_prefetch);
           if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status, kWaitEmpty)) { ok = false; break; }
           if (kb == 0) TC_TRACE((w - blockIdx.x) / gridDim.x, 0);
           if (kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 8);
@@ -977,6 +1000,7 @@ bool tc_shape_ok(const void *x, const void *y_or_w, long N, long M) {
 
 namespace {
 constexpr int kFwdBN = 128, kFwdBK = 32, kFwdStages = 4;
+constexpr int kFwdPrefetch = 8;  // k-blocks of W requested into L2 ahead of the shared-memory pipeline
 constexpr int kFwdChain = 4;  // 4 k-blocks of 32 = 128 k-values (48 MMAs) per tensor-memory accumulation chain
 constexpr int kTrBN = 192, kTrBK = 16, kTrStages = 4;
 
@@ -1016,7 +1040,7 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, kFwdBN / 32);
   if (!b3) tm.b3 = tm.b;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
-            b3 ? full_chunk_tiles(M, kFwdBN) : 0};
+            b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch};
   TcEpilogue ep{};
   ep.out = partial;
   ep.rows = B;
@@ -1090,7 +1114,7 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0};
+            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
   TcEpilogue ep{};
   ep.rows = rows;
   ep.cols = M;
@@ -1137,7 +1161,7 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0};
+            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
   TcEpilogue ep{};
   ep.out = delta + row_begin * M;
   ep.rows = rows;

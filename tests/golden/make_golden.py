@@ -1,8 +1,8 @@
 """Generate the golden input/output vectors under tests/golden/ from the UNMODIFIED
 StreamBrain reference (``BCPNN_BACKEND=cpu``), imported from its checkout.
 
-Needs a reference checkout (``SBB_REFERENCE_ROOT``, default ``/root/reference``)
-and the compiled OpenMP module built by ``oracle/build.py``.  The reference cannot
+Needs a reference checkout (environment variable ``SBB_REFERENCE_ROOT``, see
+``oracle/build.py``) and the compiled OpenMP module built by ``oracle/build.py``.  The reference cannot
 travel to other machines, so the small ``.npz`` files this script writes are
 committed and every other consumer reads those.
 
