@@ -666,6 +666,54 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       } else {
         const uint32_t buf = chain & 1u, aph = (chain >> 1) & 1u;
+        // Everything the fused epilogue needs besides the accumulator is fetched before waiting for
+        // the accumulator, so these global-memory latencies overlap the wait.
+        const bool has_mask = FUSED && ep.wmask != nullptr;
+        int hc_first = 0, hc_last = 0;
+        bool bits_ok = true, tile_fast = false;
+        float rci[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t mbits[4] = {0xFFu, 0xFFu, 0xFFu, 0xFFu};
+        float *crow[4] = {nullptr, nullptr, nullptr, nullptr};
+        float2 rcj_next[4];
+        float lane_rcj_next = 0.f;
+        long w_minus_c = 0;
+        if constexpr (FUSED) {
+          // per tile: reciprocal of Ci (0 = row below threshold), trace row pointers and the row's mask
+          // bytes for every hypercolumn this half tile touches (bit k: hypercolumn hc_first + k)
+          if (has_mask) {
+            hc_first = hc_of(n_base < ep.cols ? n_base : ep.cols - 1);
+            hc_last = hc_of(n_base + BN / 2 - 1 < ep.cols ? n_base + BN / 2 - 1 : ep.cols - 1);
+          }
+          bits_ok = hc_last - hc_first <= 7;
+          const int nhc = hc_last - hc_first + 1;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const long i = ep.row0 + grow[j];
+            rci[j] = rv[j] ? __ldg(ep.rci + i) : 0.f;
+            crow[j] = ep.Cij + i * ep.cols + n_base + lc;
+            if (has_mask && rv[j] && bits_ok) {
+              // every byte is loaded (index clamped into the row's range) so that the loads go out together
+              const uint8_t *mr = ep.wmask + i * ep.H + hc_first;
+              uint32_t byte[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) byte[k] = __ldg(mr + (k < nhc ? k : 0));
+              uint32_t bits = 0;
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                if (k < nhc && byte[k] != 0) bits |= 1u << k;
+              mbits[j] = bits;
+            }
+          }
+          // reciprocals of Cj for the first column group: this thread's pairs and, one per lane, the whole group
+#pragma unroll
+          for (int rep = 0; rep < 4; ++rep) {
+            const long n = n_base + lc + rep * 8;
+            rcj_next[rep] = n < ep.cols ? __ldg(reinterpret_cast<const float2 *>(ep.rcj + n)) : make_float2(0.f, 0.f);
+          }
+          lane_rcj_next = n_base + lane < ep.cols ? __ldg(ep.rcj + n_base + lane) : 0.f;
+          tile_fast = ep.fast_ok && bits_ok && (long)mt * 128 + 128 <= ep.rows;
+          w_minus_c = ep.W - ep.Cij;   // the weight of an element sits this far from its trace
+        }
         if (!mbar_wait(bar_acc_full(buf), aph, abort_flag, status, kWaitAccFull)) { ok = false; break; }
         if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 3);
         __syncwarp();
@@ -673,43 +721,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         // this warp's accumulator block: TMEM lanes 32q.., columns of its half tile
         const uint32_t tacc = tmem_base + buf * BN + ch * (BN / 2) + ((uint32_t)(32 * q) << 16);
         if constexpr (FUSED) {
-          // ---- per tile: reciprocal of Ci (0 = row below threshold), trace row pointers and the
-          // row's mask bytes for every hypercolumn this half tile touches (bit k: hc_first + k)
-          const bool has_mask = ep.wmask != nullptr;
-          int hc_first = 0, hc_last = 0;
-          if (has_mask) {
-            hc_first = hc_of(n_base < ep.cols ? n_base : ep.cols - 1);
-            hc_last = hc_of(n_base + BN / 2 - 1 < ep.cols ? n_base + BN / 2 - 1 : ep.cols - 1);
-          }
-          const bool bits_ok = hc_last - hc_first <= 7;
-          float rci[4];
-          uint32_t mbits[4];
-          float *crow[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const long i = ep.row0 + grow[j];
-            rci[j] = rv[j] ? __ldg(ep.rci + i) : 0.f;
-            crow[j] = ep.Cij + i * ep.cols + n_base + lc;
-            mbits[j] = 0xFFu;
-            if (has_mask && rv[j] && bits_ok) {
-              const uint8_t *mr = ep.wmask + i * ep.H + hc_first;
-              uint32_t bits = 0;
-#pragma unroll
-              for (int k = 0; k < 8; ++k)
-                if (hc_first + k <= hc_last && __ldg(mr + k) != 0) bits |= 1u << k;
-              mbits[j] = bits;
-            }
-          }
-          // reciprocals of Cj for the first column group: this thread's pairs and, one per lane, the whole group
-          float2 rcj_next[4];
-#pragma unroll
-          for (int rep = 0; rep < 4; ++rep) {
-            const long n = n_base + lc + rep * 8;
-            rcj_next[rep] = n < ep.cols ? __ldg(reinterpret_cast<const float2 *>(ep.rcj + n)) : make_float2(0.f, 0.f);
-          }
-          float lane_rcj_next = n_base + lane < ep.cols ? __ldg(ep.rcj + n_base + lane) : 0.f;
-          const bool tile_fast = ep.fast_ok && bits_ok && (long)mt * 128 + 128 <= ep.rows;
-          const long w_minus_c = ep.W - ep.Cij;   // the weight of an element sits this far from its trace
           if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 10);
 #pragma unroll 1
           for (int g = 0; g < NG; ++g) {
@@ -1000,7 +1011,7 @@ bool tc_shape_ok(const void *x, const void *y_or_w, long N, long M) {
 
 namespace {
 constexpr int kFwdBN = 128, kFwdBK = 32, kFwdStages = 4;
-constexpr int kFwdPrefetch = 8;  // k-blocks of W requested into L2 ahead of the shared-memory pipeline
+constexpr int kFwdPrefetch = 0;  // k-blocks of W requested into L2 ahead of the shared-memory pipeline (measured: no gain at 4-16)
 constexpr int kFwdChain = 4;  // 4 k-blocks of 32 = 128 k-values (48 MMAs) per tensor-memory accumulation chain
 constexpr int kTrBN = 192, kTrBK = 16, kTrStages = 4;
 
@@ -1041,6 +1052,9 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   if (!b3) tm.b3 = tm.b;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
             b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch};
+#ifdef SBB_TC_TRACE
+  if (const char *e = getenv("SBB_FWD_PREFETCH")) wk.b_prefetch = atoi(e);
+#endif
   TcEpilogue ep{};
   ep.out = partial;
   ep.rows = B;
