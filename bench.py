@@ -76,6 +76,11 @@ def algorithmic_work(N, M, H, B, s):
     return fwd_bytes, upd_bytes, flops
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one trace-update launch, from the ncu captures whose
+# summaries are profiles/step_kernels_stl10_f32_tensor_path.txt and profiles/trace_update_simt_stl10_f32.txt
+NCU_TRACE_UPDATE_DRAM_BYTES = {("stl10_f32", "tensor"): 2.000e9, ("stl10_f32", "general"): 3.24e9}
+
+
 class ClockSampler:
     """SM clock and throttle-reason samples during the timed region, read through NVML every few
     milliseconds on a thread of this process (read only; nothing is set)."""
@@ -410,11 +415,19 @@ def run_b200(args, wl, p, batch):
     roofline = None
     if per_step_trace:
         achieved = upd_b / (per_step_trace * 1e-3) / 1e9
+        # DRAM bytes of one launch from the ncu capture summarised in profiles/ (read + written);
+        # known for the workload / path that capture ran
+        traffic = NCU_TRACE_UPDATE_DRAM_BYTES.get((wl, "tensor" if tensor_path else "general")) if world == 1 and not args.dp_path else None
+        tf32_peak = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) / 2.0   # dense TF32 = half of bf16
         roofline = {"bound": "hbm", "kernel": "trace update (x^T y + EMA + log-ratio weights + mask)",
                     "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                    "traffic": None, "peak_source": peak_kind, "algorithmic_bytes": upd_b,
+                    "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes": upd_b,
                     "ms_per_launch": per_step_trace,
-                    "forward_ms": (sum(fwd_ms) / len(fwd_ms)) if fwd_ms else None}
+                    "forward_ms": (sum(fwd_ms) / len(fwd_ms)) if fwd_ms else None,
+                    # the same launch against the tensor pipe: three TF32 products per float32 product
+                    "tensor": {"achieved": 3 * flops / (per_step_trace * 1e-3) / 1e12, "peak": tf32_peak,
+                               "unit": "TFLOP/s (TF32)", "frac": 3 * flops / (per_step_trace * 1e-3) / 1e12 / tf32_peak}
+                    if tensor_path else None}
     # whole-step roofline: each phase bounded by the larger of its memory and compute time
     p32 = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) / 6.0 * 1e12  # fp32 via 3xTF32
     t_roof = max(fwd_b / (hbm * 1e9), flops / p32) + max(upd_b / (hbm * 1e9), flops / p32)

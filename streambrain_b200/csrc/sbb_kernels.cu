@@ -912,11 +912,10 @@ __device__ __forceinline__ Pick<T> shfl_pick(Pick<T> p, int off) {
 template <typename T>
 __global__ void __launch_bounds__(1024)
     mask_swap_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long M, long H, long Mc, long h,
-                     long iterations, const int *__restrict__ run_flag, T *rewrite_w,
+                     long iterations, T *rewrite_w,
                      const uint8_t *__restrict__ old_col, const T *__restrict__ Ci, const T *__restrict__ Cj,
                      const T *__restrict__ Cij, T cthr, T cthr4) {
   __shared__ Pick<T> s_max[32], s_min[32];
-  if (run_flag != nullptr && *run_flag == 0) return;   // the candidate-list path already did this update
   __shared__ long s_first0[32], s_first1[32];
   __shared__ int s_done;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -1004,8 +1003,9 @@ __global__ void __launch_bounds__(1024)
 // Phase A extracts, per chunk of rows, the `iterations` best silent rows (highest score, ties
 // to the larger index) and the `iterations` worst active rows (lowest score, ties to the
 // larger index); phase B reduces the chunk lists to one list per class and replays the swaps
-// exactly.  A NaN score makes the reference's scan order-dependent; phase A then raises a flag
-// and the one-CTA full scan (mask_swap_kernel) runs instead.
+// exactly.  A NaN score makes the reference's scan order-dependent; phase B reproduces that too
+// (see mask_replay_kernel).  Layers too small or too large for the lists, and more than
+// kSwapMaxIter iterations, take the one-CTA full scan (mask_swap_kernel).
 //
 // Scores are mapped to unsigned keys whose integer order is the class order (silent rows: score
 // descending first = larger key; active rows: the complement), so that one selection round is a
@@ -1101,8 +1101,7 @@ __device__ __forceinline__ void warp_select_regs(int cls, typename ScoreKey<T>::
 template <typename T, int R>
 __global__ void __launch_bounds__(kSwapThreads)
     mask_candidates_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ nom, const int *__restrict__ csum,
-                           long N, long H, long h, int iterations, long rows_per_chunk, T *cand_v, long *cand_i,
-                           int *nan_flag) {
+                           long N, long H, long h, int iterations, long rows_per_chunk, T *cand_v, long *cand_i) {
   typedef typename ScoreKey<T>::type K;
   __shared__ T s_lv[2][4 * kSwapMaxIter];
   __shared__ long s_li[2][4 * kSwapMaxIter];
@@ -1112,12 +1111,11 @@ __global__ void __launch_bounds__(kSwapThreads)
   const long r0 = (long)blockIdx.x * rows_per_chunk;
   const long r1 = r0 + rows_per_chunk < N ? r0 + rows_per_chunk : N;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  bool saw_nan = false;
   for (long j = r0 + threadIdx.x; j < r1; j += blockDim.x) {
     const uint8_t m = wmask[j * H + h];
     const T sc = swap_score(nom[j], csum[j]);
     uint8_t cl = m <= 1 ? m : 2;
-    if (cl < 2 && sc != sc) { saw_nan = true; cl = 2; }
+    if (sc != sc) cl = 2;   // a NaN score is in no best list (the replay handles the one place it can matter)
     s_sc[j - r0] = sc;
     s_cl[j - r0] = cl;
   }
@@ -1153,28 +1151,74 @@ __global__ void __launch_bounds__(kSwapThreads)
     const long slot = ((long)wid * gridDim.x + blockIdx.x) * iterations;
     warp_select_regs<T, 4>(wid, key, row, iterations, cand_v + slot, cand_i + slot);
   }
-  if (saw_nan) atomicOr(nan_flag, 1);
 }
 
 // Phase B, one CTA: reduce the chunk lists to the first `iterations` rows of each class, replay
 // the swaps on them (warp 0; every lane keeps one listed row and one moved row per class), then
 // rewrite the weights of hypercolumn h for the rows a swap touched (rewrite_w != null).
+//
+// NaN scores follow the reference's front-to-back scan: the scan's first row of a class holds the
+// pick until a row compares better, and nothing compares better than NaN, so a class whose
+// lowest-index row has a NaN score picks that row; a NaN score anywhere else is never picked.
+// Besides the best rows, the replay therefore tracks the `iterations + 1` lowest-index rows of
+// each class (one row leaves a class per swap) with their NaN flags; NaN rows are in no best list.
+constexpr int kLowSlots = 2 * 32;   // >= kSwapMaxIter + 1 lowest-index rows per class, two per lane
 template <typename T>
 __global__ void __launch_bounds__(kSwapThreads)
     mask_replay_kernel(uint8_t *wmask, const T *__restrict__ nom, int *csum, long N, long M, long H, long Mc, long h,
                        int iterations, int chunks, const T *__restrict__ cand_v, const long *__restrict__ cand_i,
-                       const int *__restrict__ nan_flag, T *rewrite_w, const T *__restrict__ Ci,
-                       const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr, T cthr4) {
+                       T *rewrite_w, const T *__restrict__ Ci, const T *__restrict__ Cj, const T *__restrict__ Cij,
+                       T cthr, T cthr4) {
   typedef typename ScoreKey<T>::type K;
   constexpr int R1 = kSwapSlots / 4 / 32;   // registers per lane for a quarter of one class's chunk lists
+  constexpr uint32_t kNone = 0xFFFFFFFFu;
   __shared__ T l1_v[2][4 * kSwapMaxIter], top_v[2][kSwapMaxIter];
   __shared__ long l1_i[2][4 * kSwapMaxIter], top_i[2][kSwapMaxIter];
+  __shared__ uint32_t low_row[2][kLowSlots];
+  __shared__ int low_cs[2][kLowSlots];
+  __shared__ uint8_t low_nan[2][kLowSlots];
+  __shared__ int low_cnt[2], win_cnt[kSwapThreads / 32][2];
   __shared__ long touched[2 * kSwapMaxIter];
   __shared__ int n_touched;
-  if (*nan_flag) return;   // the full scan handles this update
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int total = chunks * iterations;   // entries per class, <= kSwapSlots
-  if (threadIdx.x == 0) n_touched = 0;
+  if (threadIdx.x == 0) {
+    n_touched = 0;
+    low_cnt[0] = low_cnt[1] = 0;
+  }
+  for (int e = threadIdx.x; e < 2 * kLowSlots; e += blockDim.x) low_row[e / kLowSlots][e % kLowSlots] = kNone;
+  __syncthreads();
+  // the lowest-index rows of each class: windows of blockDim rows from row 0 until both lists are full
+  const int want = iterations + 1;
+  for (long w0 = 0; w0 < N; w0 += blockDim.x) {
+    const long j = w0 + threadIdx.x;
+    const uint8_t m = j < N ? wmask[j * H + h] : (uint8_t)2;
+    unsigned bal[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      bal[c] = __ballot_sync(0xffffffffu, m == c);
+      if (lane == 0) win_cnt[wid][c] = __popc(bal[c]);
+    }
+    __syncthreads();
+    if (m <= 1) {
+      int pos = low_cnt[m] + __popc(bal[m] & ((1u << lane) - 1u));
+      for (int w = 0; w < wid; ++w) pos += win_cnt[w][m];
+      if (pos < want) {
+        const T nm = nom[j];
+        low_row[m][pos] = (uint32_t)j;
+        low_nan[m][pos] = nm != nm ? 1 : 0;
+        low_cs[m][pos] = csum[j];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+        low_cnt[0] += win_cnt[w][0];
+        low_cnt[1] += win_cnt[w][1];
+      }
+    __syncthreads();
+    if (low_cnt[0] >= want && low_cnt[1] >= want) break;   // uniform: read after the barrier
+  }
   {
     const int cls = wid & 1, slice = wid >> 1;
     const int q = (total + 3) / 4, b = slice * q, e = b + q < total ? b + q : total;
@@ -1204,52 +1248,80 @@ __global__ void __launch_bounds__(kSwapThreads)
   }
   __syncthreads();
   if (wid == 0) {
-    // per class c: slot A = listed row number `lane`, slot B = the row moved into the class by swap `lane`
+    // per class c: slot A = listed best row number `lane`; slot B = the row moved into the class by swap
+    // `lane` (it may carry a NaN score: key 0, but still a member); L0, L1 = listed lowest rows lane, lane + 32
     K ka[2], kb[2] = {0, 0};
-    uint32_t ra[2], rb[2] = {0u, 0u};
+    uint32_t ra[2], rb[2] = {kNone, kNone}, l0[2], l1[2];
     T na[2], nb[2] = {(T)0, (T)0};
-    int ca[2], cb[2] = {0, 0};
+    int ca[2], cb[2] = {0, 0}, c0[2], c1[2];
+    bool nanb[2] = {false, false}, n0[2], n1[2];
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
       const long i = lane < iterations ? top_i[c][lane] : -1;
       ka[c] = i >= 0 ? class_key<T>(c, top_v[c][lane]) : (K)0;
-      ra[c] = i >= 0 ? (uint32_t)i : 0u;
+      ra[c] = i >= 0 ? (uint32_t)i : kNone;
       na[c] = i >= 0 ? nom[i] : (T)0;
       ca[c] = i >= 0 ? csum[i] : 0;
+      l0[c] = low_row[c][lane];      n0[c] = low_nan[c][lane] != 0;      c0[c] = low_cs[c][lane];
+      l1[c] = low_row[c][lane + 32]; n1[c] = low_nan[c][lane + 32] != 0; c1[c] = low_cs[c][lane + 32];
     }
+    const T quiet_nan = (T)NAN;
     for (int it = 0; it < iterations; ++it) {
       K best[2];
-      uint32_t win[2];
-      T mv_nom[2];
-      int mv_cs[2];
+      uint32_t pick[2];
+      bool pick_nan[2];
+      bool stop = false;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        // the class's first row in index order, and whether its score is NaN
+        uint32_t f = l0[c] < l1[c] ? l0[c] : l1[c];
+        f = rb[c] < f ? rb[c] : f;
+        const uint32_t first = __reduce_min_sync(0xffffffffu, f);
+        const bool first_is_nan = __any_sync(0xffffffffu, first != kNone && ((l0[c] == first && n0[c]) ||
+                                                                           (l1[c] == first && n1[c]) ||
+                                                                           (rb[c] == first && nanb[c])));
+        // the best row among those with a number for a score
         best[c] = ScoreKey<T>::warp_max(ka[c] > kb[c] ? ka[c] : kb[c]);
         uint32_t mine = 0;
         if (best[c] != 0 && ka[c] == best[c]) mine = ra[c] + 1u;
         if (best[c] != 0 && kb[c] == best[c] && rb[c] + 1u > mine) mine = rb[c] + 1u;
-        win[c] = __reduce_max_sync(0xffffffffu, mine);
+        const uint32_t win = __reduce_max_sync(0xffffffffu, mine);
+        pick_nan[c] = first_is_nan;
+        pick[c] = first_is_nan ? first : win - 1u;
+        if (first == kNone || (!first_is_nan && best[c] == 0)) stop = true;   // the class is empty
       }
-      // no silent or no active row left, or the best silent row scores below the worst active one
-      if (best[0] == 0 || best[1] == 0 ||
-          class_key_value<T>(0, best[0]) < class_key_value<T>(1, best[1]))
+      // the best silent row scores below the worst active one (never true with a NaN on either side)
+      if (stop || (!pick_nan[0] && !pick_nan[1] &&
+                   class_key_value<T>(0, best[0]) < class_key_value<T>(1, best[1])))
         break;   // uniform across the warp
+      T mv_nom[2];
+      int mv_cs[2];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const bool own_a = ka[c] == best[c] && ra[c] + 1u == win[c];
-        const bool own_b = !own_a && kb[c] == best[c] && rb[c] + 1u == win[c];
-        const unsigned who = __ballot_sync(0xffffffffu, own_a || own_b);
+        const uint32_t p = pick[c];
+        const bool own_a = ka[c] != 0 && ra[c] == p;
+        const bool own_b = rb[c] == p;
+        const bool own_l0 = l0[c] == p, own_l1 = l1[c] == p;
+        // the slots of the best lists know the numerator; a row picked for its NaN is only in L or B
+        unsigned who = __ballot_sync(0xffffffffu, own_a || own_b);
+        if (who == 0) who = __ballot_sync(0xffffffffu, own_l0 || own_l1);
         const int src = __ffs(who) - 1;
-        mv_nom[c] = __shfl_sync(0xffffffffu, own_a ? na[c] : nb[c], src);
-        mv_cs[c] = __shfl_sync(0xffffffffu, own_a ? ca[c] : cb[c], src);
+        const T my_nom = own_a ? na[c] : (own_b ? nb[c] : quiet_nan);
+        const int my_cs = own_a ? ca[c] : (own_b ? cb[c] : (own_l0 ? c0[c] : c1[c]));
+        mv_nom[c] = __shfl_sync(0xffffffffu, my_nom, src);
+        mv_cs[c] = __shfl_sync(0xffffffffu, my_cs, src);
         if (own_a) ka[c] = 0;
-        if (own_b) kb[c] = 0;
+        if (own_b) { kb[c] = 0; rb[c] = kNone; nanb[c] = false; }
+        if (own_l0) l0[c] = kNone;
+        if (own_l1) l1[c] = kNone;
       }
       if (lane == it) {
         // the silent row becomes active with one more connection, the active row silent with one fewer
-        const long up = (long)win[0] - 1, down = (long)win[1] - 1;
-        rb[1] = (uint32_t)up;   nb[1] = mv_nom[0]; cb[1] = mv_cs[0] + 1; kb[1] = class_key<T>(1, swap_score(nb[1], cb[1]));
-        rb[0] = (uint32_t)down; nb[0] = mv_nom[1]; cb[0] = mv_cs[1] - 1; kb[0] = class_key<T>(0, swap_score(nb[0], cb[0]));
+        const long up = (long)pick[0], down = (long)pick[1];
+        rb[1] = pick[0]; nb[1] = mv_nom[0]; cb[1] = mv_cs[0] + 1; nanb[1] = pick_nan[0];
+        kb[1] = nanb[1] ? (K)0 : class_key<T>(1, swap_score(nb[1], cb[1]));
+        rb[0] = pick[1]; nb[0] = mv_nom[1]; cb[0] = mv_cs[1] - 1; nanb[0] = pick_nan[1];
+        kb[0] = nanb[0] ? (K)0 : class_key<T>(0, swap_score(nb[0], cb[0]));
         wmask[up * H + h] = 1;
         wmask[down * H + h] = 0;
         csum[up] = cb[1];
@@ -1314,7 +1386,6 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
                                                                  h, ms.score, ms.csum, ms.old_col);
   cudaError_t e = launched();
   if (e != cudaSuccess) return e;
-  const int *run_flag = nullptr;
   // candidate lists: rows fit 32-bit indices and a chunk (<= kSwapCacheRows rows) fits shared memory
   const int max_chunks = iterations >= 1 && iterations <= kSwapMaxIter ? kSwapSlots / (int)iterations : 0;
   if (max_chunks > 0 && N >= 1024 && N < (1l << 31) && (N + max_chunks - 1) / max_chunks <= kSwapCacheRows) {
@@ -1322,13 +1393,11 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
     if (chunks > max_chunks) chunks = max_chunks;
     const long rows_per_chunk = (N + chunks - 1) / chunks;
     chunks = (int)((N + rows_per_chunk - 1) / rows_per_chunk);
-    e = cudaMemsetAsync(ms.nan_flag, 0, sizeof(int), st);
-    if (e != cudaSuccess) return e;
     const size_t dyn = (size_t)rows_per_chunk * (sizeof(T) + 1);
     const long slice = (rows_per_chunk + 3) / 4;   // rows one warp keeps in registers, 32 per register
 #define SBB_CAND(R)                                                                                              \
   mask_candidates_kernel<T, R><<<chunks, kSwapThreads, dyn, st>>>(wmask, ms.score, ms.csum, N, H, h, (int)iterations, \
-                                                                  rows_per_chunk, ms.cand_v, ms.cand_i, ms.nan_flag)
+                                                                  rows_per_chunk, ms.cand_v, ms.cand_i)
     if (slice <= 4 * 32) SBB_CAND(4);
     else if (slice <= 8 * 32) SBB_CAND(8);
     else if (slice <= 16 * 32) SBB_CAND(16);
@@ -1337,13 +1406,10 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
     e = launched();
     if (e != cudaSuccess) return e;
     mask_replay_kernel<T><<<1, kSwapThreads, 0, st>>>(wmask, ms.score, ms.csum, N, M, H, Mc, h, (int)iterations, chunks,
-                                                     ms.cand_v, ms.cand_i, ms.nan_flag, rewrite_w, Ci, Cj, Cij, cthr,
-                                                     cthr4);
-    e = launched();
-    if (e != cudaSuccess) return e;
-    run_flag = ms.nan_flag;   // the full scan below only runs when a NaN score was seen
+                                                     ms.cand_v, ms.cand_i, rewrite_w, Ci, Cj, Cij, cthr, cthr4);
+    return launched();
   }
-  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, ms.score, ms.csum, N, M, H, Mc, h, iterations, run_flag, rewrite_w,
+  mask_swap_kernel<T><<<1, 1024, 0, st>>>(wmask, ms.score, ms.csum, N, M, H, Mc, h, iterations, rewrite_w,
                                           ms.old_col, Ci, Cj, Cij, cthr, cthr4);
   return launched();
 }

@@ -147,8 +147,8 @@ def _mask_case(rs, n, hc, mc, dtype, density=0.3):
 
 
 @pytest.mark.parametrize("n,hc,mc", [(1, 1, 2), (53, 4, 6), (128, 2, 64), (700, 3, 100), (2500, 30, 10),
-                                     # 4096 rows and more take the candidate-list search instead of the full scan
-                                     (4096, 2, 8), (5000, 3, 20), (30011, 2, 10)])
+                                     # 1024 rows and more take the candidate-list search instead of the full scan
+                                     (1024, 2, 8), (4096, 2, 8), (5000, 3, 20), (30011, 2, 10)])
 def test_update_mask_f64_identical_to_oracle(k, port_kernels, n, hc, mc):
     rs = np.random.RandomState(n)
     wmask, w, Ci, Cj, Cij = _mask_case(rs, n, hc, mc, np.float64)
@@ -177,11 +177,33 @@ def test_update_mask_edge_cases(k, port_kernels):
     assert np.array_equal(k.update_mask(wmask.copy(), w, Ci, Cj, Cij, 0.01, 2, 5, 0, 0), wmask)
 
 
+@pytest.mark.parametrize("n", [1500, 6000])
+@pytest.mark.parametrize("iterations", [3, 16, 32])
+def test_update_mask_with_nan_scores_at_the_head_of_a_class(k, port_kernels, n, iterations):
+    """Always-on inputs (Ci == 1 and Cij == Cj) give NaN scores.  The reference's scan picks a NaN
+    row exactly when it is the lowest-index row of its class, which can repeat swap after swap
+    (the row heads the other class next) -- the candidate-list search must follow it move by move.
+    Several low rows of both classes are made NaN, among them row 0 and the first silent row."""
+    rs = np.random.RandomState(7 * n + iterations)
+    wmask, w, Ci, Cj, Cij = _mask_case(rs, n, 3, 6, np.float64, density=0.5)
+    with np.errstate(all="ignore"):
+        for h in range(3):
+            Ci2, Cij2 = Ci.copy(), Cij.copy()
+            first_silent = int(np.flatnonzero(wmask[:, h] == 0)[0])
+            first_active = int(np.flatnonzero(wmask[:, h] == 1)[0])
+            hot = sorted({0, 1, 2, 5, 9, first_silent, first_active, n // 2, n - 1})
+            Ci2[hot] = 1.0
+            Cij2[hot] = Cj[None, :]
+            got = k.update_mask(wmask.copy(), w, Ci2, Cj, Cij2, 0.01, 3, 6, h, iterations)
+            want = port_kernels.update_mask(wmask.copy(), w, Ci2, Cj, Cij2, 0.01, 3, 6, h, iterations)
+            assert np.array_equal(got, want), (h, np.flatnonzero((got != want).any(axis=1))[:10])
+
+
 @pytest.mark.parametrize("n", [300, 6000])
 def test_update_mask_with_nan_and_inf_scores(k, port_kernels, n):
     """Rows whose Ci is exactly 1 (an input that is always on) divide by zero in the score:
     +-inf and NaN scores must be ranked exactly as the reference's front-to-back scan ranks
-    them, in the full scan and (n >= 4096) in the candidate-list search with its fallback."""
+    them, in the full scan (small n) and in the candidate-list search."""
     rs = np.random.RandomState(n)
     wmask, w, Ci, Cj, Cij = _mask_case(rs, n, 3, 6, np.float64, density=0.4)
     for variant in range(3):
