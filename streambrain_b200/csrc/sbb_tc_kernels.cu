@@ -1015,18 +1015,34 @@ constexpr int kFwdPrefetch = 0;  // k-blocks of W requested into L2 ahead of the
 constexpr int kFwdChain = 4;  // 4 k-blocks of 32 = 128 k-values (48 MMAs) per tensor-memory accumulation chain
 constexpr int kTrBN = 192, kTrBK = 16, kTrStages = 4;
 
-// k-blocks per split and the number of (non-empty) splits for the forward product.
+// k-blocks per split and the number of (non-empty) splits for the forward product: the split count
+// that minimises (waves of CTAs) x (k-blocks per unit), plus the cost of writing and re-reading
+// one more partial result.  A unit count just above a multiple of the SM count would otherwise
+// run a nearly empty last wave (192 units on 148 SMs take as long as 296).
 void forward_split_plan(long B, long N, long M, int &splits, int &k_per_split) {
   const long tiles = ((B + 127) / 128) * ((M + kFwdBN - 1) / kFwdBN);
   const long kblocks = (N + kFwdBK - 1) / kFwdBK;
   const int dev = current_device();
   const long sms = g_sm_count_tc[dev] > 0 ? g_sm_count_tc[dev] : 148;
-  long want = tiles >= sms ? 1 : sms / tiles;
-  if (want > kblocks / 8) want = kblocks / 8 > 0 ? kblocks / 8 : 1;  // at least 8 k-blocks per split
-  if (want > 64) want = 64;
-  const long per = (kblocks + want - 1) / want;
-  splits = (int)((kblocks + per - 1) / per);
-  k_per_split = (int)per * kFwdBK;
+  long max_splits = kblocks / 8 > 0 ? kblocks / 8 : 1;   // at least 8 k-blocks per split
+  if (max_splits > 64) max_splits = 64;
+  // one partial result costs B*M*8 bytes of traffic; in units of one k-block of one CTA (about 0.8 us
+  // at 6.5 TB/s, spread over the SMs)
+  const double partial_cost = (double)B * (double)M * 8.0 / 6.5e12 / 0.8e-6;
+  double best_cost = 0.0;
+  long best_per = kblocks;
+  for (long want = 1; want <= max_splits; ++want) {
+    const long per = (kblocks + want - 1) / want;
+    const long actual = (kblocks + per - 1) / per;
+    const long waves = (tiles * actual + sms - 1) / sms;
+    const double cost = (double)waves * (double)per + (double)actual * partial_cost;
+    if (want == 1 || cost < best_cost) {
+      best_cost = cost;
+      best_per = per;
+    }
+  }
+  splits = (int)((kblocks + best_per - 1) / best_per);
+  k_per_split = (int)best_per * kFwdBK;
 }
 }  // namespace
 
