@@ -1334,13 +1334,27 @@ __global__ void __launch_bounds__(kSwapThreads)
   }
   __syncthreads();
   if (rewrite_w == nullptr) return;
-  // a touched row's weights in hypercolumn h follow its final mask bit (idempotent when a row was touched twice)
+  // a touched row's weights in hypercolumn h follow its final mask bit (idempotent when a row was touched
+  // twice).  Row data first (one thread per touched row), so that the element loop has independent loads only.
+  __shared__ T t_ci[2 * kSwapMaxIter];
+  __shared__ uint8_t t_on[2 * kSwapMaxIter];
   const int nt = n_touched;
-  for (long t = threadIdx.x; t < (long)nt * Mc; t += blockDim.x) {
-    const long i = touched[t / Mc], col = h * Mc + t % Mc;
-    const T ci = Ci[i], cj = Cj[col];
+  if ((int)threadIdx.x < nt) {
+    const long i = touched[threadIdx.x];
+    const T ci = Ci[i];
+    t_ci[threadIdx.x] = ci;
+    t_on[threadIdx.x] = wmask[i * H + h] != 0 && !(ci < cthr);
+  }
+  __syncthreads();
+  const long total_elems = (long)nt * Mc;
+#pragma unroll 4
+  for (long t = threadIdx.x; t < total_elems; t += blockDim.x) {
+    const int r = (int)(t / Mc);
+    const long i = touched[r], col = h * Mc + t % Mc;
+    const T cj = Cj[col];
+    const T cij = Cij[i * M + col];
     T v = (T)0;
-    if (wmask[i * H + h] != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[i * M + col], ci, cj, cthr4);
+    if (t_on[r] && !(cj < cthr)) v = log_ratio(cij, t_ci[r], cj, cthr4);
     rewrite_w[i * M + col] = v;
   }
 }

@@ -975,12 +975,12 @@ cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, 
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
   auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN>;
-  static bool configured[64] = {false};
+  static std::atomic<bool> configured[64];   // per device; setting the attribute twice is harmless
   const int dev = current_device();
-  if (!configured[dev]) {
+  if (!configured[dev].load()) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
     if (e != cudaSuccess) return e;
-    configured[dev] = true;
+    configured[dev].store(true);
   }
   const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
   if (total <= 0) return cudaSuccess;
@@ -1116,12 +1116,13 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
                                    const float *Cj, float *Cij, float *w, const uint8_t *wmask, const int *col_hc,
                                    float *scratch, TraceParams<float> p, long row_begin, long row_end,
                                    cudaStream_t st) {
-  static long magic_for_mc = -1, magic_for_m = -1;
-  static uint32_t magic_value = 0;
+  // verified once per layer shape and host thread
+  static thread_local long magic_for_mc = -1, magic_for_m = -1;
+  static thread_local uint32_t magic_value = 0;
   uint32_t hc_magic = 0;
   if (wmask != nullptr && H > 0) {
     const long Mc = M / H;
-    if (magic_for_mc != Mc || magic_for_m != M) {   // verified once per layer shape
+    if (magic_for_mc != Mc || magic_for_m != M) {
       magic_value = exact_division_magic(Mc, M + 2);
       magic_for_mc = Mc;
       magic_for_m = M;
