@@ -439,7 +439,7 @@ def run_b200(args, wl, p, batch):
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         try:
-            sps, med, done, kind, cores = cpu_time_steps(p, batch, 3, 1, budget_s=40.0, mask=mask)
+            sps, med, done, kind, cores = cpu_time_steps(p, batch, 12, 1, budget_s=30.0, mask=mask)
             cpu = {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "ms_per_step": med * 1e3,
                    "sample": "%d full steps of the same workload (batch %d) after 1 warm-up" % (done, batch)}
         except Exception as e:  # the CPU leg must never take the GPU line down
