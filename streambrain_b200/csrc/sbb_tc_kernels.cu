@@ -8,12 +8,15 @@
 //
 // float32 accuracy on TF32 tensor cores: every operand value v is used as
 // hi = v truncated to TF32 (what the tensor core reads of the raw float32) and
-// lo = tf32(v - hi), written beside it in shared memory, and each k-step issues
-// three MMAs  hi*hi + hi*lo + lo*hi  into one float32 accumulator in tensor
-// memory (the dropped lo*lo term is below 2^-20 relative).
+// lo = tf32(v - hi), and each k-step issues three MMAs  hi*hi + hi*lo + lo*hi
+// into one float32 accumulator in tensor memory (the dropped lo*lo term is
+// below 2^-20 relative).  A's hi and lo parts are staged in tensor memory, B's
+// lo parts beside the raw tile in shared memory: the tensor core fetches only B
+// from shared memory.
 //
 // Roles inside a CTA (448 threads, one CTA per SM, tiles walked persistently):
-//   warps 0-3   converters: wait for a TMA stage, write the lo parts beside it
+//   warps 0-3   converters: wait for a TMA stage, write A's hi / lo parts to tensor
+//               memory (one tile row per thread) and B's lo parts to shared memory
 //   warps 4-11  epilogue: tcgen05.ld the accumulator (16x256b shape, so that four
 //               lanes cover 32 contiguous bytes of a row) and either store it or run
 //               the trace / weight arithmetic against 32 x 32 blocks of Cij that TMA
@@ -261,14 +264,15 @@ __device__ __forceinline__ float tf32_lo(float v) {
   return __fsub_rn(c, __fsub_rn(c, lo));
 }
 
+// Optional timeline (compile with -DSBB_TC_TRACE): CTA 0 stamps clock64() at the hand-offs of its first
+// 64 tiles -- event numbers: 0 / 8 first / last TMA issue, 5 / 9 first / last conversion, 7 accumulator
+// free, 1 first MMA, 2 accumulator committed, 3 epilogue start, 10 epilogue data ready, 13-15 column
+// groups done, 4 epilogue end -- and sbb_tc_trace_read copies the 64 x 16 stamps out.  Compiled out otherwise.
 #ifdef SBB_TC_TRACE
 __device__ unsigned long long g_tc_trace[64 * 16];
 #define TC_TRACE(tile, ev) do { if (blockIdx.x == 0 && (tile) < 64) g_tc_trace[(tile) * 16 + (ev)] = (unsigned long long)clock64(); } while (0)
-__device__ unsigned long long g_tc_trace2[16 * 4 * 8];
-#define TC_TRACE2(tile, g, ev)
 #else
 #define TC_TRACE(tile, ev)
-#define TC_TRACE2(tile, g, ev)
 #endif
 
 // ------------------------------------------------------------------ the kernel
@@ -1069,7 +1073,7 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
             b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch};
 #ifdef SBB_TC_TRACE
-  if (const char *e = getenv("SBB_FWD_PREFETCH")) wk.b_prefetch = atoi(e);
+  if (const char *e = getenv("SBB_FWD_PREFETCH")) wk.b_prefetch = atoi(e);   // timeline builds may vary the distance
 #endif
   TcEpilogue ep{};
   ep.out = partial;
@@ -1209,10 +1213,6 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
 extern "C" int sbb_tc_trace_read(unsigned long long *out) {
   cudaDeviceSynchronize();
   return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 64 * 16);
-}
-extern "C" int sbb_tc_trace2_read(unsigned long long *out) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, g_tc_trace2, sizeof(unsigned long long) * 16 * 4 * 8);
 }
 #endif
 
