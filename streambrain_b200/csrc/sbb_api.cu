@@ -290,7 +290,9 @@ int layer_dp_apply_rows(sbb_layer *L, const T *delta, long Bg, long rb, long re,
                                       static_cast<const T *>(L->state[SBB_STATE_CJ]),
                                       static_cast<T *>(L->state[SBB_STATE_CIJ]),
                                       static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
-                                      static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 1, rb, re, st));
+                                      static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 1, rb, re, st,
+                                      // the arithmetic of the path that formed the sums (see sbb_math.cuh)
+                                      tensor_path<T>(delta, delta, L->N, L->M)));
   return SBB_OK;
 }
 

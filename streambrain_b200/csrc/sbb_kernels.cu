@@ -657,7 +657,9 @@ template cudaError_t launch_outer_product<double>(const double *, const double *
 // One thread per four consecutive columns, walking kApplyRows rows: the column data (Cj, the
 // hypercolumn of each column) is set up once per thread, rows only add Ci and the mask byte.
 constexpr int kApplyRows = 8;
-template <typename T>
+// FAST (float32 only): the tensor-core path's arithmetic (see sbb_math.cuh), so that the data-parallel
+// step and the fused single-device step of that path compute the same values from the same sums.
+template <typename T, bool FAST>
 __global__ void __launch_bounds__(256)
     trace_apply_kernel(const T *__restrict__ delta, long M, long H, long Mc, const T *__restrict__ Ci,
                        const T *__restrict__ Cj, T *Cij, T *W, const uint8_t *__restrict__ wmask, TraceParams<T> p,
@@ -674,13 +676,16 @@ __global__ void __launch_bounds__(256)
     cj[c] = c < valid ? Cj[j + c] : (T)1;
     col_on[c] = c < valid && !(cj[c] < p.cthr);
     hc[c] = wmask ? (j + (c < valid ? c : 0)) / Mc : 0;
+    if (FAST) cj[c] = (T)1 / cj[c];   // from here on the reciprocal
   }
+  const T ema_scale = p.taupdt / p.batch;
   const bool one_hc = hc[0] == hc[3] && hc[0] == hc[1] && hc[0] == hc[2];
   const long r0 = row_begin + (long)blockIdx.x * kApplyRows;
   const long r1 = r0 + kApplyRows < row_end ? r0 + kApplyRows : row_end;
   for (long i = r0; i < r1; ++i) {
-    const T ci = Ci[i];
+    T ci = Ci[i];
     const bool row_on = !(ci < p.cthr);
+    if (FAST) ci = (T)1 / ci;
     bool on[4];
     if (wmask == nullptr) {
 #pragma unroll
@@ -699,9 +704,15 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       if (c < valid) {
-        const T cij = ema ? trace_ema(c4[c], d4[c], p) : c4[c];
+        T cij = c4[c];
+        if constexpr (FAST) {
+          if (ema) cij = trace_ema_fast(c4[c], d4[c], p.one_minus, ema_scale);
+          w4[c] = on[c] ? log_ratio_fast(cij, ci, cj[c], p.cthr4) : 0.f;
+        } else {
+          if (ema) cij = trace_ema(c4[c], d4[c], p);
+          w4[c] = on[c] ? log_ratio(cij, ci, cj[c], p.cthr4) : (T)0;
+        }
         c4[c] = cij;
-        w4[c] = on[c] ? log_ratio(cij, ci, cj[c], p.cthr4) : (T)0;
       }
     }
     if (ema) store4(Cij + i * M + j, c4, vec, valid);
@@ -712,7 +723,7 @@ __global__ void __launch_bounds__(256)
 template <typename T>
 cudaError_t launch_trace_apply(const T *delta, long N, long M, long H, long Mc, const T *Ci, const T *Cj, T *Cij,
                                T *w, const uint8_t *wmask, TraceParams<T> p, int ema, long row_begin, long row_end,
-                               cudaStream_t st) {
+                               cudaStream_t st, bool fast) {
   (void)N;
   constexpr int V = Vec16<T>::N;
   if (row_end <= row_begin || M == 0) return cudaSuccess;
@@ -721,16 +732,23 @@ cudaError_t launch_trace_apply(const T *delta, long N, long M, long H, long Mc, 
   const long row_groups = (row_end - row_begin + kApplyRows - 1) / kApplyRows;
   const int threads = qpr >= 256 ? 256 : (int)((qpr + 31) / 32 * 32);
   const dim3 grid((unsigned)row_groups, (unsigned)((qpr + threads - 1) / threads));
-  trace_apply_kernel<T><<<grid, threads, 0, st>>>(delta, M, H, Mc, Ci, Cj, Cij, w, wmask, p, ema, row_begin, row_end,
-                                                  vec);
+  if constexpr (std::is_same<T, float>::value) {
+    if (fast && p.cthr4 >= 1e-30f) {
+      trace_apply_kernel<float, true><<<grid, threads, 0, st>>>(delta, M, H, Mc, Ci, Cj, Cij, w, wmask, p, ema, row_begin,
+                                                                row_end, vec);
+      return launched();
+    }
+  }
+  trace_apply_kernel<T, false><<<grid, threads, 0, st>>>(delta, M, H, Mc, Ci, Cj, Cij, w, wmask, p, ema, row_begin,
+                                                         row_end, vec);
   return launched();
 }
 template cudaError_t launch_trace_apply<float>(const float *, long, long, long, long, const float *, const float *,
                                                float *, float *, const uint8_t *, TraceParams<float>, int, long, long,
-                                               cudaStream_t);
+                                               cudaStream_t, bool);
 template cudaError_t launch_trace_apply<double>(const double *, long, long, long, long, const double *,
                                                 const double *, double *, double *, const uint8_t *,
-                                                TraceParams<double>, int, long, long, cudaStream_t);
+                                                TraceParams<double>, int, long, long, cudaStream_t, bool);
 
 // Un-fused trace update in the NumPy operation order: (1-t)*C + t*(sum/B).
 template <typename T>

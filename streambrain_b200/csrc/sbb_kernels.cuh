@@ -65,7 +65,7 @@ cudaError_t launch_outer_product(const T *x, const T *y, long B, long N, long M,
 template <typename T>
 cudaError_t launch_trace_apply(const T *delta, long N, long M, long H, long Mc, const T *Ci, const T *Cj, T *Cij,
                                T *w, const uint8_t *wmask, TraceParams<T> p, int ema, long row_begin, long row_end,
-                               cudaStream_t st);
+                               cudaStream_t st, bool fast = false);
 
 // Un-fused Cij update with the numpy operation order: (1-t)*C + t*(sum/B).
 template <typename T>

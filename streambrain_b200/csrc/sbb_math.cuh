@@ -30,17 +30,17 @@ __device__ __forceinline__ T log_ratio(T cij, T ci, T cj, T cthr4) {
   return sbb_log(num / (ci * cj));
 }
 
-// Variants used in the tensor-core epilogue, where eight warps per SM do the arithmetic of a
-// whole 128 x 256 tile: the batch mean by reciprocal multiply, the ratio by the hardware
-// reciprocal (2 ulp) and the logarithm by lg2.approx (absolute error below 2^-21 near 1,
-// 3 ulp elsewhere) -- about a quarter of the instructions of the IEEE forms above, and well
-// inside the tolerance of the weights (which are a logarithm of a ratio of noisy traces).
-__device__ __forceinline__ float trace_ema_fast(float old, float sum, const TraceParams<float> &p, float inv_batch) {
-  const float tmp = (sum * inv_batch) * p.taupdt;
-  return fmaxf(fmaf(old, p.one_minus, tmp), 0.f);
+// The arithmetic of the tensor-core path (fused epilogue, and the element-wise tail of the
+// data-parallel step when that path is selected): the batch mean and the moving-average weight
+// folded into one factor taupdt / batch, the ratio by IEEE reciprocals of Ci and Cj formed once per
+// row / column, the logarithm by lg2.approx (relative error below 2^-22) -- about a quarter of the
+// instructions of the IEEE forms above, and well inside the tolerance of the weights (which are a
+// logarithm of a ratio of noisy traces).
+__device__ __forceinline__ float trace_ema_fast(float old, float sum, float one_minus, float ema_scale) {
+  return fmaxf(fmaf(old, one_minus, sum * ema_scale), 0.f);
 }
-__device__ __forceinline__ float log_ratio_fast(float cij, float ci, float cj, float cthr4) {
-  return __logf(__fdividef(fmaxf(cij, cthr4), ci * cj));
+__device__ __forceinline__ float log_ratio_fast(float cij, float rci, float rcj, float cthr4) {
+  return __log2f(fmaxf(cij, cthr4) * (rci * rcj)) * 0.693147180559945309f;
 }
 
 }  // namespace sbb
