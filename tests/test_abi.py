@@ -59,6 +59,26 @@ def test_wrapper_rejects_silent_conversions():
         k.softmax_minicolumns(np.zeros((2, 4), dtype=np.int32), 2, 2)
 
 
+def test_process_wide_settings_round_trip():
+    """Settings that have no counterpart in the reference: host-side state only, so they work without a GPU."""
+    from streambrain_b200._lib import check, lib
+    before = lib.sbb_get_reserved_sms()
+    try:
+        check(lib.sbb_set_reserved_sms(24))
+        assert lib.sbb_get_reserved_sms() == 24
+        assert lib.sbb_set_reserved_sms(-1) != 0          # rejected, value kept
+        assert lib.sbb_get_reserved_sms() == 24
+    finally:
+        check(lib.sbb_set_reserved_sms(before))
+    path = lib.sbb_get_contraction_path()
+    try:
+        check(lib.sbb_set_contraction_path(0))
+        assert lib.sbb_get_contraction_path() == 0
+        assert lib.sbb_set_contraction_path(7) != 0
+    finally:
+        check(lib.sbb_set_contraction_path(path))
+
+
 def test_no_cpu_fallback_without_a_device():
     from streambrain_b200 import _lib
     if _lib.lib.sbb_device_count() > 0:

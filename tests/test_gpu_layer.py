@@ -141,6 +141,33 @@ def test_device_tensor_path_equals_host_path(B200):
     assert t.is_cuda and np.array_equal(t.cpu().numpy(), lb.Cij)
 
 
+def test_row_block_products_with_reserved_sms(B200):
+    """The persistent row-block product may leave multiprocessors to a collective running beside
+    it (sbb_set_reserved_sms): a smaller grid walks the same tiles and must give the same sums."""
+    import torch
+    from streambrain_b200._lib import check, lib
+
+    class Done:
+        def wait(self):
+            pass
+
+    g = load_golden("layer_f32.npz")
+    B = int(g["B"])
+    x = torch.from_numpy(np.ascontiguousarray(g["x"][:B])).cuda()
+    full, _ = _layers_from_golden(B200, g, np.float32)
+    fewer, _ = _layers_from_golden(B200, g, np.float32)
+    y = full.compute_activation(x)
+    full.dp_train_step(x, y, 1, 1, lambda t: Done(), row_blocks=2)
+    try:
+        check(lib.sbb_set_reserved_sms(140))
+        fewer.dp_train_step(x, y, 1, 1, lambda t: Done(), row_blocks=2)
+    finally:
+        check(lib.sbb_set_reserved_sms(0))
+    torch.cuda.synchronize()
+    for name in PLASTIC_STATE:
+        assert np.array_equal(getattr(fewer, name), getattr(full, name)), name
+
+
 def test_async_host_steps_equal_blocking_host_steps(B200):
     """Five pipelined host-buffer steps (copies double-buffered against the steps, page-locked
     buffers) leave the same state and return the same activations as five blocking calls."""
