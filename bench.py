@@ -365,8 +365,8 @@ def run_b200(args, wl, p, batch):
         del xl, yl, big
         xs = [torch.from_numpy(x).cuda() for x in xs_host[:4]]
 
-    # end to end through the host-buffer C-ABI call (N = 1 semantics per rank; under
-    # data parallelism the exchange needs device buffers, so e2e is measured at N = 1).
+    # end to end: at N = 1 through the host-buffer C-ABI call; under data parallelism (further down)
+    # through the device-tensor calls with every rank's copies on a copy stream.
     e2e = None
     if world == 1 and not args.no_e2e:
         # Every step uploads its own batch from page-locked host memory and reads its activation back;
@@ -399,6 +399,47 @@ def run_b200(args, wl, p, batch):
                "d2h_bytes_per_step": batch * M * s, "ms_per_step": dt / e_steps * 1e3,
                "call": "sbb_layer_step_host_async (pinned host buffers, copies double-buffered)",
                "blocking_call_value": batch * b_steps / dt_block}
+
+    if world > 1 and not args.no_e2e:
+        # Data parallel: every rank uploads its slice of the batch from page-locked host memory on a copy
+        # stream (two device slots), runs forward + the data-parallel train step on device tensors (the
+        # reduction needs them on the device), and reads its activation back; timed with the wall clock
+        # between barriers, maximum over ranks.
+        pinned = [torch.from_numpy(x).pin_memory() for x in xs_host[:4]]
+        y_host = [torch.empty((batch, M), dtype=xs[0].dtype).pin_memory() for _ in range(2)]
+        x_dev = [torch.empty((batch, N), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
+        y_dev = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
+        copy_stream = torch.cuda.Stream()
+        compute = torch.cuda.current_stream()
+        landed = [torch.cuda.Event() for _ in range(2)]
+        used = [torch.cuda.Event() for _ in range(2)]
+
+        def host_step(k):
+            slot = k % 2
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(used[slot])          # the step that last read this slot has finished
+                x_dev[slot].copy_(pinned[k % 4], non_blocking=True)
+                landed[slot].record(copy_stream)
+            compute.wait_event(landed[slot])
+            check(lib.sbb_layer_forward(layer._handle, x_dev[slot].data_ptr(), batch, y_dev[slot].data_ptr(), stream))
+            layer.dp_train_step(x_dev[slot], y_dev[slot], (k % H) if mask else None, world, all_reduce)
+            y_host[slot].copy_(y_dev[slot], non_blocking=True)
+            used[slot].record(compute)
+        for k in range(3):
+            host_step(k)
+        barrier()
+        e_steps = max(3, min(args.steps, 50))
+        t0 = time.perf_counter()
+        for k in range(e_steps):
+            host_step(3 + k)
+        torch.cuda.synchronize()
+        dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        dt = float(dt.item())
+        e2e = {"value": world * batch * e_steps / dt, "unit": "samples/s", "h2d_bytes_per_step": world * batch * N * s,
+               "d2h_bytes_per_step": world * batch * M * s, "ms_per_step": dt / e_steps * 1e3,
+               "call": "compute_activation + dp_train_step on device tensors, per-rank batch slice uploaded from "
+                       "pinned host memory on a copy stream"}
 
     if rank != 0:
         if world > 1:
