@@ -546,6 +546,10 @@ cudaError_t launch_reduce_bias_softmax(const T *partial, int splits, const T *bi
   const long per_lane = (Mc + width - 1) / width;
   if (per_lane <= 4)
     reduce_bias_softmax_kernel<T, 4><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
+  else if (per_lane <= 8)
+    reduce_bias_softmax_kernel<T, 8><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
+  else if (per_lane <= 12)
+    reduce_bias_softmax_kernel<T, 12><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
   else if (per_lane <= 16)
     reduce_bias_softmax_kernel<T, 16><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
   else

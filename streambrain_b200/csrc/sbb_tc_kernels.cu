@@ -1148,8 +1148,10 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   if (!b3) tm.b3 = tm.b;
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
-  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
+  // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
+  // fastest when x (B x N) is the larger, row tiles fastest when y (B x M) is
+  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, M > N ? 1 : 0, (int)row_begin,
+            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
   TcEpilogue ep{};
   ep.rows = rows;
   ep.cols = M;
@@ -1195,8 +1197,10 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   if (!b3) tm.b3 = tm.b;
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
-  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, 0, (int)row_begin, a3 ? 1 : 0,
-            b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
+  // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
+  // fastest when x (B x N) is the larger, row tiles fastest when y (B x M) is
+  TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, M > N ? 1 : 0, (int)row_begin,
+            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
   TcEpilogue ep{};
   ep.out = delta + row_begin * M;
   ep.rows = rows;
