@@ -24,10 +24,23 @@ import ctypes
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
+
+
+def host_cores() -> int:
+    """Host cores this process may run on."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+if "reference" in sys.argv[1:]:
+    # The CPU arm uses every host core whatever the launcher exported (torch.distributed.run sets
+    # OMP_NUM_THREADS=1 for its workers): the OpenMP and OpenBLAS runtimes read these when they load,
+    # which is after this line.
+    os.environ["OMP_NUM_THREADS"] = os.environ["OPENBLAS_NUM_THREADS"] = str(host_cores())
 
 import numpy as np
 
@@ -54,6 +67,8 @@ def parse_args():
                          "apply) with nothing to reduce: the kernels every rank runs at N > 1")
     ap.add_argument("--no-dp-large", action="store_true",
                     help="skip the extra leg on the large-batch data-parallel workload (stl10_dp_f32)")
+    ap.add_argument("--no-other-configs", action="store_true",
+                    help="skip the short legs on the other configurations (mnist_f32, mnist_f64, wide_f32)")
     ap.add_argument("--contraction", default="tensor", choices=["tensor", "general"],
                     help="tcgen05 tensor-core kernels (default) or the general-shape FFMA kernels")
     return ap.parse_args()
@@ -76,9 +91,60 @@ def algorithmic_work(N, M, H, B, s):
     return fwd_bytes, upd_bytes, flops
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one trace-update launch, from the ncu captures whose
-# summaries are profiles/step_kernels_stl10_f32_tensor_path.txt and profiles/trace_update_simt_stl10_f32.txt
-NCU_TRACE_UPDATE_DRAM_BYTES = {("stl10_f32", "tensor"): 2.000e9, ("stl10_f32", "general"): 3.24e9}
+def workload_config(wl, p, batch, world, mask, dp_path=False):
+    """The ``config`` object of the JSON line: the workload, identical for the GPU arm and the CPU arm."""
+    hp = p["hidden"]
+    N, H, Mc = hp["in_features"], hp["hypercolumns"], hp["minicolumns"]
+    s = np.dtype(p["dtype"]).itemsize
+    return {"workload": wl, "layer": "%d->%dx%d" % (N, H, Mc), "batch_per_gpu": batch,
+            "global_batch": batch * world, "mask_update": "every step" if mask else "none",
+            "start_state": "traces at the independent steady state (mask scores finite, as from epoch 2 on)",
+            "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
+                POOL, 2 * N * H * Mc * s / 1e6),
+            "parallelism": "dp%d" % world + (" (data-parallel step, nothing to reduce)" if dp_path and world == 1
+                                             else "")}
+
+
+def host_description():
+    """CPU model, OpenMP threads in force and the BLAS behind the reference module."""
+    model = "unknown"
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("model name"):
+                    model = line.split(":", 1)[1].strip()
+                    break
+    except OSError:
+        pass
+    threads = None
+    try:
+        threads = int(ctypes.CDLL("libgomp.so.1").omp_get_max_threads())
+    except OSError:
+        pass
+    blas = None
+    try:
+        sys.path.insert(0, os.path.join(REPO, "oracle"))
+        import build as oracle_build
+        info = os.path.join(os.path.dirname(oracle_build.ref_module_path()), "BUILD_INFO.txt")
+        with open(info) as f:
+            for line in f:
+                if line.startswith("blas:"):
+                    blas = line.split(":", 1)[1].strip()
+    except Exception:
+        pass
+    return {"cpu_model": model, "host_cores": host_cores(), "omp_max_threads": threads,
+            "OMP_NUM_THREADS": os.environ.get("OMP_NUM_THREADS"),
+            "OPENBLAS_NUM_THREADS": os.environ.get("OPENBLAS_NUM_THREADS"), "blas": blas}
+
+
+def use_all_host_cores():
+    """Make the OpenMP runtime already loaded in this process (if any) use every host core."""
+    n = host_cores()
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(n)
+    except OSError:
+        pass
+    return n
 
 
 class ClockSampler:
@@ -88,7 +154,7 @@ class ClockSampler:
     REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
                (0x4, "sw_power_cap"))
 
-    def __init__(self, gpu_index, period_s=0.004):
+    def __init__(self, gpu_index, period_s=0.001):
         import threading
         self.sm, self.reasons, self.max_mhz = [], set(), None
         self.stop_flag = threading.Event()
@@ -128,28 +194,6 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(sm)}
 
 
-def steady_state_traces(p, x, seed=7):
-    """Traces of a layer that has already seen data, used as the start state of both arms.
-
-    With the constructor's initial traces (Ci = 1, Cij = Cj = 1/Mc) the plasticity score
-    log((pj - pij) / ((1 - pi) pj)) is undefined (0/0), which is why the reference never
-    updates the mask in its first epoch (_cpu_base_backend.py:297).  The timed steps update
-    the mask, so they start where later epochs are: Ci = mean input, Cj = 1/Mc and
-    Cij = Ci*Cj (independent units) with 5 % seeded noise."""
-    hp = p["hidden"]
-    N, M, Mc = hp["in_features"], hp["hypercolumns"] * hp["minicolumns"], hp["minicolumns"]
-    rs = np.random.default_rng(seed)
-    dt = p["dtype"]
-    Ci = np.clip(x.mean(axis=0, dtype=np.float64), 0.02, 0.98).astype(dt)
-    Cj = np.full(M, 1.0 / Mc, dtype=dt)
-    Cij = (Ci[:, None].astype(np.float32) * Cj[None, :].astype(np.float32))
-    Cij *= 1.0 + 0.05 * rs.standard_normal(size=(N, M), dtype=np.float32)
-    # keep Cij < Cj (and < Ci): the score takes log((pj - pij) / ...), which a joint trace above its
-    # marginal would turn into NaN -- a state the moving averages cannot reach from data
-    np.minimum(Cij, 0.98 * np.minimum(Ci[:, None].astype(np.float32), Cj[None, :].astype(np.float32)), out=Cij)
-    return Ci, Cj, np.ascontiguousarray(Cij.astype(dt))
-
-
 def make_batches(p, batch, count, seed):
     xs = []
     for k in range(count):
@@ -169,22 +213,30 @@ def cpu_layer(p, kernels, seed=0):
                               taubdt=hp["taubdt"], density=hp["density"])
 
 
-def cpu_time_steps(p, batch, steps, warmup, budget_s, mask=True):
-    """Time the reference CPU implementation of the same step.  Returns
-    (samples_per_s, median_s, steps_timed, kind, cores)."""
+def global_batches(p, batch, world, count):
+    """The global batches of the GPU arm: rank r's batch k is drawn from seed DATA_SEED + 1000 r + k."""
+    out = []
+    for k in range(count):
+        parts = [make_batches(p, batch, 1, synthetic.DATA_SEED + 1000 * r + k)[0] for r in range(world)]
+        out.append(parts[0] if world == 1 else np.ascontiguousarray(np.concatenate(parts, axis=0)))
+    return out
+
+
+def cpu_time_steps(p, batch, world, steps, warmup, budget_s, mask=True, pool=2):
+    """Time the reference CPU implementation of the same step on the global batch (batch * world
+    samples: the reference's data-parallel backend equals its cpu backend on the concatenated batch,
+    BCPNN/backend/_kernels/test_mpi.py:48-59).  Returns (samples_per_s, mean_s, steps_timed, kind, cores)."""
     sys.path.insert(0, os.path.join(REPO, "oracle"))
     import oracle
+    cores = use_all_host_cores()
     kernels = oracle.best_kernels()
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
     layer = cpu_layer(p, kernels)
-    xs = make_batches(p, batch, 2, synthetic.DATA_SEED)
-    layer.Ci, layer.Cj, layer.Cij = steady_state_traces(p, xs[0])
+    xs = global_batches(p, batch, world, pool)
+    layer.Ci, layer.Cj, layer.Cij = synthetic.steady_state_traces(p, xs[0][:batch])
     H = p["hidden"]["hypercolumns"]
     times = []
     t_start = time.perf_counter()
-    total = warmup + steps
-    for s in range(total):
+    for s in range(warmup + steps):
         x = xs[s % len(xs)]
         t0 = time.perf_counter()
         act = layer.compute_activation(x)
@@ -192,28 +244,32 @@ def cpu_time_steps(p, batch, steps, warmup, budget_s, mask=True):
         dt = time.perf_counter() - t0
         if s >= warmup:
             times.append(dt)
-        if times and time.perf_counter() - t_start + dt > budget_s:
+        if len(times) >= 2 and time.perf_counter() - t_start + dt > budget_s:
             break
-    med = statistics.median(times)
-    return batch / med, med, len(times), kernels.kind, cores
+    mean = sum(times) / len(times)
+    return batch * world / mean, mean, len(times), kernels.kind, cores
 
 
 def run_reference(args, wl, p, batch):
+    """The reference arm: the same workload (the global batch the GPU arm processes at this N), same
+    steps and warm-up, on the host cores.  Under a multi-rank launcher rank 0 alone works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sps, med, done, kind, cores = cpu_time_steps(p, batch, args.steps, min(args.warmup, 1), budget_s=150.0,
-                                                 mask=not args.no_mask)
-    sample = "%d full steps (forward + train_step%s) of %s at batch %d on the host cores" % (
-        done, "" if args.no_mask else " + mask update", wl, batch)
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    mask = not args.no_mask
+    sps, mean, done, kind, cores = cpu_time_steps(p, batch, world, args.steps, args.warmup, budget_s=240.0,
+                                                  mask=mask, pool=min(POOL, 4))
+    sample = "%d of %d full steps (forward + train_step%s) of %s at the global batch %d, %d warm-up" % (
+        done, args.steps, " + mask update" if mask else "", wl, batch * world, args.warmup)
     line = {
         "impl": "reference", "metric": "training samples/sec per layer", "value": sps, "unit": "samples/s",
-        "n_gpus": args.gpus, "steps": done, "warmup": min(args.warmup, 1), "ms_per_step": med * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32" if p["dtype"] == np.float32
-        else "f64", "data": "synthetic",
-        "config": {"workload": wl, "batch_per_gpu": batch, "layer": "%d->%dx%d" % (
-            p["hidden"]["in_features"], p["hidden"]["hypercolumns"], p["hidden"]["minicolumns"])},
-        "cpu_baseline": {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "sample": sample},
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean * 1e3,
+        "higher_is_better": True, "scaling": "strong" if wl == "stl10_dp_f32" else "weak", "vs_baseline": None,
+        "dtype": "f32" if p["dtype"] == np.float32 else "f64", "data": "synthetic",
+        "config": workload_config(wl, p, batch, world, mask),
+        "cpu_baseline": {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "sample": sample,
+                         "steps_timed": done, "host": host_description()},
         "e2e": {"value": sps, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -221,6 +277,140 @@ def run_reference(args, wl, p, batch):
 
 
 # --------------------------------------------------------------------------- GPU
+FP64_PEAK_TFLOPS = 37.2   # 148 SMs x 64 FP64 lanes x 2 flops x 1.965 GHz (nominal; this pool measures no FP64 peak)
+FFMA_PEAK_TFLOPS = 74.4   # 148 SMs x 128 FP32 lanes x 2 flops x 1.965 GHz (nominal)
+
+
+def step_roofline_of(p, batch, ms_per_step, peaks, tensor_path):
+    """Whole-step roofline: each of the two phases (forward, trace update) bounded by the larger of its
+    memory time and its compute time at the peak of the datapath that ran it.  float32 on the tensor
+    path costs three TF32 products per product, i.e. a sixth of the measured bf16 rate; both the burst
+    and the sustained measurement of that rate are given, ``frac`` uses the burst (stricter) one."""
+    hp = p["hidden"]
+    N, H, Mc = hp["in_features"], hp["hypercolumns"], hp["minicolumns"]
+    s = np.dtype(p["dtype"]).itemsize
+    fwd_b, upd_b, flops = algorithmic_work(N, H * Mc, H, batch, s)
+    hbm = float(peaks["hbm_gbs"]) * 1e9
+    if s == 8:
+        burst = sustained = FP64_PEAK_TFLOPS
+        note = "peak = nominal FP64 rate (DFMA), no tensor-core path exists for float64"
+    elif tensor_path:
+        burst = float(peaks["bf16_tflops"]) / 6.0
+        sustained = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) / 6.0
+        note = "peak = measured bf16 rate / 6 (float32 by three TF32 products): burst, and sustained under the power cap"
+    else:
+        burst = sustained = FFMA_PEAK_TFLOPS
+        note = "peak = nominal FP32 FFMA rate (general-shape kernels)"
+
+    def t_roof(peak_tf):
+        c = flops / (peak_tf * 1e12)
+        return (max(fwd_b / hbm, c) + max(upd_b / hbm, c)) * 1e3
+    return {"t_roof_ms": t_roof(burst), "frac": t_roof(burst) / ms_per_step, "compute_peak_tflops": burst,
+            "t_roof_ms_sustained_peak": t_roof(sustained), "frac_sustained_peak": t_roof(sustained) / ms_per_step,
+            "compute_peak_tflops_sustained": sustained, "note": note}
+
+
+def short_leg(B200, lib, check, torch, wl, peaks, steps=20, warmup=3):
+    """One of the other configurations, timed the same way as the headline (resident batches, mask update
+    every step, CUDA events) over a short region."""
+    p = synthetic.layer_params(wl)
+    hp = p["hidden"]
+    N, H, Mc, batch = hp["in_features"], hp["hypercolumns"], hp["minicolumns"], p["batch"]
+    M = H * Mc
+    np.random.seed(0)
+    layer = B200.StructuralPlasticityLayer(N, H, Mc, hp["taupdt"], hp["khalf"], hp["pmin"], hp["taubdt"],
+                                           hp["density"], 16, hp["initial_counters"], dtype=p["dtype"])
+    state_mb = 2 * N * M * np.dtype(p["dtype"]).itemsize / 1e6
+    pool = 4 if state_mb > 126 else 16   # small layers are L2-resident by nature; their inputs still cycle
+    xs_host = make_batches(p, batch, pool, synthetic.DATA_SEED)
+    layer.Ci, layer.Cj, layer.Cij = synthetic.steady_state_traces(p, xs_host[0])
+    xs = [torch.from_numpy(x).cuda() for x in xs_host]
+    y = torch.empty((batch, M), dtype=xs[0].dtype, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def step(k):
+        x = xs[k % pool]
+        check(lib.sbb_layer_forward(layer._handle, x.data_ptr(), batch, y.data_ptr(), stream))
+        check(lib.sbb_layer_train_step(layer._handle, x.data_ptr(), y.data_ptr(), batch, k % H, stream))
+    for k in range(warmup):
+        step(k)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(steps):
+        step(warmup + k)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    tensor_path = bool(lib.sbb_tensor_path_available()) and bool(lib.sbb_get_contraction_path()) and \
+        p["dtype"] == np.float32
+    return {"workload": wl, "layer": "%d->%dx%d" % (N, H, Mc), "batch": batch,
+            "dtype": "f32" if p["dtype"] == np.float32 else "f64", "value": batch / (ms * 1e-3), "unit": "samples/s",
+            "ms_per_step": ms, "steps": steps, "warmup": warmup,
+            "l2": "state %.0f MB %s" % (state_mb, "> L2, streamed every step" if state_mb > 126 else
+                                         "(fits the 126 MB L2: this configuration is L2-resident by nature)"),
+            "step_roofline": step_roofline_of(p, batch, ms, peaks, tensor_path)}
+
+
+def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce):
+    """Outside the timed region, at N > 1: (1) the replicas of the timed layer are bit-identical
+    (checksums of Cij, weights and mask agree over ranks); (2) on a reduced shape one data-parallel
+    step over the ranks equals the fused single-GPU step at the same global batch."""
+    sums = []
+    for name in ("Cij", "weights", "wmask"):
+        t = layer.state_tensor(name)
+        bits = t.view(torch.int32) if t.dtype != torch.uint8 else t
+        sums.append(bits.to(torch.int64).sum())
+    lo = torch.stack(sums)
+    hi = lo.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    identical = bool(torch.equal(lo, hi))
+
+    N, H, Mc, b_local, h = 4096, 30, 100, 128, 3
+    M = H * Mc
+    hp = synthetic.layer_params("stl10_f32", batch=b_local * world)["hidden"]
+    rs = np.random.RandomState(4321)
+    pix = rs.rand(b_local * world, N // 2).astype(np.float32)
+    xg = synthetic.complementary_code(pix)
+    small_p = {"hidden": dict(hp, in_features=N), "dtype": np.dtype(np.float32)}
+    traces = synthetic.steady_state_traces(small_p, xg)
+
+    def make():
+        np.random.seed(0)
+        l = B200.StructuralPlasticityLayer(N, H, Mc, hp["taupdt"], hp["khalf"], hp["pmin"], hp["taubdt"],
+                                           hp["density"], 16, hp["initial_counters"], dtype=np.float32)
+        l.Ci, l.Cj, l.Cij = traces
+        return l
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    dp = make()
+    xl = torch.from_numpy(np.ascontiguousarray(xg[rank * b_local:(rank + 1) * b_local])).cuda()
+    yl = torch.empty((b_local, M), dtype=torch.float32, device="cuda")
+    check(lib.sbb_layer_forward(dp._handle, xl.data_ptr(), b_local, yl.data_ptr(), stream))
+    dp.dp_train_step(xl, yl, h, world, all_reduce)
+    torch.cuda.synchronize()
+    err, masks_equal = None, None
+    if rank == 0:
+        one = make()
+        xa = torch.from_numpy(xg).cuda()
+        ya = torch.empty((b_local * world, M), dtype=torch.float32, device="cuda")
+        check(lib.sbb_layer_forward(one._handle, xa.data_ptr(), b_local * world, ya.data_ptr(), stream))
+        check(lib.sbb_layer_train_step(one._handle, xa.data_ptr(), ya.data_ptr(), b_local * world, h, stream))
+        torch.cuda.synchronize()
+        err = 0.0
+        for name in ("Ci", "Cj", "Cij"):
+            a, b = getattr(dp, name).astype(np.float64), getattr(one, name).astype(np.float64)
+            err = max(err, float(np.abs(a - b).max() / np.abs(b).max()))
+        masks_equal = bool(np.array_equal(dp.wmask, one.wmask))
+        if masks_equal:
+            a, b = dp.weights.astype(np.float64), one.weights.astype(np.float64)
+            err = max(err, float(np.abs(a - b).max() / max(1.0, np.abs(b).max())) / 10)
+    return {"replicas_identical": identical, "dp_vs_single_rel_err": err, "dp_vs_single_masks_equal": masks_equal,
+            "dp_vs_single_shape": "%d->%dx%d, global batch %d, one step with a mask update; traces relative "
+                                  "to their maximum, weights / 10 (their tolerance is 10x the traces')" % (
+                                      N, H, Mc, b_local * world)}
+
+
 def run_b200(args, wl, p, batch):
     import torch
     import torch.distributed as dist
@@ -250,7 +440,7 @@ def run_b200(args, wl, p, batch):
                                            hp["density"], 16, hp["initial_counters"], dtype=np_dtype)
     xs_host = make_batches(p, batch, POOL, synthetic.DATA_SEED + 1000 * rank)
     ref_batch = xs_host[0] if rank == 0 else make_batches(p, batch, 1, synthetic.DATA_SEED)[0]
-    layer.Ci, layer.Cj, layer.Cij = steady_state_traces(p, ref_batch)   # identical on every rank
+    layer.Ci, layer.Cj, layer.Cij = synthetic.steady_state_traces(p, ref_batch)   # identical on every rank
     xs = [torch.from_numpy(x).cuda() for x in xs_host]
     ys = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -325,7 +515,7 @@ def run_b200(args, wl, p, batch):
         np.random.seed(0)
         big = B200.StructuralPlasticityLayer(N, H, Mc, hl["taupdt"], hl["khalf"], hl["pmin"], hl["taubdt"],
                                              hl["density"], 16, hl["initial_counters"], dtype=np_dtype)
-        big.Ci, big.Cj, big.Cij = steady_state_traces(pl, ref_batch)
+        big.Ci, big.Cj, big.Cij = synthetic.steady_state_traces(pl, ref_batch)
         gen = torch.Generator(device="cuda")
         gen.manual_seed(synthetic.DATA_SEED + 17 * rank)
         xl = []
@@ -441,6 +631,10 @@ def run_b200(args, wl, p, batch):
                "call": "compute_activation + dp_train_step on device tensors, per-rank batch slice uploaded from "
                        "pinned host memory on a copy stream"}
 
+    dp_checks = None
+    if world > 1:
+        dp_checks = data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -457,32 +651,44 @@ def run_b200(args, wl, p, batch):
     roofline = None
     if per_step_trace:
         achieved = upd_b / (per_step_trace * 1e-3) / 1e9
-        # DRAM bytes of one launch from the ncu capture summarised in profiles/ (read + written);
-        # known for the workload / path that capture ran
-        traffic = NCU_TRACE_UPDATE_DRAM_BYTES.get((wl, "tensor" if tensor_path else "general")) if world == 1 and not args.dp_path else None
-        tf32_peak = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) / 2.0   # dense TF32 = half of bf16
+        tf32_sustained = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) / 2.0   # dense TF32 = half of bf16
+        tf32_burst = float(peaks["bf16_tflops"]) / 2.0
+        tf = 3 * flops / (per_step_trace * 1e-3) / 1e12
         roofline = {"bound": "hbm", "kernel": "trace update (x^T y + EMA + log-ratio weights + mask)",
                     "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                    "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes": upd_b,
+                    # DRAM bytes are not measured by this program: the ncu capture of this kernel is summarised
+                    # in the named profile
+                    "traffic": None,
+                    "traffic_source": "profiles/tc_contraction_kernels_stl10_f32.txt (dram__bytes_read.sum + "
+                                      "dram__bytes_write.sum of one launch under ncu)" if tensor_path else
+                                      "profiles/trace_update_simt_stl10_f32.txt",
+                    "peak_source": peak_kind, "algorithmic_bytes": upd_b,
                     "ms_per_launch": per_step_trace,
                     "forward_ms": (sum(fwd_ms) / len(fwd_ms)) if fwd_ms else None,
                     # the same launch against the tensor pipe: three TF32 products per float32 product
-                    "tensor": {"achieved": 3 * flops / (per_step_trace * 1e-3) / 1e12, "peak": tf32_peak,
-                               "unit": "TFLOP/s (TF32)", "frac": 3 * flops / (per_step_trace * 1e-3) / 1e12 / tf32_peak}
+                    "tensor": {"achieved": tf, "unit": "TFLOP/s (TF32)", "peak": tf32_burst, "frac": tf / tf32_burst,
+                               "peak_sustained": tf32_sustained, "frac_sustained_peak": tf / tf32_sustained}
                     if tensor_path else None}
-    # whole-step roofline: each phase bounded by the larger of its memory and compute time
-    p32 = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) / 6.0 * 1e12  # fp32 via 3xTF32
-    t_roof = max(fwd_b / (hbm * 1e9), flops / p32) + max(upd_b / (hbm * 1e9), flops / p32)
-    step_roofline = {"t_roof_ms": t_roof * 1e3, "frac": t_roof * 1e3 / ms_per_step,
-                     "compute_peak_tflops": p32 / 1e12,
-                     "note": "peak = measured bf16 sustained / 6 (fp32 by three TF32 products)"}
+    step_roofline = step_roofline_of(p, batch, ms_per_step, peaks, tensor_path)
+
+    other = None
+    if world == 1 and wl == "stl10_f32" and not args.no_other_configs:
+        del xs
+        torch.cuda.empty_cache()
+        other = []
+        for name in ("mnist_f32", "mnist_f64", "wide_f32"):
+            try:
+                other.append(short_leg(B200, lib, check, torch, name, peaks))
+            except Exception as e:
+                other.append({"workload": name, "error": str(e)[:200]})
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         try:
-            sps, med, done, kind, cores = cpu_time_steps(p, batch, 12, 1, budget_s=30.0, mask=mask)
-            cpu = {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "ms_per_step": med * 1e3,
-                   "sample": "%d full steps of the same workload (batch %d) after 1 warm-up" % (done, batch)}
+            sps, mean, done, kind, cores = cpu_time_steps(p, batch, 1, 12, 1, budget_s=30.0, mask=mask)
+            cpu = {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "ms_per_step": mean * 1e3,
+                   "sample": "%d full steps of the same workload (batch %d) after 1 warm-up" % (done, batch),
+                   "host": host_description()}
         except Exception as e:  # the CPU leg must never take the GPU line down
             cpu = {"value": None, "unit": "samples/s", "cores": 0, "kind": "unavailable", "sample": str(e)[:200]}
 
@@ -491,14 +697,10 @@ def run_b200(args, wl, p, batch):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if wl == "stl10_dp_f32" else "weak", "vs_baseline": None,
         "dtype": "f32" if np_dtype == np.float32 else "f64", "data": "synthetic",
-        "config": {"workload": wl, "layer": "%d->%dx%d" % (N, H, Mc), "batch_per_gpu": batch,
-                   "global_batch": batch * world, "mask_update": "every step" if mask else "none",
-                   "start_state": "traces at the independent steady state (mask scores finite, as from epoch 2 on)",
-                   "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
-                       POOL, 2 * N * M * s / 1e6),
-                   "contraction": "tcgen05 3xTF32" if tensor_path else "FFMA", "parallelism": "dp%d" % world + (" (data-parallel step, nothing to reduce)" if args.dp_path and world == 1 else "")},
-        "roofline": roofline, "step_roofline": step_roofline, "dp_large_batch": dp_large, "cpu_baseline": cpu,
-        "e2e": e2e,
+        "config": workload_config(wl, p, batch, world, mask, args.dp_path),
+        "contraction": "tcgen05 3xTF32" if tensor_path else ("FFMA" if np_dtype == np.float32 else "DFMA"),
+        "roofline": roofline, "step_roofline": step_roofline, "dp_large_batch": dp_large,
+        "dp_checks": dp_checks, "other_configs": other, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

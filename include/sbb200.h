@@ -223,8 +223,8 @@ int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, l
  * array: calls that overlap in time on one GPU race and must be serialised by
  * the caller.  The first call on each device looks up the array's address
  * (cudaGetSymbolAddress) and should be made outside any stream capture.  The
- * work is enqueued on `stream`; the call does not synchronise.  Errors of this
- * entry point are reported by sbb_noalloc_last_error().
+ * work is enqueued on `stream`; the call does not synchronise.  The message of a
+ * failure is returned by sbb_noalloc_last_error() and by sbb_last_error().
  * This entry point has no counterpart in the reference. */
 #define SBB_NOALLOC_MAX_ROWS 131072
 int sbb_update_mask_noalloc(int dtype, uint8_t *wmask_dev, const void *weights_dev, const void *Ci_dev,
@@ -274,6 +274,13 @@ int sbb_tensor_path_available(void);
  * first wait that gave up (SBB_ERR_TIMEOUT is returned as well).  Synchronises
  * the device. */
 int sbb_device_wait_status(int *status);
+/* The status word is sticky: once a wait has given up, every entry point that waits for device work
+ * (sbb_layer_get_state, sbb_layer_wait, the *_host calls, sbb_count_correct, sbb_stream_sync,
+ * sbb_network_*) returns SBB_ERR_TIMEOUT after its own wait, because the kernel that gave up left its
+ * step half done: the traces and weights of the layers stepped since the last clean check are undefined
+ * and must be reloaded (sbb_layer_set_state).  This call then resets the word so that work can go on.
+ * Synchronises the device.  No counterpart in the reference (its kernels have no waits). */
+int sbb_device_clear_wait_status(void);
 
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long sbb_kernel_launches(void);

@@ -9,7 +9,7 @@ Two artefacts:
   ``BCPNN/backend/_kernels/kernels_openmp_internal.cc`` with the flags its
   ``CMakeLists.txt:24,40-41`` uses (``-O3 -march=native -ffast-math -fopenmp``).
   Only attempted when a reference checkout is present (``SBB_REFERENCE_ROOT`` or
-  the default location); the source file is compiled where it lies and nothing
+  a directory ``reference`` beside this repository); the source file is compiled where it lies and nothing
   but the resulting shared object is written.  ``<cblas.h>`` is our own shim
   header and the BLAS is the OpenBLAS shared object bundled in the SciPy (or
   OpenCV) wheel.  The reference's cmake build is not run.
@@ -33,7 +33,8 @@ REF_KERNEL_SOURCE = os.path.join("BCPNN", "backend", "_kernels", "kernels_openmp
 
 
 def reference_root() -> str | None:
-    root = os.environ.get("SBB_REFERENCE_ROOT", "/root/reference")
+    """A StreamBrain checkout: ``SBB_REFERENCE_ROOT``, else a directory ``reference`` beside this repository."""
+    root = os.environ.get("SBB_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     return root if os.path.isfile(os.path.join(root, REF_KERNEL_SOURCE)) else None
 
 

@@ -86,6 +86,7 @@ SIGNATURES = {
     "sbb_get_reserved_sms": (c_int, []),
     "sbb_tensor_path_available": (c_int, []),
     "sbb_device_wait_status": (c_int, [POINTER(c_int)]),
+    "sbb_device_clear_wait_status": (c_int, []),
     "sbb_kernel_launches": (c_ulonglong, []),
     "sbb_stream_sync": (c_int, [c_void_p]),
 }

@@ -133,6 +133,10 @@ struct Scratch {
 
 }  // namespace
 
+namespace sbb {
+void set_last_error(const char *message) { g_error = message ? message : ""; }
+}  // namespace sbb
+
 struct sbb_layer {
   sbb_layer_desc desc;
   long N, H, Mc, M;
@@ -159,6 +163,7 @@ struct sbb_layer {
   cudaEvent_t ev_end[2][SBB_PROFILE_SLOTS];
   bool ev_created = false;
   long phase_calls[2] = {0, 0};
+  bool dp_fast = false;  // the last sbb_layer_dp_local ran the tensor-core product
 };
 
 namespace {
@@ -187,7 +192,9 @@ struct PhaseTimer {
 template <typename T>
 int layer_forward(sbb_layer *L, const T *x, long B, T *y, cudaStream_t st) {
   const T *W = static_cast<const T *>(L->state[SBB_STATE_WEIGHTS]);
-  const bool tc = tensor_path<T>(x, W, L->N, L->M);
+  bool tc = tensor_path<T>(x, W, L->N, L->M);
+  // an unsplit tensor-core product writes straight into y, which must then be 8-byte aligned
+  if (tc && sbb::forward_splits_tc(B, L->N, L->M) == 1 && (reinterpret_cast<uintptr_t>(y) & 7u)) tc = false;
   const int splits = tc ? sbb::forward_splits_tc(B, L->N, L->M) : sbb::forward_splits<T>(B, L->N, L->M);
   T *partial = y;
   if (splits > 1) {
@@ -264,7 +271,9 @@ int layer_dp_local(sbb_layer *L, const T *x, const T *y, long B, T *delta, long 
   }
   PhaseTimer timer(L, SBB_PHASE_TRACE, st);
   T *xty = delta + L->N + L->M;
-  if (tensor_path<T>(x, y, L->N, L->M) && (reinterpret_cast<uintptr_t>(xty) & 7u) == 0) {
+  // remembered for sbb_layer_dp_apply_rows: the element-wise tail uses the arithmetic of the path that formed the sums
+  L->dp_fast = tensor_path<T>(x, y, L->N, L->M) && (reinterpret_cast<uintptr_t>(xty) & 7u) == 0;
+  if (L->dp_fast) {
     if constexpr (std::is_same<T, float>::value)
       SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, L->N, L->M, xty, rb, re, st));
   } else {
@@ -292,7 +301,7 @@ int layer_dp_apply_rows(sbb_layer *L, const T *delta, long Bg, long rb, long re,
                                       static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
                                       static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]), p, 1, rb, re, st,
                                       // the arithmetic of the path that formed the sums (see sbb_math.cuh)
-                                      tensor_path<T>(delta, delta, L->N, L->M)));
+                                      L->dp_fast));
   return SBB_OK;
 }
 
@@ -312,6 +321,19 @@ int check_batch(const sbb_layer *L, long B) {
 }
 
 #define DISPATCH(dtype, expr_f32, expr_f64) ((dtype) == SBB_F32 ? (expr_f32) : (expr_f64))
+
+// Called by entry points right after they have waited for their own work: a bounded device-side wait
+// that gave up leaves the step half done, which the caller must learn from the return code.
+int check_wait_status() {
+  int st = 0;
+  SBB_CUDA(sbb::tc_peek_status(&st));
+  if (st != 0)
+    return fail(SBB_ERR_TIMEOUT,
+                "a bounded device-side wait gave up (code %d): the state of layers stepped since the last check is "
+                "undefined; reload it and call sbb_device_clear_wait_status",
+                st);
+  return SBB_OK;
+}
 
 }  // namespace
 
@@ -344,10 +366,16 @@ int sbb_device_wait_status(int *status) {
   return SBB_OK;
 }
 
+int sbb_device_clear_wait_status(void) {
+  SBB_TRY(need_device());
+  SBB_CUDA(sbb::tc_clear_status());
+  return SBB_OK;
+}
+
 int sbb_stream_sync(void *stream) {
   SBB_TRY(need_device());
   SBB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-  return SBB_OK;
+  return check_wait_status();
 }
 
 // ---------------------------------------------------------------- stateless
@@ -725,7 +753,7 @@ int sbb_layer_get_state(sbb_layer *L, int which, void *host, size_t bytes) {
   SBB_TRY(check_layer(L));
   SBB_CUDA(cudaDeviceSynchronize());
   SBB_CUDA(cudaMemcpy(host, L->state[which], bytes, cudaMemcpyDeviceToHost));
-  return SBB_OK;
+  return check_wait_status();
 }
 
 int sbb_layer_state_ptr(sbb_layer *L, int which, void **device_ptr) {
@@ -822,7 +850,7 @@ int sbb_layer_forward_host(sbb_layer *L, const void *x_host, long B, void *y_hos
                    layer_forward<double>(L, (const double *)L->hx.d, B, (double *)L->hy.d, st)));
   SBB_CUDA(cudaMemcpyAsync(y_host, L->hy.d, (size_t)B * L->M * s, cudaMemcpyDeviceToHost, st));
   SBB_CUDA(cudaStreamSynchronize(st));
-  return SBB_OK;
+  return check_wait_status();
 }
 
 int sbb_layer_train_step_host(sbb_layer *L, const void *x_host, const void *y_host, long B, long hypercolumn) {
@@ -844,7 +872,7 @@ int sbb_layer_train_step_host(sbb_layer *L, const void *x_host, const void *y_ho
                    layer_train_step<float>(L, (const float *)L->hx.d, (const float *)L->ht.d, B, hypercolumn, st),
                    layer_train_step<double>(L, (const double *)L->hx.d, (const double *)L->ht.d, B, hypercolumn, st)));
   SBB_CUDA(cudaStreamSynchronize(st));
-  return SBB_OK;
+  return check_wait_status();
 }
 
 int sbb_layer_step_host(sbb_layer *L, const void *x_host, const void *target_host, long B, long hypercolumn,
@@ -875,7 +903,7 @@ int sbb_layer_step_host(sbb_layer *L, const void *x_host, const void *target_hos
   }
   if (y_host) SBB_CUDA(cudaMemcpyAsync(y_host, L->hy.d, (size_t)B * L->M * s, cudaMemcpyDeviceToHost, st));
   SBB_CUDA(cudaStreamSynchronize(st));
-  return SBB_OK;
+  return check_wait_status();
 }
 
 int sbb_layer_step_host_async(sbb_layer *L, const void *x_host, const void *target_host, long B, long hypercolumn,
@@ -942,7 +970,7 @@ int sbb_layer_wait(sbb_layer *L) {
     SBB_CUDA(cudaStreamSynchronize(L->d2h_stream));
   }
   L->async_open = false;
-  return SBB_OK;
+  return check_wait_status();
 }
 
 // ------------------------------------------------------------ data parallel
@@ -1019,7 +1047,7 @@ int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, l
   SBB_CUDA(cudaMemcpyAsync(&h, cnt.d, sizeof(h), cudaMemcpyDeviceToHost, st));
   SBB_CUDA(cudaStreamSynchronize(st));
   *correct_host = (long)h;
-  return SBB_OK;
+  return check_wait_status();
 }
 
 }  // extern "C"

@@ -26,6 +26,10 @@
 #include <cstdio>
 #include <mutex>
 
+namespace sbb {
+void set_last_error(const char *message);   // sbb_api.cu: the text sbb_last_error() returns on this thread
+}
+
 namespace {
 
 constexpr long kMaxRows = SBB_NOALLOC_MAX_ROWS;
@@ -45,6 +49,13 @@ std::mutex g_scratch_mutex;
 thread_local char g_noalloc_error[256];
 
 int scratch_for_current_device(void **out) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+    (void)cudaGetLastError();
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+             "update_mask_noalloc: no CUDA device is available; this library has no CPU path");
+    return SBB_ERR_NO_DEVICE;
+  }
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
@@ -73,9 +84,23 @@ extern "C" {
 
 const char *sbb_noalloc_last_error(void) { return g_noalloc_error; }
 
+static int update_mask_noalloc_impl(int dtype, uint8_t *wmask_dev, const void *weights_dev, const void *Ci_dev,
+                                    const void *Cj_dev, const void *Cij_dev, double cthr, long N, long M, long H,
+                                    long Mc, long h, long iterations, void *stream);
+
 int sbb_update_mask_noalloc(int dtype, uint8_t *wmask_dev, const void *weights_dev, const void *Ci_dev,
                             const void *Cj_dev, const void *Cij_dev, double cthr, long N, long M, long H, long Mc,
                             long h, long iterations, void *stream) {
+  const int rc = update_mask_noalloc_impl(dtype, wmask_dev, weights_dev, Ci_dev, Cj_dev, Cij_dev, cthr, N, M, H, Mc, h,
+                                          iterations, stream);
+  // the message is also what sbb_last_error() returns, like every other entry point's
+  if (rc != SBB_OK) sbb::set_last_error(g_noalloc_error);
+  return rc;
+}
+
+static int update_mask_noalloc_impl(int dtype, uint8_t *wmask_dev, const void *weights_dev, const void *Ci_dev,
+                                    const void *Cj_dev, const void *Cij_dev, double cthr, long N, long M, long H,
+                                    long Mc, long h, long iterations, void *stream) {
   g_noalloc_error[0] = 0;
   if (dtype != SBB_F32 && dtype != SBB_F64) {
     snprintf(g_noalloc_error, sizeof(g_noalloc_error), "update_mask_noalloc: invalid dtype %d", dtype);

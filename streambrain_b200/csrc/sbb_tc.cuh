@@ -47,5 +47,9 @@ int tc_get_reserved_sms();
 // waits completed, otherwise the code of the first wait that gave up.
 // Synchronises the device.
 cudaError_t tc_read_status(int *status);
+// The same word read without synchronising (for callers that have just waited for their own work),
+// and reset to 0 (synchronises the device first).
+cudaError_t tc_peek_status(int *status);
+cudaError_t tc_clear_status();
 
 }  // namespace sbb

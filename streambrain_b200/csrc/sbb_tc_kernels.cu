@@ -1232,6 +1232,32 @@ int tc_get_reserved_sms() {
   return v;
 }
 
+// The status word without synchronising the device: meaningful for work the caller has already waited for.
+cudaError_t tc_peek_status(int *status) {
+  *status = 0;
+  const int dev = current_device();
+  int *p = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    p = g_status[dev];
+  }
+  if (p == nullptr) return cudaSuccess;
+  return cudaMemcpy(status, p, sizeof(int), cudaMemcpyDeviceToHost);
+}
+
+cudaError_t tc_clear_status() {
+  const int dev = current_device();
+  int *p = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    p = g_status[dev];
+  }
+  if (p == nullptr) return cudaSuccess;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return e;
+  return cudaMemset(p, 0, sizeof(int));
+}
+
 cudaError_t tc_read_status(int *status) {
   *status = 0;
   const int dev = current_device();

@@ -81,3 +81,25 @@ def layer_params(name: str, batch: int | None = None) -> dict:
                initial_counters=(1 / Mc, 1 / 10, 1 / Mc / 10))
     return dict(hidden=hidden, out=out, batch=batch, dtype=np.dtype(c["dtype"]),
                 n_pixels=c["n_pixels"], sparsity=c["sparsity"])
+
+
+def steady_state_traces(p, x, seed=7):
+    """Traces of a layer that has already seen data, used as the start state of both arms.
+
+    With the constructor's initial traces (Ci = 1, Cij = Cj = 1/Mc) the plasticity score
+    log((pj - pij) / ((1 - pi) pj)) is undefined (0/0), which is why the reference never
+    updates the mask in its first epoch (_cpu_base_backend.py:297).  The timed steps update
+    the mask, so they start where later epochs are: Ci = mean input, Cj = 1/Mc and
+    Cij = Ci*Cj (independent units) with 5 % seeded noise."""
+    hp = p["hidden"]
+    N, M, Mc = hp["in_features"], hp["hypercolumns"] * hp["minicolumns"], hp["minicolumns"]
+    rs = np.random.default_rng(seed)
+    dt = p["dtype"]
+    Ci = np.clip(x.mean(axis=0, dtype=np.float64), 0.02, 0.98).astype(dt)
+    Cj = np.full(M, 1.0 / Mc, dtype=dt)
+    Cij = (Ci[:, None].astype(np.float32) * Cj[None, :].astype(np.float32))
+    Cij *= 1.0 + 0.05 * rs.standard_normal(size=(N, M), dtype=np.float32)
+    # keep Cij < Cj (and < Ci): the score takes log((pj - pij) / ...), which a joint trace above its
+    # marginal would turn into NaN -- a state the moving averages cannot reach from data
+    np.minimum(Cij, 0.98 * np.minimum(Ci[:, None].astype(np.float32), Cj[None, :].astype(np.float32)), out=Cij)
+    return Ci, Cj, np.ascontiguousarray(Cij.astype(dt))

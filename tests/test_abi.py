@@ -90,6 +90,12 @@ def test_no_cpu_fallback_without_a_device():
     import streambrain_b200 as B
     with pytest.raises(_lib.SbbError):
         B.DenseLayer(8, 1, 4, 0.01, (0.1, 0.1, 0.01), np.float32)
+    # the allocation-free mask update follows the same contract (pointers are never touched without a device)
+    fake = ctypes.c_void_p(256)
+    rc = _lib.lib.sbb_update_mask_noalloc(0, fake, fake, fake, fake, fake, 0.01, 8, 4, 2, 2, 0, 1, None)
+    assert rc == 3
+    assert b"no CUDA device" in _lib.lib.sbb_noalloc_last_error()
+    assert b"no CUDA device" in _lib.lib.sbb_last_error()
 
 
 def test_product_never_imports_the_oracle():

@@ -5,7 +5,7 @@ as well as float64 and with odd sizes -- against the CPU oracle on seeded inputs
 import numpy as np
 import pytest
 
-from conftest import TOL, load_golden, rel_inf, weight_err
+from conftest import TOL, load_golden, mask_mismatch_is_a_tie, rel_inf, weight_err
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("contraction_path")]
 
@@ -57,10 +57,11 @@ def test_kernels_match_reference_golden(k, tag, dtype):
                                 float(g["um_cthr"]), hc, mc, h, it)
             if dtype == np.float64:
                 assert np.array_equal(got, g["um_out_it%d_h%d" % (it, h)]), (it, h)
-            else:  # float32 scores can tie within rounding; the number of swaps must still agree
+            else:  # float32: a different swap only where the reference's own margin is below the score noise
                 want = g["um_out_it%d_h%d" % (it, h)]
-                assert got[:, h].sum() == want[:, h].sum()
-                assert (got != want).sum() <= 4, (it, h)
+                ref_state = {"Ci": g["um_Ci"], "Cj": g["um_Cj"], "Cij": g["um_Cij"]}
+                assert mask_mismatch_is_a_tie(got, want, h, g["um_wmask"], ref_state, float(g["um_cthr"]), mc,
+                                              1e-5), (it, h)
     assert np.array_equal(k.apply_mask(g["um_w"].copy(), g["um_wmask"], hc, mc), g["am_out"])
 
 

@@ -9,7 +9,7 @@ import random
 import numpy as np
 import pytest
 
-from conftest import TOL, load_golden, rel_inf, weight_err
+from conftest import TOL, load_golden, mask_mismatch_is_a_tie, rel_inf, weight_err
 
 import oracle
 
@@ -37,29 +37,6 @@ def _layers_from_golden(B200, g, dtype):
     for name in ("weights", "bias", "Ci", "Cj", "Cij"):
         setattr(dense, name, g["dinit_" + name])
     return layer, dense
-
-
-def mask_mismatch_is_a_tie(got, want, h, before, ref_state, cthr, Mc, noise):
-    """A float32 mask may differ from the reference's only where the reference's own
-    choice was decided by less than the float32 score noise.  Scores are recomputed
-    in float64 from the reference's post-update traces."""
-    if np.array_equal(got, want):
-        return True
-    if not np.array_equal(np.delete(got, h, axis=1), np.delete(want, h, axis=1)):
-        return False
-    if got[:, h].sum() != want[:, h].sum():
-        return False
-    Ci, Cj, Cij = (ref_state[n].astype(np.float64) for n in ("Ci", "Cj", "Cij"))
-    cols = slice(h * Mc, (h + 1) * Mc)
-    pij, pi, pj = Cij[:, cols], Ci[:, None], Cj[None, cols]
-    with np.errstate(all="ignore"):
-        w = np.log(np.maximum(pij, cthr ** 4) / (pi * pj))
-        term = pij * w + (pj - pij) * np.log((pj - pij) / ((1 - pi) * pj))
-    nom = np.where((pi >= cthr) & (pj >= cthr), term, 0.0).sum(axis=1)
-    score = nom / (1.0 + before.sum(axis=1))
-    diff = np.flatnonzero(got[:, h] != want[:, h])
-    spread = score[diff].max() - score[diff].min()
-    return spread <= noise * max(1.0, np.abs(score).max())
 
 
 @pytest.mark.parametrize("tag,dtype", DTYPES)

@@ -43,7 +43,7 @@ def _noalloc(lib, torch, dtype, wmask, w, Ci, Cj, Cij, cthr, hc, mc, h, iteratio
 
 
 @pytest.mark.parametrize("dtype", [np.float64, np.float32])
-def test_noalloc_mask_update_matches_allocating_entry_point(dtype):
+def test_noalloc_mask_update_matches_allocating_entry_point(dtype, port_kernels):
     import torch
     from streambrain_b200 import kernels_b200 as k
     from streambrain_b200._lib import lib
@@ -54,6 +54,9 @@ def test_noalloc_mask_update_matches_allocating_entry_point(dtype):
         want = k.update_mask(wmask.copy(), w, Ci, Cj, Cij, 0.01, hc, mc, h, iterations)
         got = _noalloc(lib, torch, dtype, wmask.copy(), w, Ci, Cj, Cij, 0.01, hc, mc, h, iterations)
         assert np.array_equal(got, want), (n, h)
+        if dtype == np.float64:   # and directly against the CPU statement of the algorithm
+            cpu = port_kernels.update_mask(wmask.copy(), w, Ci, Cj, Cij, 0.01, hc, mc, h, iterations)
+            assert np.array_equal(got, cpu), (n, h)
         assert not np.array_equal(got, wmask)   # the update did move connections
 
 
