@@ -133,6 +133,10 @@ typedef struct sbb_layer_desc {
 int sbb_layer_create(const sbb_layer_desc *desc, sbb_layer **out);
 int sbb_layer_destroy(sbb_layer *layer);
 
+/* The description the layer was created with (its shape attributes in_features, hypercolumns,
+ * minicolumns and hyper-parameters: BCPNN/backend/_cpu_base_backend.py:22-30, 93-105). */
+int sbb_layer_info(const sbb_layer *layer, sbb_layer_desc *out);
+
 /* Copy one state array from / to host memory (synchronous).  `bytes` must equal
  * the array's size.  These are the lazy attribute views (weights, bias, Ci, Cj,
  * Cij, kbi, wmask) of the reference's layer objects. */
@@ -204,6 +208,65 @@ int sbb_layer_dp_apply_rows(sbb_layer *layer, const void *delta_dev, long B_glob
                             long row_end, void *stream);
 /* Regularised bias and, with hypercolumn >= 0, the mask update (plastic only). */
 int sbb_layer_dp_finish(sbb_layer *layer, long hypercolumn, void *stream);
+
+/* ------------------------------------------------------------------------
+ * The fit / evaluate loops of a stack of layers, run below the host language:
+ * the dataset is kept on the device, batches are assembled there from the
+ * epoch's sample order, all kernels of all batches are queued on one stream
+ * without host synchronisation, and evaluation hits are counted on the device.
+ * Replaces Network of BCPNN/backend/_cpu_base_backend.py:174-314 (and the
+ * device-side shuffled batching of BCPNN/backend/full_cuda_backend/dataloader.h:70-132).
+ * Layers are borrowed: the caller creates and destroys them.  Random orders are
+ * drawn by the caller (the reference draws them from NumPy's global stream:
+ * _cpu_base_backend.py:258-264), so seeded runs reproduce the reference's.
+ * ---------------------------------------------------------------------- */
+typedef struct sbb_network sbb_network;
+
+/* How a data-parallel network sums the batch deltas over ranks (the reference's
+ * mpi backend calls MPI_Allreduce inside its kernel: K/kernels_mpi_internal.cc:153-161).
+ * reduce_begin starts an in-place sum over ranks of `elems` REALs at device_ptr, ordered
+ * after the work already queued on `stream`, and returns a token >= 0 (< 0 on failure);
+ * reduce_wait makes `stream` wait for that reduction and returns 0 on success. */
+typedef struct sbb_comm {
+  void *user;
+  long (*reduce_begin)(void *user, void *device_ptr, size_t elems, int dtype, void *stream);
+  int (*reduce_wait)(void *user, long token, void *stream);
+} sbb_comm;
+
+/* The schedule of one batch of an epoch, as pure arithmetic (no device): the slice
+ * [first, first + count) of the epoch's sample order that `rank` of `world_size` takes of batch
+ * number `batch` (count = floor(batch size / world_size); _cpu_base_backend.py:279-288), and
+ * the position `mask_slot` in the epoch's hypercolumn order of the hypercolumn whose mask is
+ * updated with this batch, or -1 for none (_cpu_base_backend.py:297-302).  epoch > 0 with fewer
+ * batches than hypercolumns + 1 returns SBB_ERR_UNSUPPORTED (the reference's ZeroDivisionError).
+ * sbb_network_train_batches and sbb_network_evaluate follow exactly this plan. */
+int sbb_network_batch_plan(long samples, long maximal_batch_size, long world_size, long rank, long hypercolumns,
+                           long epoch, long batch, long *first, long *count, long *mask_slot);
+
+int sbb_network_create(int dtype, sbb_network **out);
+int sbb_network_destroy(sbb_network *net);
+/* Network.add_layer: _cpu_base_backend.py:182-186 (the caller converts the layer's dtype first). */
+int sbb_network_add_layer(sbb_network *net, sbb_layer *layer);
+/* world_rank / world_size of the slice rule (_cpu_base_backend.py:179-180, 223-233, 279-288);
+ * `comm` may be NULL (ranks then train independently on their slices, as the cpu backend would);
+ * with `comm` every train step is the split data-parallel step, whatever world_size is. */
+int sbb_network_set_data_parallel(sbb_network *net, long rank, long world_size, const sbb_comm *comm);
+/* Copies images[samples, features] and labels[samples, classes] (host, REAL) to the device. */
+int sbb_network_set_dataset(sbb_network *net, const void *images_host, const void *labels_host, long samples,
+                            long features, long classes);
+/* The epoch's sample order (a permutation of [0, samples), host): _cpu_base_backend.py:258-260. */
+int sbb_network_set_epoch_order(sbb_network *net, const long *order_host);
+/* Batches [batch_begin, batch_end) of one epoch of training layer `layer_index`
+ * (_cpu_base_backend.py:266-312).  `epoch` counts from 0 inside one fit call: mask updates
+ * happen only for epoch > 0, for hypercolumn hypercolumn_order_host[i / period] at batches
+ * i % period == 0 with period = batches_per_epoch / (H + 1); period == 0 is the reference's
+ * ZeroDivisionError and returns SBB_ERR_UNSUPPORTED.  The call that includes the epoch's last
+ * batch also runs train_finalize and waits for the device; earlier calls only queue work. */
+int sbb_network_train_batches(sbb_network *net, long layer_index, long maximal_batch_size,
+                              const long *hypercolumn_order_host, long epoch, long batch_begin, long batch_end);
+/* Network.evaluate over the dataset in stored order: _cpu_base_backend.py:205-245.  Returns this
+ * rank's counts; the caller sums them over ranks (mpi_backend.py:63-69). */
+int sbb_network_evaluate(sbb_network *net, long maximal_batch_size, long *correct, long *total);
 
 /* Count argmax(pred[r,:]) == argmax(labels[r,:]) over rows, device buffers;
  * writes the count to *correct_host after synchronising the stream.
@@ -281,6 +344,26 @@ int sbb_device_wait_status(int *status);
  * and must be reloaded (sbb_layer_set_state).  This call then resets the word so that work can go on.
  * Synchronises the device.  No counterpart in the reference (its kernels have no waits). */
 int sbb_device_clear_wait_status(void);
+
+/* ------------------------------------------------------------------------
+ * Dataset files (host code; no device needed).  Images are unsigned bytes scaled
+ * to [0, 1] as REAL, labels unsigned bytes expanded to one-hot REAL rows.
+ * ---------------------------------------------------------------------- */
+/* Rank and dimensions of an IDX file (MNIST / Fashion-MNIST), validated against the
+ * file size.  Replaces the header handling of train.py:10-18 (which skips 16 / 8 bytes
+ * unchecked) and BCPNN/backend/full_cuda_backend/dataset.cpp:30-47. */
+int sbb_idx_info(const char *path, int *ndim, long dims[4]);
+/* out[samples, features] = bytes / 255.  train.py:9-15, dataset.cpp:49-60. */
+int sbb_read_idx_images(const char *path, int dtype, void *out, long samples, long features);
+/* out[samples, classes] one-hot.  train.py:17-21. */
+int sbb_read_idx_labels(const char *path, int dtype, void *out, long samples, long classes);
+/* Size in bytes of a headerless file (the STL-10 binaries). */
+int sbb_raw_u8_count(const char *path, long *bytes);
+/* out[samples, features] = bytes / 255 in file order.  load_stl_10_images: train.py:26-31. */
+int sbb_read_raw_u8_images(const char *path, int dtype, void *out, long samples, long features);
+/* out[samples, classes] one-hot of (byte - first_label).  load_stl_10_labels: train.py:34-41
+ * (first_label = 1). */
+int sbb_read_raw_u8_labels(const char *path, int dtype, void *out, long samples, long classes, long first_label);
 
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long sbb_kernel_launches(void);

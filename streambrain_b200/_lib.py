@@ -19,6 +19,7 @@ LIB_PATH = os.environ.get("SBB_LIBRARY") or os.path.join(HERE, "libsbb200.so")
 SBB_OK = 0
 ERR_NAMES = {1: "SBB_ERR_INVALID", 2: "SBB_ERR_CUDA", 3: "SBB_ERR_NO_DEVICE", 4: "SBB_ERR_UNSUPPORTED",
              5: "SBB_ERR_TIMEOUT"}
+ERR_INVALID, ERR_CUDA, ERR_NO_DEVICE, ERR_UNSUPPORTED, ERR_TIMEOUT = 1, 2, 3, 4, 5
 F32, F64 = 0, 1
 DENSE, PLASTIC = 0, 1
 STATE = {"weights": 0, "bias": 1, "Ci": 2, "Cj": 3, "Cij": 4, "kbi": 5, "wmask": 6}
@@ -34,6 +35,15 @@ class LayerDesc(ctypes.Structure):
     _fields_ = [("dtype", c_int), ("kind", c_int), ("in_features", c_long), ("hypercolumns", c_long),
                 ("minicolumns", c_long), ("taupdt", c_double), ("khalf", c_double), ("pmin", c_double),
                 ("taubdt", c_double), ("mask_iterations", c_long)]
+
+
+REDUCE_BEGIN_FN = ctypes.CFUNCTYPE(c_long, c_void_p, c_void_p, c_size_t, c_int, c_void_p)
+REDUCE_WAIT_FN = ctypes.CFUNCTYPE(c_int, c_void_p, c_long, c_void_p)
+
+
+class Comm(ctypes.Structure):
+    """``sbb_comm``: how a data-parallel network sums device buffers over ranks."""
+    _fields_ = [("user", c_void_p), ("reduce_begin", REDUCE_BEGIN_FN), ("reduce_wait", REDUCE_WAIT_FN)]
 
 
 # name -> (restype, argtypes); one entry per declaration in include/sbb200.h
@@ -71,6 +81,17 @@ SIGNATURES = {
     "sbb_layer_dp_apply_vectors": (c_int, [c_void_p, c_void_p, c_long, c_void_p]),
     "sbb_layer_dp_apply_rows": (c_int, [c_void_p, c_void_p, c_long, c_long, c_long, c_void_p]),
     "sbb_layer_dp_finish": (c_int, [c_void_p, c_long, c_void_p]),
+    "sbb_layer_info": (c_int, [c_void_p, POINTER(LayerDesc)]),
+    "sbb_network_batch_plan": (c_int, [c_long, c_long, c_long, c_long, c_long, c_long, c_long, POINTER(c_long),
+                                       POINTER(c_long), POINTER(c_long)]),
+    "sbb_network_create": (c_int, [c_int, POINTER(c_void_p)]),
+    "sbb_network_destroy": (c_int, [c_void_p]),
+    "sbb_network_add_layer": (c_int, [c_void_p, c_void_p]),
+    "sbb_network_set_data_parallel": (c_int, [c_void_p, c_long, c_long, c_void_p]),
+    "sbb_network_set_dataset": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_long, c_long]),
+    "sbb_network_set_epoch_order": (c_int, [c_void_p, c_void_p]),
+    "sbb_network_train_batches": (c_int, [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_long]),
+    "sbb_network_evaluate": (c_int, [c_void_p, c_long, POINTER(c_long), POINTER(c_long)]),
     "sbb_count_correct": (c_int, [c_int, c_void_p, c_void_p, c_long, c_long, POINTER(c_long), c_void_p]),
     "sbb_update_mask_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_double, c_long,
                                         c_long, c_long, c_long, c_long, c_long, c_void_p]),
@@ -87,6 +108,12 @@ SIGNATURES = {
     "sbb_tensor_path_available": (c_int, []),
     "sbb_device_wait_status": (c_int, [POINTER(c_int)]),
     "sbb_device_clear_wait_status": (c_int, []),
+    "sbb_idx_info": (c_int, [c_char_p, POINTER(c_int), POINTER(c_long)]),
+    "sbb_read_idx_images": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long]),
+    "sbb_read_idx_labels": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long]),
+    "sbb_raw_u8_count": (c_int, [c_char_p, POINTER(c_long)]),
+    "sbb_read_raw_u8_images": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long]),
+    "sbb_read_raw_u8_labels": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long, c_long]),
     "sbb_kernel_launches": (c_ulonglong, []),
     "sbb_stream_sync": (c_int, [c_void_p]),
 }

@@ -191,10 +191,32 @@ class _DeviceLayer:
         """Change the precision of the layer (_cpu_base_backend.py:53-59, 135-142)."""
         if np.dtype(dtype) == np.dtype(self.dtype):
             return
+        if getattr(self, "_borrowed", False):
+            raise RuntimeError("convert() a layer before adding it to a Network")
         state = {n: self._get(n) for n in self._state_names}
         lib.sbb_layer_destroy(self._handle)
         self._handle = None
         self._create(dtype, {n: (v if n == "wmask" else v.astype(dtype)) for n, v in state.items()})
+
+    # -- checkpoint ------------------------------------------------------
+    _hyper_names = ("in_features", "hypercolumns", "minicolumns", "taupdt")
+
+    def checkpoint(self) -> dict:
+        """State arrays and hyper-parameters as numpy values (see :meth:`Network.save`)."""
+        out = {n: self._get(n) for n in self._state_names}
+        out["kind"] = np.array(self._kind)
+        for n in self._hyper_names:
+            out["hp_" + n] = np.array(getattr(self, n))
+        return out
+
+    def restore(self, saved: dict) -> None:
+        if int(saved["kind"]) != self._kind:
+            raise ValueError("checkpoint layer kind %d does not match this layer (%d)" % (int(saved["kind"]), self._kind))
+        for n in ("in_features", "hypercolumns", "minicolumns"):
+            if int(saved["hp_" + n]) != getattr(self, n):
+                raise ValueError("checkpoint %s = %d, this layer has %d" % (n, int(saved["hp_" + n]), getattr(self, n)))
+        for n in self._state_names:
+            self._set(n, saved[n].astype(self._np_dtype(n)))
 
     # -- data-parallel step (one exchange: sum of the batch deltas) -------
     def delta_buffer(self):
@@ -282,6 +304,8 @@ class StructuralPlasticityLayer(_DeviceLayer):
 
     _kind = _lib.PLASTIC
     _state_names = ("weights", "bias", "Ci", "Cj", "Cij", "kbi", "wmask")
+    _hyper_names = ("in_features", "hypercolumns", "minicolumns", "taupdt", "khalf", "pmin", "taubdt", "density",
+                    "mask_iterations")
 
     def __init__(self, in_features, hypercolumns, minicolumns, taupdt, khalf, pmin, taubdt, density,
                  mask_iterations, initial_counters, dtype=np.float64, use_mask_iterations=False):
@@ -316,19 +340,21 @@ class StructuralPlasticityLayer(_DeviceLayer):
 
 
 class Network:
-    """Layer container with the reference's ``fit`` / ``evaluate`` loops
-    (_cpu_base_backend.py:174-314): per epoch one sample permutation and one
-    hypercolumn permutation from the global NumPy stream, batches of
-    ``maximal_batch_size`` (last one partial), every rank taking the slice
-    ``[start + rank*local, +local)`` with ``local = batch // world_size``, a mask
-    update every ``nb // (H+1)`` batches from the second epoch on, and
-    ``train_finalize`` after every epoch.
+    """Layer container with the reference's ``fit`` / ``evaluate`` interface
+    (_cpu_base_backend.py:174-245) on top of the native loop driver (``sbb_network_*``).
 
-    The loop is written against the layer interface only, so it drives any layer
-    type.  Layers that offer ``dp_train_step`` are trained with one sum-allreduce
-    of the batch deltas per step when ``world_size > 1`` (``all_reduce`` must be
-    supplied, see :meth:`set_data_parallel`).
+    The loops themselves run in the C library: the dataset is uploaded once per call, every batch is
+    assembled on the device from the epoch's sample order, and nothing synchronises with the host until
+    an epoch (or an evaluation) ends.  What stays here is what must come from Python to reproduce a
+    seeded reference run: per epoch one permutation of the samples and then one of the trained layer's
+    hypercolumns, both drawn from NumPy's global stream (_cpu_base_backend.py:258-264).
+
+    With ``world_size > 1`` every rank takes the reference's slice of each batch
+    (_cpu_base_backend.py:279-288) and, when :meth:`set_data_parallel` was given ``all_reduce``, the
+    trained layer sums its batch deltas over the ranks once per step (the mpi backend's scheme).
     """
+
+    CHUNK = 64   # batches queued per native call: the granularity of the progress bar
 
     def __init__(self, dtype):
         self.dtype = dtype
@@ -338,25 +364,84 @@ class Network:
         self._all_reduce = None
         self._sum_counts = None
         self.verbose = True
-        self.device_resident = True
+        self._handle = ctypes.c_void_p()
+        check(lib.sbb_network_create(dtype_code(dtype), ctypes.byref(self._handle)))
+        self._comm = None
+        self._pending = {}
 
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h is not None and h.value:
+            try:
+                lib.sbb_network_destroy(h)
+            except Exception:
+                pass
+            self._handle = None
+
+    # -- data parallelism ---------------------------------------------------
     def set_data_parallel(self, rank, world_size, all_reduce=None, sum_counts=None):
-        """``all_reduce(tensor) -> handle with wait()`` sums a device tensor over
-        ranks in place; ``sum_counts(np.ndarray) -> np.ndarray`` sums evaluation
-        counters (the mpi backend's Allreduce, mpi_backend.py:63-69)."""
+        """``all_reduce(tensor) -> handle with wait()`` starts an in-place sum of a device tensor over
+        the ranks (``dist.all_reduce(t, async_op=True)``); ``sum_counts(np.ndarray) -> np.ndarray`` sums
+        the evaluation counters (the mpi backend's Allreduce, mpi_backend.py:63-69)."""
         self.world_rank, self.world_size = rank, world_size
         self._all_reduce, self._sum_counts = all_reduce, sum_counts
+        comm = None
+        if all_reduce is not None:
+            comm = self._make_comm(all_reduce)
+        self._comm = comm   # keeps the callbacks alive
+        check(lib.sbb_network_set_data_parallel(self._handle, rank, world_size,
+                                                ctypes.byref(comm) if comm is not None else None))
 
+    def _make_comm(self, all_reduce):
+        pending = self._pending
+        tdtype = {_lib.F32: torch.float32, _lib.F64: torch.float64}
+        ticket = [0]
+
+        def begin(_user, ptr, elems, dtype, stream):
+            try:
+                typestr = "<f4" if dtype == _lib.F32 else "<f8"
+                holder = type("_DevicePtr", (), {"__cuda_array_interface__": {
+                    "shape": (int(elems),), "typestr": typestr, "data": (int(ptr), False), "version": 2}})()
+                with torch.cuda.stream(torch.cuda.ExternalStream(int(stream or 0))):
+                    t = torch.as_tensor(holder, device="cuda")
+                    assert t.dtype == tdtype[dtype]
+                    work = all_reduce(t)
+                ticket[0] += 1
+                pending[ticket[0]] = (work, t)
+                return ticket[0]
+            except Exception:   # an exception must not unwind through the C caller
+                import traceback
+                traceback.print_exc()
+                return -1
+
+        def wait(_user, token, stream):
+            try:
+                work, _t = pending.pop(int(token))
+                with torch.cuda.stream(torch.cuda.ExternalStream(int(stream or 0))):
+                    work.wait()
+                return 0
+            except Exception:
+                import traceback
+                traceback.print_exc()
+                return 1
+
+        return _lib.Comm(None, _lib.REDUCE_BEGIN_FN(begin), _lib.REDUCE_WAIT_FN(wait))
+
+    # -- reference API --------------------------------------------------------
     def add_layer(self, layer):
         if layer.dtype != self.dtype:
             layer.convert(self.dtype)
+        check(lib.sbb_network_add_layer(self._handle, layer._handle))
         self._layers.append(layer)
+        layer._borrowed = True   # the network holds the native handle: it must not be re-created
 
-    def fit(self, training_data, training_labels, maximal_batch_size, schedule):
-        training_data = training_data.astype(self.dtype)
-        training_labels = training_labels.astype(self.dtype)
-        for layer, epochs in schedule:
-            self._train_layer(layer, maximal_batch_size, training_data, training_labels, epochs)
+    def _upload(self, data, labels):
+        x = np.ascontiguousarray(data, dtype=self.dtype)
+        t = np.ascontiguousarray(labels, dtype=self.dtype)
+        if x.ndim != 2 or t.ndim != 2 or x.shape[0] != t.shape[0]:
+            raise ValueError("data and labels must be [n, features] and [n, classes]")
+        check(lib.sbb_network_set_dataset(self._handle, host_ptr(x), host_ptr(t), x.shape[0], x.shape[1], t.shape[1]))
+        return x.shape[0]
 
     def _progress(self, total, description):
         if self.world_rank == 0 and self.verbose:
@@ -366,104 +451,61 @@ class Network:
             return bar
         return nullcontext()
 
-    def _on_device(self):
-        return (self.device_resident and torch is not None and torch.cuda.is_available()
-                and all(isinstance(l, _DeviceLayer) for l in self._layers))
-
-    def _to_device(self, a):
-        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    def fit(self, training_data, training_labels, maximal_batch_size, schedule):
+        """_cpu_base_backend.py:188-203, 247-314."""
+        n = self._upload(training_data, training_labels)
+        batches = (n + maximal_batch_size - 1) // maximal_batch_size
+        for layer, epochs in schedule:
+            hypercolumns = self._layers[layer].hypercolumns
+            for epoch in range(epochs):
+                if self.world_rank == 0 and self.verbose:
+                    print('Layer - %d/%d' % (layer + 1, len(self._layers)), flush=True)
+                # the two draws of an epoch, in the reference's order
+                order = np.ascontiguousarray(np.random.permutation(range(n)), dtype=np.int64)
+                hc_order = np.ascontiguousarray(np.random.permutation(range(hypercolumns)), dtype=np.int64)
+                check(lib.sbb_network_set_epoch_order(self._handle, host_ptr(order)))
+                with self._progress(batches, 'Epoch %d/%d' % (epoch + 1, epochs)) as bar:
+                    for first in range(0, batches, self.CHUNK):
+                        upto = min(batches, first + self.CHUNK)
+                        rc = lib.sbb_network_train_batches(self._handle, layer, maximal_batch_size, host_ptr(hc_order),
+                                                           epoch, first, upto)
+                        if rc == _lib.ERR_UNSUPPORTED and b"division by zero" in (lib.sbb_last_error() or b""):
+                            # fewer batches than hypercolumns + 1: the reference fails in `i % (nb // (H + 1))`
+                            raise ZeroDivisionError(lib.sbb_last_error().decode())
+                        check(rc)
+                        if bar is not None:
+                            bar.update(upto - first)
 
     def evaluate(self, images, labels, maximal_batch_size):
-        images = images.astype(self.dtype)
-        labels = labels.astype(self.dtype)
-        correct = np.array([0])
-        total = np.array([0])
-        number_of_batches = (images.shape[0] + maximal_batch_size - 1) // maximal_batch_size
-        on_dev = self._on_device()
-        if on_dev:
-            images, labels = self._to_device(images), self._to_device(labels)
-        with self._progress(number_of_batches, "Evaluation") as pbar:
-            for i in range(number_of_batches):
-                global_start = i * maximal_batch_size
-                global_end = min(global_start + maximal_batch_size, images.shape[0])
-                local_batch_size = (global_end - global_start) // self.world_size
-                start_sample = global_start + self.world_rank * local_batch_size
-                end_sample = start_sample + local_batch_size
-                batch_images = images[start_sample:end_sample, :]
-                batch_labels = labels[start_sample:end_sample, :]
-                if batch_images.shape[0] > 0:
-                    activations = batch_images
-                    for layer in self._layers:
-                        activations = layer.compute_activation(activations)
-                    if on_dev:
-                        hit = ctypes.c_long(0)
-                        batch_labels = batch_labels.contiguous()
-                        check(lib.sbb_count_correct(dtype_code(self.dtype), activations.data_ptr(),
-                                                    batch_labels.data_ptr(), activations.shape[0],
-                                                    activations.shape[1], ctypes.byref(hit), _stream_ptr()))
-                        correct += hit.value
-                    else:
-                        correct += (np.argmax(activations, axis=1) == np.argmax(batch_labels, axis=1)).sum()
-                total += batch_images.shape[0]
-                if pbar is not None:
-                    pbar.update(1)
+        """_cpu_base_backend.py:205-245: (correct, total) as one-element arrays."""
+        self._upload(images, labels)
+        hit, seen = ctypes.c_long(0), ctypes.c_long(0)
+        with self._progress(1, "Evaluation") as bar:
+            check(lib.sbb_network_evaluate(self._handle, maximal_batch_size, ctypes.byref(hit), ctypes.byref(seen)))
+            if bar is not None:
+                bar.update(1)
+        correct, total = np.array([hit.value]), np.array([seen.value])
         if self.world_size > 1 and self._sum_counts is not None:
             correct, total = self._sum_counts(correct), self._sum_counts(total)
         return correct, total
 
-    def _train_layer(self, layer, maximal_batch_size, images, labels, epochs):
-        on_dev = self._on_device()
-        if on_dev:
-            images, labels = self._to_device(images), self._to_device(labels)
-        for epoch in range(epochs):
-            if self.world_rank == 0 and self.verbose:
-                print('Layer - %d/%d' % (layer + 1, len(self._layers)), flush=True)
-            idx = np.random.permutation(range(images.shape[0]))
-            if on_dev:
-                tidx = torch.from_numpy(idx).cuda()
-                shuffled_images = images.index_select(0, tidx)
-                shuffled_labels = labels.index_select(0, tidx)
-            else:
-                shuffled_images = images[idx, :]
-                shuffled_labels = labels[idx, :]
-            n_hypercolumns = self._layers[layer].hypercolumns
-            hypercolumns_shuffled = np.random.permutation(range(n_hypercolumns))
-            number_of_batches = (images.shape[0] + maximal_batch_size - 1) // maximal_batch_size
-            # The reference divides by this (raising ZeroDivisionError when there are
-            # fewer batches than hypercolumns + 1); kept, so short runs fail the same way.
-            mask_period = number_of_batches // (n_hypercolumns + 1)
-            with self._progress(number_of_batches, 'Epoch %d/%d' % (epoch + 1, epochs)) as pbar:
-                for i in range(number_of_batches):
-                    global_start = i * maximal_batch_size
-                    global_end = min(global_start + maximal_batch_size, images.shape[0])
-                    local_batch_size = (global_end - global_start) // self.world_size
-                    start_sample = global_start + self.world_rank * local_batch_size
-                    end_sample = start_sample + local_batch_size
-                    batch_images = shuffled_images[start_sample:end_sample, :]
-                    batch_labels = shuffled_labels[start_sample:end_sample, :]
+    # -- checkpoint / resume ----------------------------------------------------
+    def save(self, path):
+        """Write every layer's state arrays and hyper-parameters to one ``.npz`` file.  The reference has
+        no checkpointing (its only trace dump is commented out: full_cuda_backend/debug_dump.cpp:1-22)."""
+        blob = {"n_layers": np.array(len(self._layers)), "dtype": np.array(np.dtype(self.dtype).str)}
+        for k, layer in enumerate(self._layers):
+            for name, value in layer.checkpoint().items():
+                blob["l%d_%s" % (k, name)] = value
+        np.savez(path, **blob)
 
-                    prev_activation = None
-                    activation = batch_images
-                    for l in range(layer + 1):
-                        prev_activation = activation
-                        activation = self._layers[l].compute_activation(prev_activation)
-
-                    if epoch > 0 and i % mask_period == 0:
-                        h = i // mask_period
-                        h = hypercolumns_shuffled[h] if h < n_hypercolumns else None
-                    else:
-                        h = None
-
-                    target = self._layers[layer]
-                    last = layer + 1 == len(self._layers)
-                    outputs = batch_labels if last else activation
-                    if self.world_size > 1 and hasattr(target, "dp_train_step") and self._all_reduce is not None:
-                        target.dp_train_step(prev_activation, outputs, None if last else h, self.world_size,
-                                             self._all_reduce)
-                    elif last:
-                        target.train_step(prev_activation, outputs)
-                    else:
-                        target.train_step(prev_activation, outputs, h)
-                    if pbar is not None:
-                        pbar.update(1)
-                self._layers[layer].train_finalize()
+    def load(self, path):
+        """Restore the state written by :meth:`save` into this network's layers (same layer kinds and
+        shapes).  Training resumed after ``load`` continues exactly as the saved run would have."""
+        with np.load(path) as z:
+            if int(z["n_layers"]) != len(self._layers):
+                raise ValueError("checkpoint holds %d layers, the network has %d" % (int(z["n_layers"]),
+                                                                                    len(self._layers)))
+            for k, layer in enumerate(self._layers):
+                prefix = "l%d_" % k
+                layer.restore({n[len(prefix):]: z[n] for n in z.files if n.startswith(prefix)})

@@ -763,6 +763,12 @@ int sbb_layer_state_ptr(sbb_layer *L, int which, void **device_ptr) {
   return SBB_OK;
 }
 
+int sbb_layer_info(const sbb_layer *L, sbb_layer_desc *out) {
+  ARG(L && out, "layer_info: null pointer");
+  *out = L->desc;
+  return SBB_OK;
+}
+
 int sbb_layer_profile(sbb_layer *L, int enable) {
   SBB_TRY(check_layer(L));
   if (enable && !L->ev_created) {

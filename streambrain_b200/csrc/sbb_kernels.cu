@@ -1491,4 +1491,45 @@ template cudaError_t launch_count_correct<float>(const float *, const float *, l
 template cudaError_t launch_count_correct<double>(const double *, const double *, long, long, unsigned long long *,
                                                   cudaStream_t);
 
+// ----------------------------------------------------------------------------
+// Batch assembly: dst[r, :] = src[order[first + r], :] (order null: the identity).  One
+// warp copies one row in 16-byte pieces when the row pitch allows, else element-wise.
+// HBM-bound: rows * cols * sizeof(T) read and written.
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+    gather_rows_kernel(const T *__restrict__ src, const long *__restrict__ order, long first, long rows, long cols,
+                       T *__restrict__ dst, int vec16) {
+  const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long nwarps = ((long)gridDim.x * blockDim.x) >> 5;
+  for (long r = warp; r < rows; r += nwarps) {
+    const long from = order ? order[first + r] : first + r;
+    const T *s = src + from * cols;
+    T *d = dst + r * cols;
+    if (vec16) {
+      const long pieces = cols * (long)sizeof(T) / 16;
+      const uint4 *s4 = reinterpret_cast<const uint4 *>(s);
+      uint4 *d4 = reinterpret_cast<uint4 *>(d);
+      for (long k = lane; k < pieces; k += 32) d4[k] = __ldg(s4 + k);
+    } else {
+      for (long k = lane; k < cols; k += 32) d[k] = s[k];
+    }
+  }
+}
+template <typename T>
+cudaError_t launch_gather_rows(const T *src, const long *order, long first, long rows, long cols, T *dst,
+                               cudaStream_t st) {
+  if (rows <= 0) return cudaSuccess;
+  const int vec16 = (cols * (long)sizeof(T)) % 16 == 0 && aligned16(src) && aligned16(dst);
+  const long blocks = (rows + 7) / 8;   // eight warps per block, one row per warp and pass
+  const int cap = sm_count() * 8;
+  gather_rows_kernel<T><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(src, order, first, rows, cols, dst,
+                                                                                 vec16);
+  return launched();
+}
+template cudaError_t launch_gather_rows<float>(const float *, const long *, long, long, long, float *, cudaStream_t);
+template cudaError_t launch_gather_rows<double>(const double *, const long *, long, long, long, double *,
+                                                cudaStream_t);
+
 }  // namespace sbb

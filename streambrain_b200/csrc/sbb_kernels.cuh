@@ -99,4 +99,9 @@ template <typename T>
 cudaError_t launch_count_correct(const T *pred, const T *labels, long rows, long classes, unsigned long long *count,
                                  cudaStream_t st);
 
+// dst[r, :] = src[order[first + r], :] for r in [0, rows); order == nullptr means the identity.
+template <typename T>
+cudaError_t launch_gather_rows(const T *src, const long *order, long first, long rows, long cols, T *dst,
+                               cudaStream_t st);
+
 }  // namespace sbb

@@ -58,6 +58,9 @@ struct TcWork {
   int a_box3;       // A stage fetched by one 3-D box (MN-major A whose row length is a multiple of 32)
   int b_box3_tiles; // column tiles [0, b_box3_tiles) fetch their B stage by one 3-D box
   int b_prefetch;   // B k-blocks requested into L2 ahead of the load into shared memory (0 = none)
+  int chain_kb;     // kernels without register-resident sums (CHAIN == 0): k-blocks per tensor-memory
+                    // accumulation chain (0 = the whole k-range); later chains are added to the result of
+                    // the earlier ones by the epilogue, through the output itself
 };
 
 struct TcEpilogue {
@@ -176,6 +179,7 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // D[128 x N] (+)= A[128 x 8] * B[8 x N]: A read from tensor memory (128 lanes x 8 columns of 32-bit
 // values at a_tmem), B through a shared-memory descriptor, TF32 inputs, float32 accumulation.
@@ -332,7 +336,10 @@ __device__ __forceinline__ void tmem_ld_pair(uint32_t taddr_lo, uint32_t taddr_h
 // rounding, so the error of a chain grows with its length; long reductions
 // (the forward pass sums over in_features) are cut into short chains whose
 // results the epilogue warps add in full float32.
-template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
+// MULTI (kernels without register-resident sums, CHAIN == 0): the k-range of a tile is cut into chains of
+// wk.chain_kb k-blocks and the epilogue carries the running sum through its output in memory; without it a
+// tile is one chain and the epilogue is the plain one.
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false>
 // 14 warps are allocated registers as 16: 128 registers per thread is the most that fits one CTA per SM.
 __global__ void __launch_bounds__(kThreads, 1)
     tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -343,6 +350,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0 && BK <= 32, "tile shape");
   static_assert(!(FUSED && CHAIN > 0), "the fused epilogue consumes a whole-range accumulator");
   static_assert(CHAIN == 0 || BN <= 128, "register-resident running sums are sized for 128 columns");
+  static_assert(!(MULTI && CHAIN > 0), "chains are carried either in registers or through memory");
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t dyn_base = smem_u32(smem_dyn);
   const uint32_t base = (dyn_base + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -479,7 +487,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           TC_TRACE(chain, 7);
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          const int kb_end = CHAIN > 0 ? min(nkb, kb + CHAIN) : nkb;
+          const int kb_end = CHAIN > 0 ? min(nkb, kb + CHAIN) : (MULTI ? min(nkb, kb + wk.chain_kb) : nkb);
           for (bool first = true; kb < kb_end; ++kb, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
@@ -669,6 +677,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
       } else {
+        // The k-range of a tile may be cut into several tensor-memory accumulation chains (the tensor core
+        // truncates every accumulate, so the error of a chain grows with its length): chain 0 forms the
+        // result as if it were the whole sum, every later chain adds its part to what the earlier ones
+        // stored (read back through L2), and only the last chain clamps the trace and writes the weight.
+        const int nchains = MULTI ? (nkb + wk.chain_kb - 1) / wk.chain_kb : 1;
+       for (int cc = 0; cc < nchains && ok; ++cc) {
+        const bool first_chain = !MULTI || cc == 0, last_chain = !MULTI || cc == nchains - 1;
         const uint32_t buf = chain & 1u, aph = (chain >> 1) & 1u;
         // Everything the fused epilogue needs besides the accumulator is fetched before waiting for
         // the accumulator, so these global-memory latencies overlap the wait.
@@ -782,12 +797,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                   c[rr][rep] = *reinterpret_cast<const float2 *>(sl + (16 * hh + 8 * rr) * 128 + swz[rep]);
               if (hh == 1) {
                 // The buffer is about to be overwritten by the async proxy (TMA): every lane's
-                // reads above must have been performed first, not merely issued.
-                fence_async_smem();
+                // reads above must have been performed first, not merely issued.  With several chains the
+                // block about to be fetched may be one this warp stored a moment ago: those global writes
+                // are ordered before the fetch as well.
+                if (MULTI) fence_async_all(); else fence_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                  // block slab+2: two column groups ahead in this tile, or the next tile's first groups
+                  // block slab+2: two column groups ahead in this pass over the tile, else the first groups
+                  // of the tile's next chain (blocks this warp has rewritten: hence the fence above covers
+                  // global memory too), else the next tile's
                   if (g + 2 < NG) issue_slab_at(slab + 2, mt, nt, g + 2);
+                  else if (!last_chain) issue_slab_at(slab + 2, mt, nt, g + 2 - NG);
                   else if (w + gridDim.x < total) issue_slab_at(slab + 2, mt_next, nt_next, g + 2 - NG);
                 }
               }
@@ -801,8 +821,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                   for (int rep = 0; rep < 4; ++rep) {
                     float2 c2 = c[rr][rep];
-                    c2.x = fmaxf(fmaf(c2.x, ep.p.one_minus, a[rep * 4 + rr * 2 + 0] * ep.ema_scale), 0.f);
-                    c2.y = fmaxf(fmaf(c2.y, ep.p.one_minus, a[rep * 4 + rr * 2 + 1] * ep.ema_scale), 0.f);
+                    // the old trace decays once, in chain 0
+                    c2.x = fmaf(c2.x, first_chain ? ep.p.one_minus : 1.f, a[rep * 4 + rr * 2 + 0] * ep.ema_scale);
+                    c2.y = fmaf(c2.y, first_chain ? ep.p.one_minus : 1.f, a[rep * 4 + rr * 2 + 1] * ep.ema_scale);
+                    if (!last_chain) {   // a partial sum: parked in the trace matrix (it stays in L2)
+                      __stcg(reinterpret_cast<float2 *>(cp + rep * 8), c2);
+                      continue;
+                    }
+                    c2.x = fmaxf(c2.x, 0.f);
+                    c2.y = fmaxf(c2.y, 0.f);
                     const float wx = lg2_ftz(fmaxf(c2.x, ep.p.cthr4) * (r * rcj[rep].x)) * kLn2;
                     const float wy = lg2_ftz(fmaxf(c2.y, ep.p.cthr4) * (r * rcj[rep].y)) * kLn2;
                     __stcs(reinterpret_cast<float2 *>(cp + rep * 8), c2);
@@ -823,8 +850,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                     const long n = gs + lc + rep * 8;
                     if (!(n < ep.cols)) continue;   // cols is even: n + 1 is in range too
                     float2 c2 = c[rr][rep];
-                    c2.x = fmaxf(fmaf(c2.x, ep.p.one_minus, a[rep * 4 + rr * 2 + 0] * ep.ema_scale), 0.f);
-                    c2.y = fmaxf(fmaf(c2.y, ep.p.one_minus, a[rep * 4 + rr * 2 + 1] * ep.ema_scale), 0.f);
+                    // the old trace decays once, in chain 0
+                    c2.x = fmaf(c2.x, first_chain ? ep.p.one_minus : 1.f, a[rep * 4 + rr * 2 + 0] * ep.ema_scale);
+                    c2.y = fmaf(c2.y, first_chain ? ep.p.one_minus : 1.f, a[rep * 4 + rr * 2 + 1] * ep.ema_scale);
+                    if (!last_chain) {
+                      __stcg(reinterpret_cast<float2 *>(cp + rep * 8), c2);
+                      continue;
+                    }
+                    c2.x = fmaxf(c2.x, 0.f);
+                    c2.y = fmaxf(c2.y, 0.f);
                     bool on0 = rci[j] != 0.f && rcj[rep].x != 0.f, on1 = rci[j] != 0.f && rcj[rep].y != 0.f;
                     if (has_mask) {
                       const int h0 = hc_of(n), h1 = hc_of(n + 1);
@@ -862,9 +896,16 @@ __global__ void __launch_bounds__(kThreads, 1)
               float *orow = ep.out + ((long)sp * ep.rows + grow[j]) * ep.ld;
 #pragma unroll
               for (int rep = 0; rep < 4; ++rep)
-                if (n0 + rep * 8 < ep.cols)   // cols is even: n+1 is in range too
-                  __stcs(reinterpret_cast<float2 *>(orow + n0 + rep * 8),
-                         make_float2(acc[rep * 4 + (j & 1) * 2], acc[rep * 4 + (j & 1) * 2 + 1]));
+                if (n0 + rep * 8 < ep.cols) {   // cols is even: n+1 is in range too
+                  float2 v = make_float2(acc[rep * 4 + (j & 1) * 2], acc[rep * 4 + (j & 1) * 2 + 1]);
+                  float2 *dst = reinterpret_cast<float2 *>(orow + n0 + rep * 8);
+                  if (!first_chain) {   // this thread stored the sum of the earlier chains at the same place
+                    const float2 prev = __ldcg(dst);
+                    v.x += prev.x;
+                    v.y += prev.y;
+                  }
+                  if (last_chain) __stcs(dst, v); else __stcg(dst, v);
+                }
             }
           }
         }
@@ -873,6 +914,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_before();
         mbar_arrive(bar_acc_empty(buf));  // the accumulator buffer may be overwritten
         ++chain;
+       }   // chains of this tile
       }
     }
   }
@@ -972,13 +1014,13 @@ struct TcMaps {
   CUtensorMap a, b, a3, b3, c;
 };
 
-template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN>
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false>
 cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st,
                       bool leave_reserved_sms = false) {
   using SM = TcSmem<BN, BK, STAGES, FUSED>;
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
-  auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN>;
+  auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN, MULTI>;
   static std::atomic<bool> configured[64];   // per device; setting the attribute twice is harmless
   const int dev = current_device();
   if (!configured[dev].load()) {
@@ -1018,6 +1060,11 @@ constexpr int kFwdBN = 128, kFwdBK = 32, kFwdStages = 4;
 constexpr int kFwdPrefetch = 0;  // k-blocks of W requested into L2 ahead of the shared-memory pipeline (measured: no gain at 4-16)
 constexpr int kFwdChain = 4;  // 4 k-blocks of 32 = 128 k-values (48 MMAs) per tensor-memory accumulation chain
 constexpr int kTrBN = 192, kTrBK = 16, kTrStages = 4;
+// k-blocks per accumulation chain of the batch contractions: 16 x 16 = 256 samples (96 MMAs), after which the
+// epilogue takes the partial sum over in float32.  Measured on B200: the tensor-memory accumulate truncates,
+// so a chain's sum is low by about 1e-8 x (samples in the chain) relative; 256 keeps that below 4e-6.
+constexpr int kTrChainKb = 16;
+constexpr int kLongBN = 128, kLongStages = 6;   // tiles of the row-block product when the batch spans several chains
 
 // k-blocks per split and the number of (non-empty) splits for the forward product: the split count
 // that minimises (waves of CTAs) x (k-blocks per unit), plus the cost of writing and re-reading
@@ -1071,7 +1118,7 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, kFwdBN / 32);
   if (!b3) tm.b3 = tm.b;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
-            b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch};
+            b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch, 0};
 #ifdef SBB_TC_TRACE
   if (const char *e = getenv("SBB_FWD_PREFETCH")) wk.b_prefetch = atoi(e);   // timeline builds may vary the distance
 #endif
@@ -1151,7 +1198,7 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
   // fastest when x (B x N) is the larger, row tiles fastest when y (B x M) is
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, M > N ? 1 : 0, (int)row_begin,
-            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
+            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0, kTrChainKb};
   TcEpilogue ep{};
   ep.rows = rows;
   ep.cols = M;
@@ -1177,7 +1224,9 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   ep.row0 = row_begin;
   ep.p = p;
   ep.ema_scale = p.taupdt / p.batch;
-  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
+  // a batch of more than one chain carries its running sum through the trace matrix (see the kernel)
+  cudaError_t e = B > (long)kTrChainKb * kTrBK ? launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0, true>(tm, wk, ep, st)
+                                               : launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
@@ -1193,14 +1242,30 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   tm.c = tm.a;
   const bool a3 = N % 32 == 0 && make_map_chunks(&tm.a3, x, N, B, kTrBK, 4);
   if (!a3) tm.a3 = tm.a;
-  const bool b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, kTrBN / 32);
-  if (!b3) tm.b3 = tm.b;
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
+  if (B > (long)kTrChainKb * kTrBK) {
+    // More than one accumulation chain: 128-column tiles whose running sums stay in the epilogue warps'
+    // registers (as in the forward product), so no partial sum travels through memory.
+    const bool b3n = make_map_chunks(&tm.b3, y, M, B, kTrBK, kLongBN / 32);
+    if (!b3n) tm.b3 = tm.b;
+    TcWork wk{(int)((rows + 127) / 128), (int)((M + kLongBN - 1) / kLongBN), 1, (int)B, kper, M > N ? 1 : 0,
+              (int)row_begin, a3 ? 1 : 0, b3n ? full_chunk_tiles(M, kLongBN) : 0, 0, 0};
+    TcEpilogue ep{};
+    ep.out = delta + row_begin * M;
+    ep.rows = rows;
+    ep.cols = M;
+    ep.ld = M;
+    cudaError_t e = launch_tc<false, kLongBN, kTrBK, kLongStages, false, kTrChainKb>(tm, wk, ep, st, true);
+    if (e == cudaSuccess) count_launches(1);
+    return e;
+  }
+  const bool b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, kTrBN / 32);
+  if (!b3) tm.b3 = tm.b;
   // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
   // fastest when x (B x N) is the larger, row tiles fastest when y (B x M) is
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, M > N ? 1 : 0, (int)row_begin,
-            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0};
+            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0, kTrChainKb};
   TcEpilogue ep{};
   ep.out = delta + row_begin * M;
   ep.rows = rows;

@@ -116,7 +116,8 @@ def _net_worker(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import oracle
     from streambrain_b200 import synthetic
-    from streambrain_b200.backend.b200_backend import Network
+    sys.path.insert(0, os.path.join(REPO, "tests"))
+    from plan_driver import PlanNetwork
 
     seen = []
 
@@ -125,15 +126,14 @@ def _net_worker(rank, world, port, out_dir):
             seen.append((inputs.shape[0], float(inputs[:, 0::2].sum()), hypercolumn))
 
     np.random.seed(3)
-    net = Network(np.float64)
-    net.verbose = False
-    net.set_data_parallel(rank, world, sum_counts=lambda a: _sum(a))
+    net = PlanNetwork(np.float64, rank, world)
     net.add_layer(Recorder(oracle.PortKernels(), "plastic", 16, 2, 3, 0.05, (1, 1 / 3, 1 / 3), np.float64,
                            khalf=-10.0, pmin=0.1, taubdt=0.1, density=0.5))
     net.add_layer(Recorder(oracle.PortKernels(), "dense", 6, 1, 10, 0.05, (1 / 3, 0.1, 1 / 30), np.float64))
     x, lab = synthetic.make_inputs(35, 8, 0.5, np.float64)
     net.fit(x, lab, 10, [(0, 2)])
     correct, total = net.evaluate(x, lab, 10)
+    correct, total = _sum(correct), _sum(total)   # the mpi backend's Allreduce of the counters
     np.savez(os.path.join(out_dir, "net%d.npz" % rank), seen=np.array(repr(seen)), total=total, correct=correct)
     dist.destroy_process_group()
 

@@ -199,6 +199,93 @@ def test_network_fit_and_evaluate_vs_golden(B200, tag, dtype):
             assert rel_inf(getattr(net._layers[0], name), g["l0_" + name]) < 1e-3, name
 
 
+def _small_network(B200, g, dtype):
+    n_pix, H, Mc = int(g["n_pix"]), int(g["H"]), int(g["Mc"])
+    net = B200.Network(dtype)
+    net.verbose = False
+    net.add_layer(B200.StructuralPlasticityLayer(2 * n_pix, H, Mc, 0.03, -40.0, 0.1, 0.05, 0.5, 16,
+                                                 (1, 1 / Mc, 1 / Mc)))
+    net.add_layer(B200.DenseLayer(H * Mc, 1, 10, 0.02, (1 / Mc, 1 / 10, 1 / Mc / 10)))
+    return net
+
+
+def test_network_with_reduction_callbacks_reproduces_golden_run(B200):
+    """The native loop with the data-parallel callbacks installed (one rank: the sum over ranks is the
+    identity) runs the split step -- row-block products, reduction, row-block apply -- for every batch
+    and must land on the reference's golden run like the fused step does."""
+    g = load_golden("network_f64.npz")
+    B, n_train, seed = int(g["B"]), int(g["n_train"]), int(g["seed"])
+    np.random.seed(seed)
+    random.seed(seed)
+    net = _small_network(B200, g, np.float64)
+
+    class Done:
+        def wait(self):
+            pass
+
+    started = []
+    net.set_data_parallel(0, 1, all_reduce=lambda t: started.append(t.numel()) or Done())
+    x, lab = g["x"], g["labels"]
+    net.fit(x[:n_train], lab[:n_train], B, [(0, 3)])
+    net.fit(x[:n_train], lab[:n_train], B, [(1, 2)])
+    correct, total = net.evaluate(x[n_train:], lab[n_train:], B)
+    assert len(started) > 0
+    assert np.array_equal(net._layers[0].wmask, g["l0_wmask"])
+    for li, layer in enumerate(net._layers):
+        for name in ("Ci", "Cj", "Cij", "bias", "weights"):
+            assert rel_inf(getattr(layer, name), g["l%d_%s" % (li, name)]) < 1e-9, (li, name)
+    assert int(correct[0]) == int(g["correct"][0]) and int(total[0]) == int(g["total"][0])
+
+
+@pytest.mark.parametrize("tag,dtype", DTYPES)
+def test_checkpoint_resume_equals_uninterrupted_run(B200, tmp_path, tag, dtype):
+    """save() after two epochs, load() into a fresh network, continue: bit-identical to the run that was
+    never interrupted (the random stream is carried over as well, as a resumed job would)."""
+    g = load_golden("network_%s.npz" % tag)
+    B, n_train = int(g["B"]), int(g["n_train"])
+    x, lab = g["x"][:n_train], g["labels"][:n_train]
+
+    np.random.seed(5)
+    whole = _small_network(B200, g, dtype)
+    whole.fit(x, lab, B, [(0, 2)])
+    whole.fit(x, lab, B, [(0, 2), (1, 1)])
+
+    np.random.seed(5)
+    first = _small_network(B200, g, dtype)
+    first.fit(x, lab, B, [(0, 2)])
+    first.save(tmp_path / "ckpt.npz")
+    rng = np.random.get_state()
+    del first
+
+    np.random.seed(99)                      # a fresh process: other initial weights, another stream
+    resumed = _small_network(B200, g, dtype)
+    resumed.load(tmp_path / "ckpt.npz")
+    np.random.set_state(rng)
+    resumed.fit(x, lab, B, [(0, 2), (1, 1)])
+    for a, b in zip(whole._layers, resumed._layers):
+        for name in a._state_names:
+            assert np.array_equal(getattr(a, name), getattr(b, name)), name
+    assert np.array_equal(whole.evaluate(g["x"][n_train:], g["labels"][n_train:], B)[0],
+                          resumed.evaluate(g["x"][n_train:], g["labels"][n_train:], B)[0])
+    with pytest.raises(ValueError):
+        B200.Network(dtype).load(tmp_path / "ckpt.npz")     # layer count mismatch
+
+
+def test_network_too_few_batches_for_the_mask_schedule(B200):
+    np.random.seed(0)
+    net = B200.Network(np.float32)
+    net.verbose = False
+    net.add_layer(B200.StructuralPlasticityLayer(8, 4, 2, 0.05, -10.0, 0.1, 0.1, 0.5, 16, (1, 0.5, 0.5)))
+    net.add_layer(B200.DenseLayer(8, 1, 10, 0.05, (0.5, 0.1, 0.05)))
+    from streambrain_b200 import synthetic
+    x, lab = synthetic.make_inputs(16, 4, 0.5, np.float32)
+    with pytest.raises(ZeroDivisionError):
+        net.fit(x, lab, 8, [(0, 2)])
+    net.fit(x, lab, 8, [(0, 1)])
+    correct, total = net.evaluate(x, lab, 8)
+    assert int(total[0]) == 16 and 0 <= int(correct[0]) <= 16
+
+
 def _mnist_pair(B200, port_kernels, dtype, seed=0):
     from streambrain_b200 import synthetic
     p = synthetic.layer_params("mnist_f32" if dtype == np.float32 else "mnist_f64")

@@ -1,7 +1,6 @@
-"""Host-side logic that needs no GPU: the network driver (epoch shuffles, batch
-slices, mask schedule, finalize) run over CPU oracle layers against the golden
-run of the reference, the synthetic data generator, the dispatcher and the
-row-block arithmetic of the data-parallel step."""
+"""Host-side logic that needs no GPU: the library's batch planner (batch slices per rank, mask
+schedule) driving CPU oracle layers through the reference's golden network run, the synthetic data
+generator, the dispatcher and the row-block arithmetic of the data-parallel step."""
 import importlib
 import random
 
@@ -12,7 +11,7 @@ from conftest import TOL, load_golden, rel_inf
 
 import oracle
 from streambrain_b200 import parallel, synthetic
-from streambrain_b200.backend.b200_backend import Network
+from plan_driver import PlanNetwork, plan
 
 
 class _OraclePlastic(oracle.OracleLayer):
@@ -30,8 +29,7 @@ def _golden_network(port_kernels, tag, dtype, world=(0, 1)):
     seed = int(g["seed"])
     np.random.seed(seed)
     random.seed(seed)
-    net = Network(np.dtype(dtype))
-    net.verbose = False
+    net = PlanNetwork(np.dtype(dtype))
     l0 = oracle.OracleLayer(port_kernels, "plastic", 2 * n_pix, H, Mc, 0.03, (1, 1 / Mc, 1 / Mc), np.float64,
                             khalf=-40.0, pmin=0.1, taubdt=0.05, density=0.5)
     l1 = oracle.OracleLayer(port_kernels, "dense", H * Mc, 1, 10, 0.02, (1 / Mc, 1 / 10, 1 / Mc / 10), np.float64)
@@ -50,8 +48,8 @@ def _golden_network(port_kernels, tag, dtype, world=(0, 1)):
 
 def test_network_driver_reproduces_reference_run_f64(port_kernels):
     g, net, correct, total = _golden_network(port_kernels, "f64", np.float64)
-    assert np.array_equal(net._layers[0].wmask, g["l0_wmask"])
-    for li, layer in enumerate(net._layers):
+    assert np.array_equal(net.layers[0].wmask, g["l0_wmask"])
+    for li, layer in enumerate(net.layers):
         for name in ("Ci", "Cj", "Cij", "bias", "weights"):
             assert rel_inf(getattr(layer, name), g["l%d_%s" % (li, name)]) < 1e-9, (li, name)
     assert int(correct[0]) == int(g["correct"][0]) and int(total[0]) == int(g["total"][0])
@@ -59,7 +57,7 @@ def test_network_driver_reproduces_reference_run_f64(port_kernels):
 
 def test_network_driver_reproduces_reference_run_f32(port_kernels):
     g, net, correct, total = _golden_network(port_kernels, "f32", np.float32)
-    for li, layer in enumerate(net._layers):
+    for li, layer in enumerate(net.layers):
         for name in ("Ci", "Cj"):
             assert rel_inf(getattr(layer, name), g["l%d_%s" % (li, name)]) < 1e-3, (li, name)
     assert int(total[0]) == int(g["total"][0])
@@ -68,8 +66,7 @@ def test_network_driver_reproduces_reference_run_f32(port_kernels):
 def test_mask_schedule_needs_enough_batches(port_kernels):
     """Fewer batches than hypercolumns+1 divides by zero in the reference
     (_cpu_base_backend.py:297); the driver keeps that behaviour."""
-    net = Network(np.float64)
-    net.verbose = False
+    net = PlanNetwork(np.float64)
     net.add_layer(oracle.OracleLayer(port_kernels, "plastic", 8, 4, 2, 0.05, (1, 0.5, 0.5), np.float64,
                                      khalf=-10.0, pmin=0.1, taubdt=0.1, density=0.5, rng=np.random.RandomState(0)))
     net.add_layer(oracle.OracleLayer(port_kernels, "dense", 8, 1, 10, 0.05, (0.5, 0.1, 0.05), np.float64,
@@ -77,6 +74,24 @@ def test_mask_schedule_needs_enough_batches(port_kernels):
     x, lab = synthetic.make_inputs(16, 4, 0.5, np.float64)
     with pytest.raises(ZeroDivisionError):
         net.fit(x, lab, 8, [(0, 2)])
+    net.fit(x, lab, 8, [(0, 1)])   # a single epoch never reaches the mask schedule
+
+
+def test_batch_plan_arithmetic():
+    """469 batches of 128 over 60000 samples with 30 hypercolumns: exactly 30 mask updates per later
+    epoch, at batches 0, 15, ..., 435, none in the first epoch; the last batch is partial; two ranks
+    halve every batch and drop the odd sample."""
+    n, bs, H = 60000, 128, 30
+    nb = -(-n // bs)
+    assert all(plan(n, bs, 1, 0, H, 0, b)[2] == -1 for b in range(nb))
+    slots = [(b, plan(n, bs, 1, 0, H, 1, b)[2]) for b in range(nb)]
+    assert [b for b, s in slots if s >= 0] == list(range(0, 450, 15))
+    assert [s for b, s in slots if s >= 0] == list(range(30))
+    assert plan(n, bs, 1, 0, H, 1, nb - 1)[:2] == ((nb - 1) * bs, 96)
+    assert plan(35, 10, 2, 1, 2, 0, 3)[:2] == (30 + 2, 2)       # 5 samples left, 2 per rank
+    assert plan(35, 10, 2, 0, 2, 0, 1)[:2] == (10, 5)
+    with pytest.raises(Exception):
+        plan(35, 10, 2, 2, 2, 0, 0)                               # rank outside the world
 
 
 def test_synthetic_inputs_are_seeded_and_complementary():
@@ -115,4 +130,5 @@ def test_dispatcher_names(monkeypatch):
     monkeypatch.setenv("BCPNN_BACKEND", "b200")
     mod = importlib.reload(streambrain_b200)
     assert mod.backend() == "b200"
-    assert mod.Network is Network
+    from streambrain_b200.backend import b200_backend
+    assert mod.Network is b200_backend.Network
