@@ -138,8 +138,28 @@ def _build_reference_isa(root: str, isa: str, force: bool) -> None:
                 (REF_KERNEL_SOURCE, os.path.basename(blas_path), " ".join(cmd)))
 
 
+# The reference's own kernel test (a script that compares a kernel module with its NumPy kernels) and the two
+# modules it imports.  They are staged, unmodified, beside the compiled module so that the GPU box -- which has
+# no reference checkout -- can run that test against this repository's kernel module.  The directory is
+# git-ignored: nothing of the reference enters the history.
+CONTRACT_DIR = os.path.join(REF_DIR, "contract")
+CONTRACT_FILES = ("test_openmp.py", "kernels_numpy.py", "kernels_openmp.py")
+
+
+def stage_reference_contract() -> str | None:
+    root = reference_root()
+    if root is None:
+        return CONTRACT_DIR if os.path.exists(os.path.join(CONTRACT_DIR, CONTRACT_FILES[0])) else None
+    import shutil
+    os.makedirs(CONTRACT_DIR, exist_ok=True)
+    for name in CONTRACT_FILES:
+        shutil.copyfile(os.path.join(root, "BCPNN", "backend", "_kernels", name), os.path.join(CONTRACT_DIR, name))
+    return CONTRACT_DIR
+
+
 def build_all(force: bool = False) -> dict:
-    return {"oracle": build_oracle(force), "reference": build_reference(force)}
+    return {"oracle": build_oracle(force), "reference": build_reference(force),
+            "contract": stage_reference_contract()}
 
 
 if __name__ == "__main__":

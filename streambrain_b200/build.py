@@ -53,5 +53,35 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+PYBIND_SRC = os.path.join(HERE, "pybind", "bcpnn_kernels_b200_internal.cpp")
+
+
+def pybind_module_path() -> str:
+    import sysconfig
+    return os.path.join(HERE, "_bcpnn_kernels_b200_internal" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_pybind(force: bool = False) -> str | None:
+    """The pybind11 kernel module with the reference's function names, linked against libsbb200.so
+    (found at run time next to the module).  Returns None where pybind11 is not installed."""
+    import sysconfig
+    try:
+        import pybind11
+    except ImportError:
+        return None
+    out = pybind_module_path()
+    deps = [PYBIND_SRC, LIB] + glob.glob(os.path.join(INCLUDE, "*.h"))
+    if not force and os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
+        return out
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-I" + INCLUDE,
+           "-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"], "-o", out, PYBIND_SRC,
+           "-L" + HERE, "-l:libsbb200.so", "-Wl,-rpath,$ORIGIN"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("g++ failed:\n%s\n%s\n%s" % (" ".join(cmd), proc.stdout, proc.stderr))
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_pybind(force="--force" in sys.argv))

@@ -800,15 +800,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 // reads above must have been performed first, not merely issued.  With several chains the
                 // block about to be fetched may be one this warp stored a moment ago: those global writes
                 // are ordered before the fetch as well.
-                if (MULTI) fence_async_all(); else fence_async_smem();
+                fence_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                  // block slab+2: two column groups ahead in this pass over the tile, else the first groups
-                  // of the tile's next chain (blocks this warp has rewritten: hence the fence above covers
-                  // global memory too), else the next tile's
+                  // block slab+2: two column groups ahead in this tile, or the next tile's first groups.  With
+                  // several chains the blocks of the next pass are fetched at the end of this one (below).
                   if (g + 2 < NG) issue_slab_at(slab + 2, mt, nt, g + 2);
-                  else if (!last_chain) issue_slab_at(slab + 2, mt, nt, g + 2 - NG);
-                  else if (w + gridDim.x < total) issue_slab_at(slab + 2, mt_next, nt_next, g + 2 - NG);
+                  else if (!MULTI && w + gridDim.x < total) issue_slab_at(slab + 2, mt_next, nt_next, g + 2 - NG);
                 }
               }
               if (g_fast) {
@@ -880,6 +878,23 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             ++slab;
             if (threadIdx.x == kConvWarps * 32 && g < 3) TC_TRACE(chain, 13 + g);
+          }
+          if (MULTI && ok) {
+            // The next pass re-reads blocks this warp has just stored (the running sums): one fence per pass
+            // orders those global writes, and the shared-memory reads of both landing buffers, before the
+            // async-proxy fetches of the next pass's first two blocks (or the next tile's).
+            static_assert(!MULTI || NG >= 2, "two landing buffers are refilled at the end of a pass");
+            fence_async_all();
+            __syncwarp();
+            if (lane == 0) {
+              if (!last_chain) {
+                issue_slab_at(slab, mt, nt, 0);
+                issue_slab_at(slab + 1, mt, nt, 1);
+              } else if (w + gridDim.x < total) {
+                issue_slab_at(slab, mt_next, nt_next, 0);
+                issue_slab_at(slab + 1, mt_next, nt_next, 1);
+              }
+            }
           }
         } else {
 #pragma unroll 1
