@@ -67,6 +67,9 @@ def parse_args():
                          "apply) with nothing to reduce: the kernels every rank runs at N > 1")
     ap.add_argument("--no-dp-large", action="store_true",
                     help="skip the extra leg on the large-batch data-parallel workload (stl10_dp_f32)")
+    ap.add_argument("--dp-mode", default="sharded", choices=["sharded", "allreduce"],
+                    help="data-parallel step at N > 1: row-sharded over peer-mapped memory (partial sums stored "
+                         "into the owner's memory, every row updated once) or all-reduce and replicated update")
     ap.add_argument("--no-other-configs", action="store_true",
                     help="skip the short legs on the other configurations (mnist_f32, mnist_f64, wide_f32)")
     ap.add_argument("--contraction", default="tensor", choices=["tensor", "general"],
@@ -352,10 +355,13 @@ def short_leg(B200, lib, check, torch, wl, peaks, steps=20, warmup=3):
             "step_roofline": step_roofline_of(p, batch, ms, peaks, tensor_path)}
 
 
-def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce):
+def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce, sharded):
     """Outside the timed region, at N > 1: (1) the replicas of the timed layer are bit-identical
     (checksums of Cij, weights and mask agree over ranks); (2) on a reduced shape one data-parallel
     step over the ranks equals the fused single-GPU step at the same global batch."""
+    token = torch.zeros(1, device="cuda")
+    if sharded:   # a rank holds current traces only for the rows it owns until they are shared
+        layer.share_traces(lambda: dist.all_reduce(token))
     sums = []
     for name in ("Cij", "weights", "wmask"):
         t = layer.state_tensor(name)
@@ -384,10 +390,15 @@ def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_
         return l
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     dp = make()
+    if sharded:
+        from streambrain_b200 import parallel
+        dp.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
     xl = torch.from_numpy(np.ascontiguousarray(xg[rank * b_local:(rank + 1) * b_local])).cuda()
     yl = torch.empty((b_local, M), dtype=torch.float32, device="cuda")
     check(lib.sbb_layer_forward(dp._handle, xl.data_ptr(), b_local, yl.data_ptr(), stream))
     dp.dp_train_step(xl, yl, h, world, all_reduce)
+    if sharded:
+        dp.share_traces(lambda: dist.all_reduce(token))
     torch.cuda.synchronize()
     err, masks_equal = None, None
     if rank == 0:
@@ -405,7 +416,8 @@ def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_
         if masks_equal:
             a, b = dp.weights.astype(np.float64), one.weights.astype(np.float64)
             err = max(err, float(np.abs(a - b).max() / max(1.0, np.abs(b).max())) / 10)
-    return {"replicas_identical": identical, "dp_vs_single_rel_err": err, "dp_vs_single_masks_equal": masks_equal,
+    return {"mode": "row-sharded over peer-mapped memory" if sharded else "all-reduce, replicated update",
+            "replicas_identical": identical, "dp_vs_single_rel_err": err, "dp_vs_single_masks_equal": masks_equal,
             "dp_vs_single_shape": "%d->%dx%d, global batch %d, one step with a mask update; traces relative "
                                   "to their maximum, weights / 10 (their tolerance is 10x the traces')" % (
                                       N, H, Mc, b_local * world)}
@@ -441,6 +453,10 @@ def run_b200(args, wl, p, batch):
     xs_host = make_batches(p, batch, POOL, synthetic.DATA_SEED + 1000 * rank)
     ref_batch = xs_host[0] if rank == 0 else make_batches(p, batch, 1, synthetic.DATA_SEED)[0]
     layer.Ci, layer.Cj, layer.Cij = synthetic.steady_state_traces(p, ref_batch)   # identical on every rank
+    sharded = world > 1 and args.dp_mode == "sharded"
+    if sharded:
+        from streambrain_b200 import parallel
+        layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
     xs = [torch.from_numpy(x).cuda() for x in xs_host]
     ys = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -516,6 +532,8 @@ def run_b200(args, wl, p, batch):
         big = B200.StructuralPlasticityLayer(N, H, Mc, hl["taupdt"], hl["khalf"], hl["pmin"], hl["taubdt"],
                                              hl["density"], 16, hl["initial_counters"], dtype=np_dtype)
         big.Ci, big.Cj, big.Cij = synthetic.steady_state_traces(pl, ref_batch)
+        if sharded:
+            big.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
         gen = torch.Generator(device="cuda")
         gen.manual_seed(synthetic.DATA_SEED + 17 * rank)
         xl = []
@@ -633,7 +651,7 @@ def run_b200(args, wl, p, batch):
 
     dp_checks = None
     if world > 1:
-        dp_checks = data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce)
+        dp_checks = data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce, sharded)
 
     if rank != 0:
         if world > 1:

@@ -210,6 +210,44 @@ int sbb_layer_dp_apply_rows(sbb_layer *layer, const void *delta_dev, long B_glob
 int sbb_layer_dp_finish(sbb_layer *layer, long hypercolumn, void *stream);
 
 /* ------------------------------------------------------------------------
+ * Row-sharded data-parallel step over peer-mapped memory (one process per GPU, at
+ * most 8 GPUs of one node).  Every rank owns a block of input rows of the trace
+ * matrix Cij (multiples of 128 rows, equal blocks).  Per step each rank
+ *   1. sbb_layer_shard_products: forms x^T y of its batch slice and writes each
+ *      owner's rows straight into that owner's staging memory over NVLink (plain
+ *      peer stores from the product kernel's epilogue; one slot per source rank),
+ *      and its column sums into every rank's vector stage;
+ *   -- barrier over the ranks (the caller's: any collective on `stream`) --
+ *   2. sbb_layer_shard_apply: updates Ci, Cj (all ranks, identical), sums the slots
+ *      of its own rows in rank order, updates those rows of Cij, and writes the new
+ *      weight rows into EVERY rank's weight matrix; bias; with hypercolumn >= 0 also
+ *      the mask scores of its rows into every rank's work arrays;
+ *   -- barrier --
+ *   3. (mask steps) sbb_layer_shard_mask: the swaps, identically on every rank, and
+ *      the owners rewrite the weights of swapped rows everywhere;  -- barrier --.
+ * Same arithmetic as the reduce-then-update scheme of the reference's MPI backend
+ * (K/kernels_mpi_internal.cc:100-250; its row-sharded tail kernels with Allgatherv:
+ * :263-286, 352-404, 453-484) with the Allreduce replaced by stores to the owner and
+ * the update done once per row instead of once per rank.  Between barriers no kernel
+ * waits on another rank.  After a sharded step only the owner's rows of Cij are
+ * current on a rank; sbb_layer_shard_share_traces copies them to all ranks (then a
+ * barrier) when the whole matrix is wanted (checkpoints, tests).
+ * ---------------------------------------------------------------------- */
+#define SBB_SHARD_BUFFERS 5        /* staging slots, vector slots, weights, mask work arrays, Cij */
+#define SBB_SHARD_HANDLE_BYTES 64  /* one CUDA IPC memory handle */
+/* Allocates the staging memory and writes this rank's SBB_SHARD_BUFFERS IPC handles to
+ * handles_out (SBB_SHARD_BUFFERS * SBB_SHARD_HANDLE_BYTES bytes), to be exchanged by the caller. */
+int sbb_layer_shard_init(sbb_layer *layer, long rank, long world_size, unsigned char *handles_out);
+/* all_handles: the handles of ranks 0..world_size-1, concatenated in rank order. */
+int sbb_layer_shard_attach(sbb_layer *layer, const unsigned char *all_handles);
+int sbb_layer_shard_products(sbb_layer *layer, const void *x_dev, const void *y_dev, long B_local, void *stream);
+int sbb_layer_shard_apply(sbb_layer *layer, long B_global, long hypercolumn, void *stream);
+int sbb_layer_shard_mask(sbb_layer *layer, long hypercolumn, void *stream);
+int sbb_layer_shard_share_traces(sbb_layer *layer, void *stream);
+/* Rows [row_begin, row_end) of the trace matrix that `rank` owns. */
+int sbb_layer_shard_rows(const sbb_layer *layer, long rank, long *row_begin, long *row_end);
+
+/* ------------------------------------------------------------------------
  * The fit / evaluate loops of a stack of layers, run below the host language:
  * the dataset is kept on the device, batches are assembled there from the
  * epoch's sample order, all kernels of all batches are queued on one stream

@@ -226,12 +226,70 @@ class _DeviceLayer:
         return self._delta
 
     def dp_train_step(self, inputs, outputs, hypercolumn, world_size, all_reduce, row_blocks=4):
-        """Data-parallel train step: see :func:`streambrain_b200.parallel.pipelined_dp_step`.
-        ``all_reduce(tensor)`` must start an in-place sum over ranks and return a
-        handle with ``wait()``, e.g. ``dist.all_reduce(t, async_op=True)``."""
+        """Data-parallel train step.  ``all_reduce(tensor)`` must start an in-place sum over ranks and
+        return a handle with ``wait()``, e.g. ``dist.all_reduce(t, async_op=True)``.  On a layer set up
+        by :meth:`shard_rows` the step is the row-sharded one (partial sums stored straight into the
+        owner's memory, see :meth:`sharded_train_step`) and ``all_reduce`` only serves as the barrier;
+        otherwise every rank reduces and applies the whole matrix
+        (:func:`streambrain_b200.parallel.pipelined_dp_step`)."""
         x = self._dev_input(inputs, self.in_features)
         y = self._dev_input(outputs, self.out_features)
+        if getattr(self, "_shard", None) is not None:
+            if self._shard[1] != world_size:
+                raise ValueError("the layer was sharded over %d ranks, the step runs on %d" % (self._shard[1], world_size))
+            token = self._barrier_token()
+            self.sharded_train_step(x, y, hypercolumn, lambda: all_reduce(token).wait())
+            return
         pipelined_dp_step(_DeviceDPOps(self), x, y, hypercolumn, x.shape[0], world_size, all_reduce, row_blocks)
+
+    # -- row-sharded data parallelism over peer-mapped memory ----------------
+    def shard_rows(self, rank, world_size, all_gather_bytes):
+        """Give every rank a block of input rows of the trace matrix to own.  ``all_gather_bytes(b)``
+        must return the list of every rank's ``b`` in rank order (e.g. through
+        ``torch.distributed.all_gather_object``): it carries the CUDA IPC handles with which the ranks
+        map each other's staging memory and weight matrix.  One process per GPU, one node, at most 8."""
+        n = _lib.SHARD_BUFFERS * _lib.SHARD_HANDLE_BYTES
+        mine = (ctypes.c_ubyte * n)()
+        check(lib.sbb_layer_shard_init(self._handle, rank, world_size, mine))
+        parts = all_gather_bytes(bytes(mine))
+        if len(parts) != world_size or any(len(p) != n for p in parts):
+            raise ValueError("all_gather_bytes must return one %d-byte string per rank" % n)
+        blob = b"".join(parts)
+        check(lib.sbb_layer_shard_attach(self._handle, ctypes.c_char_p(blob)))
+        self._shard = (rank, world_size)
+
+    def owned_rows(self, rank=None):
+        lo, hi = ctypes.c_long(0), ctypes.c_long(0)
+        check(lib.sbb_layer_shard_rows(self._handle, self._shard[0] if rank is None else rank, ctypes.byref(lo),
+                                       ctypes.byref(hi)))
+        return lo.value, hi.value
+
+    def _barrier_token(self):
+        if getattr(self, "_token", None) is None:
+            self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
+        return self._token
+
+    def sharded_train_step(self, x, y, hypercolumn, barrier):
+        """One row-sharded data-parallel step on device tensors; ``barrier()`` must order the current
+        stream after the work every rank queued before its own ``barrier()`` call (any collective on the
+        stream does).  See ``sbb_layer_shard_*`` in the C header for the protocol."""
+        st = _stream_ptr()
+        B = x.shape[0]
+        h = -1 if hypercolumn is None else int(hypercolumn)
+        check(lib.sbb_layer_shard_products(self._handle, x.data_ptr(), y.data_ptr(), B, st))
+        barrier()
+        check(lib.sbb_layer_shard_apply(self._handle, B * self._shard[1], h, st))
+        barrier()
+        if h >= 0 and self._kind == _lib.PLASTIC:
+            check(lib.sbb_layer_shard_mask(self._handle, h, st))
+            barrier()
+
+    def share_traces(self, barrier):
+        """After sharded steps a rank holds current values only for the rows of Cij it owns; this copies
+        every owner's rows to all ranks (needed before reading ``Cij`` or writing a checkpoint)."""
+        barrier()
+        check(lib.sbb_layer_shard_share_traces(self._handle, _stream_ptr()))
+        barrier()
 
 
 class _DeviceDPOps:

@@ -164,6 +164,17 @@ struct sbb_layer {
   bool ev_created = false;
   long phase_calls[2] = {0, 0};
   bool dp_fast = false;  // the last sbb_layer_dp_local ran the tensor-core product
+  // row-sharded data parallelism over peer-mapped memory (sbb_layer_shard_*)
+  struct Shard {
+    bool on = false, attached = false;
+    long rank = 0, world = 1;
+    long rows_per_rank = 0;            // multiple of 128; rank r owns rows [r * rows_per_rank, ...) clipped to N
+    Scratch stage;                     // world slots x rows_per_rank x M: slot s = rank s's part of x^T y for MY rows
+    Scratch vec;                       // world slots x (N + M): slot s = rank s's column sums of x and y
+    void *peer[SBB_SHARD_BUFFERS][8];  // per buffer kind and rank: that rank's buffer, mapped here (own rank: local)
+    bool opened[SBB_SHARD_BUFFERS][8];
+    bool fast = false;                 // the products of the current step ran on the tensor path
+  } shard;
 };
 
 namespace {
@@ -707,6 +718,13 @@ int sbb_layer_destroy(sbb_layer *L) {
   L->ht.release();
   L->col_hc.release();
   L->rc.release();
+  if (L->shard.on) {
+    for (int b = 0; b < SBB_SHARD_BUFFERS; ++b)
+      for (int r = 0; r < 8; ++r)
+        if (L->shard.opened[b][r]) cudaIpcCloseMemHandle(L->shard.peer[b][r]);
+    L->shard.stage.release();
+    L->shard.vec.release();
+  }
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
   if (L->h2d_stream) cudaStreamDestroy(L->h2d_stream);
   if (L->d2h_stream) cudaStreamDestroy(L->d2h_stream);
@@ -1031,6 +1049,232 @@ int sbb_layer_dp_finish(sbb_layer *L, long hypercolumn, void *stream) {
   ARG(hypercolumn < L->H, "dp_finish: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return DISPATCH(L->desc.dtype, layer_finish<float>(L, hypercolumn, st), layer_finish<double>(L, hypercolumn, st));
+}
+
+}  // extern "C"
+
+// ------------------------------------------------- row-sharded data parallelism
+namespace {
+
+enum { kShardStage = 0, kShardVec = 1, kShardW = 2, kShardMask = 3, kShardCij = 4 };
+
+void *shard_local_buffer(sbb_layer *L, int which) {
+  switch (which) {
+    case kShardStage: return L->shard.stage.d;
+    case kShardVec: return L->shard.vec.d;
+    case kShardW: return L->state[SBB_STATE_WEIGHTS];
+    case kShardMask: return L->score.d;
+    default: return L->state[SBB_STATE_CIJ];
+  }
+}
+
+long shard_begin(const sbb_layer *L, long r) {
+  const long b = r * L->shard.rows_per_rank;
+  return b < L->N ? b : L->N;
+}
+
+// Table of one address per rank: that rank's buffer `which` plus a byte offset.
+sbb::PeerTable shard_table(sbb_layer *L, int which, size_t byte_offset) {
+  sbb::PeerTable t{};
+  t.n = (int)L->shard.world;
+  for (int r = 0; r < t.n; ++r) t.ptr[r] = static_cast<char *>(L->shard.peer[which][r]) + byte_offset;
+  return t;
+}
+
+int check_shard(sbb_layer *L, bool need_peers) {
+  SBB_TRY(check_layer(L));
+  ARG(L->shard.on, "the layer is not set up for row-sharded data parallelism (sbb_layer_shard_init)");
+  ARG(!need_peers || L->shard.attached, "the peers' buffers are not attached yet (sbb_layer_shard_attach)");
+  return SBB_OK;
+}
+
+template <typename T>
+int shard_products(sbb_layer *L, const T *x, const T *y, long B, cudaStream_t st) {
+  auto &S = L->shard;
+  const long N = L->N, M = L->M;
+  sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, B);
+  // this rank's column sums: into its own slot of its own vector stage, then copied into the same slot everywhere
+  T *mine = static_cast<T *>(S.vec.d) + S.rank * (N + M);
+  SBB_CUDA(sbb::launch_colsum<T>(x, B, N, mine, nullptr, p, 0, st));
+  SBB_CUDA(sbb::launch_colsum<T>(y, B, M, mine + N, nullptr, p, 0, st));
+  SBB_CUDA(sbb::launch_peer_broadcast<T>(mine, N + M, shard_table(L, kShardVec, (size_t)S.rank * (N + M) * sizeof(T)), st));
+  // x^T y, one block of rows per owner, written straight into the owner's slot for this rank.  The owners
+  // are visited starting after this rank, so that at any time every rank sends to a different owner.
+  PhaseTimer timer(L, SBB_PHASE_TRACE, st);
+  const size_t slot_bytes = (size_t)S.rows_per_rank * M * sizeof(T);
+  S.fast = false;
+  for (long k = 1; k <= S.world; ++k) {
+    const long owner = (S.rank + k) % S.world;
+    const long rb = shard_begin(L, owner), re = shard_begin(L, owner + 1);
+    if (re <= rb) continue;
+    T *slot = reinterpret_cast<T *>(static_cast<char *>(S.peer[kShardStage][owner]) + (size_t)S.rank * slot_bytes);
+    // the product kernels address their output as base[row * M + col] with absolute rows
+    T *base = slot - rb * M;
+    if (tensor_path<T>(x, y, N, M) && (reinterpret_cast<uintptr_t>(slot) & 7u) == 0) {
+      if constexpr (std::is_same<T, float>::value) SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, N, M, base, rb, re, st));
+      S.fast = true;
+    } else {
+      SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, N, M, base, rb, re, st));
+    }
+  }
+  timer.stop();
+  return SBB_OK;
+}
+
+template <typename T>
+int shard_apply(sbb_layer *L, long Bg, long h, cudaStream_t st) {
+  auto &S = L->shard;
+  const long N = L->N, M = L->M;
+  const sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, Bg);
+  T *Ci = static_cast<T *>(L->state[SBB_STATE_CI]);
+  T *Cj = static_cast<T *>(L->state[SBB_STATE_CJ]);
+  T *Cij = static_cast<T *>(L->state[SBB_STATE_CIJ]);
+  const uint8_t *wmask = static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]);
+  // Ci, Cj: every rank sums the slots of all ranks in rank order, so the replicas stay identical
+  SBB_CUDA(sbb::launch_vector_slots_ema<T>(Ci, static_cast<const T *>(S.vec.d), (int)S.world, N + M, 0, N, p, st));
+  SBB_CUDA(sbb::launch_vector_slots_ema<T>(Cj, static_cast<const T *>(S.vec.d), (int)S.world, N + M, N, M, p, st));
+  const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
+  SBB_CUDA(sbb::launch_shard_apply<T>(static_cast<const T *>(S.stage.d), (int)S.world, S.rows_per_rank * M, M, L->H,
+                                      L->Mc, Ci, Cj, Cij, shard_table(L, kShardW, 0), wmask, p, rb, re, st, S.fast));
+  if (L->desc.kind != SBB_LAYER_PLASTIC) return SBB_OK;
+  const double cthr = L->desc.taupdt / 2;
+  SBB_CUDA(sbb::launch_update_bias_regularized<T>(static_cast<T *>(L->state[SBB_STATE_BIAS]),
+                                                  static_cast<T *>(L->state[SBB_STATE_KBI]), Cj, (T)cthr,
+                                                  (T)L->desc.khalf, (T)L->desc.pmin, (T)L->desc.taubdt, M, st));
+  if (h >= 0)   // scores of the owned rows, into every rank's work arrays
+    SBB_CUDA(sbb::launch_mask_score_rows<T>(wmask, Ci, Cj, Cij, (T)cthr, N, M, L->H, L->Mc, h, rb, re,
+                                            shard_table(L, kShardMask, 0), st));
+  return SBB_OK;
+}
+
+template <typename T>
+int shard_mask(sbb_layer *L, long h, cudaStream_t st) {
+  auto &S = L->shard;
+  const double cthr = L->desc.taupdt / 2;
+  const T *Ci = static_cast<const T *>(L->state[SBB_STATE_CI]);
+  const T *Cj = static_cast<const T *>(L->state[SBB_STATE_CJ]);
+  const T *Cij = static_cast<const T *>(L->state[SBB_STATE_CIJ]);
+  uint8_t *wmask = static_cast<uint8_t *>(L->state[SBB_STATE_WMASK]);
+  // the swaps, identically on every rank (all hold all scores); weights are rewritten by the owners only
+  SBB_CUDA(sbb::launch_mask_select<T>(wmask, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, L->desc.mask_iterations,
+                                      L->score.d, st, nullptr));
+  const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
+  SBB_CUDA(sbb::launch_mask_rewrite_rows<T>(wmask, L->score.d, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, rb, re,
+                                            shard_table(L, kShardW, 0), st));
+  return SBB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sbb_layer_shard_init(sbb_layer *L, long rank, long world_size, unsigned char *handles_out) {
+  SBB_TRY(check_layer(L));
+  ARG(handles_out, "shard_init: null pointer");
+  ARG(world_size >= 1 && world_size <= 8 && rank >= 0 && rank < world_size, "shard_init: rank %ld of %ld (at most 8)",
+      rank, world_size);
+  ARG(!L->shard.on, "shard_init: the layer is already sharded");
+  auto &S = L->shard;
+  const size_t s = esize(L->desc.dtype);
+  const long tiles = (L->N + 127) / 128;
+  S.rank = rank;
+  S.world = world_size;
+  S.rows_per_rank = ((tiles + world_size - 1) / world_size) * 128;
+  SBB_TRY(S.stage.reserve((size_t)world_size * S.rows_per_rank * L->M * s));
+  SBB_TRY(S.vec.reserve((size_t)world_size * (L->N + L->M) * s));
+  if (L->score.d == nullptr) SBB_TRY(L->score.reserve(sbb::mask_scratch_bytes(L->N, s)));
+  for (int b = 0; b < SBB_SHARD_BUFFERS; ++b)
+    for (int r = 0; r < 8; ++r) {
+      S.peer[b][r] = nullptr;
+      S.opened[b][r] = false;
+    }
+  for (int b = 0; b < SBB_SHARD_BUFFERS; ++b) {
+    S.peer[b][rank] = shard_local_buffer(L, b);
+    cudaIpcMemHandle_t hnd;
+    SBB_CUDA(cudaIpcGetMemHandle(&hnd, S.peer[b][rank]));
+    static_assert(sizeof(hnd) == SBB_SHARD_HANDLE_BYTES, "IPC handle size");
+    std::memcpy(handles_out + (size_t)b * SBB_SHARD_HANDLE_BYTES, &hnd, sizeof(hnd));
+  }
+  S.on = true;
+  S.attached = world_size == 1;
+  return SBB_OK;
+}
+
+int sbb_layer_shard_attach(sbb_layer *L, const unsigned char *all_handles) {
+  SBB_TRY(check_shard(L, false));
+  ARG(all_handles, "shard_attach: null pointer");
+  auto &S = L->shard;
+  for (long r = 0; r < S.world; ++r) {
+    if (r == S.rank) continue;
+    for (int b = 0; b < SBB_SHARD_BUFFERS; ++b) {
+      if (S.opened[b][r]) continue;
+      cudaIpcMemHandle_t hnd;
+      std::memcpy(&hnd, all_handles + ((size_t)r * SBB_SHARD_BUFFERS + b) * SBB_SHARD_HANDLE_BYTES, sizeof(hnd));
+      void *p = nullptr;
+      SBB_CUDA(cudaIpcOpenMemHandle(&p, hnd, cudaIpcMemLazyEnablePeerAccess));
+      S.peer[b][r] = p;
+      S.opened[b][r] = true;
+    }
+  }
+  S.attached = true;
+  return SBB_OK;
+}
+
+int sbb_layer_shard_products(sbb_layer *L, const void *x_dev, const void *y_dev, long B_local, void *stream) {
+  SBB_TRY(check_shard(L, true));
+  ARG(x_dev && y_dev, "shard_products: null pointer");
+  SBB_TRY(check_batch(L, B_local));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, shard_products<float>(L, (const float *)x_dev, (const float *)y_dev, B_local, st),
+                  shard_products<double>(L, (const double *)x_dev, (const double *)y_dev, B_local, st));
+}
+
+int sbb_layer_shard_apply(sbb_layer *L, long B_global, long hypercolumn, void *stream) {
+  SBB_TRY(check_shard(L, true));
+  ARG(B_global > 0, "shard_apply: non-positive global batch");
+  ARG(hypercolumn < L->H, "shard_apply: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+  if (L->desc.kind != SBB_LAYER_PLASTIC) hypercolumn = -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, shard_apply<float>(L, B_global, hypercolumn, st),
+                  shard_apply<double>(L, B_global, hypercolumn, st));
+}
+
+int sbb_layer_shard_mask(sbb_layer *L, long hypercolumn, void *stream) {
+  SBB_TRY(check_shard(L, true));
+  ARG(L->desc.kind == SBB_LAYER_PLASTIC, "shard_mask: the layer has no mask");
+  ARG(hypercolumn >= 0 && hypercolumn < L->H, "shard_mask: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, shard_mask<float>(L, hypercolumn, st), shard_mask<double>(L, hypercolumn, st));
+}
+
+int sbb_layer_shard_share_traces(sbb_layer *L, void *stream) {
+  SBB_TRY(check_shard(L, true));
+  auto &S = L->shard;
+  const size_t s = esize(L->desc.dtype);
+  const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
+  if (re <= rb) return SBB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t offset = (size_t)rb * L->M * s, bytes = (size_t)(re - rb) * L->M * s;
+  const char *src = static_cast<const char *>(L->state[SBB_STATE_CIJ]) + offset;
+  sbb::PeerTable others{};
+  for (long r = 0; r < S.world; ++r)
+    if (r != S.rank) others.ptr[others.n++] = static_cast<char *>(S.peer[kShardCij][r]) + offset;
+  if (bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0)
+    SBB_CUDA(sbb::launch_peer_broadcast<uint4>(reinterpret_cast<const uint4 *>(src), (long)(bytes / 16), others, st));
+  else if (L->desc.dtype == SBB_F32)
+    SBB_CUDA(sbb::launch_peer_broadcast<float>(reinterpret_cast<const float *>(src), (long)(bytes / 4), others, st));
+  else
+    SBB_CUDA(sbb::launch_peer_broadcast<double>(reinterpret_cast<const double *>(src), (long)(bytes / 8), others, st));
+  return SBB_OK;
+}
+
+int sbb_layer_shard_rows(const sbb_layer *L, long rank, long *row_begin, long *row_end) {
+  ARG(L && row_begin && row_end, "shard_rows: null pointer");
+  ARG(L->shard.on, "shard_rows: the layer is not sharded");
+  ARG(rank >= 0 && rank < L->shard.world, "shard_rows: rank %ld outside [0,%ld)", rank, L->shard.world);
+  *row_begin = shard_begin(L, rank);
+  *row_end = shard_begin(L, rank + 1);
+  return SBB_OK;
 }
 
 int sbb_count_correct(int dtype, const void *pred_dev, const void *labels_dev, long rows, long classes,

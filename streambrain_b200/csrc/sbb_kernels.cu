@@ -1381,7 +1381,7 @@ __global__ void __launch_bounds__(kSwapThreads)
   }
 }
 
-static inline size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+__host__ __device__ static inline size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 static constexpr size_t kSwapListBytes = 256 + (size_t)2 * kSwapSlots * (sizeof(double) + sizeof(long));
 
 size_t mask_scratch_bytes(long N, size_t elem) {
@@ -1397,7 +1397,7 @@ struct MaskScratch {
   int *nan_flag;
   long *cand_i;
   T *cand_v;
-  MaskScratch(void *scratch, long N) {
+  __host__ __device__ MaskScratch(void *scratch, long N) {
     unsigned char *p = static_cast<unsigned char *>(scratch);
     score = reinterpret_cast<T *>(p);
     p += align256((size_t)N * sizeof(T));
@@ -1422,6 +1422,17 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
                                                                  h, ms.score, ms.csum, ms.old_col);
   cudaError_t e = launched();
   if (e != cudaSuccess) return e;
+  return launch_mask_select<T>(wmask, Ci, Cj, Cij, cthr, N, M, H, Mc, h, iterations, scratch, st, rewrite_w);
+}
+
+// The swaps alone, from per-row scores, active counts and the old mask column already in `scratch`.
+template <typename T>
+cudaError_t launch_mask_select(uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr, long N, long M, long H,
+                               long Mc, long h, long iterations, void *scratch, cudaStream_t st, T *rewrite_w) {
+  if (N == 0) return cudaSuccess;
+  MaskScratch<T> ms(scratch, N);
+  const T cthr4 = cthr * cthr * cthr * cthr;
+  cudaError_t e = cudaSuccess;
   // candidate lists: rows fit 32-bit indices and a chunk (<= kSwapCacheRows rows) fits shared memory
   const int max_chunks = iterations >= 1 && iterations <= kSwapMaxIter ? kSwapSlots / (int)iterations : 0;
   if (max_chunks > 0 && N >= 1024 && N < (1l << 31) && (N + max_chunks - 1) / max_chunks <= kSwapCacheRows) {
@@ -1449,6 +1460,10 @@ cudaError_t launch_mask_update(uint8_t *wmask, const T *weights, const T *Ci, co
                                           ms.old_col, Ci, Cj, Cij, cthr, cthr4);
   return launched();
 }
+template cudaError_t launch_mask_select<float>(uint8_t *, const float *, const float *, const float *, float, long, long,
+                                               long, long, long, long, void *, cudaStream_t, float *);
+template cudaError_t launch_mask_select<double>(uint8_t *, const double *, const double *, const double *, double, long,
+                                                long, long, long, long, long, void *, cudaStream_t, double *);
 template cudaError_t launch_mask_update<float>(uint8_t *, const float *, const float *, const float *, const float *,
                                                float, long, long, long, long, long, long, void *, cudaStream_t,
                                                float *);
@@ -1531,5 +1546,240 @@ cudaError_t launch_gather_rows(const T *src, const long *order, long first, long
 template cudaError_t launch_gather_rows<float>(const float *, const long *, long, long, long, float *, cudaStream_t);
 template cudaError_t launch_gather_rows<double>(const double *, const long *, long, long, long, double *,
                                                 cudaStream_t);
+
+// ----------------------------------------------------------------------------
+// Row-sharded data parallelism over peer-mapped memory.  Every rank owns a block of
+// input rows of the trace matrix; ranks write their partial batch sums straight into
+// the owner's staging slots (one slot per source rank), the owner adds the slots in
+// rank order, updates its rows and writes the new weight rows into every rank's
+// weight matrix.  The pointer tables below hold, per destination rank, an address in
+// that rank's memory (the rank's own entry is a local address).
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) peer_broadcast_kernel(const T *__restrict__ src, long n, PeerTable dst) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const T v = src[i];
+    for (int d = 0; d < dst.n; ++d) static_cast<T *>(dst.ptr[d])[i] = v;
+  }
+}
+template <typename T>
+cudaError_t launch_peer_broadcast(const T *src, long n, const PeerTable &dst, cudaStream_t st) {
+  if (n <= 0 || dst.n <= 0) return cudaSuccess;
+  const long blocks = (n + 255) / 256;
+  peer_broadcast_kernel<T><<<(unsigned)(blocks < 1184 ? blocks : 1184), 256, 0, st>>>(src, n, dst);
+  return launched();
+}
+template cudaError_t launch_peer_broadcast<float>(const float *, long, const PeerTable &, cudaStream_t);
+template cudaError_t launch_peer_broadcast<double>(const double *, long, const PeerTable &, cudaStream_t);
+template cudaError_t launch_peer_broadcast<uint4>(const uint4 *, long, const PeerTable &, cudaStream_t);
+
+// c[i] = EMA(c[i], sum over slots s (in order) of slots[s * stride + offset + i])
+template <typename T>
+__global__ void vector_slots_ema_kernel(T *c, const T *__restrict__ slots, int nslots, long stride, long offset, long n,
+                                        TraceParams<T> p) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  T s = slots[offset + i];
+  for (int k = 1; k < nslots; ++k) s += slots[(long)k * stride + offset + i];
+  c[i] = trace_ema(c[i], s, p);
+}
+template <typename T>
+cudaError_t launch_vector_slots_ema(T *c, const T *slots, int nslots, long stride, long offset, long n,
+                                    TraceParams<T> p, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  vector_slots_ema_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(c, slots, nslots, stride, offset, n, p);
+  return launched();
+}
+template cudaError_t launch_vector_slots_ema<float>(float *, const float *, int, long, long, long, TraceParams<float>,
+                                                    cudaStream_t);
+template cudaError_t launch_vector_slots_ema<double>(double *, const double *, int, long, long, long,
+                                                     TraceParams<double>, cudaStream_t);
+
+// The element-wise tail of the trace step for the rows [row_begin, row_end) this rank owns: the batch sum of an
+// element is the sum of its `nslots` staging slots (slot s = rank s's part, rows counted from row_begin), the
+// new weight row goes to every rank's weight matrix.  Same thread layout as trace_apply_kernel.
+template <typename T, bool FAST>
+__global__ void __launch_bounds__(256)
+    shard_apply_kernel(const T *__restrict__ stage, int nslots, long slot_stride, long M, long H, long Mc,
+                       const T *__restrict__ Ci, const T *__restrict__ Cj, T *Cij, PeerTable wtab,
+                       const uint8_t *__restrict__ wmask, TraceParams<T> p, long row_begin, long row_end, bool vec) {
+  const long j = ((long)blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (j >= M) return;
+  const long left = M - j;
+  const int valid = left >= 4 ? 4 : (int)left;
+  T cj[4];
+  bool col_on[4];
+  long hc[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    cj[c] = c < valid ? Cj[j + c] : (T)1;
+    col_on[c] = c < valid && !(cj[c] < p.cthr);
+    hc[c] = wmask ? (j + (c < valid ? c : 0)) / Mc : 0;
+    if (FAST) cj[c] = (T)1 / cj[c];
+  }
+  const T ema_scale = p.taupdt / p.batch;
+  const long r0 = row_begin + (long)blockIdx.x * kApplyRows;
+  const long r1 = r0 + kApplyRows < row_end ? r0 + kApplyRows : row_end;
+  for (long i = r0; i < r1; ++i) {
+    T ci = Ci[i];
+    const bool row_on = !(ci < p.cthr);
+    if (FAST) ci = (T)1 / ci;
+    bool on[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) on[c] = row_on && col_on[c] && (wmask == nullptr || wmask[i * H + hc[c]] != 0);
+    T c4[4], d4[4], w4[4];
+    load4(Cij + i * M + j, c4, vec, valid);
+    const T *srow = stage + (i - row_begin) * M + j;
+    load4(srow, d4, vec, valid);
+    for (int k = 1; k < nslots; ++k) {
+      T e4[4];
+      load4(srow + (long)k * slot_stride, e4, vec, valid);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) d4[c] += e4[c];
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (c < valid) {
+        T cij;
+        if constexpr (FAST) {
+          cij = trace_ema_fast(c4[c], d4[c], p.one_minus, ema_scale);
+          w4[c] = on[c] ? log_ratio_fast(cij, ci, cj[c], p.cthr4) : 0.f;
+        } else {
+          cij = trace_ema(c4[c], d4[c], p);
+          w4[c] = on[c] ? log_ratio(cij, ci, cj[c], p.cthr4) : (T)0;
+        }
+        c4[c] = cij;
+      }
+    }
+    store4(Cij + i * M + j, c4, vec, valid);
+    for (int d = 0; d < wtab.n; ++d) store4(static_cast<T *>(wtab.ptr[d]) + i * M + j, w4, vec, valid);
+  }
+}
+template <typename T>
+cudaError_t launch_shard_apply(const T *stage, int nslots, long slot_stride, long M, long H, long Mc, const T *Ci,
+                               const T *Cj, T *Cij, const PeerTable &wtab, const uint8_t *wmask, TraceParams<T> p,
+                               long row_begin, long row_end, cudaStream_t st, bool fast) {
+  constexpr int V = Vec16<T>::N;
+  if (row_end <= row_begin || M == 0) return cudaSuccess;
+  const long qpr = (M + 3) / 4;
+  bool vec = (M % V == 0) && aligned16(Cij) && aligned16(stage) && (slot_stride % V == 0);
+  for (int d = 0; d < wtab.n; ++d) vec = vec && aligned16(wtab.ptr[d]);
+  const long row_groups = (row_end - row_begin + kApplyRows - 1) / kApplyRows;
+  const int threads = qpr >= 256 ? 256 : (int)((qpr + 31) / 32 * 32);
+  const dim3 grid((unsigned)row_groups, (unsigned)((qpr + threads - 1) / threads));
+  if constexpr (std::is_same<T, float>::value) {
+    if (fast && p.cthr4 >= 1e-30f) {
+      shard_apply_kernel<float, true><<<grid, threads, 0, st>>>(stage, nslots, slot_stride, M, H, Mc, Ci, Cj, Cij, wtab,
+                                                                wmask, p, row_begin, row_end, vec);
+      return launched();
+    }
+  }
+  shard_apply_kernel<T, false><<<grid, threads, 0, st>>>(stage, nslots, slot_stride, M, H, Mc, Ci, Cj, Cij, wtab, wmask,
+                                                         p, row_begin, row_end, vec);
+  return launched();
+}
+template cudaError_t launch_shard_apply<float>(const float *, int, long, long, long, long, const float *, const float *,
+                                               float *, const PeerTable &, const uint8_t *, TraceParams<float>, long,
+                                               long, cudaStream_t, bool);
+template cudaError_t launch_shard_apply<double>(const double *, int, long, long, long, long, const double *,
+                                                const double *, double *, const PeerTable &, const uint8_t *,
+                                                TraceParams<double>, long, long, cudaStream_t, bool);
+
+// Mask scores of the rows [row_begin, row_end) this rank owns, written into every rank's work arrays
+// (scratch_tab: base of each rank's mask scratch, laid out for N rows).
+template <typename T>
+__global__ void __launch_bounds__(256)
+    mask_score_rows_kernel(const uint8_t *__restrict__ wmask, const T *__restrict__ Ci, const T *__restrict__ Cj,
+                           const T *__restrict__ Cij, T cthr, T cthr4, long N, long M, long H, long Mc, long h,
+                           long row_begin, long row_end, PeerTable scratch_tab) {
+  const int lane = threadIdx.x & 31;
+  const long i = row_begin + (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= row_end) return;
+  const T pi = Ci[i];
+  double s = 0.0;
+  if (pi >= cthr) {
+    for (long jj = lane; jj < Mc; jj += 32) {
+      const long col = h * Mc + jj;
+      const T pj = Cj[col];
+      if (pj >= cthr) {
+        const T pij = Cij[i * M + col];
+        const T w = log_ratio(pij, pi, pj, cthr4);
+        const T x = ((T)1 - pi) * pj;
+        const T y = (pj - pij) / x;
+        s += (double)(pij * w + (pj - pij) * sbb_log(y));
+      }
+    }
+  }
+  int cnt = 0;
+  for (long k = lane; k < H; k += 32) cnt += wmask[i * H + k];
+  for (int off = 16; off > 0; off >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, off);
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+  }
+  if (lane == 0) {
+    const uint8_t bit = wmask[i * H + h];
+    for (int d = 0; d < scratch_tab.n; ++d) {
+      MaskScratch<T> ms(scratch_tab.ptr[d], N);
+      ms.score[i] = (T)s;
+      ms.csum[i] = cnt;
+      ms.old_col[i] = bit;
+    }
+  }
+}
+template <typename T>
+cudaError_t launch_mask_score_rows(const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr, long N, long M,
+                                   long H, long Mc, long h, long row_begin, long row_end, const PeerTable &scratch_tab,
+                                   cudaStream_t st) {
+  if (row_end <= row_begin) return cudaSuccess;
+  const T cthr4 = cthr * cthr * cthr * cthr;
+  mask_score_rows_kernel<T><<<(unsigned)((row_end - row_begin + 7) / 8), 256, 0, st>>>(
+      wmask, Ci, Cj, Cij, cthr, cthr4, N, M, H, Mc, h, row_begin, row_end, scratch_tab);
+  return launched();
+}
+template cudaError_t launch_mask_score_rows<float>(const uint8_t *, const float *, const float *, const float *, float,
+                                                   long, long, long, long, long, long, long, const PeerTable &,
+                                                   cudaStream_t);
+template cudaError_t launch_mask_score_rows<double>(const uint8_t *, const double *, const double *, const double *,
+                                                    double, long, long, long, long, long, long, long, const PeerTable &,
+                                                    cudaStream_t);
+
+// After the swaps: owned rows whose mask bit changed get hypercolumn h's weights recomputed from the owner's
+// traces, in every rank's weight matrix.  One warp per owned row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    mask_rewrite_rows_kernel(const uint8_t *__restrict__ wmask, const uint8_t *__restrict__ old_col,
+                             const T *__restrict__ Ci, const T *__restrict__ Cj, const T *__restrict__ Cij, T cthr,
+                             T cthr4, long M, long H, long Mc, long h, long row_begin, long row_end, PeerTable wtab) {
+  const int lane = threadIdx.x & 31;
+  const long i = row_begin + (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= row_end) return;
+  const uint8_t now = wmask[i * H + h];
+  if (now == old_col[i]) return;
+  const T ci = Ci[i];
+  for (long jj = lane; jj < Mc; jj += 32) {
+    const long col = h * Mc + jj;
+    const T cj = Cj[col];
+    T v = (T)0;
+    if (now != 0 && !(ci < cthr) && !(cj < cthr)) v = log_ratio(Cij[i * M + col], ci, cj, cthr4);
+    for (int d = 0; d < wtab.n; ++d) static_cast<T *>(wtab.ptr[d])[i * M + col] = v;
+  }
+}
+template <typename T>
+cudaError_t launch_mask_rewrite_rows(const uint8_t *wmask, const void *scratch, const T *Ci, const T *Cj, const T *Cij,
+                                     T cthr, long N, long M, long H, long Mc, long h, long row_begin, long row_end,
+                                     const PeerTable &wtab, cudaStream_t st) {
+  if (row_end <= row_begin) return cudaSuccess;
+  MaskScratch<T> ms(const_cast<void *>(scratch), N);
+  const T cthr4 = cthr * cthr * cthr * cthr;
+  mask_rewrite_rows_kernel<T><<<(unsigned)((row_end - row_begin + 7) / 8), 256, 0, st>>>(
+      wmask, ms.old_col, Ci, Cj, Cij, cthr, cthr4, M, H, Mc, h, row_begin, row_end, wtab);
+  return launched();
+}
+template cudaError_t launch_mask_rewrite_rows<float>(const uint8_t *, const void *, const float *, const float *,
+                                                     const float *, float, long, long, long, long, long, long, long,
+                                                     const PeerTable &, cudaStream_t);
+template cudaError_t launch_mask_rewrite_rows<double>(const uint8_t *, const void *, const double *, const double *,
+                                                      const double *, double, long, long, long, long, long, long, long,
+                                                      const PeerTable &, cudaStream_t);
 
 }  // namespace sbb

@@ -99,6 +99,35 @@ template <typename T>
 cudaError_t launch_count_correct(const T *pred, const T *labels, long rows, long classes, unsigned long long *count,
                                  cudaStream_t st);
 
+// The swaps of a mask update alone, from per-row scores / active counts / old mask column already in `scratch`.
+template <typename T>
+cudaError_t launch_mask_select(uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr, long N, long M, long H,
+                               long Mc, long h, long iterations, void *scratch, cudaStream_t st, T *rewrite_w);
+
+// Row-sharded data parallelism over peer-mapped memory (see sbb_kernels.cu): one address per destination rank.
+constexpr int kMaxPeers = 8;
+struct PeerTable {
+  void *ptr[kMaxPeers];
+  int n;
+};
+template <typename T>
+cudaError_t launch_peer_broadcast(const T *src, long n, const PeerTable &dst, cudaStream_t st);
+template <typename T>
+cudaError_t launch_vector_slots_ema(T *c, const T *slots, int nslots, long stride, long offset, long n,
+                                    TraceParams<T> p, cudaStream_t st);
+template <typename T>
+cudaError_t launch_shard_apply(const T *stage, int nslots, long slot_stride, long M, long H, long Mc, const T *Ci,
+                               const T *Cj, T *Cij, const PeerTable &wtab, const uint8_t *wmask, TraceParams<T> p,
+                               long row_begin, long row_end, cudaStream_t st, bool fast);
+template <typename T>
+cudaError_t launch_mask_score_rows(const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr, long N, long M,
+                                   long H, long Mc, long h, long row_begin, long row_end, const PeerTable &scratch_tab,
+                                   cudaStream_t st);
+template <typename T>
+cudaError_t launch_mask_rewrite_rows(const uint8_t *wmask, const void *scratch, const T *Ci, const T *Cj, const T *Cij,
+                                     T cthr, long N, long M, long H, long Mc, long h, long row_begin, long row_end,
+                                     const PeerTable &wtab, cudaStream_t st);
+
 // dst[r, :] = src[order[first + r], :] for r in [0, rows); order == nullptr means the identity.
 template <typename T>
 cudaError_t launch_gather_rows(const T *src, const long *order, long first, long rows, long cols, T *dst,

@@ -60,3 +60,12 @@ def pipelined_dp_step(ops, x, y, hypercolumn, local_batch: int, world_size: int,
             ops.apply_vectors(batch)
         ops.apply_rows(batch, rb, re)
     ops.finish(hypercolumn)
+
+
+def all_gather_bytes_over(dist):
+    """``all_gather_bytes`` for :meth:`shard_rows` on an initialised ``torch.distributed`` group."""
+    def gather(blob: bytes):
+        out = [None] * dist.get_world_size()
+        dist.all_gather_object(out, blob)
+        return out
+    return gather

@@ -49,26 +49,62 @@ def _batches(world, steps):
     return [rs.rand(world * B_LOCAL, N).astype(np.float32) for _ in range(steps)]
 
 
-def _worker(rank, world, port, path, out_dir):
+def _worker(rank, world, port, path, out_dir, sharded=False):
     sys.path.insert(0, REPO)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    if os.environ.get("SBB_TEST_NVLS", "0") != "1":   # SBB_TEST_NVLS=1 leaves NCCL's NVLink-switch reductions on
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     import streambrain_b200 as B200
+    from streambrain_b200 import parallel
     layer = _make_layer(B200, path)
+    if sharded:
+        layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
     steps = 2
     for k, xb in enumerate(_batches(world, steps)):
         x = torch.from_numpy(xb[rank * B_LOCAL:(rank + 1) * B_LOCAL]).cuda()
         y = layer.compute_activation(x)
         layer.dp_train_step(x, y, (2 + k) % H, world, lambda t: dist.all_reduce(t, async_op=True), row_blocks=3)
+        if sharded:   # every rank holds only its own rows of Cij until they are shared
+            token = torch.zeros(1, device="cuda")
+            layer.share_traces(lambda: dist.all_reduce(token))
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, "rank%d_step%d.npz" % (rank, k)), Ci=layer.Ci, Cj=layer.Cj, Cij=layer.Cij,
                  weights=layer.weights, bias=layer.bias, wmask=layer.wmask)
     dist.barrier()
     dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("path", ["general", "tensor"])
+def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path):
+    """The row-sharded step (partial sums stored into the owner's memory over NVLink, each row updated once
+    by its owner, weight rows written to every rank) against the all-reduce step on the same two GPUs:
+    the same sums added in the same rank order give the same traces, weights and masks."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    a, b = tmp_path / "allreduce", tmp_path / "sharded"
+    a.mkdir()
+    b.mkdir()
+    mp.spawn(_worker, args=(world, _free_port(), path, str(a), False), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), path, str(b), True), nprocs=world, join=True)
+    tol = TOL[np.dtype(np.float32)]
+    for k in range(2):
+        s0 = np.load(b / ("rank0_step%d.npz" % k))
+        s1 = np.load(b / ("rank1_step%d.npz" % k))
+        ref = np.load(a / ("rank0_step%d.npz" % k))
+        for name in s0.files:
+            assert np.array_equal(s0[name], s1[name]), (k, name)      # replicas identical
+        assert np.array_equal(s0["wmask"], ref["wmask"]), k
+        scale = 10 ** k
+        for name in ("Ci", "Cj", "Cij", "bias"):
+            assert rel_inf(s0[name], ref[name]) < scale * tol, (k, name)
+        assert weight_err(s0["weights"], ref["weights"]) < 10 * scale * tol, k
+        assert np.array_equal(s0["weights"] == 0, ref["weights"] == 0), k
 
 
 @pytest.mark.parametrize("path", ["general", "tensor"])

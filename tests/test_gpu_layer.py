@@ -404,6 +404,32 @@ def test_data_parallel_split_step_equals_single_step(B200):
         assert rel_inf(getattr(piped, name), getattr(single, name)) < 1e-12, name
 
 
+@pytest.mark.parametrize("tag,dtype", DTYPES)
+def test_row_sharded_step_on_one_rank_equals_single_step(B200, tag, dtype):
+    """The row-sharded data-parallel step with a world of one rank (its staging slot, vector slot and weight
+    matrix are all local) runs every kernel of the sharded path and must reproduce the fused step."""
+    import torch
+    g = load_golden("layer_%s.npz" % tag)
+    B = int(g["B"])
+    x = torch.from_numpy(np.ascontiguousarray(g["x"][:B])).cuda()
+    single, _ = _layers_from_golden(B200, g, dtype)
+    sharded, _ = _layers_from_golden(B200, g, dtype)
+    sharded.shard_rows(0, 1, lambda blob: [blob])
+    assert sharded.owned_rows() == (0, sharded.in_features)
+    tol = TOL[np.dtype(dtype)]
+    for h in (2, None, 0):
+        y = single.compute_activation(x)
+        single.train_step(x, y, h)
+        sharded.dp_train_step(x, y, h, 1, lambda t: type("Done", (), {"wait": lambda self: None})())
+        torch.cuda.synchronize()
+        assert np.array_equal(sharded.wmask, single.wmask), h
+        for name in ("Ci", "Cj", "Cij", "bias", "kbi"):
+            assert rel_inf(getattr(sharded, name), getattr(single, name)) < tol, (h, name)
+        assert weight_err(sharded.weights, single.weights) < 10 * tol, h
+        for name in PLASTIC_STATE:          # both continue from the same state
+            setattr(sharded, name, getattr(single, name))
+
+
 def test_stl10_shaped_layer_full_size_properties(B200, port_kernels):
     """55296 -> 30x100, batch 256, float32 (663 MB trace matrix).  Checked without a full
     CPU run: (a) the forward pass of a sample of batch rows against the oracle;
