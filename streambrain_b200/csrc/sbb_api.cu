@@ -126,6 +126,25 @@ struct Scratch {
   }
 };
 
+// Planes for the low parts of x[B, N] and y[B, M] (float32 tensor path only): written by the column-sum
+// kernels, read by the contraction that follows them in the same step.
+struct LoPlanes {
+  float *x = nullptr, *y = nullptr;
+};
+template <typename T>
+int reserve_lo(Scratch &buf, long B, long N, long M, bool wanted, LoPlanes *out) {
+  *out = LoPlanes{};
+  if (!wanted || !std::is_same<T, float>::value) return SBB_OK;
+  SBB_TRY(buf.reserve((size_t)B * (size_t)(N + M) * sizeof(float)));
+  out->x = static_cast<float *>(buf.d);
+  out->y = out->x + (size_t)B * N;
+  return SBB_OK;
+}
+template <typename T>
+T *lo_as(float *p) {
+  return reinterpret_cast<T *>(p);   // only dereferenced for T = float (null otherwise)
+}
+
 #define ARG(cond, ...) \
   do {                 \
     if (!(cond)) return fail(SBB_ERR_INVALID, __VA_ARGS__); \
@@ -148,6 +167,8 @@ struct sbb_layer {
   Scratch hx, hy, ht;    // staging for the host-buffer entry points
   Scratch col_hc;        // M ints: hypercolumn of every output column (j / Mc)
   Scratch rc;            // threshold-gated reciprocals of Ci and Cj for the tensor-core trace update
+  Scratch lo;            // low parts of x[B, N] and y[B, M] for the split TF32 products of the batch contractions
+  long lo_batch = 0;     // batch rows the planes in `lo` were written for (0 = none)
   cudaStream_t own_stream = nullptr;
   // sbb_layer_step_host_async: two staging slots, copies on their own streams
   Scratch ax[2], ay[2], at[2];
@@ -252,10 +273,11 @@ int layer_train_step(sbb_layer *L, const T *x, const T *y, long B, long h, cudaS
   const sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, B);
   T *Ci = static_cast<T *>(L->state[SBB_STATE_CI]);
   T *Cj = static_cast<T *>(L->state[SBB_STATE_CJ]);
+  const bool tc = tensor_path<T>(x, y, L->N, L->M);
   SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, nullptr, Ci, p, 1, st));
   SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, nullptr, Cj, p, 1, st));
   PhaseTimer timer(L, SBB_PHASE_TRACE, st);
-  if (tensor_path<T>(x, y, L->N, L->M)) {
+  if (tc) {
     if constexpr (std::is_same<T, float>::value)
       SBB_CUDA(sbb::launch_trace_update_tc(x, y, B, L->N, L->M, L->H, Ci, Cj, static_cast<T *>(L->state[SBB_STATE_CIJ]),
                                            static_cast<T *>(L->state[SBB_STATE_WEIGHTS]),
@@ -276,17 +298,25 @@ int layer_train_step(sbb_layer *L, const T *x, const T *y, long B, long h, cudaS
 template <typename T>
 int layer_dp_local(sbb_layer *L, const T *x, const T *y, long B, T *delta, long rb, long re, cudaStream_t st) {
   sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, B);
-  if (rb == 0) {
-    SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, delta, nullptr, p, 0, st));
-    SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, delta + L->N, nullptr, p, 0, st));
-  }
-  PhaseTimer timer(L, SBB_PHASE_TRACE, st);
   T *xty = delta + L->N + L->M;
   // remembered for sbb_layer_dp_apply_rows: the element-wise tail uses the arithmetic of the path that formed the sums
   L->dp_fast = tensor_path<T>(x, y, L->N, L->M) && (reinterpret_cast<uintptr_t>(xty) & 7u) == 0;
+  LoPlanes lo;
+  if (rb == 0) {
+    // the first row block of a step also forms the column sums and, for the tensor path, the operands' low parts,
+    // which the later row blocks of the same step (same x, y, B) re-use
+    SBB_TRY(reserve_lo<T>(L->lo, B, L->N, L->M, L->dp_fast, &lo));
+    SBB_CUDA(sbb::launch_colsum<T>(x, B, L->N, delta, nullptr, p, 0, st, lo_as<T>(lo.x)));
+    SBB_CUDA(sbb::launch_colsum<T>(y, B, L->M, delta + L->N, nullptr, p, 0, st, lo_as<T>(lo.y)));
+    L->lo_batch = lo.x ? B : 0;
+  } else if (L->dp_fast && L->lo_batch == B) {
+    lo.x = static_cast<float *>(L->lo.d);
+    lo.y = lo.x + (size_t)B * L->N;
+  }
+  PhaseTimer timer(L, SBB_PHASE_TRACE, st);
   if (L->dp_fast) {
     if constexpr (std::is_same<T, float>::value)
-      SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, L->N, L->M, xty, rb, re, st));
+      SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, L->N, L->M, xty, rb, re, st, lo.x, lo.y));
   } else {
     SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, L->N, L->M, xty, rb, re, st));
   }
@@ -475,11 +505,17 @@ int update_counters_t(void *Ci, void *Cj, void *Cij, const void *a_i, const void
   T *sy = sx + N;
   // keep the [N, M] block 16-byte aligned whatever N + M is
   T *sxy = sx + ((N + M + 3) / 4) * 4;
-  SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, sx, nullptr, p, 0, 0));
-  SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, sy, nullptr, p, 0, 0));
-  if (tensor_path<T>(dx.d, dy.d, N, M)) {
+  const bool tc = tensor_path<T>(dx.d, dy.d, N, M);
+  Scratch lo_buf;
+  LoPlanes lo;
+  int lo_rc = reserve_lo<T>(lo_buf, B, N, M, tc, &lo);
+  struct Release { Scratch &s; ~Release() { s.release(); } } release_lo{lo_buf};
+  SBB_TRY(lo_rc);
+  SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, sx, nullptr, p, 0, 0, lo_as<T>(lo.x)));
+  SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, sy, nullptr, p, 0, 0, lo_as<T>(lo.y)));
+  if (tc) {
     if constexpr (std::is_same<T, float>::value)
-      SBB_CUDA(sbb::launch_outer_product_tc(dx.as<T>(), dy.as<T>(), B, N, M, sxy, 0, N, 0));
+      SBB_CUDA(sbb::launch_outer_product_tc(dx.as<T>(), dy.as<T>(), B, N, M, sxy, 0, N, 0, lo.x, lo.y));
   } else {
     SBB_CUDA(sbb::launch_outer_product<T>(dx.as<T>(), dy.as<T>(), B, N, M, sxy, 0, N, 0));
   }
@@ -506,9 +542,10 @@ int update_weights_t(void *Ci, void *Cj, void *Cij, const void *a_i, const void 
   Staged drc;
   SBB_TRY(drc.alloc(sbb::tc_trace_scratch_bytes(N, M)));
   const sbb::TraceParams<T> p = sbb::make_trace_params<T>(taupdt, cthr, B);
+  const bool tc = tensor_path<T>(dx.d, dy.d, N, M);
   SBB_CUDA(sbb::launch_colsum<T>(dx.as<T>(), B, N, nullptr, dci.as<T>(), p, 1, 0));
   SBB_CUDA(sbb::launch_colsum<T>(dy.as<T>(), B, M, nullptr, dcj.as<T>(), p, 1, 0));
-  if (tensor_path<T>(dx.d, dy.d, N, M)) {
+  if (tc) {
     if constexpr (std::is_same<T, float>::value)
       SBB_CUDA(sbb::launch_trace_update_tc(dx.as<T>(), dy.as<T>(), B, N, M, 1, dci.as<T>(), dcj.as<T>(), dcij.as<T>(),
                                            dw.as<T>(), nullptr, nullptr, drc.as<float>(), p, 0, N, 0));
@@ -718,6 +755,7 @@ int sbb_layer_destroy(sbb_layer *L) {
   L->ht.release();
   L->col_hc.release();
   L->rc.release();
+  L->lo.release();
   if (L->shard.on) {
     for (int b = 0; b < SBB_SHARD_BUFFERS; ++b)
       for (int r = 0; r < 8; ++r)
@@ -1095,8 +1133,11 @@ int shard_products(sbb_layer *L, const T *x, const T *y, long B, cudaStream_t st
   sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, B);
   // this rank's column sums: into its own slot of its own vector stage, then copied into the same slot everywhere
   T *mine = static_cast<T *>(S.vec.d) + S.rank * (N + M);
-  SBB_CUDA(sbb::launch_colsum<T>(x, B, N, mine, nullptr, p, 0, st));
-  SBB_CUDA(sbb::launch_colsum<T>(y, B, M, mine + N, nullptr, p, 0, st));
+  LoPlanes lo;
+  SBB_TRY(reserve_lo<T>(L->lo, B, N, M, tensor_path<T>(x, y, N, M), &lo));
+  L->lo_batch = 0;
+  SBB_CUDA(sbb::launch_colsum<T>(x, B, N, mine, nullptr, p, 0, st, lo_as<T>(lo.x)));
+  SBB_CUDA(sbb::launch_colsum<T>(y, B, M, mine + N, nullptr, p, 0, st, lo_as<T>(lo.y)));
   SBB_CUDA(sbb::launch_peer_broadcast<T>(mine, N + M, shard_table(L, kShardVec, (size_t)S.rank * (N + M) * sizeof(T)), st));
   // x^T y, one block of rows per owner, written straight into the owner's slot for this rank.  The owners
   // are visited starting after this rank, so that at any time every rank sends to a different owner.
@@ -1111,7 +1152,8 @@ int shard_products(sbb_layer *L, const T *x, const T *y, long B, cudaStream_t st
     // the product kernels address their output as base[row * M + col] with absolute rows
     T *base = slot - rb * M;
     if (tensor_path<T>(x, y, N, M) && (reinterpret_cast<uintptr_t>(slot) & 7u) == 0) {
-      if constexpr (std::is_same<T, float>::value) SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, N, M, base, rb, re, st));
+      if constexpr (std::is_same<T, float>::value)
+        SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, N, M, base, rb, re, st, lo.x, lo.y));
       S.fast = true;
     } else {
       SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, N, M, base, rb, re, st));

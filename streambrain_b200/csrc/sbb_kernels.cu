@@ -567,7 +567,7 @@ template cudaError_t launch_reduce_bias_softmax<double>(const double *, int, con
 // ----------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-    colsum_kernel(const T *__restrict__ a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema) {
+    colsum_kernel(const T *__restrict__ a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema, T *lo) {
   __shared__ T part[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const long col = (long)blockIdx.x * 32 + tx;
@@ -578,8 +578,18 @@ __global__ void __launch_bounds__(256)
       const T v0 = __ldg(a + b * cols + col), v1 = __ldg(a + (b + 8) * cols + col);
       const T v2 = __ldg(a + (b + 16) * cols + col), v3 = __ldg(a + (b + 24) * cols + col);
       s += v0; s += v1; s += v2; s += v3;
+      if (lo) {   // the operand's low parts for the split product of the tensor-core contraction that follows
+        lo[b * cols + col] = tf32_lo(v0);
+        lo[(b + 8) * cols + col] = tf32_lo(v1);
+        lo[(b + 16) * cols + col] = tf32_lo(v2);
+        lo[(b + 24) * cols + col] = tf32_lo(v3);
+      }
     }
-    for (; b < B; b += 8) s += __ldg(a + b * cols + col);
+    for (; b < B; b += 8) {
+      const T v = __ldg(a + b * cols + col);
+      s += v;
+      if (lo) lo[b * cols + col] = tf32_lo(v);
+    }
   }
   part[ty][tx] = s;
   __syncthreads();
@@ -593,15 +603,16 @@ __global__ void __launch_bounds__(256)
 }
 
 template <typename T>
-cudaError_t launch_colsum(const T *a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema, cudaStream_t st) {
+cudaError_t launch_colsum(const T *a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema, cudaStream_t st,
+                          T *lo) {
   if (cols == 0) return cudaSuccess;
-  colsum_kernel<T><<<(unsigned)((cols + 31) / 32), 256, 0, st>>>(a, B, cols, sums, c, p, ema);
+  colsum_kernel<T><<<(unsigned)((cols + 31) / 32), 256, 0, st>>>(a, B, cols, sums, c, p, ema, lo);
   return launched();
 }
 template cudaError_t launch_colsum<float>(const float *, long, long, float *, float *, TraceParams<float>, int,
-                                          cudaStream_t);
+                                          cudaStream_t, float *);
 template cudaError_t launch_colsum<double>(const double *, long, long, double *, double *, TraceParams<double>, int,
-                                           cudaStream_t);
+                                           cudaStream_t, double *);
 
 template <typename T>
 __global__ void vector_ema_kernel(T *c, const T *__restrict__ sums, long n, TraceParams<T> p) {

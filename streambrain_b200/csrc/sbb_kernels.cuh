@@ -40,8 +40,10 @@ cudaError_t launch_reduce_bias_softmax(const T *partial, int splits, const T *bi
 
 // sums[j] = sum_b a[b, j]                       (ema == 0)
 // c[j]    = EMA(c[j], sum_b a[b, j])            (ema != 0; sums unused)
+// lo != nullptr (float32): also writes lo[b, j] = the low part of a[b, j] for a split TF32 product (sbb_math.cuh).
 template <typename T>
-cudaError_t launch_colsum(const T *a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema, cudaStream_t st);
+cudaError_t launch_colsum(const T *a, long B, long cols, T *sums, T *c, TraceParams<T> p, int ema, cudaStream_t st,
+                          T *lo = nullptr);
 
 // c[j] = EMA(c[j], sums[j])
 template <typename T>

@@ -43,4 +43,17 @@ __device__ __forceinline__ float log_ratio_fast(float cij, float rci, float rcj,
   return __log2f(fmaxf(cij, cthr4) * (rci * rcj)) * 0.693147180559945309f;
 }
 
+// The "lo" part of a float32 value v for a product carried by TF32 tensor cores.  The tensor core reads
+// only the upper 19 bits of a 32-bit operand, so the untouched value already acts as hi = v truncated to TF32
+// and only lo = v - hi (exact) has to be produced; it is rounded to the 11 significant bits of TF32 (Veltkamp
+// split with 2^13 + 1, all on the FMA pipe), so that what the tensor core drops of it is zero.  hi + lo then
+// differs from v by at most 2^-22 |v|.  Inf / NaN give a NaN lo.
+__device__ __forceinline__ float tf32_lo(float v) {
+  const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+  const float lo = __fsub_rn(v, hi);
+  const float c = __fmul_rn(lo, 8193.f);
+  return __fsub_rn(c, __fsub_rn(c, lo));
+}
+__device__ __forceinline__ double tf32_lo(double v) { return v; }   // never used: float64 has no tensor path
+
 }  // namespace sbb

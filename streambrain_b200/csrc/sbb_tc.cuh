@@ -36,8 +36,11 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
                                    long row_end, cudaStream_t st);
 
 // delta[i, j] = sum_b x[b, i] y[b, j] for rows [row_begin,row_end)
+// x_lo / y_lo (both or neither): planes of the operands' low parts as launch_colsum writes them; with them the
+// kernel takes both halves of both operands by TMA and converts nothing itself.
 cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long N, long M, float *delta,
-                                    long row_begin, long row_end, cudaStream_t st);
+                                    long row_begin, long row_end, cudaStream_t st, const float *x_lo = nullptr,
+                                    const float *y_lo = nullptr);
 
 // Multiprocessors launch_outer_product_tc leaves free for kernels of other streams.
 void tc_set_reserved_sms(int sms);

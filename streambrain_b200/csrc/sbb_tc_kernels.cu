@@ -79,6 +79,10 @@ struct TcEpilogue {
   int fast_ok;         // select-word epilogue usable: Mc >= 32 (or no mask) and cthr^4 a normal float
   TraceParams<float> p;
   float ema_scale;  // taupdt / batch: weight of the batch sum in the moving average
+  // raw store of an MN-major product: the tile leaves through shared memory and TMA stores of 32 x 32 blocks
+  // (tmC = the output, row 0 = first row of this launch) instead of register stores: whole 128-byte rows per
+  // request, which is what a destination in another GPU's memory needs to be written at link speed
+  int tma_store;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -166,6 +170,16 @@ __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, int x, i
                ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+// One box from shared memory to global memory (bulk async group of the issuing thread).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// at most one store group of this thread may still be reading its shared-memory source
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
                : "memory");
@@ -190,6 +204,16 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same with A through a shared-memory descriptor as well.
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Each lane writes NCOL (16 or 32) consecutive 32-bit columns of its own tensor-memory lane.
@@ -256,18 +280,6 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr, uint32_t lbo_by
   return smem_desc(saddr, lbo_bytes, 512u, 1u);       // MN-major, SWIZZLE_128B_BASE32B
 }
 
-// The "lo" part of v for the split product.  The tensor core reads only the upper 19 bits of a
-// 32-bit TF32 operand, so the untouched value already acts as hi = v truncated to TF32 and only
-// lo = v - hi (exact) has to be produced; it is rounded to the 11 significant bits of TF32
-// (Veltkamp split with 2^13 + 1, all on the FMA pipe), so that what the tensor core drops of it
-// is zero.  hi + lo then differs from v by at most 2^-22 |v|.  Inf / NaN give a NaN lo.
-__device__ __forceinline__ float tf32_lo(float v) {
-  const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-  const float lo = __fsub_rn(v, hi);
-  const float c = __fmul_rn(lo, 8193.f);
-  return __fsub_rn(c, __fsub_rn(c, lo));
-}
-
 // Optional timeline (compile with -DSBB_TC_TRACE): CTA 0 stamps clock64() at the hand-offs of its first
 // 64 tiles -- event numbers: 0 / 8 first / last TMA issue, 5 / 9 first / last conversion, 7 accumulator
 // free, 1 first MMA, 2 accumulator committed, 3 epilogue start, 10 epilogue data ready, 13-15 column
@@ -284,20 +296,25 @@ constexpr int kSlabBytes = 32 * 32 * 4;  // one epilogue warp's 32-row x 32-colu
 
 // The A operand's hi / lo parts live in tensor memory (written by the converters), so only B
 // has a "lo" copy in shared memory and the tensor core fetches only B from there.
-template <int BN, int BK, int STAGES, bool FUSED>
+// PRESPLIT: the low parts of both operands come from memory (written by the column-sum kernels that run just
+// before), so a stage is four TMA landing zones [A | B | B lo | A lo], nothing is converted inside the kernel
+// and the tensor core takes both operands from shared memory.
+template <int BN, int BK, int STAGES, bool SLABS, bool PRESPLIT = false>
 struct TcSmem {
   static constexpr int A_BYTES = 128 * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // TMA landing zone: the raw values serve as "hi"
-  static constexpr int STAGE_BYTES = RAW_BYTES + B_BYTES;   // + B's lo parts
-  // tensor memory: two accumulators, then per stage BK columns of A hi and BK of A lo
+  static constexpr int STAGE_BYTES = PRESPLIT ? 2 * RAW_BYTES : RAW_BYTES + B_BYTES;   // + B's lo parts (+ A's)
+  static constexpr int TX_BYTES = PRESPLIT ? 2 * RAW_BYTES : RAW_BYTES;                // bytes TMA lands per stage
+  // tensor memory: two accumulators, then (not PRESPLIT) per stage BK columns of A hi and BK of A lo
   static constexpr int TMEM_A_COL = 2 * BN;
   static constexpr int TMEM_COLS = 512;
-  static_assert(2 * BN + STAGES * 2 * BK <= TMEM_COLS, "tensor memory budget");
+  static_assert(2 * BN + (PRESPLIT ? 0 : STAGES * 2 * BK) <= TMEM_COLS, "tensor memory budget");
   static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte swizzle alignment");
   static constexpr int SLAB_OFFSET = STAGES * STAGE_BYTES;
-  // fused epilogue: two landing buffers per epilogue warp for blocks of the trace matrix
-  static constexpr int SLAB_TOTAL = FUSED ? kEpiWarps * 2 * kSlabBytes : 0;
+  // two 32 x 32 block buffers per epilogue warp: landing zones for blocks of the trace matrix (fused
+  // epilogue) or staging for the TMA stores of the raw product
+  static constexpr int SLAB_TOTAL = SLABS ? kEpiWarps * 2 * kSlabBytes : 0;
   static constexpr int BAR_OFFSET = SLAB_OFFSET + SLAB_TOTAL;
   // full, conv, empty per stage; acc_full[2], acc_empty[2], drain; slab[warp][2]
   static constexpr int NUM_BARS = 3 * STAGES + 5 + 2 * kEpiWarps;
@@ -339,13 +356,16 @@ __device__ __forceinline__ void tmem_ld_pair(uint32_t taddr_lo, uint32_t taddr_h
 // MULTI (kernels without register-resident sums, CHAIN == 0): the k-range of a tile is cut into chains of
 // wk.chain_kb k-blocks and the epilogue carries the running sum through its output in memory; without it a
 // tile is one chain and the epilogue is the plain one.
-template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false>
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false, bool PRESPLIT = false>
 // 14 warps are allocated registers as 16: 128 registers per thread is the most that fits one CTA per SM.
 __global__ void __launch_bounds__(kThreads, 1)
     tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA3, const __grid_constant__ CUtensorMap tmB3,
-                          const __grid_constant__ CUtensorMap tmC, TcWork wk, TcEpilogue ep, int *status) {
-  using SM = TcSmem<BN, BK, STAGES, FUSED>;
+                          const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAlo,
+                          const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmA3lo,
+                          const __grid_constant__ CUtensorMap tmB3lo, TcWork wk, TcEpilogue ep, int *status) {
+  using SM = TcSmem<BN, BK, STAGES, FUSED || !A_KMAJOR, PRESPLIT>;
+  static_assert(!(PRESPLIT && A_KMAJOR), "pre-split operands are the two MN-major ones of the batch contractions");
   static_assert(!A_KMAJOR || BK == 32, "a K-major operand is loaded as one 128-byte-wide box");
   static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0 && BK <= 32, "tile shape");
   static_assert(!(FUSED && CHAIN > 0), "the fused epilogue consumes a whole-range accumulator");
@@ -439,10 +459,27 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status, kWaitEmpty)) { ok = false; break; }
           if (kb == 0) TC_TRACE((w - blockIdx.x) / gridDim.x, 0);
           if (kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 8);
-          mbar_arrive_expect_tx(bar_full(s), SM::RAW_BYTES);
+          mbar_arrive_expect_tx(bar_full(s), SM::TX_BYTES);
           const uint32_t a_dst = base + s * SM::STAGE_BYTES;
           const uint32_t b_dst = a_dst + SM::A_BYTES;
           const int k0 = kbeg + kb * BK;
+          if constexpr (PRESPLIT) {   // the low parts, same boxes from the low-part planes
+            const uint32_t blo_dst = a_dst + SM::RAW_BYTES, alo_dst = blo_dst + SM::B_BYTES;
+            if (wk.a_box3) {
+              tma_load_3d(alo_dst, &tmA3lo, 0, k0, (wk.a_row0 + mt * 128) / 32, bar_full(s));
+            } else {
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                tma_load_2d(alo_dst + c * (BK * 128), &tmAlo, wk.a_row0 + mt * 128 + 32 * c, k0, bar_full(s));
+            }
+            if (nt < wk.b_box3_tiles) {
+              tma_load_3d(blo_dst, &tmB3lo, 0, k0, nt * (BN / 32), bar_full(s));
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / 32; ++c)
+                tma_load_2d(blo_dst + c * (BK * 128), &tmBlo, nt * BN + 32 * c, k0, bar_full(s));
+            }
+          }
           if (A_KMAJOR) {
             tma_load_2d(a_dst, &tmA, k0, wk.a_row0 + mt * 128, bar_full(s));
           } else if (wk.a_box3) {
@@ -473,7 +510,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // D float32, A and B TF32; A (tensor memory) K-major, B (shared memory) MN-major
-      constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) |
+      // (PRESPLIT: A from shared memory too, MN-major like B)
+      constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((PRESPLIT ? 1u : 0u) << 15) | (1u << 16) |
                                  ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       uint32_t it = 0, chain = 0;
       bool ok = true;
@@ -491,7 +529,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (bool first = true; kb < kb_end; ++kb, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
-            if (!mbar_wait(bar_conv(s), ph, abort_flag, status, kWaitConv)) { ok = false; break; }
+            // the stage is ready when the converters have split it, or (PRESPLIT) as soon as TMA has landed it
+            if (!mbar_wait(PRESPLIT ? bar_full(s) : bar_conv(s), ph, abort_flag, status, kWaitConv)) { ok = false; break; }
             if (first) TC_TRACE(chain, 1);
             tc_fence_after();
             const uint32_t b_hi = base + s * SM::STAGE_BYTES + SM::A_BYTES;
@@ -503,9 +542,18 @@ __global__ void __launch_bounds__(kThreads, 1)
               // (two 4-row swizzle atoms) of the MN-major B in shared memory.
               const uint64_t db_hi = smem_desc_mn(b_hi + kk * 1024, BK * 128);
               const uint64_t db_lo = smem_desc_mn(b_lo + kk * 1024, BK * 128);
-              mma_tf32_ts(d_tmem, ta_hi + BK + kk * 8, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
-              mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_lo, idesc, 1u);
-              mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_hi, idesc, 1u);
+              if constexpr (PRESPLIT) {
+                const uint32_t a_hi = base + s * SM::STAGE_BYTES, a_lo = b_lo + SM::B_BYTES;
+                const uint64_t da_hi = smem_desc_mn(a_hi + kk * 1024, BK * 128);
+                const uint64_t da_lo = smem_desc_mn(a_lo + kk * 1024, BK * 128);
+                mma_tf32_ss(d_tmem, da_lo, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
+                mma_tf32_ss(d_tmem, da_hi, db_lo, idesc, 1u);
+                mma_tf32_ss(d_tmem, da_hi, db_hi, idesc, 1u);
+              } else {
+                mma_tf32_ts(d_tmem, ta_hi + BK + kk * 8, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
+                mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_lo, idesc, 1u);
+                mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_hi, idesc, 1u);
+              }
             }
             first = false;
             mma_commit(bar_empty(s));  // the stage may be refilled once these MMAs have read it
@@ -522,10 +570,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_wait(bar_drain, 0, abort_flag, status, kWaitDrain);
     }
   } else if (warp < kConvWarps) {
-    // ------------------------------------------------------------ hi / lo converters
+    // ------------------------------------------------------------ hi / lo converters (idle when PRESPLIT)
     uint32_t it = 0;
     bool ok = true;
-    for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+    for (long w = blockIdx.x; !PRESPLIT && w < total && ok; w += gridDim.x) {
       int mt, nt, sp, kbeg, nkb;
       decode(w, mt, nt, sp, kbeg, nkb);
       for (int kb = 0; kb < nkb; ++kb, ++it) {
@@ -613,6 +661,32 @@ __global__ void __launch_bounds__(kThreads, 1)
       issue_slab_at(0, mt, nt, 0);
       issue_slab_at(1, mt, nt, 1);
     }
+    // Raw product leaving by TMA: this warp's 32 x 32 block of column group g (lo: tile rows lr, lr + 8; hi:
+    // 16 + lr, 24 + lr; four column pairs each) goes to a staging buffer in the swizzled layout of the
+    // tensor map and one lane sends it.  Blocks past the edge of the output are clipped by the TMA unit.
+    uint32_t stores = 0;
+    auto store_block = [&](const float (&lo)[16], const float (&hi)[16], int mt, int nt, int g) {
+      const uint32_t sb = stores & 1u;
+      if (lane == 0) bulk_wait_read_1();   // the store that used this buffer two blocks ago has read it
+      __syncwarp();
+      uint8_t *sl = smem + SM::SLAB_OFFSET + (ew * 2 + sb) * kSlabBytes + lr * 128;
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int rep = 0; rep < 4; ++rep) {
+          *reinterpret_cast<float2 *>(sl + (8 * rr) * 128 + swz[rep]) = make_float2(lo[rep * 4 + rr * 2], lo[rep * 4 + rr * 2 + 1]);
+          *reinterpret_cast<float2 *>(sl + (16 + 8 * rr) * 128 + swz[rep]) =
+              make_float2(hi[rep * 4 + rr * 2], hi[rep * 4 + rr * 2 + 1]);
+        }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmC, base + SM::SLAB_OFFSET + (ew * 2 + sb) * kSlabBytes, nt * BN + ch * (BN / 2) + g * 32,
+                     mt * 128 + 32 * q);
+        bulk_commit();
+      }
+      ++stores;
+    };
     for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
       int mt, nt, sp, kbeg, nkb;
       decode(w, mt, nt, sp, kbeg, nkb);
@@ -660,7 +734,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_fence_before();
           mbar_arrive(bar_acc_empty(buf));
         }
-        if (ok) {
+        if (ok && !A_KMAJOR && ep.tma_store) {
+#pragma unroll
+          for (int g = 0; g < NG; ++g) store_block(sum[g][0], sum[g][1], mt, nt, g);
+        } else if (ok) {
 #pragma unroll
           for (int g = 0; g < NG; ++g)
 #pragma unroll
@@ -903,6 +980,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t t0 = tacc + g * 32;
             __syncwarp();  // tcgen05.ld is warp-collective
             tmem_ld_pair(t0, t0 + (16u << 16), a0, a1);
+            if (!A_KMAJOR && !MULTI && ep.tma_store) {
+              store_block(a0, a1, mt, nt, g);
+              continue;
+            }
             const long n0 = n_base + g * 32 + lc;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -934,6 +1015,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
 
+  // stores this thread sent by TMA must have left shared memory (and landed) before the CTA retires
+  if (!FUSED && !A_KMAJOR && warp >= kConvWarps && warp < kTmaWarp && lane == 0) bulk_wait_all();
   // ------------------------------------------------------------ tear-down
   __syncwarp();
   tc_fence_before();
@@ -1027,15 +1110,16 @@ int full_chunk_tiles(long cols, int bn) { return (int)(((cols / 32) * 32) / bn);
 
 struct TcMaps {
   CUtensorMap a, b, a3, b3, c;
+  CUtensorMap alo, blo, a3lo, b3lo;   // the operands' low-part planes (pre-split kernels)
 };
 
-template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false>
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false, bool PRESPLIT = false>
 cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st,
                       bool leave_reserved_sms = false) {
-  using SM = TcSmem<BN, BK, STAGES, FUSED>;
+  using SM = TcSmem<BN, BK, STAGES, FUSED || !A_KMAJOR, PRESPLIT>;
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
-  auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN, MULTI>;
+  auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN, MULTI, PRESPLIT>;
   static std::atomic<bool> configured[64];   // per device; setting the attribute twice is harmless
   const int dev = current_device();
   if (!configured[dev].load()) {
@@ -1048,7 +1132,8 @@ cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, 
   int sms = g_sm_count_tc[dev] - (leave_reserved_sms ? tc_get_reserved_sms() : 0);
   if (sms < 1) sms = 1;
   const unsigned grid = (unsigned)(total < sms ? total : sms);
-  kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, wk, ep, status);
+  kernel<<<grid, kThreads, SM::TOTAL, st>>>(tm.a, tm.b, tm.a3, tm.b3, tm.c, tm.alo, tm.blo, tm.a3lo, tm.b3lo, wk, ep,
+                                            status);
   return cudaGetLastError();
 }
 
@@ -1079,7 +1164,7 @@ constexpr int kTrBN = 192, kTrBK = 16, kTrStages = 4;
 // epilogue takes the partial sum over in float32.  Measured on B200: the tensor-memory accumulate truncates,
 // so a chain's sum is low by about 1e-8 x (samples in the chain) relative; 256 keeps that below 4e-6.
 constexpr int kTrChainKb = 16;
-constexpr int kLongBN = 128, kLongStages = 6;   // tiles of the row-block product when the batch spans several chains
+constexpr int kLongBN = 128, kLongStages = 5;   // tiles of the row-block product when the batch spans several chains
 
 // k-blocks per split and the number of (non-empty) splits for the forward product: the split count
 // that minimises (waves of CTAs) x (k-blocks per unit), plus the cost of writing and re-reading
@@ -1132,6 +1217,7 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   tm.c = tm.a;
   const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, kFwdBN / 32);
   if (!b3) tm.b3 = tm.b;
+  tm.alo = tm.blo = tm.a3lo = tm.b3lo = tm.a;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
             b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch, 0};
 #ifdef SBB_TC_TRACE
@@ -1176,6 +1262,33 @@ __global__ void trace_reciprocals_kernel(const float *__restrict__ Ci, long row_
 }
 }  // namespace
 
+namespace {
+// Tensor maps of the two MN-major operands x[B, N] and y[B, M] of a batch contraction with `bn`-column tiles, and
+// (pre != 0) of their low-part planes.  a3 / b3 report whether the one-box 3-D forms exist.
+bool batch_operand_maps(TcMaps &tm, const float *x, const float *y, const float *x_lo, const float *y_lo, bool pre,
+                        long B, long N, long M, int bn, bool &a3, bool &b3) {
+  if (!make_map(&tm.a, x, N, B, 32, kTrBK, true) || !make_map(&tm.b, y, M, B, 32, kTrBK, true)) return false;
+  a3 = N % 32 == 0 && make_map_chunks(&tm.a3, x, N, B, kTrBK, 4);
+  if (!a3) tm.a3 = tm.a;
+  b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, bn / 32);
+  if (!b3) tm.b3 = tm.b;
+  tm.alo = tm.a;
+  tm.blo = tm.b;
+  tm.a3lo = tm.a3;
+  tm.b3lo = tm.b3;
+  if (pre) {
+    if (!make_map(&tm.alo, x_lo, N, B, 32, kTrBK, true) || !make_map(&tm.blo, y_lo, M, B, 32, kTrBK, true)) return false;
+    if (a3 && !make_map_chunks(&tm.a3lo, x_lo, N, B, kTrBK, 4)) return false;
+    if (b3 && !make_map_chunks(&tm.b3lo, y_lo, M, B, kTrBK, bn / 32)) return false;
+  }
+  return true;
+}
+bool lo_planes_usable(const float *x_lo, const float *y_lo) {
+  return x_lo != nullptr && y_lo != nullptr && (reinterpret_cast<uintptr_t>(x_lo) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(y_lo) & 15u) == 0;
+}
+}  // namespace
+
 size_t tc_trace_scratch_bytes(long N, long M) { return (size_t)(((N + 3) / 4) * 4 + M + 4) * sizeof(float); }
 
 cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long N, long M, long H, const float *Ci,
@@ -1202,12 +1315,12 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
     return cudaErrorNotSupported;
   if (row_end <= row_begin) return cudaSuccess;
   TcMaps tm;
-  if (!make_map(&tm.a, x, N, B, 32, kTrBK, true) || !make_map(&tm.b, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  bool a3 = false, b3 = false;
+  // The fused kernel splits its operands itself (A's parts go to tensor memory): with pre-split planes both
+  // operands would come from shared memory, whose bandwidth the Cij blocks of the epilogue also need; measured
+  // on the 55296 x 3000 layer the launch takes 0.608 ms that way against 0.587 ms.
+  if (!batch_operand_maps(tm, x, y, nullptr, nullptr, false, B, N, M, kTrBN, a3, b3)) return cudaErrorInvalidValue;
   if (!make_map(&tm.c, Cij, M, N, 32, 32, false)) return cudaErrorInvalidValue;   // 32 x 32 blocks, 128-byte swizzle
-  const bool a3 = N % 32 == 0 && make_map_chunks(&tm.a3, x, N, B, kTrBK, 4);
-  if (!a3) tm.a3 = tm.a;
-  const bool b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, kTrBN / 32);
-  if (!b3) tm.b3 = tm.b;
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
   // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
@@ -1240,30 +1353,32 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   ep.p = p;
   ep.ema_scale = p.taupdt / p.batch;
   // a batch of more than one chain carries its running sum through the trace matrix (see the kernel)
-  cudaError_t e = B > (long)kTrChainKb * kTrBK ? launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0, true>(tm, wk, ep, st)
-                                               : launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
+  const bool multi = B > (long)kTrChainKb * kTrBK;
+  cudaError_t e = multi ? launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0, true>(tm, wk, ep, st)
+                        : launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
 
 cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long N, long M, float *delta,
-                                    long row_begin, long row_end, cudaStream_t st) {
+                                    long row_begin, long row_end, cudaStream_t st, const float *x_lo,
+                                    const float *y_lo) {
   if (!tc_available() || !tc_shape_ok(x, y, N, M) || row_begin % 128 != 0 ||
       (reinterpret_cast<uintptr_t>(delta) & 7u))
     return cudaErrorNotSupported;
   if (row_end <= row_begin) return cudaSuccess;
   TcMaps tm;
-  if (!make_map(&tm.a, x, N, B, 32, kTrBK, true) || !make_map(&tm.b, y, M, B, 32, kTrBK, true)) return cudaErrorInvalidValue;
+  const bool pre = lo_planes_usable(x_lo, y_lo);
+  const bool longb = B > (long)kTrChainKb * kTrBK;
+  bool a3 = false, b3 = false;
+  if (!batch_operand_maps(tm, x, y, x_lo, y_lo, pre, B, N, M, longb ? kLongBN : kTrBN, a3, b3)) return cudaErrorInvalidValue;
   tm.c = tm.a;
-  const bool a3 = N % 32 == 0 && make_map_chunks(&tm.a3, x, N, B, kTrBK, 4);
-  if (!a3) tm.a3 = tm.a;
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
-  if (B > (long)kTrChainKb * kTrBK) {
+  if (longb) {
     // More than one accumulation chain: 128-column tiles whose running sums stay in the epilogue warps'
     // registers (as in the forward product), so no partial sum travels through memory.
-    const bool b3n = make_map_chunks(&tm.b3, y, M, B, kTrBK, kLongBN / 32);
-    if (!b3n) tm.b3 = tm.b;
+    const bool b3n = b3;
     TcWork wk{(int)((rows + 127) / 128), (int)((M + kLongBN - 1) / kLongBN), 1, (int)B, kper, M > N ? 1 : 0,
               (int)row_begin, a3 ? 1 : 0, b3n ? full_chunk_tiles(M, kLongBN) : 0, 0, 0};
     TcEpilogue ep{};
@@ -1271,12 +1386,13 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
     ep.rows = rows;
     ep.cols = M;
     ep.ld = M;
-    cudaError_t e = launch_tc<false, kLongBN, kTrBK, kLongStages, false, kTrChainKb>(tm, wk, ep, st, true);
+    ep.tma_store = (reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 && make_map(&tm.c, ep.out, M, rows, 32, 32, false);
+    if (!ep.tma_store) tm.c = tm.a;
+    cudaError_t e = pre ? launch_tc<false, kLongBN, kTrBK, kLongStages, false, kTrChainKb, false, true>(tm, wk, ep, st, true)
+                        : launch_tc<false, kLongBN, kTrBK, kLongStages, false, kTrChainKb>(tm, wk, ep, st, true);
     if (e == cudaSuccess) count_launches(1);
     return e;
   }
-  const bool b3 = make_map_chunks(&tm.b3, y, M, B, kTrBK, kTrBN / 32);
-  if (!b3) tm.b3 = tm.b;
   // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
   // fastest when x (B x N) is the larger, row tiles fastest when y (B x M) is
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, M > N ? 1 : 0, (int)row_begin,
@@ -1286,8 +1402,11 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   ep.rows = rows;
   ep.cols = M;
   ep.ld = M;
+  ep.tma_store = (reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 && make_map(&tm.c, ep.out, M, rows, 32, 32, false);
+  if (!ep.tma_store) tm.c = tm.a;
   // the one contraction that runs beside a collective (the reduction of the previous row block)
-  cudaError_t e = launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0>(tm, wk, ep, st, true);
+  cudaError_t e = pre ? launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0, false, true>(tm, wk, ep, st, true)
+                      : launch_tc<false, kTrBN, kTrBK, kTrStages, false, 0>(tm, wk, ep, st, true);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
