@@ -195,6 +195,15 @@ struct sbb_layer {
     void *peer[SBB_SHARD_BUFFERS][8];  // per buffer kind and rank: that rank's buffer, mapped here (own rank: local)
     bool opened[SBB_SHARD_BUFFERS][8];
     bool fast = false;                 // the products of the current step ran on the tensor path
+    // Transport of the partial sums and of the new weight rows: copy engines (the product / apply kernels write
+    // local memory and peer copies on a side stream carry the blocks over NVLink beside the next block's
+    // kernel), or plain peer stores from the kernels themselves (TMA stores of the product's epilogue).
+    bool copy_engines = true;
+    Scratch outbox;                    // copy engines: this rank's x^T y for the rows of the OTHER ranks, [N, M]
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev[32];
+    int ev_next = 0;
+    bool ev_created = false;
   } shard;
 };
 
@@ -762,6 +771,10 @@ int sbb_layer_destroy(sbb_layer *L) {
         if (L->shard.opened[b][r]) cudaIpcCloseMemHandle(L->shard.peer[b][r]);
     L->shard.stage.release();
     L->shard.vec.release();
+    L->shard.outbox.release();
+    if (L->shard.copy_stream) cudaStreamDestroy(L->shard.copy_stream);
+    if (L->shard.ev_created)
+      for (int k = 0; k < 32; ++k) cudaEventDestroy(L->shard.ev[k]);
   }
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
   if (L->h2d_stream) cudaStreamDestroy(L->h2d_stream);
@@ -1144,20 +1157,48 @@ int shard_products(sbb_layer *L, const T *x, const T *y, long B, cudaStream_t st
   PhaseTimer timer(L, SBB_PHASE_TRACE, st);
   const size_t slot_bytes = (size_t)S.rows_per_rank * M * sizeof(T);
   S.fast = false;
+  const bool ce = S.copy_engines && S.world > 1;
+  // with copy engines an owner's rows are formed in sub-blocks, so that the copy of one runs beside the product
+  // of the next: about eight blocks per step whatever the number of ranks
+  const long nsub = ce ? (S.world >= 8 ? 1 : 8 / S.world) : 1;
+  bool copied = false;
   for (long k = 1; k <= S.world; ++k) {
     const long owner = (S.rank + k) % S.world;
     const long rb = shard_begin(L, owner), re = shard_begin(L, owner + 1);
     if (re <= rb) continue;
     T *slot = reinterpret_cast<T *>(static_cast<char *>(S.peer[kShardStage][owner]) + (size_t)S.rank * slot_bytes);
-    // the product kernels address their output as base[row * M + col] with absolute rows
-    T *base = slot - rb * M;
-    if (tensor_path<T>(x, y, N, M) && (reinterpret_cast<uintptr_t>(slot) & 7u) == 0) {
-      if constexpr (std::is_same<T, float>::value)
-        SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, N, M, base, rb, re, st, lo.x, lo.y));
-      S.fast = true;
-    } else {
-      SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, N, M, base, rb, re, st));
+    const bool remote = owner != S.rank;
+    const long tiles = (re - rb + 127) / 128;
+    const long parts = remote && ce ? (nsub < tiles ? nsub : tiles) : 1;
+    for (long part = 0; part < parts; ++part) {
+      const long pb = rb + (tiles * part / parts) * 128;
+      long pe = rb + (tiles * (part + 1) / parts) * 128;
+      if (pe > re) pe = re;
+      // where rows [pb, pe) go: straight into the owner's slot, or (copy engines) into the local outbox first.
+      // The product kernels address their output as base[row * M + col] with absolute rows.
+      T *dst = remote && ce ? static_cast<T *>(S.outbox.d) + pb * M : slot + (pb - rb) * M;
+      T *base = dst - pb * M;
+      if (tensor_path<T>(x, y, N, M) && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+        if constexpr (std::is_same<T, float>::value)
+          SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, N, M, base, pb, pe, st, lo.x, lo.y));
+        S.fast = true;
+      } else {
+        SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, N, M, base, pb, pe, st));
+      }
+      if (remote && ce) {
+        cudaEvent_t e = S.ev[S.ev_next++ & 31];
+        SBB_CUDA(cudaEventRecord(e, st));
+        SBB_CUDA(cudaStreamWaitEvent(S.copy_stream, e, 0));
+        SBB_CUDA(cudaMemcpyAsync(slot + (pb - rb) * M, dst, (size_t)(pe - pb) * M * sizeof(T), cudaMemcpyDeviceToDevice,
+                                 S.copy_stream));
+        copied = true;
+      }
     }
+  }
+  if (copied) {   // the step's stream continues (towards the caller's barrier) only when every block has left
+    cudaEvent_t e = S.ev[S.ev_next++ & 31];
+    SBB_CUDA(cudaEventRecord(e, S.copy_stream));
+    SBB_CUDA(cudaStreamWaitEvent(st, e, 0));
   }
   timer.stop();
   return SBB_OK;
@@ -1176,8 +1217,39 @@ int shard_apply(sbb_layer *L, long Bg, long h, cudaStream_t st) {
   SBB_CUDA(sbb::launch_vector_slots_ema<T>(Ci, static_cast<const T *>(S.vec.d), (int)S.world, N + M, 0, N, p, st));
   SBB_CUDA(sbb::launch_vector_slots_ema<T>(Cj, static_cast<const T *>(S.vec.d), (int)S.world, N + M, N, M, p, st));
   const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
-  SBB_CUDA(sbb::launch_shard_apply<T>(static_cast<const T *>(S.stage.d), (int)S.world, S.rows_per_rank * M, M, L->H,
-                                      L->Mc, Ci, Cj, Cij, shard_table(L, kShardW, 0), wmask, p, rb, re, st, S.fast));
+  const bool ce = S.copy_engines && S.world > 1 && re > rb;
+  if (!ce) {
+    SBB_CUDA(sbb::launch_shard_apply<T>(static_cast<const T *>(S.stage.d), (int)S.world, S.rows_per_rank * M, M, L->H,
+                                        L->Mc, Ci, Cj, Cij, shard_table(L, kShardW, 0), wmask, p, rb, re, st, S.fast));
+  } else {
+    // the new weight rows are written here only, in a few row blocks, and copy engines carry each block to
+    // every other rank while the next block is computed
+    sbb::PeerTable local{};
+    local.n = 1;
+    local.ptr[0] = L->state[SBB_STATE_WEIGHTS];
+    const long tiles = (re - rb + 127) / 128;
+    const long parts = tiles < 4 ? tiles : 4;
+    T *W = static_cast<T *>(L->state[SBB_STATE_WEIGHTS]);
+    for (long part = 0; part < parts; ++part) {
+      const long pb = rb + (tiles * part / parts) * 128;
+      long pe = rb + (tiles * (part + 1) / parts) * 128;
+      if (pe > re) pe = re;
+      SBB_CUDA(sbb::launch_shard_apply<T>(static_cast<const T *>(S.stage.d) + (pb - rb) * M, (int)S.world,
+                                          S.rows_per_rank * M, M, L->H, L->Mc, Ci, Cj, Cij, local, wmask, p, pb, pe, st,
+                                          S.fast));
+      cudaEvent_t e = S.ev[S.ev_next++ & 31];
+      SBB_CUDA(cudaEventRecord(e, st));
+      SBB_CUDA(cudaStreamWaitEvent(S.copy_stream, e, 0));
+      for (long k = 1; k < S.world; ++k) {
+        const long peer = (S.rank + k) % S.world;
+        SBB_CUDA(cudaMemcpyAsync(static_cast<T *>(S.peer[kShardW][peer]) + pb * M, W + pb * M,
+                                 (size_t)(pe - pb) * M * sizeof(T), cudaMemcpyDeviceToDevice, S.copy_stream));
+      }
+    }
+    cudaEvent_t e = S.ev[S.ev_next++ & 31];
+    SBB_CUDA(cudaEventRecord(e, S.copy_stream));
+    SBB_CUDA(cudaStreamWaitEvent(st, e, 0));
+  }
   if (L->desc.kind != SBB_LAYER_PLASTIC) return SBB_OK;
   const double cthr = L->desc.taupdt / 2;
   SBB_CUDA(sbb::launch_update_bias_regularized<T>(static_cast<T *>(L->state[SBB_STATE_BIAS]),
@@ -1236,6 +1308,13 @@ int sbb_layer_shard_init(sbb_layer *L, long rank, long world_size, unsigned char
     SBB_CUDA(cudaIpcGetMemHandle(&hnd, S.peer[b][rank]));
     static_assert(sizeof(hnd) == SBB_SHARD_HANDLE_BYTES, "IPC handle size");
     std::memcpy(handles_out + (size_t)b * SBB_SHARD_HANDLE_BYTES, &hnd, sizeof(hnd));
+  }
+  if (const char *e = std::getenv("SBB_SHARD_TRANSPORT")) S.copy_engines = std::strcmp(e, "stores") != 0;
+  if (S.copy_engines && world_size > 1) {
+    SBB_TRY(S.outbox.reserve((size_t)L->N * L->M * s));
+    SBB_CUDA(cudaStreamCreateWithFlags(&S.copy_stream, cudaStreamNonBlocking));
+    for (int k = 0; k < 32; ++k) SBB_CUDA(cudaEventCreateWithFlags(&S.ev[k], cudaEventDisableTiming));
+    S.ev_created = true;
   }
   S.on = true;
   S.attached = world_size == 1;

@@ -1077,10 +1077,67 @@ int *status_word() {
   return g_status[dev];
 }
 
+// Encoded tensor maps are kept per host thread, keyed by everything that goes into them: a layer's step
+// re-encodes the same handful of maps (same buffers, same shapes) every call, and the driver's encoder
+// costs about a microsecond each, which is a tenth of the step of a small layer.
+struct MapKey {
+  const void *base;
+  long inner, outer;
+  int box_a, box_b, kind;
+  bool operator==(const MapKey &o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && box_a == o.box_a && box_b == o.box_b && kind == o.kind;
+  }
+};
+struct MapCache {
+  static constexpr int kSlots = 128;
+  MapKey key[kSlots];
+  CUtensorMap map[kSlots];
+  bool used[kSlots] = {false};
+  static unsigned slot(const MapKey &k) {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (uint64_t)k.inner * 0xC2B2AE3D27D4EB4Full + (uint64_t)k.outer * 0x165667B19E3779F9ull +
+         (uint64_t)(k.box_a * 131 + k.box_b * 17 + k.kind);
+    return (unsigned)(h >> 40) % kSlots;
+  }
+  bool find(const MapKey &k, CUtensorMap *out) const {
+    const unsigned s = slot(k);
+    if (!used[s] || !(key[s] == k)) return false;
+    *out = map[s];
+    return true;
+  }
+  void put(const MapKey &k, const CUtensorMap &m) {
+    const unsigned s = slot(k);
+    key[s] = k;
+    map[s] = m;
+    used[s] = true;
+  }
+};
+thread_local MapCache g_map_cache;
+
+bool make_map_uncached(CUtensorMap *map, const float *base, long inner, long outer, int box_inner, int box_outer,
+                       bool mn_major);
+bool make_map_chunks_uncached(CUtensorMap *map, const float *base, long cols, long rows, int box_rows, int box_chunks);
+
 // 2-D float32 tensor map over a row-major [outer, inner] matrix, zero fill.  `mn_major` selects the
 // 32-byte-base flavour of the 128-byte swizzle that MN-major 32-bit operands need.
 bool make_map(CUtensorMap *map, const float *base, long inner, long outer, int box_inner, int box_outer,
               bool mn_major) {
+  const MapKey k{base, inner, outer, box_inner, box_outer, mn_major ? 1 : 0};
+  if (g_map_cache.find(k, map)) return true;
+  if (!make_map_uncached(map, base, inner, outer, box_inner, box_outer, mn_major)) return false;
+  g_map_cache.put(k, *map);
+  return true;
+}
+bool make_map_chunks(CUtensorMap *map, const float *base, long cols, long rows, int box_rows, int box_chunks) {
+  const MapKey k{base, cols, rows, box_rows, box_chunks, 2};
+  if (g_map_cache.find(k, map)) return true;
+  if (!make_map_chunks_uncached(map, base, cols, rows, box_rows, box_chunks)) return false;
+  g_map_cache.put(k, *map);
+  return true;
+}
+
+bool make_map_uncached(CUtensorMap *map, const float *base, long inner, long outer, int box_inner, int box_outer,
+                       bool mn_major) {
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)inner * sizeof(float)};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
@@ -1094,7 +1151,7 @@ bool make_map(CUtensorMap *map, const float *base, long inner, long outer, int b
 
 // 3-D view {32, rows, cols/32} of a row-major [rows, cols] float32 matrix (element (i, r, c) = m[r][32c + i]);
 // a box {32, box_rows, box_chunks} lands in shared memory as [chunk][row][32], the MN-major stage layout.
-bool make_map_chunks(CUtensorMap *map, const float *base, long cols, long rows, int box_rows, int box_chunks) {
+bool make_map_chunks_uncached(CUtensorMap *map, const float *base, long cols, long rows, int box_rows, int box_chunks) {
   if (cols < 32) return false;
   cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(cols / 32)};
   cuuint64_t strides[2] = {(cuuint64_t)cols * sizeof(float), 128};

@@ -49,8 +49,9 @@ def _batches(world, steps):
     return [rs.rand(world * B_LOCAL, N).astype(np.float32) for _ in range(steps)]
 
 
-def _worker(rank, world, port, path, out_dir, sharded=False):
+def _worker(rank, world, port, path, out_dir, sharded=False, transport="copy_engines"):
     sys.path.insert(0, REPO)
+    os.environ["SBB_SHARD_TRANSPORT"] = transport
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     if os.environ.get("SBB_TEST_NVLS", "0") != "1":   # SBB_TEST_NVLS=1 leaves NCCL's NVLink-switch reductions on
@@ -78,11 +79,13 @@ def _worker(rank, world, port, path, out_dir, sharded=False):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("transport", ["copy_engines", "stores"])
 @pytest.mark.parametrize("path", ["general", "tensor"])
-def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path):
-    """The row-sharded step (partial sums stored into the owner's memory over NVLink, each row updated once
-    by its owner, weight rows written to every rank) against the all-reduce step on the same two GPUs:
-    the same sums added in the same rank order give the same traces, weights and masks."""
+def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path, transport):
+    """The row-sharded step (partial sums delivered into the owner's memory over NVLink -- by copy engines beside
+    the product kernels, or by the product kernels' own stores -- each row updated once by its owner, weight
+    rows delivered to every rank) against the all-reduce step on the same two GPUs: the same sums added in the
+    same rank order give the same traces, weights and masks."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -91,7 +94,7 @@ def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path):
     a.mkdir()
     b.mkdir()
     mp.spawn(_worker, args=(world, _free_port(), path, str(a), False), nprocs=world, join=True)
-    mp.spawn(_worker, args=(world, _free_port(), path, str(b), True), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), path, str(b), True, transport), nprocs=world, join=True)
     tol = TOL[np.dtype(np.float32)]
     for k in range(2):
         s0 = np.load(b / ("rank0_step%d.npz" % k))
