@@ -244,6 +244,8 @@ int sbb_layer_shard_products(sbb_layer *layer, const void *x_dev, const void *y_
 int sbb_layer_shard_apply(sbb_layer *layer, long B_global, long hypercolumn, void *stream);
 int sbb_layer_shard_mask(sbb_layer *layer, long hypercolumn, void *stream);
 int sbb_layer_shard_share_traces(sbb_layer *layer, void *stream);
+/* Number of ranks the layer is sharded over (peers attached), 0 if it is not. */
+long sbb_layer_shard_world(const sbb_layer *layer);
 /* Rows [row_begin, row_end) of the trace matrix that `rank` owns. */
 int sbb_layer_shard_rows(const sbb_layer *layer, long rank, long *row_begin, long *row_end);
 
@@ -287,7 +289,9 @@ int sbb_network_destroy(sbb_network *net);
 int sbb_network_add_layer(sbb_network *net, sbb_layer *layer);
 /* world_rank / world_size of the slice rule (_cpu_base_backend.py:179-180, 223-233, 279-288);
  * `comm` may be NULL (ranks then train independently on their slices, as the cpu backend would);
- * with `comm` every train step is the split data-parallel step, whatever world_size is. */
+ * with `comm` every train step is the split data-parallel step, whatever world_size is: the
+ * row-sharded one (sbb_layer_shard_*, the reduction callbacks then only serve as the barrier) for
+ * layers sharded over world_size ranks, else reduce-and-replicate (sbb_layer_dp_*). */
 int sbb_network_set_data_parallel(sbb_network *net, long rank, long world_size, const sbb_comm *comm);
 /* Copies images[samples, features] and labels[samples, classes] (host, REAL) to the device. */
 int sbb_network_set_dataset(sbb_network *net, const void *images_host, const void *labels_host, long samples,

@@ -99,6 +99,7 @@ SIGNATURES = {
     "sbb_layer_shard_apply": (c_int, [c_void_p, c_long, c_long, c_void_p]),
     "sbb_layer_shard_mask": (c_int, [c_void_p, c_long, c_void_p]),
     "sbb_layer_shard_share_traces": (c_int, [c_void_p, c_void_p]),
+    "sbb_layer_shard_world": (c_long, [c_void_p]),
     "sbb_layer_shard_rows": (c_int, [c_void_p, c_long, POINTER(c_long), POINTER(c_long)]),
     "sbb_count_correct": (c_int, [c_int, c_void_p, c_void_p, c_long, c_long, POINTER(c_long), c_void_p]),
     "sbb_update_mask_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_double, c_long,

@@ -421,6 +421,7 @@ class Network:
         self.world_size = 1
         self._all_reduce = None
         self._sum_counts = None
+        self._all_gather_bytes = None
         self.verbose = True
         self._handle = ctypes.c_void_p()
         check(lib.sbb_network_create(dtype_code(dtype), ctypes.byref(self._handle)))
@@ -437,12 +438,19 @@ class Network:
             self._handle = None
 
     # -- data parallelism ---------------------------------------------------
-    def set_data_parallel(self, rank, world_size, all_reduce=None, sum_counts=None):
+    def set_data_parallel(self, rank, world_size, all_reduce=None, sum_counts=None, all_gather_bytes=None):
         """``all_reduce(tensor) -> handle with wait()`` starts an in-place sum of a device tensor over
         the ranks (``dist.all_reduce(t, async_op=True)``); ``sum_counts(np.ndarray) -> np.ndarray`` sums
-        the evaluation counters (the mpi backend's Allreduce, mpi_backend.py:63-69)."""
+        the evaluation counters (the mpi backend's Allreduce, mpi_backend.py:63-69).  With
+        ``all_gather_bytes`` (see :meth:`_DeviceLayer.shard_rows`) every layer is row-sharded over the
+        ranks and trains with the sharded step instead of reduce-and-replicate."""
         self.world_rank, self.world_size = rank, world_size
         self._all_reduce, self._sum_counts = all_reduce, sum_counts
+        self._all_gather_bytes = all_gather_bytes
+        if all_gather_bytes is not None:
+            for layer in self._layers:
+                if getattr(layer, "_shard", None) is None:
+                    layer.shard_rows(rank, world_size, all_gather_bytes)
         comm = None
         if all_reduce is not None:
             comm = self._make_comm(all_reduce)
@@ -491,6 +499,8 @@ class Network:
             layer.convert(self.dtype)
         check(lib.sbb_network_add_layer(self._handle, layer._handle))
         self._layers.append(layer)
+        if getattr(self, "_all_gather_bytes", None) is not None and getattr(layer, "_shard", None) is None:
+            layer.shard_rows(self.world_rank, self.world_size, self._all_gather_bytes)
         layer._borrowed = True   # the network holds the native handle: it must not be re-created
 
     def _upload(self, data, labels):

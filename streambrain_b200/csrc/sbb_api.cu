@@ -1389,6 +1389,8 @@ int sbb_layer_shard_share_traces(sbb_layer *L, void *stream) {
   return SBB_OK;
 }
 
+long sbb_layer_shard_world(const sbb_layer *L) { return L != nullptr && L->shard.on && L->shard.attached ? L->shard.world : 0; }
+
 int sbb_layer_shard_rows(const sbb_layer *L, long rank, long *row_begin, long *row_end) {
   ARG(L && row_begin && row_end, "shard_rows: null pointer");
   ARG(L->shard.on, "shard_rows: the layer is not sharded");

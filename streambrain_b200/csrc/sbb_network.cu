@@ -104,6 +104,7 @@ struct sbb_network {
   std::vector<DeviceBuffer> act;   // activation of every layer
   DeviceBuffer delta;              // data-parallel batch sums of the layer being trained
   DeviceBuffer hits;               // evaluation counter
+  DeviceBuffer token;              // one float: the barrier of the row-sharded step
   cudaStream_t stream = nullptr;
   size_t esize() const { return dtype == SBB_F32 ? 4 : 8; }
   long out_features(size_t k) const { return desc[k].hypercolumns * desc[k].minicolumns; }
@@ -173,6 +174,26 @@ int dp_train_step(sbb_network *net, sbb_layer *layer, const sbb_layer_desc &d, c
                   long count, long hypercolumn) {
   const long N = d.in_features, M = d.hypercolumns * d.minicolumns;
   const size_t s = net->esize();
+  if (sbb_layer_shard_world(layer) == net->world && net->world > 0) {
+    // Row-sharded step: partial sums go straight to the rows' owners; a one-element reduction on the step's
+    // stream is the barrier between its phases (it orders this stream after every rank's earlier work).
+    NET_TRY(net->token.reserve(sizeof(float)));
+    auto barrier = [&]() -> int {
+      const long t = net->comm.reduce_begin(net->comm.user, net->token.d, 1, SBB_F32, net->stream);
+      if (t < 0 || net->comm.reduce_wait(net->comm.user, t, net->stream) != 0)
+        return net_fail(SBB_ERR_INVALID, "the reduction callback failed (barrier of the row-sharded step)");
+      return SBB_OK;
+    };
+    NET_TRY(sbb_layer_shard_products(layer, x, y, count, net->stream));
+    NET_TRY(barrier());
+    NET_TRY(sbb_layer_shard_apply(layer, count * net->world, hypercolumn, net->stream));
+    NET_TRY(barrier());
+    if (hypercolumn >= 0 && d.kind == SBB_LAYER_PLASTIC) {
+      NET_TRY(sbb_layer_shard_mask(layer, hypercolumn, net->stream));
+      NET_TRY(barrier());
+    }
+    return SBB_OK;
+  }
   NET_TRY(net->delta.reserve(sbb_layer_delta_elems(layer) * s));
   char *delta = static_cast<char *>(net->delta.d);
   const auto blocks = row_blocks(N, 4);
@@ -253,6 +274,7 @@ int sbb_network_destroy(sbb_network *net) {
   net->batch_t.release();
   net->delta.release();
   net->hits.release();
+  net->token.release();
   for (auto &a : net->act) a.release();
   if (net->stream) cudaStreamDestroy(net->stream);
   delete net;

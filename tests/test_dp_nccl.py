@@ -157,3 +157,91 @@ def test_two_gpu_step_equals_big_batch(tmp_path, path):
             assert errs["wmask bits that differ"] == 0, (k, errs)
             assert all(errs[name] < scale * tol for name in ("Ci", "Cj", "Cij", "bias")), (k, errs)
             assert errs["weights"] < 10 * scale * tol, (k, errs)
+
+
+def _net_worker(rank, world, port, out_dir, sharded):
+    sys.path.insert(0, REPO)
+    sys.path.insert(0, os.path.join(REPO, "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import streambrain_b200 as B200
+    from streambrain_b200 import parallel
+    from conftest import load_golden
+    g = load_golden("network_f64.npz")
+    net, x, lab, B, n_train = _golden_net(B200, g)
+
+    def sum_counts(a):
+        t = torch.from_numpy(np.asarray(a).copy()).cuda()
+        dist.all_reduce(t)
+        return t.cpu().numpy()
+
+    net.set_data_parallel(rank, world, all_reduce=lambda t: dist.all_reduce(t, async_op=True), sum_counts=sum_counts,
+                          all_gather_bytes=parallel.all_gather_bytes_over(dist) if sharded else None)
+    net.fit(x[:n_train], lab[:n_train], B, [(0, 3)])
+    net.fit(x[:n_train], lab[:n_train], B, [(1, 2)])
+    correct, total = net.evaluate(x[n_train:], lab[n_train:], B)
+    if sharded:
+        token = torch.zeros(1, device="cuda")
+        for layer in net._layers:
+            layer.share_traces(lambda: dist.all_reduce(token))
+    torch.cuda.synchronize()
+    out = {"correct": correct, "total": total, "wmask": net._layers[0].wmask}
+    for li, layer in enumerate(net._layers):
+        for name in ("Ci", "Cj", "Cij", "weights", "bias"):
+            out["l%d_%s" % (li, name)] = getattr(layer, name)
+    np.savez(os.path.join(out_dir, "net_rank%d.npz" % rank), **out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _golden_net(B200, g):
+    import random
+    n_pix, H, Mc, B = int(g["n_pix"]), int(g["H"]), int(g["Mc"]), int(g["B"])
+    B -= B % 2                                     # two ranks halve every batch: keep them even
+    n_train = int(g["n_train"])
+    n_train -= n_train % 2
+    np.random.seed(int(g["seed"]))
+    random.seed(int(g["seed"]))
+    net = B200.Network(np.float64)
+    net.verbose = False
+    net.add_layer(B200.StructuralPlasticityLayer(2 * n_pix, H, Mc, 0.03, -40.0, 0.1, 0.05, 0.5, 16,
+                                                 (1, 1 / Mc, 1 / Mc)))
+    net.add_layer(B200.DenseLayer(H * Mc, 1, 10, 0.02, (1 / Mc, 1 / 10, 1 / Mc / 10)))
+    return net, g["x"], g["labels"], B, n_train
+
+
+@pytest.mark.parametrize("sharded", [False, True])
+def test_two_gpu_network_fit_equals_single_gpu_fit(tmp_path, sharded):
+    """Network.fit / evaluate through the native loop on two ranks (each takes half of every batch, the trained
+    layer sums its batch deltas over the ranks) against the same seeded run on one GPU: float64, so the
+    masks must be identical and the state equal to summation-order rounding."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from conftest import load_golden
+    world = 2
+    mp.spawn(_net_worker, args=(world, _free_port(), str(tmp_path), sharded), nprocs=world, join=True)
+    r0, r1 = np.load(tmp_path / "net_rank0.npz"), np.load(tmp_path / "net_rank1.npz")
+    for name in r0.files:
+        assert np.array_equal(r0[name], r1[name]), name
+    import streambrain_b200 as B200
+    torch.cuda.set_device(0)
+    g = load_golden("network_f64.npz")
+    net, x, lab, B, n_train = _golden_net(B200, g)
+    net.fit(x[:n_train], lab[:n_train], B, [(0, 3)])
+    net.fit(x[:n_train], lab[:n_train], B, [(1, 2)])
+    correct, total = net.evaluate(x[n_train:], lab[n_train:], B)
+    assert np.array_equal(r0["wmask"], net._layers[0].wmask)
+    for li, layer in enumerate(net._layers):
+        for name in ("Ci", "Cj", "Cij", "bias", "weights"):
+            assert rel_inf(r0["l%d_%s" % (li, name)], getattr(layer, name)) < 1e-9, (li, name)
+    # every rank evaluates floor(batch / 2) samples of each batch (an odd last batch drops one sample)
+    n_test = x.shape[0] - n_train
+    expect_total = sum(2 * (min(B, n_test - s) // 2) for s in range(0, n_test, B))
+    assert int(r0["total"][0]) == expect_total
+    if expect_total == int(total[0]):
+        assert int(r0["correct"][0]) == int(correct[0])
