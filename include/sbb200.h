@@ -386,6 +386,14 @@ int sbb_device_wait_status(int *status);
  * and must be reloaded (sbb_layer_set_state).  This call then resets the word so that work can go on.
  * Synchronises the device.  No counterpart in the reference (its kernels have no waits). */
 int sbb_device_clear_wait_status(void);
+/* Time limit of one device-side wait, in SM clock cycles (initially 4e9, about two seconds).  Process-wide. */
+int sbb_set_wait_limit_cycles(long long cycles);
+long long sbb_get_wait_limit_cycles(void);
+/* Test hook: each of the next `launches` tensor-core launches of the forward product or the fused trace update
+ * loses one barrier arrival in its first CTA, so that a wait inside the kernel runs into its time limit, the CTA
+ * gives up in order (no trap, no endless loop) and the status word reports it.  Used with a short time limit to
+ * check that path; results of such a launch are undefined. */
+int sbb_debug_lose_arrival(int launches);
 
 /* ------------------------------------------------------------------------
  * Dataset files (host code; no device needed).  Images are unsigned bytes scaled

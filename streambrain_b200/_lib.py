@@ -117,6 +117,9 @@ SIGNATURES = {
     "sbb_tensor_path_available": (c_int, []),
     "sbb_device_wait_status": (c_int, [POINTER(c_int)]),
     "sbb_device_clear_wait_status": (c_int, []),
+    "sbb_set_wait_limit_cycles": (c_int, [ctypes.c_longlong]),
+    "sbb_get_wait_limit_cycles": (ctypes.c_longlong, []),
+    "sbb_debug_lose_arrival": (c_int, [c_int]),
     "sbb_idx_info": (c_int, [c_char_p, POINTER(c_int), POINTER(c_long)]),
     "sbb_read_idx_images": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long]),
     "sbb_read_idx_labels": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long]),

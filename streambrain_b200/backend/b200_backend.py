@@ -413,6 +413,7 @@ class Network:
     """
 
     CHUNK = 64   # batches queued per native call: the granularity of the progress bar
+    verbose = True
 
     def __init__(self, dtype):
         self.dtype = dtype
@@ -422,7 +423,6 @@ class Network:
         self._all_reduce = None
         self._sum_counts = None
         self._all_gather_bytes = None
-        self.verbose = True
         self._handle = ctypes.c_void_p()
         check(lib.sbb_network_create(dtype_code(dtype), ctypes.byref(self._handle)))
         self._comm = None

@@ -416,6 +416,17 @@ int sbb_device_wait_status(int *status) {
   return SBB_OK;
 }
 
+int sbb_set_wait_limit_cycles(long long cycles) {
+  if (cycles <= 0) return fail(SBB_ERR_INVALID, "sbb_set_wait_limit_cycles: the limit must be positive");
+  sbb::tc_set_wait_limit(cycles);
+  return SBB_OK;
+}
+long long sbb_get_wait_limit_cycles(void) { return sbb::tc_get_wait_limit(); }
+int sbb_debug_lose_arrival(int launches) {
+  sbb::tc_debug_lose_arrive(launches);
+  return SBB_OK;
+}
+
 int sbb_device_clear_wait_status(void) {
   SBB_TRY(need_device());
   SBB_CUDA(sbb::tc_clear_status());

@@ -46,6 +46,13 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
 void tc_set_reserved_sms(int sms);
 int tc_get_reserved_sms();
 
+// Time limit of one device-side wait in SM clock cycles (default 4e9, about two seconds), process-wide.
+void tc_set_wait_limit(long long cycles);
+long long tc_get_wait_limit();
+// Test hook: each of the next `launches` tensor-core launches that convert operands inside the kernel loses one
+// barrier arrival in its first CTA, so that a wait there runs into its time limit.
+void tc_debug_lose_arrive(int launches);
+
 // Status word of the bounded device-side waits on the current device: 0 = all
 // waits completed, otherwise the code of the first wait that gave up.
 // Synchronises the device.

@@ -45,7 +45,7 @@ constexpr int kEpiWarps = 8;
 constexpr int kTmaWarp = kConvWarps + kEpiWarps;
 constexpr int kMmaWarp = kTmaWarp + 1;
 constexpr int kThreads = (kMmaWarp + 1) * 32;  // 448
-constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock per wait
+constexpr long long kWaitLimitCycles = 4000000000ll;  // default limit of one wait: about 2 s of SM clock
 
 enum WaitCode { kWaitEmpty = 1, kWaitFull = 2, kWaitConv = 3, kWaitAccEmpty = 4, kWaitAccFull = 5, kWaitDrain = 6, kWaitSlab = 7 };
 
@@ -58,6 +58,8 @@ struct TcWork {
   int a_box3;       // A stage fetched by one 3-D box (MN-major A whose row length is a multiple of 32)
   int b_box3_tiles; // column tiles [0, b_box3_tiles) fetch their B stage by one 3-D box
   int b_prefetch;   // B k-blocks requested into L2 ahead of the load into shared memory (0 = none)
+  long long wait_limit;  // SM clock cycles after which a wait on an mbarrier gives up
+  int lose_arrive;  // test hook: converter thread 0 of CTA 0 skips its arrival for the first stage
   int chain_kb;     // kernels without register-resident sums (CHAIN == 0): k-blocks per tensor-memory
                     // accumulation chain (0 = the whole k-range); later chains are added to the result of
                     // the earlier ones by the epilogue, through the output itself
@@ -122,15 +124,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // counted on the SM's own cycle counter: %globaltimer is read through the memory
 // system and costs microseconds per read on a busy GPU, which a wait taken
 // thousands of times per launch cannot afford.
+// The limit (cycles) sits in shared memory right behind the abort flag (written once at start-up).
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                            int code) {
+                                            int code, bool heed_abort = true) {
   const long long t0 = clock64();
+  const long long limit = *reinterpret_cast<volatile long long *>(abort_flag + 1);
   unsigned spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 1023u) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (heed_abort && *abort_flag) return false;
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -404,6 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_slab(e, 1), 1);
     }
     *abort_flag = 0;
+    *reinterpret_cast<volatile long long *>(abort_flag + 1) = wk.wait_limit;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {
@@ -566,8 +571,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       // Drain: nothing of this CTA may still be running in the tensor pipe when TMEM is freed.
+      // (bounded by time alone: also a CTA that is giving up lets its MMAs in flight finish before TMEM goes)
       mma_commit(bar_drain);
-      mbar_wait(bar_drain, 0, abort_flag, status, kWaitDrain);
+      if (!mbar_try_wait(bar_drain, 0)) mbar_wait_slow(bar_drain, 0, abort_flag, status, kWaitDrain, false);
     }
   } else if (warp < kConvWarps) {
     // ------------------------------------------------------------ hi / lo converters (idle when PRESPLIT)
@@ -625,7 +631,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         tmem_wait_st();
         tc_fence_before();
         fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
-        mbar_arrive(bar_conv(s));
+        // (test hook: one lost arrival leaves the MMA warp waiting until its time limit, see tc_debug_lose_arrive)
+        if (!(wk.lose_arrive && it == 0 && threadIdx.x == 0 && blockIdx.x == 0)) mbar_arrive(bar_conv(s));
       }
     }
   } else {
@@ -1038,6 +1045,15 @@ int g_available = -1;           // -1 unknown, 0 no, 1 yes
 int *g_status[64] = {nullptr};  // per-device status word
 int g_sm_count_tc[64] = {0};
 std::atomic<int> g_reserved_sms{-1};   // -1: not set yet (the environment decides on first use)
+std::atomic<long long> g_wait_limit{kWaitLimitCycles};
+std::atomic<int> g_lose_arrive{0};     // launches that still have to lose one arrival (test hook)
+long long wait_limit_now() { return g_wait_limit.load(); }
+int take_lose_arrive() {
+  int n = g_lose_arrive.load();
+  while (n > 0 && !g_lose_arrive.compare_exchange_weak(n, n - 1)) {
+  }
+  return n > 0 ? 1 : 0;
+}
 
 int current_device() {
   int dev = 0;
@@ -1276,7 +1292,7 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   if (!b3) tm.b3 = tm.b;
   tm.alo = tm.blo = tm.a3lo = tm.b3lo = tm.a;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
-            b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch, 0};
+            b3 ? full_chunk_tiles(M, kFwdBN) : 0, kFwdPrefetch, wait_limit_now(), take_lose_arrive(), 0};
 #ifdef SBB_TC_TRACE
   if (const char *e = getenv("SBB_FWD_PREFETCH")) wk.b_prefetch = atoi(e);   // timeline builds may vary the distance
 #endif
@@ -1383,7 +1399,7 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
   // fastest when x (B x N) is the larger, row tiles fastest when y (B x M) is
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, M > N ? 1 : 0, (int)row_begin,
-            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0, kTrChainKb};
+            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0, wait_limit_now(), take_lose_arrive(), kTrChainKb};
   TcEpilogue ep{};
   ep.rows = rows;
   ep.cols = M;
@@ -1437,7 +1453,7 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
     // registers (as in the forward product), so no partial sum travels through memory.
     const bool b3n = b3;
     TcWork wk{(int)((rows + 127) / 128), (int)((M + kLongBN - 1) / kLongBN), 1, (int)B, kper, M > N ? 1 : 0,
-              (int)row_begin, a3 ? 1 : 0, b3n ? full_chunk_tiles(M, kLongBN) : 0, 0, 0};
+              (int)row_begin, a3 ? 1 : 0, b3n ? full_chunk_tiles(M, kLongBN) : 0, 0, wait_limit_now(), 0, 0};
     TcEpilogue ep{};
     ep.out = delta + row_begin * M;
     ep.rows = rows;
@@ -1453,7 +1469,7 @@ cudaError_t launch_outer_product_tc(const float *x, const float *y, long B, long
   // tiles are walked so that the larger operand is the one re-used by consecutive tiles: column tiles
   // fastest when x (B x N) is the larger, row tiles fastest when y (B x M) is
   TcWork wk{(int)((rows + 127) / 128), (int)((M + kTrBN - 1) / kTrBN), 1, (int)B, kper, M > N ? 1 : 0, (int)row_begin,
-            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0, kTrChainKb};
+            a3 ? 1 : 0, b3 ? full_chunk_tiles(M, kTrBN) : 0, 0, wait_limit_now(), take_lose_arrive(), kTrChainKb};
   TcEpilogue ep{};
   ep.out = delta + row_begin * M;
   ep.rows = rows;
@@ -1475,6 +1491,10 @@ extern "C" int sbb_tc_trace_read(unsigned long long *out) {
   return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 64 * 16);
 }
 #endif
+
+void tc_set_wait_limit(long long cycles) { g_wait_limit.store(cycles > 0 ? cycles : kWaitLimitCycles); }
+long long tc_get_wait_limit() { return g_wait_limit.load(); }
+void tc_debug_lose_arrive(int launches) { g_lose_arrive.store(launches > 0 ? launches : 0); }
 
 void tc_set_reserved_sms(int sms) { g_reserved_sms.store(sms < 0 ? 0 : sms); }
 int tc_get_reserved_sms() {

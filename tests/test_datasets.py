@@ -91,3 +91,21 @@ def test_hyperparameter_table_scales_with_the_batch_size():
     assert hpm.for_dataset("fashion_mnist", 128)["n_minicolumns"] == 100
     with pytest.raises(ValueError):
         hpm.for_dataset("cifar", 128)
+
+
+@pytest.mark.gpu
+def test_training_driver_runs_on_idx_files(tmp_path, monkeypatch, capsys):
+    """The reference's driver (train.py:44-202) on this backend, on small IDX files written here: 200 training
+    and 50 test images, two epochs of the hidden layer (the second one with mask updates) and one of the
+    classifier."""
+    from streambrain_b200 import hyperparameters, train
+    rs = np.random.RandomState(0)
+    for stem, n in (("train", 200), ("t10k", 50)):
+        _write_idx(tmp_path / ("%s-images-idx3-ubyte" % stem), rs.randint(0, 256, size=(n, 28, 28)).astype(np.uint8))
+        _write_idx(tmp_path / ("%s-labels-idx1-ubyte" % stem), rs.randint(0, 10, size=n).astype(np.uint8))
+    short = dict(hyperparameters.DATASETS["mnist"], l1_epochs=2, l2_epochs=1)
+    monkeypatch.setitem(hyperparameters.DATASETS, "mnist", short)
+    monkeypatch.setattr("streambrain_b200.backend.b200_backend.Network.verbose", False, raising=False)
+    assert train.main(["train", "mnist", "single", "8", str(tmp_path)]) == 0
+    out = capsys.readouterr().out
+    assert "Accuracy:" in out and "Training duration:" in out

@@ -221,3 +221,35 @@ def test_update_mask_with_nan_and_inf_scores(k, port_kernels, n):
                 got = k.update_mask(wmask.copy(), w, Ci2, Cj, Cij2, 0.01, 3, 6, h, 16)
                 want = port_kernels.update_mask(wmask.copy(), w, Ci2, Cj, Cij2, 0.01, 3, 6, h, 16)
                 assert np.array_equal(got, want), (variant, h)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(k):
+    """The tensor-core kernels bound every wait on a barrier by a time limit.  With the limit set to about a
+    millisecond and one barrier arrival withheld (a test hook of the library) the waiting warp must give up in
+    order: the launch returns, the status word names the wait, the entry point reports SBB_ERR_TIMEOUT, and after
+    clearing the word the same call works again on the same device."""
+    import ctypes
+    from streambrain_b200 import _lib
+    from streambrain_b200._lib import lib
+    if lib.sbb_get_contraction_path() != 1 or not lib.sbb_tensor_path_available():
+        pytest.skip("the bounded waits belong to the tensor-core kernels")
+    rs = np.random.RandomState(3)
+    x, w, b = rs.rand(64, 256).astype(np.float32), rs.randn(256, 128).astype(np.float32), rs.randn(128).astype(np.float32)
+    want = k.update_state(np.zeros((64, 128), dtype=np.float32), w, b, x)
+    before = lib.sbb_get_wait_limit_cycles()
+    try:
+        assert lib.sbb_set_wait_limit_cycles(2_000_000) == 0
+        assert lib.sbb_debug_lose_arrival(1) == 0
+        k.update_state(np.zeros((64, 128), dtype=np.float32), w, b, x)      # result undefined, must return
+        status = ctypes.c_int(0)
+        assert lib.sbb_device_wait_status(ctypes.byref(status)) == _lib.ERR_TIMEOUT
+        assert status.value == 3                                             # the MMA warp's wait for a converted stage
+        assert lib.sbb_stream_sync(None) == _lib.ERR_TIMEOUT                 # sticky until cleared
+    finally:
+        lib.sbb_debug_lose_arrival(0)
+        lib.sbb_set_wait_limit_cycles(before)
+        assert lib.sbb_device_clear_wait_status() == 0
+    got = k.update_state(np.zeros((64, 128), dtype=np.float32), w, b, x)
+    assert np.array_equal(got, want)
+    status = ctypes.c_int(7)
+    assert lib.sbb_device_wait_status(ctypes.byref(status)) == 0 and status.value == 0
