@@ -63,6 +63,9 @@ CONFIGS = {
     "mnist_f64": dict(n_pixels=784, sparsity=0.8, H=30, Mc=100, batch=128, dtype="float64", hp=_MNIST),
     "wide_f32": dict(n_pixels=784, sparsity=0.8, H=100, Mc=300, batch=1024, dtype="float32", hp=_MNIST),
     "stl10_f32": dict(n_pixels=27648, sparsity=0.0, H=30, Mc=100, batch=256, dtype="float32", hp=_STL10),
+    # not a reference configuration: the STL-10 shape in float64, to characterise the float64 kernels at a size
+    # where launch and pipeline-fill overheads do not dominate
+    "stl10_f64": dict(n_pixels=27648, sparsity=0.0, H=30, Mc=100, batch=256, dtype="float64", hp=_STL10),
     "stl10_dp_f32": dict(n_pixels=27648, sparsity=0.0, H=30, Mc=100, batch=8192, dtype="float32", hp=_STL10),
 }
 

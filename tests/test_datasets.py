@@ -105,7 +105,8 @@ def test_training_driver_runs_on_idx_files(tmp_path, monkeypatch, capsys):
         _write_idx(tmp_path / ("%s-labels-idx1-ubyte" % stem), rs.randint(0, 10, size=n).astype(np.uint8))
     short = dict(hyperparameters.DATASETS["mnist"], l1_epochs=2, l2_epochs=1)
     monkeypatch.setitem(hyperparameters.DATASETS, "mnist", short)
-    monkeypatch.setattr("streambrain_b200.backend.b200_backend.Network.verbose", False, raising=False)
+    from streambrain_b200.backend import b200_backend
+    monkeypatch.setattr(b200_backend.Network, "verbose", False)
     assert train.main(["train", "mnist", "single", "8", str(tmp_path)]) == 0
     out = capsys.readouterr().out
     assert "Accuracy:" in out and "Training duration:" in out
