@@ -104,8 +104,8 @@ def workload_config(wl, p, batch, world, mask, dp_path=False):
             "start_state": "traces at the independent steady state (mask scores finite, as from epoch 2 on)",
             "l2": "inputs larger than L2: %d resident batches cycled, %.0f MB of state streamed per step" % (
                 POOL, 2 * N * H * Mc * s / 1e6),
-            "parallelism": "dp%d" % world + (" (data-parallel step, nothing to reduce)" if dp_path and world == 1
-                                             else "")}
+            "parallelism": "dp%d" % world + (" (data-parallel step on one rank, nothing to exchange)"
+                                             if dp_path and world == 1 else "")}
 
 
 def host_description():
@@ -284,7 +284,21 @@ FP64_PEAK_TFLOPS = 37.2   # 148 SMs x 64 FP64 lanes x 2 flops x 1.965 GHz (nomin
 FFMA_PEAK_TFLOPS = 74.4   # 148 SMs x 128 FP32 lanes x 2 flops x 1.965 GHz (nominal)
 
 
-def step_roofline_of(p, batch, ms_per_step, peaks, tensor_path):
+_FP64_RATES = {}
+
+
+def fp64_rates(lib):
+    """Measured DFMA and float64 tensor-core (mma.sync m8n8k4) rates of the device, TFLOP/s (measured once)."""
+    if not _FP64_RATES:
+        a, b = ctypes.c_double(0), ctypes.c_double(0)
+        if lib.sbb_measure_fp64_rates(ctypes.byref(a), ctypes.byref(b)) == 0 and a.value > 0:
+            _FP64_RATES.update(dfma=a.value, dmma=b.value)
+        else:
+            _FP64_RATES.update(dfma=None, dmma=None)
+    return _FP64_RATES
+
+
+def step_roofline_of(p, batch, ms_per_step, peaks, tensor_path, fp64=None):
     """Whole-step roofline: each of the two phases (forward, trace update) bounded by the larger of its
     memory time and its compute time at the peak of the datapath that ran it.  float32 on the tensor
     path costs three TF32 products per product, i.e. a sixth of the measured bf16 rate; both the burst
@@ -294,7 +308,11 @@ def step_roofline_of(p, batch, ms_per_step, peaks, tensor_path):
     s = np.dtype(p["dtype"]).itemsize
     fwd_b, upd_b, flops = algorithmic_work(N, H * Mc, H, batch, s)
     hbm = float(peaks["hbm_gbs"]) * 1e9
-    if s == 8:
+    if s == 8 and fp64 and fp64.get("dfma"):
+        burst = sustained = max(fp64["dfma"], fp64.get("dmma") or 0.0)
+        note = ("peak = float64 rate measured on this device: DFMA loop %.1f TFLOP/s, mma.sync m8n8k4 loop %.1f "
+                "TFLOP/s (tcgen05 has no float64 kind)" % (fp64["dfma"], fp64.get("dmma") or 0.0))
+    elif s == 8:
         burst = sustained = FP64_PEAK_TFLOPS
         note = "peak = nominal FP64 rate (DFMA), no tensor-core path exists for float64"
     elif tensor_path:
@@ -313,7 +331,7 @@ def step_roofline_of(p, batch, ms_per_step, peaks, tensor_path):
             "compute_peak_tflops_sustained": sustained, "note": note}
 
 
-def short_leg(B200, lib, check, torch, wl, peaks, steps=20, warmup=3):
+def short_leg(B200, lib, check, torch, wl, peaks, steps=20, warmup=3, profile_phases=False):
     """One of the other configurations, timed the same way as the headline (resident batches, mask update
     every step, CUDA events) over a short region."""
     p = synthetic.layer_params(wl)
@@ -338,6 +356,8 @@ def short_leg(B200, lib, check, torch, wl, peaks, steps=20, warmup=3):
     for k in range(warmup):
         step(k)
     torch.cuda.synchronize()
+    if profile_phases:
+        check(lib.sbb_layer_profile(layer._handle, 1))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for k in range(steps):
@@ -347,12 +367,36 @@ def short_leg(B200, lib, check, torch, wl, peaks, steps=20, warmup=3):
     ms = e0.elapsed_time(e1) / steps
     tensor_path = bool(lib.sbb_tensor_path_available()) and bool(lib.sbb_get_contraction_path()) and \
         p["dtype"] == np.float32
+    phases = None
+    if profile_phases:   # the two contractions alone, against the float64 rate of the device
+        def mean_ms(phase):
+            n = ctypes.c_long(0)
+            check(lib.sbb_layer_phase_calls(layer._handle, phase, ctypes.byref(n)))
+            out = []
+            for i in range(max(0, n.value - 64), n.value):
+                t = ctypes.c_float(0)
+                check(lib.sbb_layer_phase_ms(layer._handle, phase, i, ctypes.byref(t)))
+                out.append(t.value)
+            return sum(out) / len(out) if out else None
+        fwd, upd = mean_ms(0), mean_ms(1)
+        check(lib.sbb_layer_profile(layer._handle, 0))
+        flops = 2.0 * batch * N * M
+        rates = fp64_rates(lib) if p["dtype"] == np.float64 else {}
+        peak = max(rates.get("dfma") or 0.0, rates.get("dmma") or 0.0) or None
+        phases = {"forward_ms": fwd, "trace_update_ms": upd,
+                  "forward_tflops": flops / (fwd * 1e-3) / 1e12 if fwd else None,
+                  "trace_update_tflops": flops / (upd * 1e-3) / 1e12 if upd else None,
+                  "fp64_rates_tflops": rates or None,
+                  "forward_frac_of_fp64_rate": flops / (fwd * 1e-3) / 1e12 / peak if fwd and peak else None,
+                  "trace_update_frac_of_fp64_rate": flops / (upd * 1e-3) / 1e12 / peak if upd and peak else None}
+    fp64 = fp64_rates(lib) if p["dtype"] == np.float64 else None
     return {"workload": wl, "layer": "%d->%dx%d" % (N, H, Mc), "batch": batch,
             "dtype": "f32" if p["dtype"] == np.float32 else "f64", "value": batch / (ms * 1e-3), "unit": "samples/s",
             "ms_per_step": ms, "steps": steps, "warmup": warmup,
             "l2": "state %.0f MB %s" % (state_mb, "> L2, streamed every step" if state_mb > 126 else
                                          "(fits the 126 MB L2: this configuration is L2-resident by nature)"),
-            "step_roofline": step_roofline_of(p, batch, ms, peaks, tensor_path)}
+            "contractions": phases,
+            "step_roofline": step_roofline_of(p, batch, ms, peaks, tensor_path, fp64)}
 
 
 def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce, sharded):
@@ -457,6 +501,8 @@ def run_b200(args, wl, p, batch):
     if sharded:
         from streambrain_b200 import parallel
         layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
+    elif world == 1 and args.dp_path and args.dp_mode == "sharded":
+        layer.shard_rows(0, 1, lambda blob: [blob])   # the sharded step's kernels on one rank (nothing crosses NVLink)
     xs = [torch.from_numpy(x).cuda() for x in xs_host]
     ys = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -588,7 +634,7 @@ def run_b200(args, wl, p, batch):
         for k in range(3):
             host_step(k)
         check(lib.sbb_layer_wait(layer._handle))
-        e_steps = max(3, min(args.steps, 50))
+        e_steps = max(args.steps, 60)   # wall-clock timed: long enough for the host's scheduling noise to average out
         t0 = time.perf_counter()
         for k in range(e_steps):
             host_step(3 + k)
@@ -636,7 +682,7 @@ def run_b200(args, wl, p, batch):
         for k in range(3):
             host_step(k)
         barrier()
-        e_steps = max(3, min(args.steps, 50))
+        e_steps = max(args.steps, 60)   # wall-clock timed: long enough for the host's scheduling noise to average out
         t0 = time.perf_counter()
         for k in range(e_steps):
             host_step(3 + k)
@@ -694,9 +740,12 @@ def run_b200(args, wl, p, batch):
         del xs
         torch.cuda.empty_cache()
         other = []
-        for name in ("mnist_f32", "mnist_f64", "wide_f32"):
+        # the three other reference configurations, and the float64 kernels at the large shape (not a reference
+        # configuration: it shows their rate where launch and pipeline-fill overheads do not dominate)
+        for name, kw in (("mnist_f32", {}), ("mnist_f64", {"profile_phases": True}), ("wide_f32", {}),
+                         ("stl10_f64", {"steps": 5, "warmup": 2, "profile_phases": True})):
             try:
-                other.append(short_leg(B200, lib, check, torch, name, peaks))
+                other.append(short_leg(B200, lib, check, torch, name, peaks, **kw))
             except Exception as e:
                 other.append({"workload": name, "error": str(e)[:200]})
 
@@ -717,6 +766,8 @@ def run_b200(args, wl, p, batch):
         "dtype": "f32" if np_dtype == np.float32 else "f64", "data": "synthetic",
         "config": workload_config(wl, p, batch, world, mask, args.dp_path),
         "contraction": "tcgen05 3xTF32" if tensor_path else ("FFMA" if np_dtype == np.float32 else "DFMA"),
+        "dp_step": (("row-sharded over peer-mapped memory (%s transport)" % os.environ.get("SBB_SHARD_TRANSPORT", "copy_engines"))
+                    if args.dp_mode == "sharded" else "all-reduce, replicated update") if dp_path else None,
         "roofline": roofline, "step_roofline": step_roofline, "dp_large_batch": dp_large,
         "dp_checks": dp_checks, "other_configs": other, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,

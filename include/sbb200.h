@@ -415,6 +415,12 @@ int sbb_read_raw_u8_images(const char *path, int dtype, void *out, long samples,
  * (first_label = 1). */
 int sbb_read_raw_u8_labels(const char *path, int dtype, void *out, long samples, long classes, long first_label);
 
+/* Measured float64 rates of the current device in TFLOP/s: a register-resident DFMA loop and a loop of the
+ * float64 tensor-core instruction (mma.sync.m8n8k4): the denominators of the float64 kernels' roofline, and the
+ * evidence for running them on the FP64 pipe (on B200 the two rates are equal).  Synchronises the device.  No
+ * counterpart in the reference. */
+int sbb_measure_fp64_rates(double *dfma_tflops, double *dmma_tflops);
+
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long sbb_kernel_launches(void);
 

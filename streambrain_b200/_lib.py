@@ -126,6 +126,7 @@ SIGNATURES = {
     "sbb_raw_u8_count": (c_int, [c_char_p, POINTER(c_long)]),
     "sbb_read_raw_u8_images": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long]),
     "sbb_read_raw_u8_labels": (c_int, [c_char_p, c_int, c_void_p, c_long, c_long, c_long]),
+    "sbb_measure_fp64_rates": (c_int, [POINTER(c_double), POINTER(c_double)]),
     "sbb_kernel_launches": (c_ulonglong, []),
     "sbb_stream_sync": (c_int, [c_void_p]),
 }

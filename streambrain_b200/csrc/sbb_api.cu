@@ -427,6 +427,13 @@ int sbb_debug_lose_arrival(int launches) {
   return SBB_OK;
 }
 
+int sbb_measure_fp64_rates(double *dfma_tflops, double *dmma_tflops) {
+  ARG(dfma_tflops && dmma_tflops, "measure_fp64_rates: null pointer");
+  SBB_TRY(need_device());
+  SBB_CUDA(sbb::measure_fp64_rates(dfma_tflops, dmma_tflops));
+  return SBB_OK;
+}
+
 int sbb_device_clear_wait_status(void) {
   SBB_TRY(need_device());
   SBB_CUDA(sbb::tc_clear_status());

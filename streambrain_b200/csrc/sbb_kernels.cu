@@ -1794,3 +1794,80 @@ template cudaError_t launch_mask_rewrite_rows<double>(const uint8_t *, const voi
                                                       const PeerTable &, cudaStream_t);
 
 }  // namespace sbb
+
+// ----------------------------------------------------------------------------
+// Measured float64 rates of the device, for the roofline of the float64 kernels:
+// a register-resident DFMA loop and a loop of mma.sync.m8n8k4 (the float64 tensor-core
+// instruction).  Both keep every operand in registers; the result is stored once so
+// that the loops are not removed.
+// ----------------------------------------------------------------------------
+namespace sbb {
+namespace {
+__global__ void __launch_bounds__(256) dfma_rate_kernel(double *out, int iters) {
+  double a[8];
+  const double x = 1.0 + 1e-9 * threadIdx.x, y = 1e-9;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a[k] = (double)k;
+  for (int i = 0; i < iters; ++i) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = fma(a[k], x, y);
+  }
+  double s = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += a[k];
+  if (s == 12345.678) out[0] = s;   // never true: keeps the loop alive
+}
+__global__ void __launch_bounds__(256) dmma_rate_kernel(double *out, int iters) {
+  double c[4][2];
+  const double a = 1.0 + 1e-9 * threadIdx.x, b = 1e-9;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) c[k][0] = c[k][1] = (double)k;
+  for (int i = 0; i < iters; ++i) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+                   : "+d"(c[k][0]), "+d"(c[k][1])
+                   : "d"(a), "d"(b));
+  }
+  double s = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) s += c[k][0] + c[k][1];
+  if (s == 12345.678) out[0] = s;
+}
+}  // namespace
+
+// TFLOP/s of both loops on the current device (CUDA events, best of three launches).
+cudaError_t measure_fp64_rates(double *dfma_tflops, double *dmma_tflops) {
+  double *out = nullptr;
+  cudaError_t e = cudaMalloc(&out, sizeof(double));
+  if (e != cudaSuccess) return e;
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  const int blocks = sm_count() * 4, iters = 20000;
+  double best[2] = {0.0, 0.0};
+  for (int which = 0; which < 2; ++which)
+    for (int rep = 0; rep < 4; ++rep) {
+      cudaEventRecord(e0, 0);
+      if (which == 0) dfma_rate_kernel<<<blocks, 256>>>(out, iters);
+      else dmma_rate_kernel<<<blocks, 256>>>(out, iters);
+      cudaEventRecord(e1, 0);
+      e = cudaEventSynchronize(e1);
+      if (e != cudaSuccess) break;
+      launched();
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      // DFMA: 8 FMAs per thread and iteration; DMMA: 4 instructions of 8 x 8 x 4 FMAs per warp and iteration
+      const double flops = which == 0 ? 2.0 * 8 * iters * 256.0 * blocks : 2.0 * 4 * 256 * iters * 8.0 * blocks;
+      const double tf = flops / (ms * 1e-3) / 1e12;
+      if (rep > 0 && tf > best[which]) best[which] = tf;
+    }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(out);
+  if (e != cudaSuccess) return e;
+  *dfma_tflops = best[0];
+  *dmma_tflops = best[1];
+  return cudaGetLastError();
+}
+}  // namespace sbb

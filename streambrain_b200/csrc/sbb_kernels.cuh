@@ -130,6 +130,10 @@ cudaError_t launch_mask_rewrite_rows(const uint8_t *wmask, const void *scratch, 
                                      T cthr, long N, long M, long H, long Mc, long h, long row_begin, long row_end,
                                      const PeerTable &wtab, cudaStream_t st);
 
+// Measured float64 rates (TFLOP/s) of the current device: a register-resident DFMA loop and a loop of the
+// float64 tensor-core instruction mma.sync.m8n8k4.  Synchronises; takes a few milliseconds.
+cudaError_t measure_fp64_rates(double *dfma_tflops, double *dmma_tflops);
+
 // dst[r, :] = src[order[first + r], :] for r in [0, rows); order == nullptr means the identity.
 template <typename T>
 cudaError_t launch_gather_rows(const T *src, const long *order, long first, long rows, long cols, T *dst,
