@@ -872,20 +872,25 @@ __global__ void __launch_bounds__(256)
   const int lane = threadIdx.x & 31;
   const long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= N) return;  // whole warp leaves together
+  // Every load of the row (its trace, the mask bytes, the trace block) is issued before the first use of any of
+  // them: the loads do not depend on the row's trace value, only the arithmetic does, so the warp pays one
+  // memory round trip instead of three.
   const T pi = Ci[i];
+  int cnt = 0;
+  for (long k = lane; k < H; k += 32) cnt += wmask[i * H + k];
   double s = 0.0;
-  if (pi >= cthr) {
-    // four strided elements per lane at a time, all loads issued before the arithmetic
-    for (long j0 = 0; j0 < Mc; j0 += 128) {
-      T pj[4], pij[4], wv[4];
+  // four strided elements per lane at a time, all loads issued before the arithmetic
+  for (long j0 = 0; j0 < Mc; j0 += 128) {
+    T pj[4], pij[4], wv[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const long jj = j0 + lane + 32 * u, col = h * Mc + jj;
-        const bool in = jj < Mc;
-        pj[u] = in ? Cj[col] : (T)0;
-        pij[u] = in ? Cij[i * M + col] : (T)0;
-        wv[u] = (in && weights) ? weights[i * M + col] : (T)0;
-      }
+    for (int u = 0; u < 4; ++u) {
+      const long jj = j0 + lane + 32 * u, col = h * Mc + jj;
+      const bool in = jj < Mc;
+      pj[u] = in ? Cj[col] : (T)0;
+      pij[u] = in ? Cij[i * M + col] : (T)0;
+      wv[u] = (in && weights) ? weights[i * M + col] : (T)0;
+    }
+    if (pi >= cthr) {
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         if (j0 + lane + 32 * u < Mc && pj[u] >= cthr) {
@@ -897,8 +902,6 @@ __global__ void __launch_bounds__(256)
       }
     }
   }
-  int cnt = 0;
-  for (long k = lane; k < H; k += 32) cnt += wmask[i * H + k];
   for (int off = 16; off > 0; off >>= 1) {
     s += __shfl_xor_sync(0xffffffffu, s, off);
     cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
