@@ -105,6 +105,27 @@ __device__ __forceinline__ void store4(double *p, const double *r, bool vec, int
   }
 }
 
+// One group of a micro-tile row (four floats / two doubles) from / to memory, same contract as load4 / store4.
+__device__ __forceinline__ void loadg(const float *p, float *r, bool vec, int valid) { load4(p, r, vec, valid); }
+__device__ __forceinline__ void storeg(float *p, const float *r, bool vec, int valid) { store4(p, r, vec, valid); }
+__device__ __forceinline__ void loadg(const double *p, double *r, bool vec, int valid) {
+  if (vec && valid == 2) {
+    unpack(*reinterpret_cast<const double2 *>(p), r);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) r[c] = c < valid ? p[c] : 0.0;
+  }
+}
+__device__ __forceinline__ void storeg(double *p, const double *r, bool vec, int valid) {
+  if (vec && valid == 2) {
+    *reinterpret_cast<double2 *>(p) = pack(r);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+      if (c < valid) p[c] = r[c];
+  }
+}
+
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ----------------------------------------------------------------------------
@@ -207,15 +228,32 @@ __device__ __forceinline__ void lds4(const double *p, double *r) {
   unpack(*reinterpret_cast<const double2 *>(p + 2), r + 2);
 }
 
+// Columns of a thread's micro-tile.  A thread owns 8 columns as groups of one 16-byte vector each: float32
+// two groups of four (columns g*64 + tx*4 ..), float64 four groups of two (columns g*32 + tx*2 ..), so that
+// the 16 threads of a half-warp read (and later store) contiguous 16-byte pieces: 256 bytes per request, no
+// shared-memory bank conflicts.  (With four doubles per thread and group the 16-byte reads of a half-warp sat
+// 32 bytes apart: two-way conflicts on 40 % of the wavefronts of the float64 kernels.)
+template <typename T>
+struct MicroCols {
+  static constexpr int GW = 16 / (int)sizeof(T);   // columns per group
+  static constexpr int NG = 8 / GW;                // groups per thread
+  static constexpr int STRIDE = 128 / NG;          // columns between the starts of a thread's groups
+  __device__ static __forceinline__ int group_start(int tx, int g) { return g * STRIDE + tx * GW; }
+  __device__ static __forceinline__ int col(int tx, int e) { return group_start(tx, e / GW) + e % GW; }
+};
+__device__ __forceinline__ void ldsv(const float *p, float *r) { unpack(*reinterpret_cast<const float4 *>(p), r); }
+__device__ __forceinline__ void ldsv(const double *p, double *r) { unpack(*reinterpret_cast<const double2 *>(p), r); }
+
 template <typename T>
 __device__ __forceinline__ void multiply_slab(const T *As, const T *Bs, T (&acc)[8][8], int ty, int tx) {
+  using MC = MicroCols<T>;
 #pragma unroll
   for (int k = 0; k < Tile<T>::BK; ++k) {
     T a[8], b[8];
     lds4(As + k * Tile<T>::LD + ty * 4, a);
     lds4(As + k * Tile<T>::LD + 64 + ty * 4, a + 4);
-    lds4(Bs + k * Tile<T>::LD + tx * 4, b);
-    lds4(Bs + k * Tile<T>::LD + 64 + tx * 4, b + 4);
+#pragma unroll
+    for (int g = 0; g < MC::NG; ++g) ldsv(Bs + k * Tile<T>::LD + MC::group_start(tx, g), b + g * MC::GW);
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
@@ -296,11 +334,12 @@ struct StoreEpilogue {
       const long m = m0 + micro_index(ty, r);
       if (m >= rows) continue;
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        const long n = n0 + g * 64 + tx * 4;
+      for (int g = 0; g < MicroCols<T>::NG; ++g) {
+        constexpr int GW = MicroCols<T>::GW;
+        const long n = n0 + MicroCols<T>::group_start(tx, g);
         const long left = cols - n;
         if (left <= 0) continue;
-        store4(base + m * ld + n, &acc[r][g * 4], vec, left >= 4 ? 4 : (int)left);
+        storeg(base + m * ld + n, &acc[r][g * GW], vec, left >= GW ? GW : (int)left);
       }
     }
   }
@@ -326,7 +365,7 @@ struct TraceEpilogue {
     bool cj_low[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      const long j = n0 + micro_index(tx, c);
+      const long j = n0 + MicroCols<T>::col(tx, c);
       const bool in = j < M;
       cj[c] = in ? Cj[j] : (T)1;
       cj_low[c] = cj[c] < p.cthr;
@@ -340,26 +379,27 @@ struct TraceEpilogue {
       const bool skip = ci < p.cthr;
       const uint8_t *mrow = wmask ? wmask + i * H : nullptr;
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        const long j = n0 + g * 64 + tx * 4;
+      for (int g = 0; g < MicroCols<T>::NG; ++g) {
+        constexpr int GW = MicroCols<T>::GW;
+        const long j = n0 + MicroCols<T>::group_start(tx, g);
         const long left = M - j;
         if (left <= 0) continue;
-        const int valid = left >= 4 ? 4 : (int)left;
-        T c4[4], w4[4];
-        load4(Cij + i * M + j, c4, vec, valid);
+        const int valid = left >= GW ? GW : (int)left;
+        T c4[GW], w4[GW];
+        loadg(Cij + i * M + j, c4, vec, valid);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < GW; ++c) {
           if (c < valid) {
-            const T cij = trace_ema(c4[c], acc[r][g * 4 + c], p);
+            const T cij = trace_ema(c4[c], acc[r][g * GW + c], p);
             c4[c] = cij;
             T w = (T)0;
-            if (!skip && !cj_low[g * 4 + c] && (mrow == nullptr || mrow[hc[g * 4 + c]] != 0))
-              w = log_ratio(cij, ci, cj[g * 4 + c], p.cthr4);
+            if (!skip && !cj_low[g * GW + c] && (mrow == nullptr || mrow[hc[g * GW + c]] != 0))
+              w = log_ratio(cij, ci, cj[g * GW + c], p.cthr4);
             w4[c] = w;
           }
         }
-        store4(Cij + i * M + j, c4, vec, valid);
-        store4(W + i * M + j, w4, vec, valid);
+        storeg(Cij + i * M + j, c4, vec, valid);
+        storeg(W + i * M + j, w4, vec, valid);
       }
     }
   }
@@ -513,6 +553,48 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The same for groups of more than 16 entries (one whole warp per group) with every per-element index a
+// compile-time multiple of 32 from three pointers formed once: the general kernel above spends most of its
+// instructions on 64-bit index arithmetic (about 100 per element at Mc = 300, which made it issue-bound: 183 us
+// for 246 MB at the 1568 -> 100 x 300 layer).
+template <typename T, int NC, bool SPLIT>
+__global__ void __launch_bounds__(256)
+    softmax_warp_kernel(const T *partial, int splits, long slice, const T *__restrict__ bias, T *out, long groups,
+                        int H, int Mc) {
+  const int lane = threadIdx.x & 31;
+  const long g = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (g >= groups) return;   // whole warps leave together
+  const T *src = partial + g * Mc + lane;
+  const T *bs = bias ? bias + (g % H) * (long)Mc + lane : nullptr;
+  T *dst = out + g * Mc + lane;
+  const int left = Mc - lane;   // entry e of this lane exists when e * 32 < left
+  T v[NC];
+  T mx = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < NC; ++e) {
+    T s = -INFINITY;
+    if (e * 32 < left) {
+      s = src[e * 32];
+      if (SPLIT)
+        for (int z = 1; z < splits; ++z) s += src[(long)z * slice + e * 32];
+      if (bs) s += bs[e * 32];
+    }
+    v[e] = s;
+    mx = s > mx ? s : mx;
+  }
+  mx = subwarp_max(mx, 32);
+  T sum = (T)0;
+#pragma unroll
+  for (int e = 0; e < NC; ++e) {
+    v[e] = e * 32 < left ? sbb_exp(v[e] - mx) : (T)0;
+    sum += v[e];
+  }
+  sum = subwarp_sum(sum, 32);
+#pragma unroll
+  for (int e = 0; e < NC; ++e)
+    if (e * 32 < left) dst[e * 32] = v[e] / sum;
+}
+
 // out[r, j] = sum_s partial[s, r, j] + bias[j]   (no softmax)
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -544,6 +626,24 @@ cudaError_t launch_reduce_bias_softmax(const T *partial, int splits, const T *bi
   const long warps = (groups + per_warp - 1) / per_warp;
   const unsigned blocks = (unsigned)((warps + 7) / 8);
   const long per_lane = (Mc + width - 1) / width;
+  if (width == 32 && per_lane <= 16 && H < (1l << 31) && Mc < (1l << 31)) {
+    // one warp per group: the lean kernel (same arithmetic, same summation order)
+#define SBB_SOFTMAX_WARP(NC)                                                                                      \
+  do {                                                                                                            \
+    if (splits > 1)                                                                                               \
+      softmax_warp_kernel<T, NC, true><<<(unsigned)((groups + 7) / 8), 256, 0, st>>>(partial, splits, total, bias, out, \
+                                                                                    groups, (int)H, (int)Mc);    \
+    else                                                                                                          \
+      softmax_warp_kernel<T, NC, false><<<(unsigned)((groups + 7) / 8), 256, 0, st>>>(partial, splits, total, bias, out, \
+                                                                                     groups, (int)H, (int)Mc);   \
+  } while (0)
+    if (per_lane <= 4) SBB_SOFTMAX_WARP(4);
+    else if (per_lane <= 8) SBB_SOFTMAX_WARP(8);
+    else if (per_lane <= 12) SBB_SOFTMAX_WARP(12);
+    else SBB_SOFTMAX_WARP(16);
+#undef SBB_SOFTMAX_WARP
+    return launched();
+  }
   if (per_lane <= 4)
     reduce_bias_softmax_kernel<T, 4><<<blocks, 256, 0, st>>>(partial, splits, total, bias, out, groups, H, Mc, width);
   else if (per_lane <= 8)
