@@ -68,8 +68,9 @@ def parse_args():
     ap.add_argument("--no-dp-large", action="store_true",
                     help="skip the extra leg on the large-batch data-parallel workload (stl10_dp_f32)")
     ap.add_argument("--dp-mode", default="sharded", choices=["sharded", "allreduce"],
-                    help="data-parallel step at N > 1: row-sharded over peer-mapped memory (partial sums stored "
-                         "into the owner's memory, every row updated once) or all-reduce and replicated update")
+                    help="data-parallel step at N > 1: the layer's input rows sharded over the ranks (inputs exchanged "
+                         "by columns over peer-mapped memory, supports summed, every row updated once by its "
+                         "owner) or all-reduce of the batch sums and replicated update")
     ap.add_argument("--no-other-configs", action="store_true",
                     help="skip the short legs on the other configurations (mnist_f32, mnist_f64, wide_f32)")
     ap.add_argument("--contraction", default="tensor", choices=["tensor", "general"],
@@ -403,9 +404,8 @@ def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_
     """Outside the timed region, at N > 1: (1) the replicas of the timed layer are bit-identical
     (checksums of Cij, weights and mask agree over ranks); (2) on a reduced shape one data-parallel
     step over the ranks equals the fused single-GPU step at the same global batch."""
-    token = torch.zeros(1, device="cuda")
-    if sharded:   # a rank holds current traces only for the rows it owns until they are shared
-        layer.share_traces(lambda: dist.all_reduce(token))
+    if sharded:   # a rank holds current weights and traces only for the rows it owns until they are shared
+        layer.share_rows(all_reduce)
     sums = []
     for name in ("Cij", "weights", "wmask"):
         t = layer.state_tensor(name)
@@ -436,13 +436,15 @@ def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_
     dp = make()
     if sharded:
         from streambrain_b200 import parallel
-        dp.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
+        dp.shard_rows(rank, world, parallel.all_gather_bytes_over(dist), b_local)
     xl = torch.from_numpy(np.ascontiguousarray(xg[rank * b_local:(rank + 1) * b_local])).cuda()
     yl = torch.empty((b_local, M), dtype=torch.float32, device="cuda")
-    check(lib.sbb_layer_forward(dp._handle, xl.data_ptr(), b_local, yl.data_ptr(), stream))
-    dp.dp_train_step(xl, yl, h, world, all_reduce)
     if sharded:
-        dp.share_traces(lambda: dist.all_reduce(token))
+        dp.sharded_step(xl, h, all_reduce, out=yl)
+        dp.share_rows(all_reduce)
+    else:
+        check(lib.sbb_layer_forward(dp._handle, xl.data_ptr(), b_local, yl.data_ptr(), stream))
+        dp.dp_train_step(xl, yl, h, world, all_reduce)
     torch.cuda.synchronize()
     err, masks_equal = None, None
     if rank == 0:
@@ -460,7 +462,7 @@ def data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_
         if masks_equal:
             a, b = dp.weights.astype(np.float64), one.weights.astype(np.float64)
             err = max(err, float(np.abs(a - b).max() / max(1.0, np.abs(b).max())) / 10)
-    return {"mode": "row-sharded over peer-mapped memory" if sharded else "all-reduce, replicated update",
+    return {"mode": "row-sharded layer over peer-mapped memory" if sharded else "all-reduce, replicated update",
             "replicas_identical": identical, "dp_vs_single_rel_err": err, "dp_vs_single_masks_equal": masks_equal,
             "dp_vs_single_shape": "%d->%dx%d, global batch %d, one step with a mask update; traces relative "
                                   "to their maximum, weights / 10 (their tolerance is 10x the traces')" % (
@@ -500,9 +502,10 @@ def run_b200(args, wl, p, batch):
     sharded = world > 1 and args.dp_mode == "sharded"
     if sharded:
         from streambrain_b200 import parallel
-        layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
+        layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist), batch)
     elif world == 1 and args.dp_path and args.dp_mode == "sharded":
-        layer.shard_rows(0, 1, lambda blob: [blob])   # the sharded step's kernels on one rank (nothing crosses NVLink)
+        layer.shard_rows(0, 1, lambda blob: [blob], batch)   # the sharded step's kernels on one rank (nothing crosses NVLink)
+    shard_step = getattr(layer, "_shard", None) is not None
     xs = [torch.from_numpy(x).cuda() for x in xs_host]
     ys = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -515,8 +518,11 @@ def run_b200(args, wl, p, batch):
 
     def step(k):
         x, y = xs[k % POOL], ys[k % 2]
-        check(lib.sbb_layer_forward(layer._handle, x.data_ptr(), batch, y.data_ptr(), stream))
         h = (k % H) if mask else None
+        if shard_step:   # forward + train in one: the layer's rows are spread over the ranks
+            layer.sharded_step(x, h, all_reduce, out=y)
+            return
+        check(lib.sbb_layer_forward(layer._handle, x.data_ptr(), batch, y.data_ptr(), stream))
         if dp_path:
             layer.dp_train_step(x, y, h, world, all_reduce)
         else:
@@ -579,7 +585,9 @@ def run_b200(args, wl, p, batch):
                                              hl["density"], 16, hl["initial_counters"], dtype=np_dtype)
         big.Ci, big.Cj, big.Cij = synthetic.steady_state_traces(pl, ref_batch)
         if sharded:
-            big.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
+            big.shard_rows(rank, world, parallel.all_gather_bytes_over(dist), bl)
+        elif shard_step:
+            big.shard_rows(0, 1, lambda blob: [blob], bl)
         gen = torch.Generator(device="cuda")
         gen.manual_seed(synthetic.DATA_SEED + 17 * rank)
         xl = []
@@ -591,8 +599,11 @@ def run_b200(args, wl, p, batch):
 
         def big_step(k):
             x = xl[k % 2]
-            check(lib.sbb_layer_forward(big._handle, x.data_ptr(), bl, yl.data_ptr(), stream))
             h = (k % H) if mask else None
+            if shard_step:
+                big.sharded_step(x, h, all_reduce, out=yl)
+                return
+            check(lib.sbb_layer_forward(big._handle, x.data_ptr(), bl, yl.data_ptr(), stream))
             if dp_path:
                 big.dp_train_step(x, yl, h, world, all_reduce)
             else:
@@ -675,8 +686,11 @@ def run_b200(args, wl, p, batch):
                 x_dev[slot].copy_(pinned[k % 4], non_blocking=True)
                 landed[slot].record(copy_stream)
             compute.wait_event(landed[slot])
-            check(lib.sbb_layer_forward(layer._handle, x_dev[slot].data_ptr(), batch, y_dev[slot].data_ptr(), stream))
-            layer.dp_train_step(x_dev[slot], y_dev[slot], (k % H) if mask else None, world, all_reduce)
+            if shard_step:
+                layer.sharded_step(x_dev[slot], (k % H) if mask else None, all_reduce, out=y_dev[slot])
+            else:
+                check(lib.sbb_layer_forward(layer._handle, x_dev[slot].data_ptr(), batch, y_dev[slot].data_ptr(), stream))
+                layer.dp_train_step(x_dev[slot], y_dev[slot], (k % H) if mask else None, world, all_reduce)
             y_host[slot].copy_(y_dev[slot], non_blocking=True)
             used[slot].record(compute)
         for k in range(3):
@@ -692,8 +706,8 @@ def run_b200(args, wl, p, batch):
         dt = float(dt.item())
         e2e = {"value": world * batch * e_steps / dt, "unit": "samples/s", "h2d_bytes_per_step": world * batch * N * s,
                "d2h_bytes_per_step": world * batch * M * s, "ms_per_step": dt / e_steps * 1e3,
-               "call": "compute_activation + dp_train_step on device tensors, per-rank batch slice uploaded from "
-                       "pinned host memory on a copy stream"}
+               "call": ("sharded_step" if shard_step else "compute_activation + dp_train_step") +
+                       " on device tensors, per-rank batch slice uploaded from pinned host memory on a copy stream"}
 
     dp_checks = None
     if world > 1:
@@ -706,6 +720,8 @@ def run_b200(args, wl, p, batch):
 
     peaks, peak_kind = measured_peaks()
     fwd_b, upd_b, flops = algorithmic_work(N, M, H, batch, s)
+    if shard_step and world > 1:   # a rank's launch updates its own rows from the global batch
+        _, upd_b, flops = algorithmic_work(layer.owned_rows()[1] - layer.owned_rows()[0], M, H, batch * world, s)
     ms_per_step = elapsed_ms / args.steps
     value = world * batch * args.steps / (elapsed_ms * 1e-3)
     # one launch per step on one GPU; under data parallelism the product is cut into row blocks,
@@ -766,8 +782,8 @@ def run_b200(args, wl, p, batch):
         "dtype": "f32" if np_dtype == np.float32 else "f64", "data": "synthetic",
         "config": workload_config(wl, p, batch, world, mask, args.dp_path),
         "contraction": "tcgen05 3xTF32" if tensor_path else ("FFMA" if np_dtype == np.float32 else "DFMA"),
-        "dp_step": (("row-sharded over peer-mapped memory (%s transport)" % os.environ.get("SBB_SHARD_TRANSPORT", "copy_engines"))
-                    if args.dp_mode == "sharded" else "all-reduce, replicated update") if dp_path else None,
+        "dp_step": ("row-sharded layer over peer-mapped memory (inputs exchanged by columns, supports summed)"
+                    if shard_step else "all-reduce, replicated update") if dp_path else None,
         "roofline": roofline, "step_roofline": step_roofline, "dp_large_batch": dp_large,
         "dp_checks": dp_checks, "other_configs": other, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,

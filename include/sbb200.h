@@ -211,42 +211,60 @@ int sbb_layer_dp_finish(sbb_layer *layer, long hypercolumn, void *stream);
 
 /* ------------------------------------------------------------------------
  * Row-sharded data-parallel step over peer-mapped memory (one process per GPU, at
- * most 8 GPUs of one node).  Every rank owns a block of input rows of the trace
- * matrix Cij (multiples of 128 rows, equal blocks).  Per step each rank
- *   1. sbb_layer_shard_products: forms x^T y of its batch slice and writes each
- *      owner's rows straight into that owner's staging memory over NVLink (plain
- *      peer stores from the product kernel's epilogue; one slot per source rank),
- *      and its column sums into every rank's vector stage;
+ * most 8 GPUs of one node).  Every rank owns an equal block of input rows of the
+ * layer (multiples of 128): those rows of the weights, of Cij, of Ci and of the mask
+ * work.  The batch stays split by samples on the way in and out (rank r feeds and
+ * receives samples [r*B, (r+1)*B) of the global batch of world_size*B), and one step
+ * is forward + train of an unsupervised layer, which learns from its own activations:
+ *   1. sbb_layer_shard_scatter: column block o of this rank's input batch goes to
+ *      rank o over NVLink (plain peer stores), so that every owner holds its columns
+ *      of the whole global batch;
  *   -- barrier over the ranks (the caller's: any collective on `stream`) --
- *   2. sbb_layer_shard_apply: updates Ci, Cj (all ranks, identical), sums the slots
- *      of its own rows in rank order, updates those rows of Cij, and writes the new
- *      weight rows into EVERY rank's weight matrix; bias; with hypercolumn >= 0 also
- *      the mask scores of its rows into every rank's work arrays;
- *   -- barrier --
- *   3. (mask steps) sbb_layer_shard_mask: the swaps, identically on every rank, and
- *      the owners rewrite the weights of swapped rows everywhere;  -- barrier --.
- * Same arithmetic as the reduce-then-update scheme of the reference's MPI backend
- * (K/kernels_mpi_internal.cc:100-250; its row-sharded tail kernels with Allgatherv:
- * :263-286, 352-404, 453-484) with the Allreduce replaced by stores to the owner and
- * the update done once per row instead of once per rank.  Between barriers no kernel
- * waits on another rank.  After a sharded step only the owner's rows of Cij are
- * current on a rank; sbb_layer_shard_share_traces copies them to all ranks (then a
- * barrier) when the whole matrix is wanted (checkpoints, tests).
+ *   2. sbb_layer_shard_forward: the owner's part of every sample's support,
+ *      x[:, own rows] * W[own rows, :], into support_dev [world_size*B, M];
+ *   -- the caller sums support_dev over the ranks in place (one all-reduce of
+ *      world_size*B*M elements: the only collective that carries data) --
+ *   3. sbb_layer_shard_activate: bias + softmax of the summed supports, identically on
+ *      every rank; this rank's B rows are copied to y_local_dev when it is not NULL;
+ *   4. sbb_layer_shard_train: Ci of the own rows, Cj, the own rows of Cij and of the
+ *      weights from the global batch (one fused launch, as on one GPU), bias; with
+ *      hypercolumn >= 0 also the mask scores of the own rows into every rank's work
+ *      arrays, and then  -- barrier --  5. sbb_layer_shard_mask: the swaps, identically
+ *      on every rank, and the owner rewrites the weights of its swapped rows.
+ * The result is the single-GPU step at the global batch, which is also what the
+ * reduce-then-update scheme of the reference's MPI backend computes
+ * (K/kernels_mpi_internal.cc:100-250; its own row-sharded tail kernels with
+ * Allgatherv: :263-286, 352-404, 453-484).  Per rank and step about
+ * (world_size-1)/world_size * B*N elements cross NVLink on the way out plus the
+ * all-reduce of the supports, instead of two passes over an N x M matrix, and every
+ * rank does 1/world_size of the global step's arithmetic and memory traffic.
+ * Between barriers no kernel waits on another rank.  While a layer is sharded a rank
+ * holds current values only for its own rows of the weights, Cij and Ci;
+ * sbb_layer_shard_share_rows copies them to all ranks (then a barrier) when the whole
+ * layer is wanted everywhere: the plain forward pass, checkpoints, tests.
  * ---------------------------------------------------------------------- */
-#define SBB_SHARD_BUFFERS 5        /* staging slots, vector slots, weights, mask work arrays, Cij */
+#define SBB_SHARD_BUFFERS 6        /* two gathered-input buffers, mask work arrays, weights, Cij, Ci */
 #define SBB_SHARD_HANDLE_BYTES 64  /* one CUDA IPC memory handle */
-/* Allocates the staging memory and writes this rank's SBB_SHARD_BUFFERS IPC handles to
- * handles_out (SBB_SHARD_BUFFERS * SBB_SHARD_HANDLE_BYTES bytes), to be exchanged by the caller. */
-int sbb_layer_shard_init(sbb_layer *layer, long rank, long world_size, unsigned char *handles_out);
+/* Allocates the gathered-input buffers for local batches of up to max_local_batch samples and writes
+ * this rank's SBB_SHARD_BUFFERS IPC handles to handles_out (SBB_SHARD_BUFFERS * SBB_SHARD_HANDLE_BYTES
+ * bytes), to be exchanged by the caller. */
+int sbb_layer_shard_init(sbb_layer *layer, long rank, long world_size, long max_local_batch,
+                         unsigned char *handles_out);
 /* all_handles: the handles of ranks 0..world_size-1, concatenated in rank order. */
 int sbb_layer_shard_attach(sbb_layer *layer, const unsigned char *all_handles);
-int sbb_layer_shard_products(sbb_layer *layer, const void *x_dev, const void *y_dev, long B_local, void *stream);
-int sbb_layer_shard_apply(sbb_layer *layer, long B_global, long hypercolumn, void *stream);
+/* x_dev: this rank's [B_local, in_features] slice of the global batch; every rank passes the same B_local. */
+int sbb_layer_shard_scatter(sbb_layer *layer, const void *x_dev, long B_local, void *stream);
+/* support_dev: [world_size * B_local, M] REALs, written in full (the caller then sums it over the ranks). */
+int sbb_layer_shard_forward(sbb_layer *layer, long B_local, void *support_dev, void *stream);
+/* support_dev: the summed supports; y_local_dev: NULL or [B_local, M] for this rank's activations. */
+int sbb_layer_shard_activate(sbb_layer *layer, long B_local, const void *support_dev, void *y_local_dev,
+                             void *stream);
+int sbb_layer_shard_train(sbb_layer *layer, long B_local, long hypercolumn, void *stream);
 int sbb_layer_shard_mask(sbb_layer *layer, long hypercolumn, void *stream);
-int sbb_layer_shard_share_traces(sbb_layer *layer, void *stream);
+int sbb_layer_shard_share_rows(sbb_layer *layer, void *stream);
 /* Number of ranks the layer is sharded over (peers attached), 0 if it is not. */
 long sbb_layer_shard_world(const sbb_layer *layer);
-/* Rows [row_begin, row_end) of the trace matrix that `rank` owns. */
+/* Input rows [row_begin, row_end) of the layer that `rank` owns. */
 int sbb_layer_shard_rows(const sbb_layer *layer, long rank, long *row_begin, long *row_end);
 
 /* ------------------------------------------------------------------------
@@ -290,8 +308,9 @@ int sbb_network_add_layer(sbb_network *net, sbb_layer *layer);
 /* world_rank / world_size of the slice rule (_cpu_base_backend.py:179-180, 223-233, 279-288);
  * `comm` may be NULL (ranks then train independently on their slices, as the cpu backend would);
  * with `comm` every train step is the split data-parallel step, whatever world_size is: the
- * row-sharded one (sbb_layer_shard_*, the reduction callbacks then only serve as the barrier) for
- * layers sharded over world_size ranks, else reduce-and-replicate (sbb_layer_dp_*). */
+ * row-sharded one (sbb_layer_shard_*; the reduction callbacks sum the supports and serve as the
+ * barrier) for unsupervised layers sharded over world_size ranks, else reduce-and-replicate
+ * (sbb_layer_dp_*).  At the end of an epoch a sharded layer's rows are shared with all ranks. */
 int sbb_network_set_data_parallel(sbb_network *net, long rank, long world_size, const sbb_comm *comm);
 /* Copies images[samples, features] and labels[samples, classes] (host, REAL) to the device. */
 int sbb_network_set_dataset(sbb_network *net, const void *images_host, const void *labels_host, long samples,

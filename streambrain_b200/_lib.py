@@ -21,7 +21,7 @@ ERR_NAMES = {1: "SBB_ERR_INVALID", 2: "SBB_ERR_CUDA", 3: "SBB_ERR_NO_DEVICE", 4:
              5: "SBB_ERR_TIMEOUT"}
 ERR_INVALID, ERR_CUDA, ERR_NO_DEVICE, ERR_UNSUPPORTED, ERR_TIMEOUT = 1, 2, 3, 4, 5
 F32, F64 = 0, 1
-SHARD_BUFFERS, SHARD_HANDLE_BYTES = 5, 64
+SHARD_BUFFERS, SHARD_HANDLE_BYTES = 6, 64
 DENSE, PLASTIC = 0, 1
 STATE = {"weights": 0, "bias": 1, "Ci": 2, "Cj": 3, "Cij": 4, "kbi": 5, "wmask": 6}
 
@@ -93,12 +93,14 @@ SIGNATURES = {
     "sbb_network_set_epoch_order": (c_int, [c_void_p, c_void_p]),
     "sbb_network_train_batches": (c_int, [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_long]),
     "sbb_network_evaluate": (c_int, [c_void_p, c_long, POINTER(c_long), POINTER(c_long)]),
-    "sbb_layer_shard_init": (c_int, [c_void_p, c_long, c_long, c_void_p]),
+    "sbb_layer_shard_init": (c_int, [c_void_p, c_long, c_long, c_long, c_void_p]),
     "sbb_layer_shard_attach": (c_int, [c_void_p, c_void_p]),
-    "sbb_layer_shard_products": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_void_p]),
-    "sbb_layer_shard_apply": (c_int, [c_void_p, c_long, c_long, c_void_p]),
+    "sbb_layer_shard_scatter": (c_int, [c_void_p, c_void_p, c_long, c_void_p]),
+    "sbb_layer_shard_forward": (c_int, [c_void_p, c_long, c_void_p, c_void_p]),
+    "sbb_layer_shard_activate": (c_int, [c_void_p, c_long, c_void_p, c_void_p, c_void_p]),
+    "sbb_layer_shard_train": (c_int, [c_void_p, c_long, c_long, c_void_p]),
     "sbb_layer_shard_mask": (c_int, [c_void_p, c_long, c_void_p]),
-    "sbb_layer_shard_share_traces": (c_int, [c_void_p, c_void_p]),
+    "sbb_layer_shard_share_rows": (c_int, [c_void_p, c_void_p]),
     "sbb_layer_shard_world": (c_long, [c_void_p]),
     "sbb_layer_shard_rows": (c_int, [c_void_p, c_long, POINTER(c_long), POINTER(c_long)]),
     "sbb_count_correct": (c_int, [c_int, c_void_p, c_void_p, c_long, c_long, POINTER(c_long), c_void_p]),

@@ -226,37 +226,34 @@ class _DeviceLayer:
         return self._delta
 
     def dp_train_step(self, inputs, outputs, hypercolumn, world_size, all_reduce, row_blocks=4):
-        """Data-parallel train step.  ``all_reduce(tensor)`` must start an in-place sum over ranks and
-        return a handle with ``wait()``, e.g. ``dist.all_reduce(t, async_op=True)``.  On a layer set up
-        by :meth:`shard_rows` the step is the row-sharded one (partial sums stored straight into the
-        owner's memory, see :meth:`sharded_train_step`) and ``all_reduce`` only serves as the barrier;
-        otherwise every rank reduces and applies the whole matrix
-        (:func:`streambrain_b200.parallel.pipelined_dp_step`)."""
+        """Reduce-and-replicate data-parallel train step.  ``all_reduce(tensor)`` must start an in-place
+        sum over ranks and return a handle with ``wait()``, e.g. ``dist.all_reduce(t, async_op=True)``;
+        every rank reduces and applies the whole matrix
+        (:func:`streambrain_b200.parallel.pipelined_dp_step`).  A layer set up by :meth:`shard_rows`
+        steps with :meth:`sharded_step` instead (forward and train in one)."""
+        if getattr(self, "_shard", None) is not None:
+            raise ValueError("the layer is row-sharded: its forward pass and train step run as one sharded_step")
         x = self._dev_input(inputs, self.in_features)
         y = self._dev_input(outputs, self.out_features)
-        if getattr(self, "_shard", None) is not None:
-            if self._shard[1] != world_size:
-                raise ValueError("the layer was sharded over %d ranks, the step runs on %d" % (self._shard[1], world_size))
-            token = self._barrier_token()
-            self.sharded_train_step(x, y, hypercolumn, lambda: all_reduce(token).wait())
-            return
         pipelined_dp_step(_DeviceDPOps(self), x, y, hypercolumn, x.shape[0], world_size, all_reduce, row_blocks)
 
-    # -- row-sharded data parallelism over peer-mapped memory ----------------
-    def shard_rows(self, rank, world_size, all_gather_bytes):
-        """Give every rank a block of input rows of the trace matrix to own.  ``all_gather_bytes(b)``
-        must return the list of every rank's ``b`` in rank order (e.g. through
-        ``torch.distributed.all_gather_object``): it carries the CUDA IPC handles with which the ranks
-        map each other's staging memory and weight matrix.  One process per GPU, one node, at most 8."""
+    # -- row-sharded layer over peer-mapped memory ----------------------------
+    def shard_rows(self, rank, world_size, all_gather_bytes, max_local_batch):
+        """Give every rank a block of input rows of the layer to own (those rows of the weights, of Cij
+        and of Ci).  ``all_gather_bytes(b)`` must return the list of every rank's ``b`` in rank order
+        (e.g. through ``torch.distributed.all_gather_object``): it carries the CUDA IPC handles with
+        which the ranks map each other's buffers.  ``max_local_batch`` bounds the per-rank batch of
+        :meth:`sharded_step`.  One process per GPU, one node, at most 8."""
         n = _lib.SHARD_BUFFERS * _lib.SHARD_HANDLE_BYTES
         mine = (ctypes.c_ubyte * n)()
-        check(lib.sbb_layer_shard_init(self._handle, rank, world_size, mine))
+        check(lib.sbb_layer_shard_init(self._handle, rank, world_size, int(max_local_batch), mine))
         parts = all_gather_bytes(bytes(mine))
         if len(parts) != world_size or any(len(p) != n for p in parts):
             raise ValueError("all_gather_bytes must return one %d-byte string per rank" % n)
         blob = b"".join(parts)
         check(lib.sbb_layer_shard_attach(self._handle, ctypes.c_char_p(blob)))
         self._shard = (rank, world_size)
+        self._support = None
 
     def owned_rows(self, rank=None):
         lo, hi = ctypes.c_long(0), ctypes.c_long(0)
@@ -269,27 +266,44 @@ class _DeviceLayer:
             self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
         return self._token
 
-    def sharded_train_step(self, x, y, hypercolumn, barrier):
-        """One row-sharded data-parallel step on device tensors; ``barrier()`` must order the current
-        stream after the work every rank queued before its own ``barrier()`` call (any collective on the
-        stream does).  See ``sbb_layer_shard_*`` in the C header for the protocol."""
+    def sharded_step(self, inputs, hypercolumn, all_reduce, out=None, train=True):
+        """Forward pass + train step of an unsupervised layer, row-sharded over the ranks: ``inputs`` is
+        this rank's slice of the global batch (the same number of samples on every rank), the return
+        value its activations.  ``all_reduce(tensor)`` as in :meth:`dp_train_step`; it sums the supports
+        of the global batch and, on a one-element token, serves as the barrier between ranks.  The
+        result on every rank's rows equals the single-GPU step at the global batch.  With
+        ``train=False`` only the forward pass runs.  See ``sbb_layer_shard_*`` in the C header."""
+        x = self._dev_input(inputs, self.in_features)
         st = _stream_ptr()
         B = x.shape[0]
+        world = self._shard[1]
         h = -1 if hypercolumn is None else int(hypercolumn)
-        check(lib.sbb_layer_shard_products(self._handle, x.data_ptr(), y.data_ptr(), B, st))
-        barrier()
-        check(lib.sbb_layer_shard_apply(self._handle, B * self._shard[1], h, st))
-        barrier()
-        if h >= 0 and self._kind == _lib.PLASTIC:
-            check(lib.sbb_layer_shard_mask(self._handle, h, st))
-            barrier()
+        if self._support is None or self._support.shape[0] != B * world:
+            self._support = torch.empty((B * world, self.out_features), dtype=_torch_dtype(self.dtype), device="cuda")
+        if out is None:
+            out = torch.empty((B, self.out_features), dtype=_torch_dtype(self.dtype), device="cuda")
+        token = self._barrier_token()
+        check(lib.sbb_layer_shard_scatter(self._handle, x.data_ptr(), B, st))
+        all_reduce(token).wait()
+        check(lib.sbb_layer_shard_forward(self._handle, B, self._support.data_ptr(), st))
+        all_reduce(self._support).wait()
+        check(lib.sbb_layer_shard_activate(self._handle, B, self._support.data_ptr(), out.data_ptr(), st))
+        if train:
+            mask = h >= 0 and self._kind == _lib.PLASTIC
+            check(lib.sbb_layer_shard_train(self._handle, B, h if mask else -1, st))
+            if mask:
+                all_reduce(token).wait()
+                check(lib.sbb_layer_shard_mask(self._handle, h, st))
+        return out
 
-    def share_traces(self, barrier):
-        """After sharded steps a rank holds current values only for the rows of Cij it owns; this copies
-        every owner's rows to all ranks (needed before reading ``Cij`` or writing a checkpoint)."""
-        barrier()
-        check(lib.sbb_layer_shard_share_traces(self._handle, _stream_ptr()))
-        barrier()
+    def share_rows(self, all_reduce):
+        """While a layer is sharded a rank holds current weights, Cij and Ci only for the rows it owns;
+        this copies every owner's rows to all ranks (needed before the plain forward pass, before
+        reading the state or writing a checkpoint)."""
+        token = self._barrier_token()
+        all_reduce(token).wait()
+        check(lib.sbb_layer_shard_share_rows(self._handle, _stream_ptr()))
+        all_reduce(token).wait()
 
 
 class _DeviceDPOps:
@@ -442,15 +456,12 @@ class Network:
         """``all_reduce(tensor) -> handle with wait()`` starts an in-place sum of a device tensor over
         the ranks (``dist.all_reduce(t, async_op=True)``); ``sum_counts(np.ndarray) -> np.ndarray`` sums
         the evaluation counters (the mpi backend's Allreduce, mpi_backend.py:63-69).  With
-        ``all_gather_bytes`` (see :meth:`_DeviceLayer.shard_rows`) every layer is row-sharded over the
-        ranks and trains with the sharded step instead of reduce-and-replicate."""
+        ``all_gather_bytes`` (see :meth:`_DeviceLayer.shard_rows`) the layers that learn from their own
+        activations (all but the last) are row-sharded over the ranks when :meth:`fit` first trains them
+        and step with the sharded step instead of reduce-and-replicate."""
         self.world_rank, self.world_size = rank, world_size
         self._all_reduce, self._sum_counts = all_reduce, sum_counts
         self._all_gather_bytes = all_gather_bytes
-        if all_gather_bytes is not None:
-            for layer in self._layers:
-                if getattr(layer, "_shard", None) is None:
-                    layer.shard_rows(rank, world_size, all_gather_bytes)
         comm = None
         if all_reduce is not None:
             comm = self._make_comm(all_reduce)
@@ -499,8 +510,6 @@ class Network:
             layer.convert(self.dtype)
         check(lib.sbb_network_add_layer(self._handle, layer._handle))
         self._layers.append(layer)
-        if getattr(self, "_all_gather_bytes", None) is not None and getattr(layer, "_shard", None) is None:
-            layer.shard_rows(self.world_rank, self.world_size, self._all_gather_bytes)
         layer._borrowed = True   # the network holds the native handle: it must not be re-created
 
     def _upload(self, data, labels):
@@ -525,6 +534,12 @@ class Network:
         batches = (n + maximal_batch_size - 1) // maximal_batch_size
         for layer, epochs in schedule:
             hypercolumns = self._layers[layer].hypercolumns
+            target = self._layers[layer]
+            if (self._all_gather_bytes is not None and layer + 1 < len(self._layers)
+                    and getattr(target, "_shard", None) is None):
+                # every rank takes floor(batch / world_size) samples of a batch (sbb_network_batch_plan)
+                target.shard_rows(self.world_rank, self.world_size, self._all_gather_bytes,
+                                  max(1, maximal_batch_size // self.world_size))
             for epoch in range(epochs):
                 if self.world_rank == 0 and self.verbose:
                     print('Layer - %d/%d' % (layer + 1, len(self._layers)), flush=True)

@@ -185,25 +185,21 @@ struct sbb_layer {
   bool ev_created = false;
   long phase_calls[2] = {0, 0};
   bool dp_fast = false;  // the last sbb_layer_dp_local ran the tensor-core product
-  // row-sharded data parallelism over peer-mapped memory (sbb_layer_shard_*)
+  // row-sharded layer over peer-mapped memory (sbb_layer_shard_*)
   struct Shard {
     bool on = false, attached = false;
     long rank = 0, world = 1;
     long rows_per_rank = 0;            // multiple of 128; rank r owns rows [r * rows_per_rank, ...) clipped to N
-    Scratch stage;                     // world slots x rows_per_rank x M: slot s = rank s's part of x^T y for MY rows
-    Scratch vec;                       // world slots x (N + M): slot s = rank s's column sums of x and y
+    long max_batch = 0;                // largest local batch the gathered-input buffers hold
+    // The own columns of the global batch, [world * B, own rows] with rank s's samples at rows [s * B, (s + 1) * B).
+    // Two buffers used in turn: a fast rank may already scatter step t + 1 while a slow one still reads step t
+    // (the barrier of step t + 1 is what stops it from reaching step t + 2).
+    Scratch xg[2];
+    int parity = 0;                    // buffer of the step in flight
+    long batch = 0;                    // local batch of the step in flight (0: no scatter yet)
+    Scratch yg;                        // activations of the global batch, [world * B, M]
     void *peer[SBB_SHARD_BUFFERS][8];  // per buffer kind and rank: that rank's buffer, mapped here (own rank: local)
     bool opened[SBB_SHARD_BUFFERS][8];
-    bool fast = false;                 // the products of the current step ran on the tensor path
-    // Transport of the partial sums and of the new weight rows: copy engines (the product / apply kernels write
-    // local memory and peer copies on a side stream carry the blocks over NVLink beside the next block's
-    // kernel), or plain peer stores from the kernels themselves (TMA stores of the product's epilogue).
-    bool copy_engines = true;
-    Scratch outbox;                    // copy engines: this rank's x^T y for the rows of the OTHER ranks, [N, M]
-    cudaStream_t copy_stream = nullptr;
-    cudaEvent_t ev[32];
-    int ev_next = 0;
-    bool ev_created = false;
   } shard;
 };
 
@@ -787,12 +783,9 @@ int sbb_layer_destroy(sbb_layer *L) {
     for (int b = 0; b < SBB_SHARD_BUFFERS; ++b)
       for (int r = 0; r < 8; ++r)
         if (L->shard.opened[b][r]) cudaIpcCloseMemHandle(L->shard.peer[b][r]);
-    L->shard.stage.release();
-    L->shard.vec.release();
-    L->shard.outbox.release();
-    if (L->shard.copy_stream) cudaStreamDestroy(L->shard.copy_stream);
-    if (L->shard.ev_created)
-      for (int k = 0; k < 32; ++k) cudaEventDestroy(L->shard.ev[k]);
+    L->shard.xg[0].release();
+    L->shard.xg[1].release();
+    L->shard.yg.release();
   }
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
   if (L->h2d_stream) cudaStreamDestroy(L->h2d_stream);
@@ -1122,18 +1115,19 @@ int sbb_layer_dp_finish(sbb_layer *L, long hypercolumn, void *stream) {
 
 }  // extern "C"
 
-// ------------------------------------------------- row-sharded data parallelism
+// ------------------------------------------------- row-sharded layer over peer-mapped memory
 namespace {
 
-enum { kShardStage = 0, kShardVec = 1, kShardW = 2, kShardMask = 3, kShardCij = 4 };
+enum { kShardX0 = 0, kShardX1 = 1, kShardMask = 2, kShardW = 3, kShardCij = 4, kShardCi = 5 };
 
 void *shard_local_buffer(sbb_layer *L, int which) {
   switch (which) {
-    case kShardStage: return L->shard.stage.d;
-    case kShardVec: return L->shard.vec.d;
-    case kShardW: return L->state[SBB_STATE_WEIGHTS];
+    case kShardX0: return L->shard.xg[0].d;
+    case kShardX1: return L->shard.xg[1].d;
     case kShardMask: return L->score.d;
-    default: return L->state[SBB_STATE_CIJ];
+    case kShardW: return L->state[SBB_STATE_WEIGHTS];
+    case kShardCij: return L->state[SBB_STATE_CIJ];
+    default: return L->state[SBB_STATE_CI];
   }
 }
 
@@ -1152,128 +1146,115 @@ sbb::PeerTable shard_table(sbb_layer *L, int which, size_t byte_offset) {
 
 int check_shard(sbb_layer *L, bool need_peers) {
   SBB_TRY(check_layer(L));
-  ARG(L->shard.on, "the layer is not set up for row-sharded data parallelism (sbb_layer_shard_init)");
+  ARG(L->shard.on, "the layer is not row-sharded (sbb_layer_shard_init)");
   ARG(!need_peers || L->shard.attached, "the peers' buffers are not attached yet (sbb_layer_shard_attach)");
   return SBB_OK;
 }
 
-template <typename T>
-int shard_products(sbb_layer *L, const T *x, const T *y, long B, cudaStream_t st) {
-  auto &S = L->shard;
-  const long N = L->N, M = L->M;
-  sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, B);
-  // this rank's column sums: into its own slot of its own vector stage, then copied into the same slot everywhere
-  T *mine = static_cast<T *>(S.vec.d) + S.rank * (N + M);
-  LoPlanes lo;
-  SBB_TRY(reserve_lo<T>(L->lo, B, N, M, tensor_path<T>(x, y, N, M), &lo));
-  L->lo_batch = 0;
-  SBB_CUDA(sbb::launch_colsum<T>(x, B, N, mine, nullptr, p, 0, st, lo_as<T>(lo.x)));
-  SBB_CUDA(sbb::launch_colsum<T>(y, B, M, mine + N, nullptr, p, 0, st, lo_as<T>(lo.y)));
-  SBB_CUDA(sbb::launch_peer_broadcast<T>(mine, N + M, shard_table(L, kShardVec, (size_t)S.rank * (N + M) * sizeof(T)), st));
-  // x^T y, one block of rows per owner, written straight into the owner's slot for this rank.  The owners
-  // are visited starting after this rank, so that at any time every rank sends to a different owner.
-  PhaseTimer timer(L, SBB_PHASE_TRACE, st);
-  const size_t slot_bytes = (size_t)S.rows_per_rank * M * sizeof(T);
-  S.fast = false;
-  const bool ce = S.copy_engines && S.world > 1;
-  // with copy engines an owner's rows are formed in sub-blocks, so that the copy of one runs beside the product
-  // of the next: about eight blocks per step whatever the number of ranks
-  const long nsub = ce ? (S.world >= 8 ? 1 : 8 / S.world) : 1;
-  bool copied = false;
-  for (long k = 1; k <= S.world; ++k) {
-    const long owner = (S.rank + k) % S.world;
-    const long rb = shard_begin(L, owner), re = shard_begin(L, owner + 1);
-    if (re <= rb) continue;
-    T *slot = reinterpret_cast<T *>(static_cast<char *>(S.peer[kShardStage][owner]) + (size_t)S.rank * slot_bytes);
-    const bool remote = owner != S.rank;
-    const long tiles = (re - rb + 127) / 128;
-    const long parts = remote && ce ? (nsub < tiles ? nsub : tiles) : 1;
-    for (long part = 0; part < parts; ++part) {
-      const long pb = rb + (tiles * part / parts) * 128;
-      long pe = rb + (tiles * (part + 1) / parts) * 128;
-      if (pe > re) pe = re;
-      // where rows [pb, pe) go: straight into the owner's slot, or (copy engines) into the local outbox first.
-      // The product kernels address their output as base[row * M + col] with absolute rows.
-      T *dst = remote && ce ? static_cast<T *>(S.outbox.d) + pb * M : slot + (pb - rb) * M;
-      T *base = dst - pb * M;
-      if (tensor_path<T>(x, y, N, M) && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
-        if constexpr (std::is_same<T, float>::value)
-          SBB_CUDA(sbb::launch_outer_product_tc(x, y, B, N, M, base, pb, pe, st, lo.x, lo.y));
-        S.fast = true;
-      } else {
-        SBB_CUDA(sbb::launch_outer_product<T>(x, y, B, N, M, base, pb, pe, st));
-      }
-      if (remote && ce) {
-        cudaEvent_t e = S.ev[S.ev_next++ & 31];
-        SBB_CUDA(cudaEventRecord(e, st));
-        SBB_CUDA(cudaStreamWaitEvent(S.copy_stream, e, 0));
-        SBB_CUDA(cudaMemcpyAsync(slot + (pb - rb) * M, dst, (size_t)(pe - pb) * M * sizeof(T), cudaMemcpyDeviceToDevice,
-                                 S.copy_stream));
-        copied = true;
-      }
-    }
-  }
-  if (copied) {   // the step's stream continues (towards the caller's barrier) only when every block has left
-    cudaEvent_t e = S.ev[S.ev_next++ & 31];
-    SBB_CUDA(cudaEventRecord(e, S.copy_stream));
-    SBB_CUDA(cudaStreamWaitEvent(st, e, 0));
-  }
-  timer.stop();
+// The step in flight must have been opened by a scatter of the same local batch.
+int check_shard_step(sbb_layer *L, long B, const char *what) {
+  SBB_TRY(check_shard(L, true));
+  ARG(B > 0 && B == L->shard.batch, "%s: local batch %ld, but the last sbb_layer_shard_scatter carried %ld", what, B,
+      L->shard.batch);
   return SBB_OK;
 }
 
 template <typename T>
-int shard_apply(sbb_layer *L, long Bg, long h, cudaStream_t st) {
+int shard_scatter(sbb_layer *L, const T *x, long B, cudaStream_t st) {
   auto &S = L->shard;
-  const long N = L->N, M = L->M;
+  S.parity ^= 1;
+  S.batch = B;
+  // rank o receives this rank's samples as rows [rank * B, (rank + 1) * B) of its [world * B, rows of o] buffer
+  sbb::PeerTable t{};
+  t.n = (int)S.world;
+  for (long o = 0; o < S.world; ++o) {
+    const long width = shard_begin(L, o + 1) - shard_begin(L, o);
+    t.ptr[o] = static_cast<T *>(S.peer[kShardX0 + S.parity][o]) + (size_t)S.rank * B * width;
+  }
+  SBB_CUDA(sbb::launch_scatter_columns<T>(x, B, L->N, S.rows_per_rank, t, st));
+  return SBB_OK;
+}
+
+template <typename T>
+int shard_forward(sbb_layer *L, long B, T *support, cudaStream_t st) {
+  auto &S = L->shard;
+  const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
+  const long nr = re - rb, Bg = B * S.world, M = L->M;
+  if (nr <= 0) {   // more ranks than 128-row blocks: this rank owns nothing and adds nothing
+    SBB_CUDA(cudaMemsetAsync(support, 0, (size_t)Bg * M * sizeof(T), st));
+    return SBB_OK;
+  }
+  const T *xg = static_cast<const T *>(S.xg[S.parity].d);
+  const T *W = static_cast<const T *>(L->state[SBB_STATE_WEIGHTS]) + rb * M;
+  bool tc = tensor_path<T>(xg, W, nr, M) && (reinterpret_cast<uintptr_t>(support) & 7u) == 0;
+  const int splits = tc ? sbb::forward_splits_tc(Bg, nr, M) : sbb::forward_splits<T>(Bg, nr, M);
+  T *partial = support;
+  if (splits > 1) {
+    SBB_TRY(L->fwd_partial.reserve((size_t)splits * Bg * M * sizeof(T)));
+    partial = static_cast<T *>(L->fwd_partial.d);
+  }
+  PhaseTimer timer(L, SBB_PHASE_FORWARD, st);
+  if (tc) {
+    if constexpr (std::is_same<T, float>::value)
+      SBB_CUDA(sbb::launch_forward_product_tc(xg, W, partial, Bg, nr, M, splits, st));
+  } else {
+    SBB_CUDA(sbb::launch_forward_product<T>(xg, W, partial, Bg, nr, M, splits, st));
+  }
+  timer.stop();
+  if (splits > 1) SBB_CUDA(sbb::launch_sum_partials<T>(partial, splits, Bg * M, support, st));
+  return SBB_OK;
+}
+
+template <typename T>
+int shard_activate(sbb_layer *L, long B, const T *support, T *y_local, cudaStream_t st) {
+  auto &S = L->shard;
+  const long Bg = B * S.world, M = L->M;
+  SBB_TRY(S.yg.reserve((size_t)Bg * M * sizeof(T)));
+  T *yg = static_cast<T *>(S.yg.d);
+  SBB_CUDA(sbb::launch_reduce_bias_softmax<T>(support, 1, static_cast<const T *>(L->state[SBB_STATE_BIAS]), yg, Bg, L->H,
+                                              L->Mc, 1, st));
+  if (y_local)
+    SBB_CUDA(cudaMemcpyAsync(y_local, yg + (size_t)S.rank * B * M, (size_t)B * M * sizeof(T), cudaMemcpyDeviceToDevice, st));
+  return SBB_OK;
+}
+
+template <typename T>
+int shard_train(sbb_layer *L, long B, long h, cudaStream_t st) {
+  auto &S = L->shard;
+  const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
+  const long nr = re - rb, Bg = B * S.world, N = L->N, M = L->M;
+  ARG(S.yg.d != nullptr && S.yg.cap >= (size_t)Bg * M * sizeof(T), "shard_train: no activations (sbb_layer_shard_activate)");
   const sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, Bg);
+  const T *xg = static_cast<const T *>(S.xg[S.parity].d);
+  const T *yg = static_cast<const T *>(S.yg.d);
   T *Ci = static_cast<T *>(L->state[SBB_STATE_CI]);
   T *Cj = static_cast<T *>(L->state[SBB_STATE_CJ]);
   T *Cij = static_cast<T *>(L->state[SBB_STATE_CIJ]);
+  T *W = static_cast<T *>(L->state[SBB_STATE_WEIGHTS]);
   const uint8_t *wmask = static_cast<const uint8_t *>(L->state[SBB_STATE_WMASK]);
-  // Ci, Cj: every rank sums the slots of all ranks in rank order, so the replicas stay identical
-  SBB_CUDA(sbb::launch_vector_slots_ema<T>(Ci, static_cast<const T *>(S.vec.d), (int)S.world, N + M, 0, N, p, st));
-  SBB_CUDA(sbb::launch_vector_slots_ema<T>(Cj, static_cast<const T *>(S.vec.d), (int)S.world, N + M, N, M, p, st));
-  const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
-  const bool ce = S.copy_engines && S.world > 1 && re > rb;
-  if (!ce) {
-    SBB_CUDA(sbb::launch_shard_apply<T>(static_cast<const T *>(S.stage.d), (int)S.world, S.rows_per_rank * M, M, L->H,
-                                        L->Mc, Ci, Cj, Cij, shard_table(L, kShardW, 0), wmask, p, rb, re, st, S.fast));
-  } else {
-    // the new weight rows are written here only, in a few row blocks, and copy engines carry each block to
-    // every other rank while the next block is computed
-    sbb::PeerTable local{};
-    local.n = 1;
-    local.ptr[0] = L->state[SBB_STATE_WEIGHTS];
-    const long tiles = (re - rb + 127) / 128;
-    const long parts = tiles < 4 ? tiles : 4;
-    T *W = static_cast<T *>(L->state[SBB_STATE_WEIGHTS]);
-    for (long part = 0; part < parts; ++part) {
-      const long pb = rb + (tiles * part / parts) * 128;
-      long pe = rb + (tiles * (part + 1) / parts) * 128;
-      if (pe > re) pe = re;
-      SBB_CUDA(sbb::launch_shard_apply<T>(static_cast<const T *>(S.stage.d) + (pb - rb) * M, (int)S.world,
-                                          S.rows_per_rank * M, M, L->H, L->Mc, Ci, Cj, Cij, local, wmask, p, pb, pe, st,
-                                          S.fast));
-      cudaEvent_t e = S.ev[S.ev_next++ & 31];
-      SBB_CUDA(cudaEventRecord(e, st));
-      SBB_CUDA(cudaStreamWaitEvent(S.copy_stream, e, 0));
-      for (long k = 1; k < S.world; ++k) {
-        const long peer = (S.rank + k) % S.world;
-        SBB_CUDA(cudaMemcpyAsync(static_cast<T *>(S.peer[kShardW][peer]) + pb * M, W + pb * M,
-                                 (size_t)(pe - pb) * M * sizeof(T), cudaMemcpyDeviceToDevice, S.copy_stream));
-      }
+  // Cj from the whole batch on every rank (identical inputs, identical results); Ci, Cij and the weights for the
+  // own rows only, addressed as a layer of `nr` inputs that starts at row rb
+  SBB_CUDA(sbb::launch_colsum<T>(yg, Bg, M, nullptr, Cj, p, 1, st));
+  if (nr > 0) {
+    SBB_CUDA(sbb::launch_colsum<T>(xg, Bg, nr, nullptr, Ci + rb, p, 1, st));
+    PhaseTimer timer(L, SBB_PHASE_TRACE, st);
+    if (tensor_path<T>(xg, yg, nr, M)) {
+      if constexpr (std::is_same<T, float>::value)
+        SBB_CUDA(sbb::launch_trace_update_tc(xg, yg, Bg, nr, M, L->H, Ci + rb, Cj, Cij + rb * M, W + rb * M,
+                                             wmask ? wmask + rb * L->H : nullptr, static_cast<const int *>(L->col_hc.d),
+                                             static_cast<float *>(L->rc.d), p, 0, nr, st));
+    } else {
+      SBB_CUDA(sbb::launch_trace_update_fused<T>(xg, yg, Bg, nr, M, L->H, L->Mc, Ci + rb, Cj, Cij + rb * M, W + rb * M,
+                                                 wmask ? wmask + rb * L->H : nullptr, p, 0, nr, st));
     }
-    cudaEvent_t e = S.ev[S.ev_next++ & 31];
-    SBB_CUDA(cudaEventRecord(e, S.copy_stream));
-    SBB_CUDA(cudaStreamWaitEvent(st, e, 0));
+    timer.stop();
   }
   if (L->desc.kind != SBB_LAYER_PLASTIC) return SBB_OK;
   const double cthr = L->desc.taupdt / 2;
   SBB_CUDA(sbb::launch_update_bias_regularized<T>(static_cast<T *>(L->state[SBB_STATE_BIAS]),
                                                   static_cast<T *>(L->state[SBB_STATE_KBI]), Cj, (T)cthr,
                                                   (T)L->desc.khalf, (T)L->desc.pmin, (T)L->desc.taubdt, M, st));
-  if (h >= 0)   // scores of the owned rows, into every rank's work arrays
+  if (h >= 0 && nr > 0)   // scores of the owned rows, into every rank's work arrays
     SBB_CUDA(sbb::launch_mask_score_rows<T>(wmask, Ci, Cj, Cij, (T)cthr, N, M, L->H, L->Mc, h, rb, re,
                                             shard_table(L, kShardMask, 0), st));
   return SBB_OK;
@@ -1287,12 +1268,32 @@ int shard_mask(sbb_layer *L, long h, cudaStream_t st) {
   const T *Cj = static_cast<const T *>(L->state[SBB_STATE_CJ]);
   const T *Cij = static_cast<const T *>(L->state[SBB_STATE_CIJ]);
   uint8_t *wmask = static_cast<uint8_t *>(L->state[SBB_STATE_WMASK]);
-  // the swaps, identically on every rank (all hold all scores); weights are rewritten by the owners only
+  // the swaps, identically on every rank (all hold all scores); every owner rewrites the weights of its own rows
   SBB_CUDA(sbb::launch_mask_select<T>(wmask, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, L->desc.mask_iterations,
                                       L->score.d, st, nullptr));
   const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
+  sbb::PeerTable own{};
+  own.n = 1;
+  own.ptr[0] = L->state[SBB_STATE_WEIGHTS];
   SBB_CUDA(sbb::launch_mask_rewrite_rows<T>(wmask, L->score.d, Ci, Cj, Cij, (T)cthr, L->N, L->M, L->H, L->Mc, h, rb, re,
-                                            shard_table(L, kShardW, 0), st));
+                                            own, st));
+  return SBB_OK;
+}
+
+// Copies `bytes` at `offset` of this rank's buffer `which` to the same place in every other rank's.
+int shard_share(sbb_layer *L, int which, size_t offset, size_t bytes, cudaStream_t st) {
+  auto &S = L->shard;
+  if (bytes == 0) return SBB_OK;
+  const char *src = static_cast<const char *>(S.peer[which][S.rank]) + offset;
+  sbb::PeerTable others{};
+  for (long r = 0; r < S.world; ++r)
+    if (r != S.rank) others.ptr[others.n++] = static_cast<char *>(S.peer[which][r]) + offset;
+  if (bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0)
+    SBB_CUDA(sbb::launch_peer_broadcast<uint4>(reinterpret_cast<const uint4 *>(src), (long)(bytes / 16), others, st));
+  else if (bytes % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 7u) == 0)
+    SBB_CUDA(sbb::launch_peer_broadcast<double>(reinterpret_cast<const double *>(src), (long)(bytes / 8), others, st));
+  else
+    SBB_CUDA(sbb::launch_peer_broadcast<float>(reinterpret_cast<const float *>(src), (long)(bytes / 4), others, st));
   return SBB_OK;
 }
 
@@ -1300,20 +1301,25 @@ int shard_mask(sbb_layer *L, long h, cudaStream_t st) {
 
 extern "C" {
 
-int sbb_layer_shard_init(sbb_layer *L, long rank, long world_size, unsigned char *handles_out) {
+int sbb_layer_shard_init(sbb_layer *L, long rank, long world_size, long max_local_batch, unsigned char *handles_out) {
   SBB_TRY(check_layer(L));
   ARG(handles_out, "shard_init: null pointer");
   ARG(world_size >= 1 && world_size <= 8 && rank >= 0 && rank < world_size, "shard_init: rank %ld of %ld (at most 8)",
       rank, world_size);
+  ARG(max_local_batch > 0, "shard_init: non-positive batch");
+  SBB_TRY(check_batch(L, max_local_batch * world_size));
   ARG(!L->shard.on, "shard_init: the layer is already sharded");
   auto &S = L->shard;
   const size_t s = esize(L->desc.dtype);
   const long tiles = (L->N + 127) / 128;
   S.rank = rank;
   S.world = world_size;
+  S.max_batch = max_local_batch;
   S.rows_per_rank = ((tiles + world_size - 1) / world_size) * 128;
-  SBB_TRY(S.stage.reserve((size_t)world_size * S.rows_per_rank * L->M * s));
-  SBB_TRY(S.vec.reserve((size_t)world_size * (L->N + L->M) * s));
+  // every rank allocates a full block's width, so that the buffers have one size everywhere
+  const size_t xg_bytes = (size_t)world_size * max_local_batch * S.rows_per_rank * s;
+  SBB_TRY(S.xg[0].reserve(xg_bytes));
+  SBB_TRY(S.xg[1].reserve(xg_bytes));
   if (L->score.d == nullptr) SBB_TRY(L->score.reserve(sbb::mask_scratch_bytes(L->N, s)));
   for (int b = 0; b < SBB_SHARD_BUFFERS; ++b)
     for (int r = 0; r < 8; ++r) {
@@ -1327,13 +1333,8 @@ int sbb_layer_shard_init(sbb_layer *L, long rank, long world_size, unsigned char
     static_assert(sizeof(hnd) == SBB_SHARD_HANDLE_BYTES, "IPC handle size");
     std::memcpy(handles_out + (size_t)b * SBB_SHARD_HANDLE_BYTES, &hnd, sizeof(hnd));
   }
-  if (const char *e = std::getenv("SBB_SHARD_TRANSPORT")) S.copy_engines = std::strcmp(e, "stores") != 0;
-  if (S.copy_engines && world_size > 1) {
-    SBB_TRY(S.outbox.reserve((size_t)L->N * L->M * s));
-    SBB_CUDA(cudaStreamCreateWithFlags(&S.copy_stream, cudaStreamNonBlocking));
-    for (int k = 0; k < 32; ++k) SBB_CUDA(cudaEventCreateWithFlags(&S.ev[k], cudaEventDisableTiming));
-    S.ev_created = true;
-  }
+  S.parity = 0;
+  S.batch = 0;
   S.on = true;
   S.attached = world_size == 1;
   return SBB_OK;
@@ -1359,23 +1360,39 @@ int sbb_layer_shard_attach(sbb_layer *L, const unsigned char *all_handles) {
   return SBB_OK;
 }
 
-int sbb_layer_shard_products(sbb_layer *L, const void *x_dev, const void *y_dev, long B_local, void *stream) {
+int sbb_layer_shard_scatter(sbb_layer *L, const void *x_dev, long B_local, void *stream) {
   SBB_TRY(check_shard(L, true));
-  ARG(x_dev && y_dev, "shard_products: null pointer");
-  SBB_TRY(check_batch(L, B_local));
+  ARG(x_dev, "shard_scatter: null pointer");
+  ARG(B_local > 0 && B_local <= L->shard.max_batch, "shard_scatter: local batch %ld outside [1, %ld] (sbb_layer_shard_init)",
+      B_local, L->shard.max_batch);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return DISPATCH(L->desc.dtype, shard_products<float>(L, (const float *)x_dev, (const float *)y_dev, B_local, st),
-                  shard_products<double>(L, (const double *)x_dev, (const double *)y_dev, B_local, st));
+  return DISPATCH(L->desc.dtype, shard_scatter<float>(L, (const float *)x_dev, B_local, st),
+                  shard_scatter<double>(L, (const double *)x_dev, B_local, st));
 }
 
-int sbb_layer_shard_apply(sbb_layer *L, long B_global, long hypercolumn, void *stream) {
-  SBB_TRY(check_shard(L, true));
-  ARG(B_global > 0, "shard_apply: non-positive global batch");
-  ARG(hypercolumn < L->H, "shard_apply: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
+int sbb_layer_shard_forward(sbb_layer *L, long B_local, void *support_dev, void *stream) {
+  SBB_TRY(check_shard_step(L, B_local, "shard_forward"));
+  ARG(support_dev, "shard_forward: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, shard_forward<float>(L, B_local, (float *)support_dev, st),
+                  shard_forward<double>(L, B_local, (double *)support_dev, st));
+}
+
+int sbb_layer_shard_activate(sbb_layer *L, long B_local, const void *support_dev, void *y_local_dev, void *stream) {
+  SBB_TRY(check_shard_step(L, B_local, "shard_activate"));
+  ARG(support_dev, "shard_activate: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return DISPATCH(L->desc.dtype, shard_activate<float>(L, B_local, (const float *)support_dev, (float *)y_local_dev, st),
+                  shard_activate<double>(L, B_local, (const double *)support_dev, (double *)y_local_dev, st));
+}
+
+int sbb_layer_shard_train(sbb_layer *L, long B_local, long hypercolumn, void *stream) {
+  SBB_TRY(check_shard_step(L, B_local, "shard_train"));
+  ARG(hypercolumn < L->H, "shard_train: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
   if (L->desc.kind != SBB_LAYER_PLASTIC) hypercolumn = -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return DISPATCH(L->desc.dtype, shard_apply<float>(L, B_global, hypercolumn, st),
-                  shard_apply<double>(L, B_global, hypercolumn, st));
+  return DISPATCH(L->desc.dtype, shard_train<float>(L, B_local, hypercolumn, st),
+                  shard_train<double>(L, B_local, hypercolumn, st));
 }
 
 int sbb_layer_shard_mask(sbb_layer *L, long hypercolumn, void *stream) {
@@ -1386,24 +1403,16 @@ int sbb_layer_shard_mask(sbb_layer *L, long hypercolumn, void *stream) {
   return DISPATCH(L->desc.dtype, shard_mask<float>(L, hypercolumn, st), shard_mask<double>(L, hypercolumn, st));
 }
 
-int sbb_layer_shard_share_traces(sbb_layer *L, void *stream) {
+int sbb_layer_shard_share_rows(sbb_layer *L, void *stream) {
   SBB_TRY(check_shard(L, true));
   auto &S = L->shard;
   const size_t s = esize(L->desc.dtype);
   const long rb = shard_begin(L, S.rank), re = shard_begin(L, S.rank + 1);
   if (re <= rb) return SBB_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t offset = (size_t)rb * L->M * s, bytes = (size_t)(re - rb) * L->M * s;
-  const char *src = static_cast<const char *>(L->state[SBB_STATE_CIJ]) + offset;
-  sbb::PeerTable others{};
-  for (long r = 0; r < S.world; ++r)
-    if (r != S.rank) others.ptr[others.n++] = static_cast<char *>(S.peer[kShardCij][r]) + offset;
-  if (bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0)
-    SBB_CUDA(sbb::launch_peer_broadcast<uint4>(reinterpret_cast<const uint4 *>(src), (long)(bytes / 16), others, st));
-  else if (L->desc.dtype == SBB_F32)
-    SBB_CUDA(sbb::launch_peer_broadcast<float>(reinterpret_cast<const float *>(src), (long)(bytes / 4), others, st));
-  else
-    SBB_CUDA(sbb::launch_peer_broadcast<double>(reinterpret_cast<const double *>(src), (long)(bytes / 8), others, st));
+  SBB_TRY(shard_share(L, kShardCij, (size_t)rb * L->M * s, (size_t)(re - rb) * L->M * s, st));
+  SBB_TRY(shard_share(L, kShardW, (size_t)rb * L->M * s, (size_t)(re - rb) * L->M * s, st));
+  SBB_TRY(shard_share(L, kShardCi, (size_t)rb * s, (size_t)(re - rb) * s, st));
   return SBB_OK;
 }
 

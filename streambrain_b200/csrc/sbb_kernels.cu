@@ -1662,12 +1662,13 @@ template cudaError_t launch_gather_rows<double>(const double *, const long *, lo
                                                 cudaStream_t);
 
 // ----------------------------------------------------------------------------
-// Row-sharded data parallelism over peer-mapped memory.  Every rank owns a block of
-// input rows of the trace matrix; ranks write their partial batch sums straight into
-// the owner's staging slots (one slot per source rank), the owner adds the slots in
-// rank order, updates its rows and writes the new weight rows into every rank's
-// weight matrix.  The pointer tables below hold, per destination rank, an address in
-// that rank's memory (the rank's own entry is a local address).
+// Row-sharded layer over peer-mapped memory.  Every rank owns a block of input rows of
+// the layer (those rows of the weights, of Cij and of Ci).  Per step the ranks exchange the
+// matching COLUMNS of their input batches, so that every owner holds its columns of the
+// whole global batch; each owner then forms its part of every sample's support, the parts
+// are summed across the ranks, and the owner updates its rows from the global batch.
+// The pointer tables below hold, per destination rank, an address in that rank's memory
+// (the rank's own entry is a local address).
 // ----------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) peer_broadcast_kernel(const T *__restrict__ src, long n, PeerTable dst) {
@@ -1687,117 +1688,61 @@ template cudaError_t launch_peer_broadcast<float>(const float *, long, const Pee
 template cudaError_t launch_peer_broadcast<double>(const double *, long, const PeerTable &, cudaStream_t);
 template cudaError_t launch_peer_broadcast<uint4>(const uint4 *, long, const PeerTable &, cudaStream_t);
 
-// c[i] = EMA(c[i], sum over slots s (in order) of slots[s * stride + offset + i])
-template <typename T>
-__global__ void vector_slots_ema_kernel(T *c, const T *__restrict__ slots, int nslots, long stride, long offset, long n,
-                                        TraceParams<T> p) {
-  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  T s = slots[offset + i];
-  for (int k = 1; k < nslots; ++k) s += slots[(long)k * stride + offset + i];
-  c[i] = trace_ema(c[i], s, p);
-}
-template <typename T>
-cudaError_t launch_vector_slots_ema(T *c, const T *slots, int nslots, long stride, long offset, long n,
-                                    TraceParams<T> p, cudaStream_t st) {
-  if (n == 0) return cudaSuccess;
-  vector_slots_ema_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(c, slots, nslots, stride, offset, n, p);
-  return launched();
-}
-template cudaError_t launch_vector_slots_ema<float>(float *, const float *, int, long, long, long, TraceParams<float>,
-                                                    cudaStream_t);
-template cudaError_t launch_vector_slots_ema<double>(double *, const double *, int, long, long, long,
-                                                     TraceParams<double>, cudaStream_t);
-
-// The element-wise tail of the trace step for the rows [row_begin, row_end) this rank owns: the batch sum of an
-// element is the sum of its `nslots` staging slots (slot s = rank s's part, rows counted from row_begin), the
-// new weight row goes to every rank's weight matrix.  Same thread layout as trace_apply_kernel.
-template <typename T, bool FAST>
+// Column block o of x[B, N] (columns [o * block, min(N, (o + 1) * block))) goes to rank o as a dense
+// [B, width_o] matrix at dst.ptr[o].  V = elements moved per thread (a 16-byte vector when the shapes allow).
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
-    shard_apply_kernel(const T *__restrict__ stage, int nslots, long slot_stride, long M, long H, long Mc,
-                       const T *__restrict__ Ci, const T *__restrict__ Cj, T *Cij, PeerTable wtab,
-                       const uint8_t *__restrict__ wmask, TraceParams<T> p, long row_begin, long row_end, bool vec) {
-  const long j = ((long)blockIdx.y * blockDim.x + threadIdx.x) * 4;
-  if (j >= M) return;
-  const long left = M - j;
-  const int valid = left >= 4 ? 4 : (int)left;
-  T cj[4];
-  bool col_on[4];
-  long hc[4];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    cj[c] = c < valid ? Cj[j + c] : (T)1;
-    col_on[c] = c < valid && !(cj[c] < p.cthr);
-    hc[c] = wmask ? (j + (c < valid ? c : 0)) / Mc : 0;
-    if (FAST) cj[c] = (T)1 / cj[c];
-  }
-  const T ema_scale = p.taupdt / p.batch;
-  const long r0 = row_begin + (long)blockIdx.x * kApplyRows;
-  const long r1 = r0 + kApplyRows < row_end ? r0 + kApplyRows : row_end;
-  for (long i = r0; i < r1; ++i) {
-    T ci = Ci[i];
-    const bool row_on = !(ci < p.cthr);
-    if (FAST) ci = (T)1 / ci;
-    bool on[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) on[c] = row_on && col_on[c] && (wmask == nullptr || wmask[i * H + hc[c]] != 0);
-    T c4[4], d4[4], w4[4];
-    load4(Cij + i * M + j, c4, vec, valid);
-    const T *srow = stage + (i - row_begin) * M + j;
-    load4(srow, d4, vec, valid);
-    for (int k = 1; k < nslots; ++k) {
-      T e4[4];
-      load4(srow + (long)k * slot_stride, e4, vec, valid);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) d4[c] += e4[c];
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      if (c < valid) {
-        T cij;
-        if constexpr (FAST) {
-          cij = trace_ema_fast(c4[c], d4[c], p.one_minus, ema_scale);
-          w4[c] = on[c] ? log_ratio_fast(cij, ci, cj[c], p.cthr4) : 0.f;
-        } else {
-          cij = trace_ema(c4[c], d4[c], p);
-          w4[c] = on[c] ? log_ratio(cij, ci, cj[c], p.cthr4) : (T)0;
-        }
-        c4[c] = cij;
-      }
-    }
-    store4(Cij + i * M + j, c4, vec, valid);
-    for (int d = 0; d < wtab.n; ++d) store4(static_cast<T *>(wtab.ptr[d]) + i * M + j, w4, vec, valid);
+    scatter_columns_kernel(const T *__restrict__ x, long B, long N, long block, PeerTable dst) {
+  struct alignas(sizeof(T) * V) Pack {
+    T v[V];
+  };
+  const long per_row = N / V;
+  const long total = B * per_row;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long)gridDim.x * blockDim.x) {
+    const long b = t / per_row;
+    const long c = (t - b * per_row) * V;
+    const long o = c / block;
+    const long first = o * block;
+    const long width = first + block <= N ? block : N - first;
+    const Pack v = *reinterpret_cast<const Pack *>(x + b * N + c);
+    *reinterpret_cast<Pack *>(static_cast<T *>(dst.ptr[o]) + b * width + (c - first)) = v;
   }
 }
 template <typename T>
-cudaError_t launch_shard_apply(const T *stage, int nslots, long slot_stride, long M, long H, long Mc, const T *Ci,
-                               const T *Cj, T *Cij, const PeerTable &wtab, const uint8_t *wmask, TraceParams<T> p,
-                               long row_begin, long row_end, cudaStream_t st, bool fast) {
+cudaError_t launch_scatter_columns(const T *x, long B, long N, long block, const PeerTable &dst, cudaStream_t st) {
+  if (B <= 0 || N <= 0) return cudaSuccess;
   constexpr int V = Vec16<T>::N;
-  if (row_end <= row_begin || M == 0) return cudaSuccess;
-  const long qpr = (M + 3) / 4;
-  bool vec = (M % V == 0) && aligned16(Cij) && aligned16(stage) && (slot_stride % V == 0);
-  for (int d = 0; d < wtab.n; ++d) vec = vec && aligned16(wtab.ptr[d]);
-  const long row_groups = (row_end - row_begin + kApplyRows - 1) / kApplyRows;
-  const int threads = qpr >= 256 ? 256 : (int)((qpr + 31) / 32 * 32);
-  const dim3 grid((unsigned)row_groups, (unsigned)((qpr + threads - 1) / threads));
-  if constexpr (std::is_same<T, float>::value) {
-    if (fast && p.cthr4 >= 1e-30f) {
-      shard_apply_kernel<float, true><<<grid, threads, 0, st>>>(stage, nslots, slot_stride, M, H, Mc, Ci, Cj, Cij, wtab,
-                                                                wmask, p, row_begin, row_end, vec);
-      return launched();
-    }
-  }
-  shard_apply_kernel<T, false><<<grid, threads, 0, st>>>(stage, nslots, slot_stride, M, H, Mc, Ci, Cj, Cij, wtab, wmask,
-                                                         p, row_begin, row_end, vec);
+  // a vector never straddles two owners when both N and the block width are multiples of V
+  bool vec = N % V == 0 && block % V == 0 && aligned16(x);
+  for (int d = 0; d < dst.n; ++d) vec = vec && aligned16(dst.ptr[d]);
+  const long total = vec ? B * (N / V) : B * N;
+  const long blocks = (total + 255) / 256;
+  const unsigned grid = (unsigned)(blocks < 2368 ? blocks : 2368);
+  if (vec) scatter_columns_kernel<T, V><<<grid, 256, 0, st>>>(x, B, N, block, dst);
+  else scatter_columns_kernel<T, 1><<<grid, 256, 0, st>>>(x, B, N, block, dst);
   return launched();
 }
-template cudaError_t launch_shard_apply<float>(const float *, int, long, long, long, long, const float *, const float *,
-                                               float *, const PeerTable &, const uint8_t *, TraceParams<float>, long,
-                                               long, cudaStream_t, bool);
-template cudaError_t launch_shard_apply<double>(const double *, int, long, long, long, long, const double *,
-                                                const double *, double *, const PeerTable &, const uint8_t *,
-                                                TraceParams<double>, long, long, cudaStream_t, bool);
+template cudaError_t launch_scatter_columns<float>(const float *, long, long, long, const PeerTable &, cudaStream_t);
+template cudaError_t launch_scatter_columns<double>(const double *, long, long, long, const PeerTable &, cudaStream_t);
+
+// out[i] = sum over s (in order) of partial[s * n + i]
+template <typename T>
+__global__ void __launch_bounds__(256) sum_partials_kernel(const T *__restrict__ partial, int splits, long n, T *out) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    T s = partial[i];
+    for (int k = 1; k < splits; ++k) s += partial[(long)k * n + i];
+    out[i] = s;
+  }
+}
+template <typename T>
+cudaError_t launch_sum_partials(const T *partial, int splits, long n, T *out, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  const long blocks = (n + 255) / 256;
+  sum_partials_kernel<T><<<(unsigned)(blocks < 2368 ? blocks : 2368), 256, 0, st>>>(partial, splits, n, out);
+  return launched();
+}
+template cudaError_t launch_sum_partials<float>(const float *, int, long, float *, cudaStream_t);
+template cudaError_t launch_sum_partials<double>(const double *, int, long, double *, cudaStream_t);
 
 // Mask scores of the rows [row_begin, row_end) this rank owns, written into every rank's work arrays
 // (scratch_tab: base of each rank's mask scratch, laid out for N rows).

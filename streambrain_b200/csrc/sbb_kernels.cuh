@@ -106,7 +106,7 @@ template <typename T>
 cudaError_t launch_mask_select(uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr, long N, long M, long H,
                                long Mc, long h, long iterations, void *scratch, cudaStream_t st, T *rewrite_w);
 
-// Row-sharded data parallelism over peer-mapped memory (see sbb_kernels.cu): one address per destination rank.
+// Row-sharded layer over peer-mapped memory (see sbb_kernels.cu): one address per destination rank.
 constexpr int kMaxPeers = 8;
 struct PeerTable {
   void *ptr[kMaxPeers];
@@ -114,13 +114,12 @@ struct PeerTable {
 };
 template <typename T>
 cudaError_t launch_peer_broadcast(const T *src, long n, const PeerTable &dst, cudaStream_t st);
+// Column block o (of width `block`, the last one clipped to N) of x[B, N] -> dense [B, width_o] matrix at dst.ptr[o].
 template <typename T>
-cudaError_t launch_vector_slots_ema(T *c, const T *slots, int nslots, long stride, long offset, long n,
-                                    TraceParams<T> p, cudaStream_t st);
+cudaError_t launch_scatter_columns(const T *x, long B, long N, long block, const PeerTable &dst, cudaStream_t st);
+// out[i] = sum_s partial[s * n + i]
 template <typename T>
-cudaError_t launch_shard_apply(const T *stage, int nslots, long slot_stride, long M, long H, long Mc, const T *Ci,
-                               const T *Cj, T *Cij, const PeerTable &wtab, const uint8_t *wmask, TraceParams<T> p,
-                               long row_begin, long row_end, cudaStream_t st, bool fast);
+cudaError_t launch_sum_partials(const T *partial, int splits, long n, T *out, cudaStream_t st);
 template <typename T>
 cudaError_t launch_mask_score_rows(const uint8_t *wmask, const T *Ci, const T *Cj, const T *Cij, T cthr, long N, long M,
                                    long H, long Mc, long h, long row_begin, long row_end, const PeerTable &scratch_tab,

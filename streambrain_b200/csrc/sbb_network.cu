@@ -105,6 +105,7 @@ struct sbb_network {
   DeviceBuffer delta;              // data-parallel batch sums of the layer being trained
   DeviceBuffer hits;               // evaluation counter
   DeviceBuffer token;              // one float: the barrier of the row-sharded step
+  DeviceBuffer support;            // row-sharded step: supports of the global batch, summed over the ranks in place
   cudaStream_t stream = nullptr;
   size_t esize() const { return dtype == SBB_F32 ? 4 : 8; }
   long out_features(size_t k) const { return desc[k].hypercolumns * desc[k].minicolumns; }
@@ -168,32 +169,48 @@ int forward_through(sbb_network *net, const void *x, long count, size_t upto, co
   return SBB_OK;
 }
 
+// A one-element reduction on the network's stream: orders the stream after every rank's earlier work.
+int rank_barrier(sbb_network *net) {
+  NET_TRY(net->token.reserve(sizeof(float)));
+  const long t = net->comm.reduce_begin(net->comm.user, net->token.d, 1, SBB_F32, net->stream);
+  if (t < 0 || net->comm.reduce_wait(net->comm.user, t, net->stream) != 0)
+    return net_fail(SBB_ERR_INVALID, "the reduction callback failed (barrier of the row-sharded step)");
+  return SBB_OK;
+}
+
+bool row_sharded(const sbb_network *net, const sbb_layer *layer) {
+  return net->have_comm && net->world > 0 && sbb_layer_shard_world(layer) == net->world;
+}
+
+// Forward + train step of an unsupervised, row-sharded layer on this rank's `count` samples of the global batch;
+// the rank's activations land in `y`.
+int sharded_step(sbb_network *net, sbb_layer *layer, const sbb_layer_desc &d, const void *x, void *y, long count,
+                 long hypercolumn) {
+  const long M = d.hypercolumns * d.minicolumns;
+  const size_t elems = (size_t)count * net->world * M;
+  NET_TRY(net->support.reserve(elems * net->esize()));
+  NET_TRY(sbb_layer_shard_scatter(layer, x, count, net->stream));
+  NET_TRY(rank_barrier(net));
+  NET_TRY(sbb_layer_shard_forward(layer, count, net->support.d, net->stream));
+  const long t = net->comm.reduce_begin(net->comm.user, net->support.d, elems, net->dtype, net->stream);
+  if (t < 0 || net->comm.reduce_wait(net->comm.user, t, net->stream) != 0)
+    return net_fail(SBB_ERR_INVALID, "the reduction callback failed (supports of the row-sharded step)");
+  NET_TRY(sbb_layer_shard_activate(layer, count, net->support.d, y, net->stream));
+  const bool mask = hypercolumn >= 0 && d.kind == SBB_LAYER_PLASTIC;
+  NET_TRY(sbb_layer_shard_train(layer, count, mask ? hypercolumn : -1, net->stream));
+  if (mask) {
+    NET_TRY(rank_barrier(net));
+    NET_TRY(sbb_layer_shard_mask(layer, hypercolumn, net->stream));
+  }
+  return SBB_OK;
+}
+
 // One data-parallel train step of `layer`: the reduction of one row block of x^T y runs beside the product of
 // the next (BCPNN/backend/_kernels/kernels_mpi_internal.cc:100-161 with the Allreduce pipelined by rows).
 int dp_train_step(sbb_network *net, sbb_layer *layer, const sbb_layer_desc &d, const void *x, const void *y,
                   long count, long hypercolumn) {
   const long N = d.in_features, M = d.hypercolumns * d.minicolumns;
   const size_t s = net->esize();
-  if (sbb_layer_shard_world(layer) == net->world && net->world > 0) {
-    // Row-sharded step: partial sums go straight to the rows' owners; a one-element reduction on the step's
-    // stream is the barrier between its phases (it orders this stream after every rank's earlier work).
-    NET_TRY(net->token.reserve(sizeof(float)));
-    auto barrier = [&]() -> int {
-      const long t = net->comm.reduce_begin(net->comm.user, net->token.d, 1, SBB_F32, net->stream);
-      if (t < 0 || net->comm.reduce_wait(net->comm.user, t, net->stream) != 0)
-        return net_fail(SBB_ERR_INVALID, "the reduction callback failed (barrier of the row-sharded step)");
-      return SBB_OK;
-    };
-    NET_TRY(sbb_layer_shard_products(layer, x, y, count, net->stream));
-    NET_TRY(barrier());
-    NET_TRY(sbb_layer_shard_apply(layer, count * net->world, hypercolumn, net->stream));
-    NET_TRY(barrier());
-    if (hypercolumn >= 0 && d.kind == SBB_LAYER_PLASTIC) {
-      NET_TRY(sbb_layer_shard_mask(layer, hypercolumn, net->stream));
-      NET_TRY(barrier());
-    }
-    return SBB_OK;
-  }
   NET_TRY(net->delta.reserve(sbb_layer_delta_elems(layer) * s));
   char *delta = static_cast<char *>(net->delta.d);
   const auto blocks = row_blocks(N, 4);
@@ -275,6 +292,7 @@ int sbb_network_destroy(sbb_network *net) {
   net->delta.release();
   net->hits.release();
   net->token.release();
+  net->support.release();
   for (auto &a : net->act) a.release();
   if (net->stream) cudaStreamDestroy(net->stream);
   delete net;
@@ -369,6 +387,8 @@ int sbb_network_train_batches(sbb_network *net, long layer_index, long maximal_b
                         hypercolumn_order_host[k], H);
   }
   const bool dp = net->have_comm;   // with callbacks the split step runs even for one rank (a sum over one)
+  // a layer that learns from its own activations and is sharded over the ranks takes the row-sharded step
+  const bool sharded = !last && row_sharded(net, net->layers[li]);
   if (batch_begin == 0) NET_CUDA(cudaDeviceSynchronize());   // state written through other streams has landed
   for (long i = batch_begin; i < batch_end; ++i) {
     long first = 0, count = 0, slot = -1;
@@ -377,13 +397,27 @@ int sbb_network_train_batches(sbb_network *net, long layer_index, long maximal_b
     if (count <= 0) continue;
     const void *x = nullptr, *t = nullptr, *in_last = nullptr, *out_last = nullptr;
     NET_TRY(assemble(net, first, count, true, last, &x, &t));
-    NET_TRY(forward_through(net, x, count, li, &in_last, &out_last));
     const long h = slot >= 0 ? hypercolumn_order_host[slot] : -1;
+    if (sharded) {   // the layer's own forward pass is part of its sharded step
+      in_last = x;
+      if (li > 0) {
+        const void *unused = nullptr;
+        NET_TRY(forward_through(net, x, count, li - 1, &unused, &in_last));
+      }
+      NET_TRY(net->act[li].reserve((size_t)count * net->out_features(li) * net->esize()));
+      NET_TRY(sharded_step(net, net->layers[li], net->desc[li], in_last, net->act[li].d, count, h));
+      continue;
+    }
+    NET_TRY(forward_through(net, x, count, li, &in_last, &out_last));
     const void *target = last ? t : out_last;
     if (dp) NET_TRY(dp_train_step(net, net->layers[li], net->desc[li], in_last, target, count, last ? -1 : h));
     else NET_TRY(sbb_layer_train_step(net->layers[li], in_last, target, count, last ? -1 : h, net->stream));
   }
   if (batch_end == nb) {
+    if (sharded) {   // every rank gets the whole layer: the plain forward pass and checkpoints need it
+      NET_TRY(sbb_layer_shard_share_rows(net->layers[li], net->stream));
+      NET_TRY(rank_barrier(net));
+    }
     NET_TRY(sbb_layer_train_finalize(net->layers[li], net->stream));
     return sbb_stream_sync(net->stream);   // one wait per epoch; also surfaces a device-side wait that gave up
   }

@@ -49,9 +49,8 @@ def _batches(world, steps):
     return [rs.rand(world * B_LOCAL, N).astype(np.float32) for _ in range(steps)]
 
 
-def _worker(rank, world, port, path, out_dir, sharded=False, transport="copy_engines"):
+def _worker(rank, world, port, path, out_dir, sharded=False):
     sys.path.insert(0, REPO)
-    os.environ["SBB_SHARD_TRANSPORT"] = transport
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     if os.environ.get("SBB_TEST_NVLS", "0") != "1":   # SBB_TEST_NVLS=1 leaves NCCL's NVLink-switch reductions on
@@ -63,15 +62,17 @@ def _worker(rank, world, port, path, out_dir, sharded=False, transport="copy_eng
     from streambrain_b200 import parallel
     layer = _make_layer(B200, path)
     if sharded:
-        layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist))
+        layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist), B_LOCAL)
     steps = 2
+    all_reduce = lambda t: dist.all_reduce(t, async_op=True)
     for k, xb in enumerate(_batches(world, steps)):
         x = torch.from_numpy(xb[rank * B_LOCAL:(rank + 1) * B_LOCAL]).cuda()
-        y = layer.compute_activation(x)
-        layer.dp_train_step(x, y, (2 + k) % H, world, lambda t: dist.all_reduce(t, async_op=True), row_blocks=3)
-        if sharded:   # every rank holds only its own rows of Cij until they are shared
-            token = torch.zeros(1, device="cuda")
-            layer.share_traces(lambda: dist.all_reduce(token))
+        if sharded:   # forward + train in one; a rank holds only its own rows until they are shared
+            layer.sharded_step(x, (2 + k) % H, all_reduce)
+            layer.share_rows(all_reduce)
+        else:
+            y = layer.compute_activation(x)
+            layer.dp_train_step(x, y, (2 + k) % H, world, all_reduce, row_blocks=3)
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, "rank%d_step%d.npz" % (rank, k)), Ci=layer.Ci, Cj=layer.Cj, Cij=layer.Cij,
                  weights=layer.weights, bias=layer.bias, wmask=layer.wmask)
@@ -79,13 +80,12 @@ def _worker(rank, world, port, path, out_dir, sharded=False, transport="copy_eng
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["copy_engines", "stores"])
 @pytest.mark.parametrize("path", ["general", "tensor"])
-def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path, transport):
-    """The row-sharded step (partial sums delivered into the owner's memory over NVLink -- by copy engines beside
-    the product kernels, or by the product kernels' own stores -- each row updated once by its owner, weight
-    rows delivered to every rank) against the all-reduce step on the same two GPUs: the same sums added in the
-    same rank order give the same traces, weights and masks."""
+def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path):
+    """The row-sharded step (every rank owns half of the input rows: the ranks exchange the matching columns of
+    their batches over NVLink, sum their parts of the supports, and each updates its own rows from the whole
+    global batch) against the all-reduce step on the same two GPUs: the same traces, weights and masks to
+    summation-order rounding."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -94,7 +94,7 @@ def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path, transpor
     a.mkdir()
     b.mkdir()
     mp.spawn(_worker, args=(world, _free_port(), path, str(a), False), nprocs=world, join=True)
-    mp.spawn(_worker, args=(world, _free_port(), path, str(b), True, transport), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), path, str(b), True), nprocs=world, join=True)
     tol = TOL[np.dtype(np.float32)]
     for k in range(2):
         s0 = np.load(b / ("rank0_step%d.npz" % k))
@@ -184,10 +184,8 @@ def _net_worker(rank, world, port, out_dir, sharded):
     net.fit(x[:n_train], lab[:n_train], B, [(0, 3)])
     net.fit(x[:n_train], lab[:n_train], B, [(1, 2)])
     correct, total = net.evaluate(x[n_train:], lab[n_train:], B)
-    if sharded:
-        token = torch.zeros(1, device="cuda")
-        for layer in net._layers:
-            layer.share_traces(lambda: dist.all_reduce(token))
+    if sharded:   # the hidden layer was sharded by fit, which shares its rows at the end of every epoch
+        assert net._layers[0]._shard == (rank, world) and getattr(net._layers[1], "_shard", None) is None
     torch.cuda.synchronize()
     out = {"correct": correct, "total": total, "wmask": net._layers[0].wmask}
     for li, layer in enumerate(net._layers):

@@ -406,28 +406,35 @@ def test_data_parallel_split_step_equals_single_step(B200):
 
 @pytest.mark.parametrize("tag,dtype", DTYPES)
 def test_row_sharded_step_on_one_rank_equals_single_step(B200, tag, dtype):
-    """The row-sharded data-parallel step with a world of one rank (its staging slot, vector slot and weight
-    matrix are all local) runs every kernel of the sharded path and must reproduce the fused step."""
+    """The row-sharded step with a world of one rank (it owns every row; the scatter, the partial forward
+    product, the activation and the row-block update all run locally) must reproduce forward + fused step."""
     import torch
     g = load_golden("layer_%s.npz" % tag)
     B = int(g["B"])
     x = torch.from_numpy(np.ascontiguousarray(g["x"][:B])).cuda()
     single, _ = _layers_from_golden(B200, g, dtype)
     sharded, _ = _layers_from_golden(B200, g, dtype)
-    sharded.shard_rows(0, 1, lambda blob: [blob])
+    sharded.shard_rows(0, 1, lambda blob: [blob], B)
     assert sharded.owned_rows() == (0, sharded.in_features)
     tol = TOL[np.dtype(dtype)]
+    done = type("Done", (), {"wait": lambda self: None})
     for h in (2, None, 0):
         y = single.compute_activation(x)
         single.train_step(x, y, h)
-        sharded.dp_train_step(x, y, h, 1, lambda t: type("Done", (), {"wait": lambda self: None})())
+        ys = sharded.sharded_step(x, h, lambda t: done())
         torch.cuda.synchronize()
+        assert rel_inf(ys.cpu().numpy(), y.cpu().numpy() if hasattr(y, "cpu") else y) < tol, h
         assert np.array_equal(sharded.wmask, single.wmask), h
         for name in ("Ci", "Cj", "Cij", "bias", "kbi"):
             assert rel_inf(getattr(sharded, name), getattr(single, name)) < tol, (h, name)
         assert weight_err(sharded.weights, single.weights) < 10 * tol, h
         for name in PLASTIC_STATE:          # both continue from the same state
             setattr(sharded, name, getattr(single, name))
+    with pytest.raises(Exception):          # the plain data-parallel step refuses a sharded layer
+        sharded.dp_train_step(x, y, None, 1, lambda t: done())
+    big = torch.zeros((B + 1, sharded.in_features), dtype=x.dtype, device="cuda")
+    with pytest.raises(Exception):          # more samples than the gathered-input buffers were sized for
+        sharded.sharded_step(big, None, lambda t: done())
 
 
 def test_stl10_shaped_layer_full_size_properties(B200, port_kernels):
