@@ -519,8 +519,9 @@ def run_b200(args, wl, p, batch):
     def step(k):
         x, y = xs[k % POOL], ys[k % 2]
         h = (k % H) if mask else None
-        if shard_step:   # forward + train in one: the layer's rows are spread over the ranks
-            layer.sharded_step(x, h, all_reduce, out=y)
+        if shard_step:   # forward + train in one: the layer's rows are spread over the ranks; the next batch's
+            # exchange is staged beside this step
+            layer.sharded_step(x, h, all_reduce, out=y, next_inputs=xs[(k + 1) % POOL])
             return
         check(lib.sbb_layer_forward(layer._handle, x.data_ptr(), batch, y.data_ptr(), stream))
         if dp_path:
@@ -549,6 +550,8 @@ def run_b200(args, wl, p, batch):
     barrier()
     elapsed_ms = ev0.elapsed_time(ev1)
     launches = int(lib.sbb_kernel_launches()) - launches0
+    if shard_step:
+        layer.drop_staged()   # the batch staged by the last timed step is not consumed
     clocks = sampler.stop() if sampler else None
     if world > 1:
         t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
@@ -601,7 +604,7 @@ def run_b200(args, wl, p, batch):
             x = xl[k % 2]
             h = (k % H) if mask else None
             if shard_step:
-                big.sharded_step(x, h, all_reduce, out=yl)
+                big.sharded_step(x, h, all_reduce, out=yl, next_inputs=xl[(k + 1) % 2])
                 return
             check(lib.sbb_layer_forward(big._handle, x.data_ptr(), bl, yl.data_ptr(), stream))
             if dp_path:
@@ -672,27 +675,47 @@ def run_b200(args, wl, p, batch):
         # between barriers, maximum over ranks.
         pinned = [torch.from_numpy(x).pin_memory() for x in xs_host[:4]]
         y_host = [torch.empty((batch, M), dtype=xs[0].dtype).pin_memory() for _ in range(2)]
-        x_dev = [torch.empty((batch, N), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
+        x_dev = [torch.empty((batch, N), dtype=xs[0].dtype, device="cuda") for _ in range(3 if shard_step else 2)]
         y_dev = [torch.empty((batch, M), dtype=xs[0].dtype, device="cuda") for _ in range(2)]
         copy_stream = torch.cuda.Stream()
         compute = torch.cuda.current_stream()
-        landed = [torch.cuda.Event() for _ in range(2)]
-        used = [torch.cuda.Event() for _ in range(2)]
+        landed = [torch.cuda.Event() for _ in range(3)]
+        used = [torch.cuda.Event() for _ in range(3)]
+
+        def upload(k):
+            slot = k % 3
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(used[slot])          # the exchange that last read this slot has run
+                x_dev[slot].copy_(pinned[k % 4], non_blocking=True)
+                landed[slot].record(copy_stream)
+
+        def sharded_host_step(k):
+            # batch k + 1 is uploaded and exchanged while step k computes; batch k was staged by step k - 1
+            upload(k + 1)
+            layer.sharded_step(x_dev[k % 3], (k % H) if mask else None, all_reduce, out=y_dev[k % 2],
+                               next_inputs=x_dev[(k + 1) % 3], next_ready=landed[(k + 1) % 3])
+            used[(k + 1) % 3] = layer.staged_event
+            if k == 0:   # the first batch was exchanged on the compute stream by this very call
+                used[0] = torch.cuda.Event()
+                used[0].record(compute)
+            y_host[k % 2].copy_(y_dev[k % 2], non_blocking=True)
 
         def host_step(k):
+            if shard_step:
+                return sharded_host_step(k)
             slot = k % 2
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(used[slot])          # the step that last read this slot has finished
                 x_dev[slot].copy_(pinned[k % 4], non_blocking=True)
                 landed[slot].record(copy_stream)
             compute.wait_event(landed[slot])
-            if shard_step:
-                layer.sharded_step(x_dev[slot], (k % H) if mask else None, all_reduce, out=y_dev[slot])
-            else:
-                check(lib.sbb_layer_forward(layer._handle, x_dev[slot].data_ptr(), batch, y_dev[slot].data_ptr(), stream))
-                layer.dp_train_step(x_dev[slot], y_dev[slot], (k % H) if mask else None, world, all_reduce)
+            check(lib.sbb_layer_forward(layer._handle, x_dev[slot].data_ptr(), batch, y_dev[slot].data_ptr(), stream))
+            layer.dp_train_step(x_dev[slot], y_dev[slot], (k % H) if mask else None, world, all_reduce)
             y_host[slot].copy_(y_dev[slot], non_blocking=True)
             used[slot].record(compute)
+        if shard_step:   # the first step's batch is not staged by a step before it
+            upload(0)
+            compute.wait_event(landed[0])
         for k in range(3):
             host_step(k)
         barrier()
@@ -709,6 +732,8 @@ def run_b200(args, wl, p, batch):
                "call": ("sharded_step" if shard_step else "compute_activation + dp_train_step") +
                        " on device tensors, per-rank batch slice uploaded from pinned host memory on a copy stream"}
 
+    if shard_step:
+        layer.drop_staged()
     dp_checks = None
     if world > 1:
         dp_checks = data_parallel_checks(B200, lib, check, torch, dist, layer, world, rank, all_reduce, sharded)

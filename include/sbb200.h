@@ -238,12 +238,23 @@ int sbb_layer_dp_finish(sbb_layer *layer, long hypercolumn, void *stream);
  * (world_size-1)/world_size * B*N elements cross NVLink on the way out plus the
  * all-reduce of the supports, instead of two passes over an N x M matrix, and every
  * rank does 1/world_size of the global step's arithmetic and memory traffic.
- * Between barriers no kernel waits on another rank.  While a layer is sharded a rank
+ * Between barriers no kernel waits on another rank.
+ * Staging ahead.  The gathered inputs live in three buffers used in turn, so a rank may scatter
+ * batch t+1 while step t is still running: sbb_layer_shard_scatter stages a batch (at most two
+ * staged at a time) and sbb_layer_shard_forward takes the oldest staged one.  The rules that keep
+ * this free of races: (i) a rank starts the scatter of batch t+1 only after the all-reduce of step
+ * t-1's supports has completed on its stream (every rank entered it, so every rank has finished
+ * step t-2, the last reader of the buffer being refilled); (ii) between every rank's scatter of
+ * batch t+1 and any rank's forward pass on it lies a collective that each rank enters after its
+ * own scatter has completed -- the all-reduce of step t's supports serves when the scatter ran on
+ * a side stream that `stream` waited for before that all-reduce, and then step t+1 needs no
+ * barrier of its own; the first step of a run uses the explicit barrier of point 1.
+ * While a layer is sharded a rank
  * holds current values only for its own rows of the weights, Cij and Ci;
  * sbb_layer_shard_share_rows copies them to all ranks (then a barrier) when the whole
  * layer is wanted everywhere: the plain forward pass, checkpoints, tests.
  * ---------------------------------------------------------------------- */
-#define SBB_SHARD_BUFFERS 6        /* two gathered-input buffers, mask work arrays, weights, Cij, Ci */
+#define SBB_SHARD_BUFFERS 7        /* three gathered-input buffers, mask work arrays, weights, Cij, Ci */
 #define SBB_SHARD_HANDLE_BYTES 64  /* one CUDA IPC memory handle */
 /* Allocates the gathered-input buffers for local batches of up to max_local_batch samples and writes
  * this rank's SBB_SHARD_BUFFERS IPC handles to handles_out (SBB_SHARD_BUFFERS * SBB_SHARD_HANDLE_BYTES
@@ -252,9 +263,11 @@ int sbb_layer_shard_init(sbb_layer *layer, long rank, long world_size, long max_
                          unsigned char *handles_out);
 /* all_handles: the handles of ranks 0..world_size-1, concatenated in rank order. */
 int sbb_layer_shard_attach(sbb_layer *layer, const unsigned char *all_handles);
-/* x_dev: this rank's [B_local, in_features] slice of the global batch; every rank passes the same B_local. */
+/* Stages x_dev, this rank's [B_local, in_features] slice of a global batch, for the oldest step not yet
+ * started; every rank passes the same B_local and makes the same sequence of calls. */
 int sbb_layer_shard_scatter(sbb_layer *layer, const void *x_dev, long B_local, void *stream);
-/* support_dev: [world_size * B_local, M] REALs, written in full (the caller then sums it over the ranks). */
+/* Starts the step on the oldest staged batch.  support_dev: [world_size * B_local, M] REALs, written in
+ * full (the caller then sums it over the ranks). */
 int sbb_layer_shard_forward(sbb_layer *layer, long B_local, void *support_dev, void *stream);
 /* support_dev: the summed supports; y_local_dev: NULL or [B_local, M] for this rank's activations. */
 int sbb_layer_shard_activate(sbb_layer *layer, long B_local, const void *support_dev, void *y_local_dev,
@@ -262,6 +275,8 @@ int sbb_layer_shard_activate(sbb_layer *layer, long B_local, const void *support
 int sbb_layer_shard_train(sbb_layer *layer, long B_local, long hypercolumn, void *stream);
 int sbb_layer_shard_mask(sbb_layer *layer, long hypercolumn, void *stream);
 int sbb_layer_shard_share_rows(sbb_layer *layer, void *stream);
+/* Forgets the batches that are staged but that no step will consume (every rank alike; host state only). */
+int sbb_layer_shard_drop_staged(sbb_layer *layer);
 /* Number of ranks the layer is sharded over (peers attached), 0 if it is not. */
 long sbb_layer_shard_world(const sbb_layer *layer);
 /* Input rows [row_begin, row_end) of the layer that `rank` owns. */

@@ -21,7 +21,7 @@ ERR_NAMES = {1: "SBB_ERR_INVALID", 2: "SBB_ERR_CUDA", 3: "SBB_ERR_NO_DEVICE", 4:
              5: "SBB_ERR_TIMEOUT"}
 ERR_INVALID, ERR_CUDA, ERR_NO_DEVICE, ERR_UNSUPPORTED, ERR_TIMEOUT = 1, 2, 3, 4, 5
 F32, F64 = 0, 1
-SHARD_BUFFERS, SHARD_HANDLE_BYTES = 6, 64
+SHARD_BUFFERS, SHARD_HANDLE_BYTES = 7, 64
 DENSE, PLASTIC = 0, 1
 STATE = {"weights": 0, "bias": 1, "Ci": 2, "Cj": 3, "Cij": 4, "kbi": 5, "wmask": 6}
 
@@ -101,6 +101,7 @@ SIGNATURES = {
     "sbb_layer_shard_train": (c_int, [c_void_p, c_long, c_long, c_void_p]),
     "sbb_layer_shard_mask": (c_int, [c_void_p, c_long, c_void_p]),
     "sbb_layer_shard_share_rows": (c_int, [c_void_p, c_void_p]),
+    "sbb_layer_shard_drop_staged": (c_int, [c_void_p]),
     "sbb_layer_shard_world": (c_long, [c_void_p]),
     "sbb_layer_shard_rows": (c_int, [c_void_p, c_long, POINTER(c_long), POINTER(c_long)]),
     "sbb_count_correct": (c_int, [c_int, c_void_p, c_void_p, c_long, c_long, POINTER(c_long), c_void_p]),

@@ -266,13 +266,20 @@ class _DeviceLayer:
             self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
         return self._token
 
-    def sharded_step(self, inputs, hypercolumn, all_reduce, out=None, train=True):
+    def sharded_step(self, inputs, hypercolumn, all_reduce, out=None, train=True, next_inputs=None, next_ready=None):
         """Forward pass + train step of an unsupervised layer, row-sharded over the ranks: ``inputs`` is
         this rank's slice of the global batch (the same number of samples on every rank), the return
         value its activations.  ``all_reduce(tensor)`` as in :meth:`dp_train_step`; it sums the supports
         of the global batch and, on a one-element token, serves as the barrier between ranks.  The
         result on every rank's rows equals the single-GPU step at the global batch.  With
-        ``train=False`` only the forward pass runs.  See ``sbb_layer_shard_*`` in the C header."""
+        ``train=False`` only the forward pass runs.
+
+        ``next_inputs`` (a device tensor, the slice of the batch the NEXT call will pass as ``inputs``)
+        stages that batch ahead: its exchange runs on a side stream beside this step's forward product and
+        the step's own all-reduce doubles as its barrier, so the next step starts without one.  The side
+        stream waits for the work queued on the current stream so far and for ``next_ready`` (an event,
+        e.g. the upload of that batch); :attr:`staged_event` fires when the exchange has read
+        ``next_inputs``.  Every rank must make the same choice.  See ``sbb_layer_shard_*`` in the C header for the protocol."""
         x = self._dev_input(inputs, self.in_features)
         st = _stream_ptr()
         B = x.shape[0]
@@ -283,9 +290,33 @@ class _DeviceLayer:
         if out is None:
             out = torch.empty((B, self.out_features), dtype=_torch_dtype(self.dtype), device="cuda")
         token = self._barrier_token()
-        check(lib.sbb_layer_shard_scatter(self._handle, x.data_ptr(), B, st))
-        all_reduce(token).wait()
+        staged = getattr(self, "_staged", None)
+        if staged is None:
+            check(lib.sbb_layer_shard_scatter(self._handle, x.data_ptr(), B, st))
+            all_reduce(token).wait()
+        elif staged[0].data_ptr() != x.data_ptr() or staged[0].shape[0] != B:
+            raise ValueError("the previous sharded_step staged another batch as next_inputs; pass that batch, or "
+                             "call drop_staged() on every rank")
+        self._staged = None
+        main = torch.cuda.current_stream()
+        staged_event = None
+        if next_inputs is not None:
+            xn = self._dev_input(next_inputs, self.in_features)
+            if getattr(self, "_side", None) is None:
+                self._side = torch.cuda.Stream()
+            # the previous step has finished on this rank (so every rank is past the step before it) ...
+            self._side.wait_stream(main)
+            if next_ready is not None:
+                self._side.wait_event(next_ready)
+            with torch.cuda.stream(self._side):
+                check(lib.sbb_layer_shard_scatter(self._handle, xn.data_ptr(), xn.shape[0], _stream_ptr()))
+                staged_event = torch.cuda.Event()
+                staged_event.record(self._side)
+            self._staged = (xn,)
+            self.staged_event = staged_event
         check(lib.sbb_layer_shard_forward(self._handle, B, self._support.data_ptr(), st))
+        if staged_event is not None:   # ... and this step's all-reduce certifies that every rank's exchange is complete
+            main.wait_event(staged_event)
         all_reduce(self._support).wait()
         check(lib.sbb_layer_shard_activate(self._handle, B, self._support.data_ptr(), out.data_ptr(), st))
         if train:
@@ -295,6 +326,13 @@ class _DeviceLayer:
                 all_reduce(token).wait()
                 check(lib.sbb_layer_shard_mask(self._handle, h, st))
         return out
+
+    def drop_staged(self):
+        """Forget a batch staged by ``next_inputs`` that no step will consume (every rank alike)."""
+        if getattr(self, "_staged", None) is not None:
+            self._side.synchronize()
+            check(lib.sbb_layer_shard_drop_staged(self._handle))
+            self._staged = None
 
     def share_rows(self, all_reduce):
         """While a layer is sharded a rank holds current weights, Cij and Ci only for the rows it owns;

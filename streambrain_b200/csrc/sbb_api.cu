@@ -192,11 +192,13 @@ struct sbb_layer {
     long rows_per_rank = 0;            // multiple of 128; rank r owns rows [r * rows_per_rank, ...) clipped to N
     long max_batch = 0;                // largest local batch the gathered-input buffers hold
     // The own columns of the global batch, [world * B, own rows] with rank s's samples at rows [s * B, (s + 1) * B).
-    // Two buffers used in turn: a fast rank may already scatter step t + 1 while a slow one still reads step t
-    // (the barrier of step t + 1 is what stops it from reaching step t + 2).
-    Scratch xg[2];
-    int parity = 0;                    // buffer of the step in flight
-    long batch = 0;                    // local batch of the step in flight (0: no scatter yet)
+    // Three buffers used in turn: while this rank's step t reads one, the peers may already fill the next with
+    // batch t + 1, and a peer that is still inside step t - 1 reads the third.
+    Scratch xg[3];
+    int cur = 0;                       // buffer of the step in flight
+    int staged = 0;                    // batches scattered but not yet taken by a forward pass (0..2)
+    long slot_batch[3] = {0, 0, 0};    // local batch each buffer was filled with
+    long batch = 0;                    // local batch of the step in flight (0: no forward pass yet)
     Scratch yg;                        // activations of the global batch, [world * B, M]
     void *peer[SBB_SHARD_BUFFERS][8];  // per buffer kind and rank: that rank's buffer, mapped here (own rank: local)
     bool opened[SBB_SHARD_BUFFERS][8];
@@ -783,8 +785,7 @@ int sbb_layer_destroy(sbb_layer *L) {
     for (int b = 0; b < SBB_SHARD_BUFFERS; ++b)
       for (int r = 0; r < 8; ++r)
         if (L->shard.opened[b][r]) cudaIpcCloseMemHandle(L->shard.peer[b][r]);
-    L->shard.xg[0].release();
-    L->shard.xg[1].release();
+    for (auto &b : L->shard.xg) b.release();
     L->shard.yg.release();
   }
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
@@ -1118,12 +1119,13 @@ int sbb_layer_dp_finish(sbb_layer *L, long hypercolumn, void *stream) {
 // ------------------------------------------------- row-sharded layer over peer-mapped memory
 namespace {
 
-enum { kShardX0 = 0, kShardX1 = 1, kShardMask = 2, kShardW = 3, kShardCij = 4, kShardCi = 5 };
+enum { kShardX0 = 0, kShardX1 = 1, kShardX2 = 2, kShardMask = 3, kShardW = 4, kShardCij = 5, kShardCi = 6 };
 
 void *shard_local_buffer(sbb_layer *L, int which) {
   switch (which) {
     case kShardX0: return L->shard.xg[0].d;
     case kShardX1: return L->shard.xg[1].d;
+    case kShardX2: return L->shard.xg[2].d;
     case kShardMask: return L->score.d;
     case kShardW: return L->state[SBB_STATE_WEIGHTS];
     case kShardCij: return L->state[SBB_STATE_CIJ];
@@ -1151,27 +1153,42 @@ int check_shard(sbb_layer *L, bool need_peers) {
   return SBB_OK;
 }
 
-// The step in flight must have been opened by a scatter of the same local batch.
+// The step in flight was opened by sbb_layer_shard_forward with the same local batch.
 int check_shard_step(sbb_layer *L, long B, const char *what) {
   SBB_TRY(check_shard(L, true));
-  ARG(B > 0 && B == L->shard.batch, "%s: local batch %ld, but the last sbb_layer_shard_scatter carried %ld", what, B,
-      L->shard.batch);
+  ARG(B > 0 && B == L->shard.batch, "%s: local batch %ld, but the step in flight (sbb_layer_shard_forward) has %ld", what,
+      B, L->shard.batch);
   return SBB_OK;
 }
 
 template <typename T>
 int shard_scatter(sbb_layer *L, const T *x, long B, cudaStream_t st) {
   auto &S = L->shard;
-  S.parity ^= 1;
-  S.batch = B;
+  const int slot = (S.cur + 1 + S.staged) % 3;   // every rank makes the same calls, so the slots agree
+  S.staged += 1;
+  S.slot_batch[slot] = B;
   // rank o receives this rank's samples as rows [rank * B, (rank + 1) * B) of its [world * B, rows of o] buffer
   sbb::PeerTable t{};
   t.n = (int)S.world;
   for (long o = 0; o < S.world; ++o) {
     const long width = shard_begin(L, o + 1) - shard_begin(L, o);
-    t.ptr[o] = static_cast<T *>(S.peer[kShardX0 + S.parity][o]) + (size_t)S.rank * B * width;
+    t.ptr[o] = static_cast<T *>(S.peer[kShardX0 + slot][o]) + (size_t)S.rank * B * width;
   }
-  SBB_CUDA(sbb::launch_scatter_columns<T>(x, B, L->N, S.rows_per_rank, t, st));
+  if (S.world == 1) {
+    SBB_CUDA(sbb::launch_scatter_columns<T>(x, B, L->N, S.rows_per_rank, t, st));
+    return SBB_OK;
+  }
+  // Across ranks the column blocks travel by copy engines (strided 2-D copies over NVLink): the exchange of a
+  // batch staged ahead then runs beside the current step's contractions without taking issue slots or
+  // shared-memory bandwidth from them (a store kernel on a side stream cost the forward product 7 %).
+  // Owners are visited starting after this rank, so that at any time every rank sends to a different owner.
+  for (long k = 1; k <= S.world; ++k) {
+    const long o = (S.rank + k) % S.world;
+    const long rb = shard_begin(L, o), width = shard_begin(L, o + 1) - rb;
+    if (width <= 0) continue;
+    SBB_CUDA(cudaMemcpy2DAsync(t.ptr[o], (size_t)width * sizeof(T), x + rb, (size_t)L->N * sizeof(T),
+                               (size_t)width * sizeof(T), (size_t)B, cudaMemcpyDeviceToDevice, st));
+  }
   return SBB_OK;
 }
 
@@ -1184,7 +1201,7 @@ int shard_forward(sbb_layer *L, long B, T *support, cudaStream_t st) {
     SBB_CUDA(cudaMemsetAsync(support, 0, (size_t)Bg * M * sizeof(T), st));
     return SBB_OK;
   }
-  const T *xg = static_cast<const T *>(S.xg[S.parity].d);
+  const T *xg = static_cast<const T *>(S.xg[S.cur].d);
   const T *W = static_cast<const T *>(L->state[SBB_STATE_WEIGHTS]) + rb * M;
   bool tc = tensor_path<T>(xg, W, nr, M) && (reinterpret_cast<uintptr_t>(support) & 7u) == 0;
   const int splits = tc ? sbb::forward_splits_tc(Bg, nr, M) : sbb::forward_splits<T>(Bg, nr, M);
@@ -1225,7 +1242,7 @@ int shard_train(sbb_layer *L, long B, long h, cudaStream_t st) {
   const long nr = re - rb, Bg = B * S.world, N = L->N, M = L->M;
   ARG(S.yg.d != nullptr && S.yg.cap >= (size_t)Bg * M * sizeof(T), "shard_train: no activations (sbb_layer_shard_activate)");
   const sbb::TraceParams<T> p = sbb::make_trace_params<T>(L->desc.taupdt, L->desc.taupdt / 2, Bg);
-  const T *xg = static_cast<const T *>(S.xg[S.parity].d);
+  const T *xg = static_cast<const T *>(S.xg[S.cur].d);
   const T *yg = static_cast<const T *>(S.yg.d);
   T *Ci = static_cast<T *>(L->state[SBB_STATE_CI]);
   T *Cj = static_cast<T *>(L->state[SBB_STATE_CJ]);
@@ -1318,8 +1335,7 @@ int sbb_layer_shard_init(sbb_layer *L, long rank, long world_size, long max_loca
   S.rows_per_rank = ((tiles + world_size - 1) / world_size) * 128;
   // every rank allocates a full block's width, so that the buffers have one size everywhere
   const size_t xg_bytes = (size_t)world_size * max_local_batch * S.rows_per_rank * s;
-  SBB_TRY(S.xg[0].reserve(xg_bytes));
-  SBB_TRY(S.xg[1].reserve(xg_bytes));
+  for (auto &b : S.xg) SBB_TRY(b.reserve(xg_bytes));
   if (L->score.d == nullptr) SBB_TRY(L->score.reserve(sbb::mask_scratch_bytes(L->N, s)));
   for (int b = 0; b < SBB_SHARD_BUFFERS; ++b)
     for (int r = 0; r < 8; ++r) {
@@ -1333,7 +1349,8 @@ int sbb_layer_shard_init(sbb_layer *L, long rank, long world_size, long max_loca
     static_assert(sizeof(hnd) == SBB_SHARD_HANDLE_BYTES, "IPC handle size");
     std::memcpy(handles_out + (size_t)b * SBB_SHARD_HANDLE_BYTES, &hnd, sizeof(hnd));
   }
-  S.parity = 0;
+  S.cur = 0;
+  S.staged = 0;
   S.batch = 0;
   S.on = true;
   S.attached = world_size == 1;
@@ -1365,14 +1382,25 @@ int sbb_layer_shard_scatter(sbb_layer *L, const void *x_dev, long B_local, void 
   ARG(x_dev, "shard_scatter: null pointer");
   ARG(B_local > 0 && B_local <= L->shard.max_batch, "shard_scatter: local batch %ld outside [1, %ld] (sbb_layer_shard_init)",
       B_local, L->shard.max_batch);
+  ARG(L->shard.staged < 2, "shard_scatter: two batches are already staged; run a step (sbb_layer_shard_forward) first");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return DISPATCH(L->desc.dtype, shard_scatter<float>(L, (const float *)x_dev, B_local, st),
                   shard_scatter<double>(L, (const double *)x_dev, B_local, st));
 }
 
 int sbb_layer_shard_forward(sbb_layer *L, long B_local, void *support_dev, void *stream) {
-  SBB_TRY(check_shard_step(L, B_local, "shard_forward"));
+  SBB_TRY(check_shard(L, true));
   ARG(support_dev, "shard_forward: null pointer");
+  {
+    auto &S = L->shard;
+    ARG(S.staged >= 1, "shard_forward: no batch is staged (sbb_layer_shard_scatter)");
+    const int next = (S.cur + 1) % 3;
+    ARG(B_local == S.slot_batch[next], "shard_forward: local batch %ld, but the staged batch has %ld", B_local,
+        S.slot_batch[next]);
+    S.cur = next;   // the oldest staged batch becomes the step in flight
+    S.staged -= 1;
+    S.batch = B_local;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return DISPATCH(L->desc.dtype, shard_forward<float>(L, B_local, (float *)support_dev, st),
                   shard_forward<double>(L, B_local, (double *)support_dev, st));
@@ -1401,6 +1429,12 @@ int sbb_layer_shard_mask(sbb_layer *L, long hypercolumn, void *stream) {
   ARG(hypercolumn >= 0 && hypercolumn < L->H, "shard_mask: hypercolumn %ld outside [0,%ld)", hypercolumn, L->H);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return DISPATCH(L->desc.dtype, shard_mask<float>(L, hypercolumn, st), shard_mask<double>(L, hypercolumn, st));
+}
+
+int sbb_layer_shard_drop_staged(sbb_layer *L) {
+  SBB_TRY(check_shard(L, false));
+  L->shard.staged = 0;
+  return SBB_OK;
 }
 
 int sbb_layer_shard_share_rows(sbb_layer *L, void *stream) {

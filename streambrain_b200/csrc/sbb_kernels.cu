@@ -1690,8 +1690,10 @@ template cudaError_t launch_peer_broadcast<uint4>(const uint4 *, long, const Pee
 
 // Column block o of x[B, N] (columns [o * block, min(N, (o + 1) * block))) goes to rank o as a dense
 // [B, width_o] matrix at dst.ptr[o].  V = elements moved per thread (a 16-byte vector when the shapes allow).
+// Blocks of 128 threads with few registers, so that the kernel can run on a side stream beside a
+// tensor-core contraction, whose one CTA per SM leaves room for little else.
 template <typename T, int V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
     scatter_columns_kernel(const T *__restrict__ x, long B, long N, long block, PeerTable dst) {
   struct alignas(sizeof(T) * V) Pack {
     T v[V];
@@ -1716,10 +1718,10 @@ cudaError_t launch_scatter_columns(const T *x, long B, long N, long block, const
   bool vec = N % V == 0 && block % V == 0 && aligned16(x);
   for (int d = 0; d < dst.n; ++d) vec = vec && aligned16(dst.ptr[d]);
   const long total = vec ? B * (N / V) : B * N;
-  const long blocks = (total + 255) / 256;
+  const long blocks = (total + 127) / 128;
   const unsigned grid = (unsigned)(blocks < 2368 ? blocks : 2368);
-  if (vec) scatter_columns_kernel<T, V><<<grid, 256, 0, st>>>(x, B, N, block, dst);
-  else scatter_columns_kernel<T, 1><<<grid, 256, 0, st>>>(x, B, N, block, dst);
+  if (vec) scatter_columns_kernel<T, V><<<grid, 128, 0, st>>>(x, B, N, block, dst);
+  else scatter_columns_kernel<T, 1><<<grid, 128, 0, st>>>(x, B, N, block, dst);
   return launched();
 }
 template cudaError_t launch_scatter_columns<float>(const float *, long, long, long, const PeerTable &, cudaStream_t);

@@ -106,6 +106,9 @@ struct sbb_network {
   DeviceBuffer hits;               // evaluation counter
   DeviceBuffer token;              // one float: the barrier of the row-sharded step
   DeviceBuffer support;            // row-sharded step: supports of the global batch, summed over the ranks in place
+  DeviceBuffer ahead_x[2];         // row-sharded step: the batch staged ahead is assembled here, in turn
+  cudaStream_t side = nullptr;     // row-sharded step: assembles and exchanges the next batch beside the current step
+  cudaEvent_t ev_step = nullptr, ev_staged = nullptr;
   cudaStream_t stream = nullptr;
   size_t esize() const { return dtype == SBB_F32 ? 4 : 8; }
   long out_features(size_t k) const { return desc[k].hypercolumns * desc[k].minicolumns; }
@@ -182,16 +185,31 @@ bool row_sharded(const sbb_network *net, const sbb_layer *layer) {
   return net->have_comm && net->world > 0 && sbb_layer_shard_world(layer) == net->world;
 }
 
-// Forward + train step of an unsupervised, row-sharded layer on this rank's `count` samples of the global batch;
-// the rank's activations land in `y`.
-int sharded_step(sbb_network *net, sbb_layer *layer, const sbb_layer_desc &d, const void *x, void *y, long count,
-                 long hypercolumn) {
+// Shuffled rows [first, first + count) of the dataset, assembled into `buf` on `stream`.
+int assemble_images(sbb_network *net, long first, long count, DeviceBuffer &buf, cudaStream_t stream, const void **x) {
+  NET_TRY(buf.reserve((size_t)count * net->features * net->esize()));
+  const long *order = static_cast<const long *>(net->order.d);
+  if (net->dtype == SBB_F32)
+    NET_CUDA(sbb::launch_gather_rows<float>((const float *)net->images.d, order, first, count, net->features,
+                                            (float *)buf.d, stream));
+  else
+    NET_CUDA(sbb::launch_gather_rows<double>((const double *)net->images.d, order, first, count, net->features,
+                                             (double *)buf.d, stream));
+  *x = buf.d;
+  return SBB_OK;
+}
+
+// The part of the row-sharded step after the exchange of the inputs: forward product of the staged batch, sum of
+// the supports over the ranks, activation into `y`, train step, mask update.  `staged_ahead`: the next batch was
+// scattered on the side stream, which the network's stream joins before the all-reduce (so that the all-reduce
+// also tells every rank that all exchanges of the next batch are complete).
+int sharded_step(sbb_network *net, sbb_layer *layer, const sbb_layer_desc &d, void *y, long count, long hypercolumn,
+                 bool staged_ahead) {
   const long M = d.hypercolumns * d.minicolumns;
   const size_t elems = (size_t)count * net->world * M;
   NET_TRY(net->support.reserve(elems * net->esize()));
-  NET_TRY(sbb_layer_shard_scatter(layer, x, count, net->stream));
-  NET_TRY(rank_barrier(net));
   NET_TRY(sbb_layer_shard_forward(layer, count, net->support.d, net->stream));
+  if (staged_ahead) NET_CUDA(cudaStreamWaitEvent(net->stream, net->ev_staged, 0));
   const long t = net->comm.reduce_begin(net->comm.user, net->support.d, elems, net->dtype, net->stream);
   if (t < 0 || net->comm.reduce_wait(net->comm.user, t, net->stream) != 0)
     return net_fail(SBB_ERR_INVALID, "the reduction callback failed (supports of the row-sharded step)");
@@ -293,6 +311,11 @@ int sbb_network_destroy(sbb_network *net) {
   net->hits.release();
   net->token.release();
   net->support.release();
+  net->ahead_x[0].release();
+  net->ahead_x[1].release();
+  if (net->side) cudaStreamDestroy(net->side);
+  if (net->ev_step) cudaEventDestroy(net->ev_step);
+  if (net->ev_staged) cudaEventDestroy(net->ev_staged);
   for (auto &a : net->act) a.release();
   if (net->stream) cudaStreamDestroy(net->stream);
   delete net;
@@ -389,6 +412,12 @@ int sbb_network_train_batches(sbb_network *net, long layer_index, long maximal_b
   const bool dp = net->have_comm;   // with callbacks the split step runs even for one rank (a sum over one)
   // a layer that learns from its own activations and is sharded over the ranks takes the row-sharded step
   const bool sharded = !last && row_sharded(net, net->layers[li]);
+  bool staged_ahead = false;   // the batch of this iteration was already exchanged during the previous one
+  if (sharded && net->side == nullptr) {
+    NET_CUDA(cudaStreamCreateWithFlags(&net->side, cudaStreamNonBlocking));
+    NET_CUDA(cudaEventCreateWithFlags(&net->ev_step, cudaEventDisableTiming));
+    NET_CUDA(cudaEventCreateWithFlags(&net->ev_staged, cudaEventDisableTiming));
+  }
   if (batch_begin == 0) NET_CUDA(cudaDeviceSynchronize());   // state written through other streams has landed
   for (long i = batch_begin; i < batch_end; ++i) {
     long first = 0, count = 0, slot = -1;
@@ -396,16 +425,37 @@ int sbb_network_train_batches(sbb_network *net, long layer_index, long maximal_b
                                    &slot));
     if (count <= 0) continue;
     const void *x = nullptr, *t = nullptr, *in_last = nullptr, *out_last = nullptr;
-    NET_TRY(assemble(net, first, count, true, last, &x, &t));
+    if (!staged_ahead) NET_TRY(assemble(net, first, count, true, last, &x, &t));
     const long h = slot >= 0 ? hypercolumn_order_host[slot] : -1;
     if (sharded) {   // the layer's own forward pass is part of its sharded step
-      in_last = x;
-      if (li > 0) {
-        const void *unused = nullptr;
-        NET_TRY(forward_through(net, x, count, li - 1, &unused, &in_last));
+      if (!staged_ahead) {
+        in_last = x;
+        if (li > 0) {
+          const void *unused = nullptr;
+          NET_TRY(forward_through(net, x, count, li - 1, &unused, &in_last));
+        }
+        NET_TRY(sbb_layer_shard_scatter(net->layers[li], in_last, count, net->stream));
+        NET_TRY(rank_barrier(net));
+      }
+      // The first layer's next batch is assembled and exchanged on the side stream beside this step's forward
+      // product; it starts once the previous step has finished here (every rank is then past the step before it).
+      staged_ahead = false;
+      long first2 = 0, count2 = 0, slot2 = -1;
+      if (li == 0 && i + 1 < batch_end) {
+        NET_TRY(sbb_network_batch_plan(net->samples, maximal_batch_size, net->world, net->rank, H, epoch, i + 1, &first2,
+                                       &count2, &slot2));
+        if (count2 > 0) {
+          const void *x2 = nullptr;
+          NET_CUDA(cudaEventRecord(net->ev_step, net->stream));
+          NET_CUDA(cudaStreamWaitEvent(net->side, net->ev_step, 0));
+          NET_TRY(assemble_images(net, first2, count2, net->ahead_x[(i + 1) & 1], net->side, &x2));
+          NET_TRY(sbb_layer_shard_scatter(net->layers[li], x2, count2, net->side));
+          NET_CUDA(cudaEventRecord(net->ev_staged, net->side));
+          staged_ahead = true;
+        }
       }
       NET_TRY(net->act[li].reserve((size_t)count * net->out_features(li) * net->esize()));
-      NET_TRY(sharded_step(net, net->layers[li], net->desc[li], in_last, net->act[li].d, count, h));
+      NET_TRY(sharded_step(net, net->layers[li], net->desc[li], net->act[li].d, count, h, staged_ahead));
       continue;
     }
     NET_TRY(forward_through(net, x, count, li, &in_last, &out_last));

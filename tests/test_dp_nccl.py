@@ -49,7 +49,7 @@ def _batches(world, steps):
     return [rs.rand(world * B_LOCAL, N).astype(np.float32) for _ in range(steps)]
 
 
-def _worker(rank, world, port, path, out_dir, sharded=False):
+def _worker(rank, world, port, path, out_dir, sharded=False, staged=False):
     sys.path.insert(0, REPO)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -65,10 +65,13 @@ def _worker(rank, world, port, path, out_dir, sharded=False):
         layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist), B_LOCAL)
     steps = 2
     all_reduce = lambda t: dist.all_reduce(t, async_op=True)
-    for k, xb in enumerate(_batches(world, steps)):
-        x = torch.from_numpy(xb[rank * B_LOCAL:(rank + 1) * B_LOCAL]).cuda()
+    batches = _batches(world, steps)
+    mine = [torch.from_numpy(xb[rank * B_LOCAL:(rank + 1) * B_LOCAL]).cuda() for xb in batches]
+    for k, xb in enumerate(batches):
+        x = mine[k]
         if sharded:   # forward + train in one; a rank holds only its own rows until they are shared
-            layer.sharded_step(x, (2 + k) % H, all_reduce)
+            ahead = staged and k + 1 < steps   # the next batch's exchange runs beside this step
+            layer.sharded_step(x, (2 + k) % H, all_reduce, next_inputs=mine[k + 1] if ahead else None)
             layer.share_rows(all_reduce)
         else:
             y = layer.compute_activation(x)
@@ -80,8 +83,9 @@ def _worker(rank, world, port, path, out_dir, sharded=False):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("staged", [False, True])
 @pytest.mark.parametrize("path", ["general", "tensor"])
-def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path):
+def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path, staged):
     """The row-sharded step (every rank owns half of the input rows: the ranks exchange the matching columns of
     their batches over NVLink, sum their parts of the supports, and each updates its own rows from the whole
     global batch) against the all-reduce step on the same two GPUs: the same traces, weights and masks to
@@ -94,7 +98,7 @@ def test_two_gpu_row_sharded_step_equals_allreduce_step(tmp_path, path):
     a.mkdir()
     b.mkdir()
     mp.spawn(_worker, args=(world, _free_port(), path, str(a), False), nprocs=world, join=True)
-    mp.spawn(_worker, args=(world, _free_port(), path, str(b), True), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), path, str(b), True, staged), nprocs=world, join=True)
     tol = TOL[np.dtype(np.float32)]
     for k in range(2):
         s0 = np.load(b / ("rank0_step%d.npz" % k))

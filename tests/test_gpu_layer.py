@@ -430,6 +430,21 @@ def test_row_sharded_step_on_one_rank_equals_single_step(B200, tag, dtype):
         assert weight_err(sharded.weights, single.weights) < 10 * tol, h
         for name in PLASTIC_STATE:          # both continue from the same state
             setattr(sharded, name, getattr(single, name))
+    # the same with every next batch staged ahead on the side stream (three input buffers used in turn)
+    xs = [torch.from_numpy(np.ascontiguousarray(g["x"][:B] * s)).cuda() for s in (1.0, 0.5, 0.25, 0.75, 1.0)]
+    for k, h in enumerate((1, None, 3, 0)):
+        y = single.compute_activation(xs[k])
+        single.train_step(xs[k], y, h)
+        ys = sharded.sharded_step(xs[k], h, lambda t: done(), next_inputs=xs[k + 1])
+        torch.cuda.synchronize()
+        assert rel_inf(ys.cpu().numpy(), y.cpu().numpy() if hasattr(y, "cpu") else y) < tol * 10 ** k, k
+        assert np.array_equal(sharded.wmask, single.wmask), k
+        for name in ("Ci", "Cj", "Cij", "bias", "kbi"):
+            assert rel_inf(getattr(sharded, name), getattr(single, name)) < tol * 10 ** k, (k, name)
+    with pytest.raises(ValueError):         # the batch staged ahead must be the next one passed
+        sharded.sharded_step(xs[0], None, lambda t: done())
+    sharded.drop_staged()
+    sharded.sharded_step(xs[0], None, lambda t: done())
     with pytest.raises(Exception):          # the plain data-parallel step refuses a sharded layer
         sharded.dp_train_step(x, y, None, 1, lambda t: done())
     big = torch.zeros((B + 1, sharded.in_features), dtype=x.dtype, device="cuda")
