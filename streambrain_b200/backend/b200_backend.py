@@ -26,7 +26,7 @@ import numpy as np
 
 from .. import _lib
 from .._lib import STATE, LayerDesc, check, dtype_code, host_ptr, lib
-from ..parallel import pipelined_dp_step
+from ..parallel import pipelined_dp_step, sharded_step
 
 try:  # torch is plumbing only: device tensors, streams, torch.distributed
     import torch
@@ -281,51 +281,9 @@ class _DeviceLayer:
         e.g. the upload of that batch); :attr:`staged_event` fires when the exchange has read
         ``next_inputs``.  Every rank must make the same choice.  See ``sbb_layer_shard_*`` in the C header for the protocol."""
         x = self._dev_input(inputs, self.in_features)
-        st = _stream_ptr()
-        B = x.shape[0]
-        world = self._shard[1]
-        h = -1 if hypercolumn is None else int(hypercolumn)
-        if self._support is None or self._support.shape[0] != B * world:
-            self._support = torch.empty((B * world, self.out_features), dtype=_torch_dtype(self.dtype), device="cuda")
-        if out is None:
-            out = torch.empty((B, self.out_features), dtype=_torch_dtype(self.dtype), device="cuda")
-        token = self._barrier_token()
-        staged = getattr(self, "_staged", None)
-        if staged is None:
-            check(lib.sbb_layer_shard_scatter(self._handle, x.data_ptr(), B, st))
-            all_reduce(token).wait()
-        elif staged[0].data_ptr() != x.data_ptr() or staged[0].shape[0] != B:
-            raise ValueError("the previous sharded_step staged another batch as next_inputs; pass that batch, or "
-                             "call drop_staged() on every rank")
-        self._staged = None
-        main = torch.cuda.current_stream()
-        staged_event = None
-        if next_inputs is not None:
-            xn = self._dev_input(next_inputs, self.in_features)
-            if getattr(self, "_side", None) is None:
-                self._side = torch.cuda.Stream()
-            # the previous step has finished on this rank (so every rank is past the step before it) ...
-            self._side.wait_stream(main)
-            if next_ready is not None:
-                self._side.wait_event(next_ready)
-            with torch.cuda.stream(self._side):
-                check(lib.sbb_layer_shard_scatter(self._handle, xn.data_ptr(), xn.shape[0], _stream_ptr()))
-                staged_event = torch.cuda.Event()
-                staged_event.record(self._side)
-            self._staged = (xn,)
-            self.staged_event = staged_event
-        check(lib.sbb_layer_shard_forward(self._handle, B, self._support.data_ptr(), st))
-        if staged_event is not None:   # ... and this step's all-reduce certifies that every rank's exchange is complete
-            main.wait_event(staged_event)
-        all_reduce(self._support).wait()
-        check(lib.sbb_layer_shard_activate(self._handle, B, self._support.data_ptr(), out.data_ptr(), st))
-        if train:
-            mask = h >= 0 and self._kind == _lib.PLASTIC
-            check(lib.sbb_layer_shard_train(self._handle, B, h if mask else -1, st))
-            if mask:
-                all_reduce(token).wait()
-                check(lib.sbb_layer_shard_mask(self._handle, h, st))
-        return out
+        xn = None if next_inputs is None else self._dev_input(next_inputs, self.in_features)
+        ops = _DeviceShardOps(self, out, next_ready)
+        return sharded_step(ops, x, None if hypercolumn is None else int(hypercolumn), all_reduce, xn, train)
 
     def drop_staged(self):
         """Forget a batch staged by ``next_inputs`` that no step will consume (every rank alike)."""
@@ -342,6 +300,72 @@ class _DeviceLayer:
         all_reduce(token).wait()
         check(lib.sbb_layer_shard_share_rows(self._handle, _stream_ptr()))
         all_reduce(token).wait()
+
+
+class _DeviceShardOps:
+    """CUDA implementation of the ``ops`` protocol of :func:`streambrain_b200.parallel.sharded_step`."""
+
+    def __init__(self, layer, out, next_ready):
+        self.layer, self.out, self.next_ready = layer, out, next_ready
+        self.token = layer._barrier_token()
+        self.plastic = layer._kind == _lib.PLASTIC
+        self.world = layer._shard[1]
+
+    def take_staged(self, x):
+        layer = self.layer
+        staged = getattr(layer, "_staged", None)
+        layer._staged = None
+        if staged is None:
+            return False
+        if staged[0].data_ptr() != x.data_ptr() or staged[0].shape[0] != x.shape[0]:
+            layer._staged = staged
+            raise ValueError("the previous sharded_step staged another batch as next_inputs; pass that batch, or "
+                             "call drop_staged() on every rank")
+        return True
+
+    def scatter(self, x, ahead):
+        layer = self.layer
+        if not ahead:
+            check(lib.sbb_layer_shard_scatter(layer._handle, x.data_ptr(), x.shape[0], _stream_ptr()))
+            return
+        if getattr(layer, "_side", None) is None:
+            layer._side = torch.cuda.Stream()
+        # the previous step has finished on this rank, so every rank is past the step before it ...
+        layer._side.wait_stream(torch.cuda.current_stream())
+        if self.next_ready is not None:
+            layer._side.wait_event(self.next_ready)
+        with torch.cuda.stream(layer._side):
+            check(lib.sbb_layer_shard_scatter(layer._handle, x.data_ptr(), x.shape[0], _stream_ptr()))
+            layer.staged_event = torch.cuda.Event()
+            layer.staged_event.record(layer._side)
+        layer._staged = (x,)
+
+    def forward(self, x):
+        layer, B = self.layer, x.shape[0]
+        if layer._support is None or layer._support.shape[0] != B * self.world:
+            layer._support = torch.empty((B * self.world, layer.out_features), dtype=_torch_dtype(layer.dtype),
+                                         device="cuda")
+        self.B = B
+        check(lib.sbb_layer_shard_forward(layer._handle, B, layer._support.data_ptr(), _stream_ptr()))
+        return layer._support
+
+    def join_staged(self):
+        # ... and this step's all-reduce then certifies that every rank's exchange is complete
+        torch.cuda.current_stream().wait_event(self.layer.staged_event)
+
+    def activate(self, support):
+        layer = self.layer
+        out = self.out
+        if out is None:
+            out = torch.empty((self.B, layer.out_features), dtype=_torch_dtype(layer.dtype), device="cuda")
+        check(lib.sbb_layer_shard_activate(layer._handle, self.B, support.data_ptr(), out.data_ptr(), _stream_ptr()))
+        return out
+
+    def train(self, h):
+        check(lib.sbb_layer_shard_train(self.layer._handle, self.B, -1 if h is None else h, _stream_ptr()))
+
+    def mask(self, h):
+        check(lib.sbb_layer_shard_mask(self.layer._handle, h, _stream_ptr()))
 
 
 class _DeviceDPOps:

@@ -1,4 +1,5 @@
-"""Host-side orchestration of the batch data-parallel train step.
+"""Host-side orchestration of the two batch data-parallel train steps: reduce-and-replicate
+(``pipelined_dp_step``) and the row-sharded layer (``sharded_step``).
 
 The reference's only parallel scheme is batch data parallelism
 (BCPNN/backend/_kernels/kernels_mpi_internal.cc:71-250): every rank forms the
@@ -60,6 +61,53 @@ def pipelined_dp_step(ops, x, y, hypercolumn, local_batch: int, world_size: int,
             ops.apply_vectors(batch)
         ops.apply_rows(batch, rb, re)
     ops.finish(hypercolumn)
+
+
+def shard_bounds(n_rows: int, world_size: int) -> list[tuple[int, int]]:
+    """Input rows [begin, end) each rank of a row-sharded layer owns: equal blocks of whole 128-row
+    tiles, the last ones clipped to ``n_rows`` (possibly empty) -- ``sbb_layer_shard_rows``."""
+    tiles = (n_rows + 127) // 128
+    per = ((tiles + world_size - 1) // world_size) * 128
+    return [(min(n_rows, r * per), min(n_rows, (r + 1) * per)) for r in range(world_size)]
+
+
+def sharded_step(ops, x, hypercolumn, all_reduce, next_x=None, train=True):
+    """Forward + train step of a row-sharded, unsupervised layer on this rank's slice ``x`` of the global
+    batch; returns the rank's activations.  Every rank owns a block of input rows (``shard_bounds``):
+    the ranks exchange the matching columns of their slices, each forms its part of every sample's
+    support, ``all_reduce`` sums the parts, and each rank updates its own rows from the whole global
+    batch -- the single-device step at the global batch.  With ``next_x`` the exchange of the next
+    call's slice is started beside this step's forward product, and this step's all-reduce doubles as
+    its barrier.  The ``ops`` protocol (CUDA: the layer's ``sbb_layer_shard_*`` calls; CPU tests: numpy
+    over gloo):
+
+        ops.token                  one-element tensor, reduced as a barrier
+        ops.plastic                the layer has a mask
+        ops.take_staged(x)         True if ``x`` was staged by the previous call (raises on another batch)
+        ops.scatter(x, ahead)      exchange the columns of ``x`` (ahead: beside the current step)
+        ops.forward(x)             tensor of partial supports of the global batch, to be summed over ranks
+        ops.join_staged()          order the step after the exchange started with ahead=True
+        ops.activate(support)      bias + softmax; returns this rank's rows
+        ops.train(h)               traces and weights of the own rows, bias, (h is not None) mask scores
+        ops.mask(h)                the swaps, and the weights of the own swapped rows
+    """
+    if not ops.take_staged(x):
+        ops.scatter(x, False)
+        all_reduce(ops.token).wait()
+    if next_x is not None:
+        ops.scatter(next_x, True)
+    support = ops.forward(x)
+    if next_x is not None:
+        ops.join_staged()
+    all_reduce(support).wait()
+    y = ops.activate(support)
+    if train:
+        mask = hypercolumn is not None and ops.plastic
+        ops.train(hypercolumn if mask else None)
+        if mask:
+            all_reduce(ops.token).wait()
+            ops.mask(hypercolumn)
+    return y
 
 
 def all_gather_bytes_over(dist):

@@ -161,3 +161,173 @@ def test_network_slices_batches_per_rank(tmp_path):
     assert all(a[1] != b[1] for a, b in zip(seen[0], seen[1]))  # different slices
     assert int(r[0]["total"][0]) == 2 * (5 + 5 + 5 + 2) == int(r[1]["total"][0])
     assert int(r[0]["correct"][0]) == int(r[1]["correct"][0])
+
+
+# ---------------------------------------------------------------------------
+# The row-sharded layer step (streambrain_b200.parallel.sharded_step) on CPU
+# ---------------------------------------------------------------------------
+SN, SH, SMC, SB = 300, 3, 4, 5      # 300 rows = 3 tiles of 128: rank 0 owns 256 rows, rank 1 the other 44
+SM = SH * SMC
+S_HP = dict(taupdt=0.05, khalf=-10.0, pmin=0.1, taubdt=0.1, density=0.5)
+
+
+def _shard_layer(oracle):
+    rng = np.random.RandomState(21)
+    layer = oracle.OracleLayer(oracle.PortKernels(), "plastic", SN, SH, SMC, S_HP["taupdt"], (0.5, 1 / SMC, 0.5 / SMC),
+                               np.float64, khalf=S_HP["khalf"], pmin=S_HP["pmin"], taubdt=S_HP["taubdt"],
+                               density=S_HP["density"], rng=rng)
+    layer.Cij = (np.outer(layer.Ci, layer.Cj) * (0.9 + 0.2 * rng.rand(SN, SM)))
+    return layer
+
+
+def _shard_batches(world, steps):
+    rs = np.random.RandomState(8)
+    return [rs.rand(world * SB, SN) for _ in range(steps)]
+
+
+class NumpyShardOps:
+    """numpy / gloo implementation of the ops protocol of parallel.sharded_step: the layer arithmetic is the
+    oracle's, applied to the rows this rank owns; three gathered-input slots used in turn, as in the library."""
+
+    def __init__(self, layer, rank, world, bounds):
+        self.layer, self.rank, self.world = layer, rank, world
+        self.rb, self.re = bounds[rank]
+        self.bounds = bounds
+        self.token = torch.zeros(1)
+        self.plastic = True
+        self.slots, self.cur, self.staged, self.staged_x = [None] * 3, 0, 0, None
+        self.calls = []
+
+    def take_staged(self, x):
+        if self.staged_x is None:
+            return False
+        assert self.staged_x is x
+        self.staged_x = None
+        return True
+
+    def scatter(self, x, ahead):
+        parts = [torch.zeros(x.shape[0], SN, dtype=torch.float64) for _ in range(self.world)]
+        dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(x)))
+        slot = (self.cur + 1 + self.staged) % 3
+        self.staged += 1
+        # rank s's samples at rows [s * B, (s + 1) * B), own columns only
+        self.slots[slot] = np.concatenate([p.numpy()[:, self.rb:self.re] for p in parts])
+        if ahead:
+            self.staged_x = x
+        self.calls.append(("scatter", ahead, slot))
+
+    def forward(self, x):
+        assert self.staged >= 1
+        self.cur = (self.cur + 1) % 3
+        self.staged -= 1
+        self.xg = self.slots[self.cur]
+        self.B = x.shape[0]
+        self.calls.append(("forward", self.cur))
+        return torch.from_numpy(self.xg @ self.layer.weights[self.rb:self.re])
+
+    def join_staged(self):
+        self.calls.append(("join",))
+
+    def activate(self, support):
+        L = self.layer
+        act = support.numpy() + L.bias
+        self.yg = L.k.softmax_minicolumns(np.ascontiguousarray(act), SH, SMC)
+        self.calls.append(("activate",))
+        return self.yg[self.rank * self.B:(self.rank + 1) * self.B]
+
+    def train(self, h):
+        L, rb, re = self.layer, self.rb, self.re
+        cthr = L.taupdt / 2
+        ci, cij, w = L.Ci[rb:re].copy(), L.Cij[rb:re].copy(), L.weights[rb:re].copy()
+        _, L.Cj, cij, w = L.k.update_weights(ci, L.Cj, cij, np.ascontiguousarray(self.xg), self.yg, L.taupdt, w, cthr)
+        L.Ci[rb:re], L.Cij[rb:re], L.weights[rb:re] = ci, cij, w
+        L.bias, L.kbi = L.k.update_bias_regularized(L.bias, L.kbi, L.Cj, cthr, L.khalf, L.pmin, L.taubdt)
+        if h is None:   # the masked weights of the own rows (the fused step applies the mask every time)
+            L.weights[rb:re] = L.k.apply_mask(np.ascontiguousarray(L.weights[rb:re]),
+                                              np.ascontiguousarray(L.wmask[rb:re]), SH, SMC)
+        self.calls.append(("train", h))
+
+    def _all_rows(self, a):
+        """Every owner's rows of `a`, gathered (stands in for the owners' scores reaching every rank)."""
+        width = int(np.prod(a.shape[1:])) if a.ndim > 1 else 1
+        rows = max(e - b for b, e in self.bounds)
+        mine = np.zeros((rows, width))
+        mine[:self.re - self.rb] = a[self.rb:self.re].reshape(self.re - self.rb, width)
+        parts = [torch.zeros(rows, width, dtype=torch.float64) for _ in range(self.world)]
+        dist.all_gather(parts, torch.from_numpy(mine))
+        full = np.concatenate([p.numpy()[:e - b] for p, (b, e) in zip(parts, self.bounds)])
+        return full.reshape(a.shape)
+
+    def mask(self, h):
+        L, rb, re = self.layer, self.rb, self.re
+        cthr = L.taupdt / 2
+        Ci, Cij, W = self._all_rows(L.Ci), self._all_rows(L.Cij), self._all_rows(L.weights)
+        L.wmask = L.k.update_mask(L.wmask, W, Ci, L.Cj, Cij, cthr, SH, SMC, int(h), 16)
+        L.weights[rb:re] = L.k.apply_mask(np.ascontiguousarray(L.weights[rb:re]), np.ascontiguousarray(L.wmask[rb:re]),
+                                          SH, SMC)
+        self.calls.append(("mask", h))
+
+
+def _shard_worker(rank, world, port, out_dir):
+    sys.path.insert(0, REPO)
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from streambrain_b200 import parallel
+    layer = _shard_layer(oracle)
+    bounds = parallel.shard_bounds(SN, world)
+    ops = NumpyShardOps(layer, rank, world, bounds)
+    batches = _shard_batches(world, 4)
+    mine = [xb[rank * SB:(rank + 1) * SB] for xb in batches]
+    outs = []
+    for k, h in enumerate((1, None, 2, 0)):
+        ahead = mine[k + 1] if k in (0, 1) else None    # steps 1 and 2 run on batches staged ahead, step 3 does not
+        y = parallel.sharded_step(ops, mine[k], h, lambda t: dist.all_reduce(t, async_op=True), next_x=ahead)
+        outs.append(np.array(y))
+    rb, re = bounds[rank]
+    np.savez(os.path.join(out_dir, "shard%d.npz" % rank), calls=np.array(repr(ops.calls)), y=np.stack(outs),
+             Ci=layer.Ci[rb:re], Cij=layer.Cij[rb:re], weights=layer.weights[rb:re], Cj=layer.Cj, bias=layer.bias,
+             kbi=layer.kbi, wmask=layer.wmask, rows=np.array([rb, re]))
+    dist.destroy_process_group()
+
+
+def test_two_rank_sharded_step_equals_big_batch(tmp_path):
+    """Two gloo ranks run the row-sharded step's orchestration (column exchange, sum of the partial supports,
+    every owner updating its rows from the global batch, mask swaps on gathered rows; two of the four batches
+    staged one step ahead) and must reproduce the oracle's forward + train step on the whole batches."""
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import oracle
+    from streambrain_b200 import parallel
+    world = 2
+    assert parallel.shard_bounds(SN, world) == [(0, 256), (256, 300)]
+    assert parallel.shard_bounds(55296, 8)[7] == (48384, 55296)
+    assert parallel.shard_bounds(256, 4) == [(0, 128), (128, 256), (256, 256), (256, 256)]   # more ranks than tiles
+    mp.spawn(_shard_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    r = [np.load(tmp_path / ("shard%d.npz" % k)) for k in range(world)]
+    whole = _shard_layer(oracle)
+    ys = []
+    for k, (xb, h) in enumerate(zip(_shard_batches(world, 4), (1, None, 2, 0))):
+        y = whole.compute_activation(xb)
+        whole.train_step(xb, y, h)
+        ys.append(y)
+    for k in range(world):
+        rb, re = r[k]["rows"]
+        for step in range(4):
+            assert rel_inf(r[k]["y"][step], ys[step][k * SB:(k + 1) * SB]) < 1e-11, (k, step)
+        assert np.array_equal(r[k]["wmask"], whole.wmask), k
+        for name in ("Ci", "Cij", "weights"):
+            assert rel_inf(r[k][name], getattr(whole, name)[rb:re]) < 1e-11, (k, name)
+        for name in ("Cj", "bias", "kbi"):
+            assert rel_inf(r[k][name], getattr(whole, name)) < 1e-11, (k, name)
+            assert np.array_equal(r[k][name], r[0][name]), name      # replicated state stays identical
+    calls = eval(str(r[0]["calls"]))
+    kinds = [c[0] for c in calls]
+    assert kinds == ["scatter", "scatter", "forward", "join", "activate", "train", "mask",     # step 0: own + next
+                     "scatter", "forward", "join", "activate", "train",                        # step 1: staged; next
+                     "forward", "activate", "train", "mask",                                   # step 2: staged
+                     "scatter", "forward", "activate", "train", "mask"]                        # step 3: not staged
+    # the gathered-input slots are taken in turn, and a forward pass always takes the oldest staged one
+    assert [c[2] for c in calls if c[0] == "scatter"] == [1, 2, 0, 1]
+    assert [c[1] for c in calls if c[0] == "forward"] == [1, 2, 0, 1]

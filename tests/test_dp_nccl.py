@@ -63,6 +63,7 @@ def _worker(rank, world, port, path, out_dir, sharded=False, staged=False):
     layer = _make_layer(B200, path)
     if sharded:
         layer.shard_rows(rank, world, parallel.all_gather_bytes_over(dist), B_LOCAL)
+        assert [layer.owned_rows(r) for r in range(world)] == parallel.shard_bounds(N, world)
     steps = 2
     all_reduce = lambda t: dist.all_reduce(t, async_op=True)
     batches = _batches(world, steps)
