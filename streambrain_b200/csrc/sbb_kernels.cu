@@ -11,6 +11,7 @@
 // product's x, which is contiguous along the reduction dimension and is
 // transposed on its way into shared memory.
 #include "sbb_kernels.cuh"
+#include "sbb_f64_mma.cuh"
 #include "sbb_math.cuh"
 
 #include <atomic>
@@ -405,11 +406,154 @@ struct TraceEpilogue {
   }
 };
 
+// ----------------------------------------------------------------------------
+// float64 on the FP64 tensor-core instruction (sbb_f64_mma.cuh): the same two epilogues, fed with the
+// accumulator pairs of the mma.sync fragment layout (element (m, n) and (m, n + 1), n even).
+// ----------------------------------------------------------------------------
+struct StorePairs {
+  double *out;
+  long rows, cols, ld, zstride;
+  bool vec;
+  __device__ __forceinline__ void begin(long, long) {}
+  __device__ __forceinline__ void pair(int, int, long m, long n, double c0, double c1, int z) const {
+    if (m >= rows || n >= cols) return;
+    double *p = out + (long)z * zstride + m * ld + n;
+    if (vec) {
+      *reinterpret_cast<double2 *>(p) = make_double2(c0, c1);   // cols is even: n + 1 is inside too
+    } else {
+      p[0] = c0;
+      if (n + 1 < cols) p[1] = c1;
+    }
+  }
+};
+
+struct TracePairs {
+  const double *Ci, *Cj;
+  double *Cij, *W;
+  const uint8_t *wmask;
+  long row0, row_end, M, H, Mc;
+  TraceParams<double> p;
+  bool vec;
+  // per thread: its four rows (8 apart) and its four column pairs (8 apart)
+  double ci[4], cj[4][2];
+  int hc[4][2];
+  bool row_off[4], col_off[4][2];
+  __device__ __forceinline__ void begin(long m_first, long n_first) {
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+      const long i = row0 + m_first + mi * 8;
+      ci[mi] = i < row_end ? Ci[i] : 1.0;
+      row_off[mi] = ci[mi] < p.cthr;
+    }
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const long j = n_first + ni * 8 + e;
+        const bool in = j < M;
+        cj[ni][e] = in ? Cj[j] : 1.0;
+        col_off[ni][e] = cj[ni][e] < p.cthr;
+        hc[ni][e] = in ? (int)(j / Mc) : 0;
+      }
+  }
+  __device__ __forceinline__ void pair(int mi, int ni, long m, long n, double c0, double c1, int) const {
+    const long i = row0 + m;
+    if (i >= row_end || n >= M) return;
+    const bool two = n + 1 < M;
+    double *cp = Cij + i * M + n, *wp = W + i * M + n;
+    double old0, old1 = 0.0;
+    if (vec) {
+      const double2 o = *reinterpret_cast<const double2 *>(cp);
+      old0 = o.x;
+      old1 = o.y;
+    } else {
+      old0 = cp[0];
+      if (two) old1 = cp[1];
+    }
+    const double n0 = trace_ema(old0, c0, p), n1 = trace_ema(old1, c1, p);
+    const uint8_t *mrow = wmask ? wmask + i * H : nullptr;
+    double w0 = 0.0, w1 = 0.0;
+    if (!row_off[mi]) {
+      if (!col_off[ni][0] && (mrow == nullptr || mrow[hc[ni][0]] != 0)) w0 = log_ratio(n0, ci[mi], cj[ni][0], p.cthr4);
+      if (two && !col_off[ni][1] && (mrow == nullptr || mrow[hc[ni][1]] != 0))
+        w1 = log_ratio(n1, ci[mi], cj[ni][1], p.cthr4);
+    }
+    if (vec) {
+      *reinterpret_cast<double2 *>(cp) = make_double2(n0, n1);
+      *reinterpret_cast<double2 *>(wp) = make_double2(w0, w1);
+    } else {
+      cp[0] = n0;
+      wp[0] = w0;
+      if (two) {
+        cp[1] = n1;
+        wp[1] = w1;
+      }
+    }
+  }
+};
+
+static StorePairs to_pairs(const StoreEpilogue<double> &e) { return StorePairs{e.out, e.rows, e.cols, e.ld, e.zstride, e.vec}; }
+static TracePairs to_pairs(const TraceEpilogue<double> &e) {
+  TracePairs t{};
+  t.Ci = e.Ci;
+  t.Cj = e.Cj;
+  t.Cij = e.Cij;
+  t.W = e.W;
+  t.wmask = e.wmask;
+  t.row0 = e.row0;
+  t.row_end = e.row_end;
+  t.M = e.M;
+  t.H = e.H;
+  t.Mc = e.Mc;
+  t.p = e.p;
+  t.vec = e.vec;
+  return t;
+}
+template <typename T>
+static int to_pairs(const T &) { return 0; }   // float32 epilogues never take this path
+
+// SBB_F64_CONTRACTION=dfma keeps float64 on the DFMA tile kernel (read once).
+static bool f64_mma_enabled() {
+  static const bool on = [] {
+    const char *e = getenv("SBB_F64_CONTRACTION");
+    return !(e != nullptr && strcmp(e, "dfma") == 0);
+  }();
+  return on;
+}
+
+template <bool A_KMAJOR, class Pairs>
+static cudaError_t launch_f64_mma(const double *A, long lda, const double *Bm, long ldb, long Mdim, long Ndim, int K,
+                                  int splits, bool cols_fastest, Pairs ep, cudaStream_t st) {
+  namespace F = f64mma;
+  auto kernel = F::contraction_kernel<A_KMAJOR, Pairs>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const unsigned mt = (unsigned)((Mdim + F::BM - 1) / F::BM), nt = (unsigned)((Ndim + F::BN - 1) / F::BN);
+  if (cols_fastest && mt > 65535u) cols_fastest = false;
+  dim3 grid(cols_fastest ? nt : mt, cols_fastest ? mt : nt, (unsigned)splits);
+  if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidConfiguration;
+  const int slabs = (K + F::BK - 1) / F::BK;
+  const int kper = (slabs + splits - 1) / splits * F::BK;
+  kernel<<<grid, F::THREADS, F::SMEM_BYTES, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, cols_fastest, ep);
+  return launched();
+}
+
 template <typename T, bool A_KMAJOR, class Ep>
 static cudaError_t launch_contraction(const T *A, long lda, const T *Bm, long ldb, long Mdim, long Ndim, int K,
                                       int splits, int kper, bool vec, bool cols_fastest, Ep ep, cudaStream_t st) {
   const unsigned mt = (unsigned)((Mdim + 127) / 128), nt = (unsigned)((Ndim + 127) / 128);
   if (mt == 0 || nt == 0 || K <= 0) return cudaSuccess;
+  if constexpr (std::is_same<T, double>::value) {
+    // `vec`: every operand row starts on a 16-byte boundary and holds an even number of elements
+    if (vec && lda % 2 == 0 && ldb % 2 == 0 && f64_mma_enabled())
+      return launch_f64_mma<A_KMAJOR>(A, lda, Bm, ldb, Mdim, Ndim, K, splits, cols_fastest, to_pairs(ep), st);
+  }
   if (cols_fastest && mt > 65535u) cols_fastest = false;
   dim3 grid(cols_fastest ? nt : mt, cols_fastest ? mt : nt, (unsigned)splits);
   if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidConfiguration;
@@ -439,7 +583,8 @@ static int sm_count() {
 
 template <typename T>
 int forward_splits(long B, long N, long M) {
-  const long tiles = ((B + 127) / 128) * ((M + 127) / 128);
+  // output tiles: 128 x 128 (float32 FFMA kernel), 128 x 64 (float64 tensor-core kernel)
+  const long tiles = ((B + 127) / 128) * (sizeof(T) == 8 ? (M + 63) / 64 : (M + 127) / 128);
   const long want = 2L * sm_count();           // two resident CTAs per SM
   long s = tiles >= want ? 1 : want / (tiles > 0 ? tiles : 1);
   const long slabs = (N + Tile<T>::BK - 1) / Tile<T>::BK;
