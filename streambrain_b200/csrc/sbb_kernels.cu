@@ -414,79 +414,127 @@ struct StorePairs {
   double *out;
   long rows, cols, ld, zstride;
   bool vec;
-  __device__ __forceinline__ void begin(long, long) {}
-  __device__ __forceinline__ void pair(int, int, long m, long n, double c0, double c1, int z) const {
-    if (m >= rows || n >= cols) return;
-    double *p = out + (long)z * zstride + m * ld + n;
-    if (vec) {
-      *reinterpret_cast<double2 *>(p) = make_double2(c0, c1);   // cols is even: n + 1 is inside too
-    } else {
-      p[0] = c0;
-      if (n + 1 < cols) p[1] = c1;
+  __device__ __forceinline__ void prefetch(long, long, int) const {}
+  __device__ __forceinline__ void tile(const double (&acc)[4][4][2], long m_first, long n_first, int z) const {
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+      const long m = m_first + mi * 8;
+      if (m >= rows) continue;
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const long n = n_first + ni * 8;
+        if (n >= cols) continue;
+        double *p = out + (long)z * zstride + m * ld + n;
+        if (vec) {
+          *reinterpret_cast<double2 *>(p) = make_double2(acc[mi][ni][0], acc[mi][ni][1]);   // cols is even
+        } else {
+          p[0] = acc[mi][ni][0];
+          if (n + 1 < cols) p[1] = acc[mi][ni][1];
+        }
+      }
     }
   }
 };
 
+// The fused trace epilogue on accumulator pairs.  Its memory accesses are what it waits for, so they are
+// arranged in two phases: first every load the thread needs (its 16 pairs of the old trace, the mask bytes,
+// Ci and Cj; the trace block was requested into L2 before the main loop), folded into the accumulators as
+// they arrive; then the arithmetic and the stores.  With a load, a logarithm and two stores per pair in turn,
+// the sixteen dependent memory round trips per thread left the tensor pipe idle half of the time.
 struct TracePairs {
   const double *Ci, *Cj;
   double *Cij, *W;
   const uint8_t *wmask;
   long row0, row_end, M, H, Mc;
   TraceParams<double> p;
+  double inv_batch;
   bool vec;
-  // per thread: its four rows (8 apart) and its four column pairs (8 apart)
-  double ci[4], cj[4][2];
-  int hc[4][2];
-  bool row_off[4], col_off[4][2];
-  __device__ __forceinline__ void begin(long m_first, long n_first) {
+  __device__ __forceinline__ void prefetch(long m_warp, long n_warp, int lane) const {
+    // the warp's 32 x 32 block of Cij: 256 bytes per row, two 128-byte lines, one request per line
 #pragma unroll
-    for (int mi = 0; mi < 4; ++mi) {
-      const long i = row0 + m_first + mi * 8;
-      ci[mi] = i < row_end ? Ci[i] : 1.0;
-      row_off[mi] = ci[mi] < p.cthr;
+    for (int k = 0; k < 2; ++k) {
+      const int line = lane + 32 * k;
+      const long i = row0 + m_warp + (line >> 1), n = n_warp + (line & 1) * 16;
+      if (i < row_end && n < M) asm volatile("prefetch.global.L2 [%0];" ::"l"(Cij + i * M + n));
     }
+  }
+  __device__ __forceinline__ void tile(double (&acc)[4][4][2], long m_first, long n_first, int) const {
+    // ---- phase 1: loads
+    double rci[4];
+    unsigned on = 0;   // bit 8*mi + 2*ni + e: the element keeps a weight (row, column and mask allow it)
+    double rcj[4][2];
+    int hc[4][2];
+    bool col_on[4][2];
 #pragma unroll
     for (int ni = 0; ni < 4; ++ni)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const long j = n_first + ni * 8 + e;
         const bool in = j < M;
-        cj[ni][e] = in ? Cj[j] : 1.0;
-        col_off[ni][e] = cj[ni][e] < p.cthr;
+        const double cj = in ? Cj[j] : 1.0;
+        col_on[ni][e] = in && !(cj < p.cthr);
+        rcj[ni][e] = col_on[ni][e] ? 1.0 / cj : 0.0;
         hc[ni][e] = in ? (int)(j / Mc) : 0;
       }
-  }
-  __device__ __forceinline__ void pair(int mi, int ni, long m, long n, double c0, double c1, int) const {
-    const long i = row0 + m;
-    if (i >= row_end || n >= M) return;
-    const bool two = n + 1 < M;
-    double *cp = Cij + i * M + n, *wp = W + i * M + n;
-    double old0, old1 = 0.0;
-    if (vec) {
-      const double2 o = *reinterpret_cast<const double2 *>(cp);
-      old0 = o.x;
-      old1 = o.y;
-    } else {
-      old0 = cp[0];
-      if (two) old1 = cp[1];
+    const double scale = inv_batch * p.taupdt;
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+      const long i = row0 + m_first + mi * 8;
+      const bool row_in = i < row_end;
+      const double ci = row_in ? Ci[i] : 1.0;
+      const bool row_on = row_in && !(ci < p.cthr);
+      rci[mi] = row_on ? 1.0 / ci : 0.0;
+      const uint8_t *mrow = wmask ? wmask + i * H : nullptr;
+      double2 old[4];
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const long n = n_first + ni * 8;
+        old[ni] = make_double2(0.0, 0.0);
+        if (row_in && n < M) {
+          const double *cp = Cij + i * M + n;
+          if (vec) old[ni] = *reinterpret_cast<const double2 *>(cp);
+          else old[ni] = make_double2(cp[0], n + 1 < M ? cp[1] : 0.0);
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          if (row_on && col_on[ni][e] && (mrow == nullptr || mrow[hc[ni][e]] != 0)) on |= 1u << (8 * mi + 2 * ni + e);
+      }
+      // the moving average, with the batch mean and the averaging weight folded into one factor (the reciprocal
+      // of the batch size is exact for powers of two, one rounding more otherwise); a NaN clamps to zero
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const double a0 = fma(old[ni].x, p.one_minus, acc[mi][ni][0] * scale);
+        const double a1 = fma(old[ni].y, p.one_minus, acc[mi][ni][1] * scale);
+        acc[mi][ni][0] = a0 > 0.0 ? a0 : 0.0;
+        acc[mi][ni][1] = a1 > 0.0 ? a1 : 0.0;
+      }
     }
-    const double n0 = trace_ema(old0, c0, p), n1 = trace_ema(old1, c1, p);
-    const uint8_t *mrow = wmask ? wmask + i * H : nullptr;
-    double w0 = 0.0, w1 = 0.0;
-    if (!row_off[mi]) {
-      if (!col_off[ni][0] && (mrow == nullptr || mrow[hc[ni][0]] != 0)) w0 = log_ratio(n0, ci[mi], cj[ni][0], p.cthr4);
-      if (two && !col_off[ni][1] && (mrow == nullptr || mrow[hc[ni][1]] != 0))
-        w1 = log_ratio(n1, ci[mi], cj[ni][1], p.cthr4);
-    }
-    if (vec) {
-      *reinterpret_cast<double2 *>(cp) = make_double2(n0, n1);
-      *reinterpret_cast<double2 *>(wp) = make_double2(w0, w1);
-    } else {
-      cp[0] = n0;
-      wp[0] = w0;
-      if (two) {
-        cp[1] = n1;
-        wp[1] = w1;
+    // ---- phase 2: weights and stores.  Cij / (Ci * Cj) by the reciprocals taken above: three roundings more
+    // than the division, a few 1e-16 on the weight.
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+      const long i = row0 + m_first + mi * 8;
+      if (i >= row_end) continue;
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const long n = n_first + ni * 8;
+        if (n >= M) continue;
+        const double n0 = acc[mi][ni][0], n1 = acc[mi][ni][1];
+        double w0 = 0.0, w1 = 0.0;
+        if (on & (1u << (8 * mi + 2 * ni))) w0 = f64mma::log_positive((n0 < p.cthr4 ? p.cthr4 : n0) * (rci[mi] * rcj[ni][0]));
+        if (on & (2u << (8 * mi + 2 * ni))) w1 = f64mma::log_positive((n1 < p.cthr4 ? p.cthr4 : n1) * (rci[mi] * rcj[ni][1]));
+        double *cp = Cij + i * M + n, *wp = W + i * M + n;
+        if (vec) {
+          *reinterpret_cast<double2 *>(cp) = make_double2(n0, n1);
+          *reinterpret_cast<double2 *>(wp) = make_double2(w0, w1);
+        } else {
+          cp[0] = n0;
+          wp[0] = w0;
+          if (n + 1 < M) {
+            cp[1] = n1;
+            wp[1] = w1;
+          }
+        }
       }
     }
   }
@@ -506,6 +554,7 @@ static TracePairs to_pairs(const TraceEpilogue<double> &e) {
   t.H = e.H;
   t.Mc = e.Mc;
   t.p = e.p;
+  t.inv_batch = 1.0 / e.p.batch;
   t.vec = e.vec;
   return t;
 }
