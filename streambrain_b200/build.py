@@ -44,10 +44,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found; libsbb200.so must be built where the CUDA toolkit is installed")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-I" + INCLUDE, "-o", LIB] + sources()
+    # linked under another name and moved into place: an interrupted build never leaves a torn library behind
+    tmp = LIB + ".%d.tmp" % os.getpid()
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-I" + INCLUDE, "-o", tmp] + sources()
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed:\n%s\n%s\n%s" % (" ".join(cmd), proc.stdout, proc.stderr))
+    os.replace(tmp, LIB)
     if verbose:
         print(proc.stderr)
     return LIB

@@ -4,9 +4,11 @@
 // the register file (32 accumulators per thread instead of 64) are left with room to hide latencies:
 // two CTAs of eight warps per SM instead of one.
 //
-// CTA tile 128 x 64, k-slabs of 16 in a three-stage cp.async pipeline, warp tile 32 x 32 (4 x 4
-// instruction tiles).  Shared-memory rows are padded so that a half-warp's fragment loads (four
-// rows of four consecutive doubles) fall into 16 different bank pairs.
+// CTA tile 128 x 64 (eight warps, two CTAs per SM) or 64 x 64 (four warps, three CTAs per SM: for
+// launches whose 128-row tiles would leave most of a last round of CTAs empty), k-slabs of 16 in a
+// three-stage cp.async pipeline, warp tile 32 x 32 (4 x 4 instruction tiles).  Shared-memory rows
+// are padded so that a half-warp's fragment loads (four rows of four consecutive doubles) fall into
+// 16 different bank pairs.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -14,13 +16,19 @@
 namespace sbb {
 namespace f64mma {
 
-constexpr int BM = 128, BN = 64, BK = 16, STAGES = 3, THREADS = 256;
+constexpr int BN = 64, BK = 16, STAGES = 3;
 constexpr int LDA_K = BK + 4;   // K-major A in shared memory: [m][k]
-constexpr int LDA_M = BM + 4;   // MN-major A: [k][m]
 constexpr int LDB = BN + 4;     // B: [k][n]
-constexpr int A_STAGE = BM * LDA_K > BK * LDA_M ? BM * LDA_K : BK * LDA_M;   // doubles
 constexpr int B_STAGE = BK * LDB;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE + B_STAGE) * sizeof(double);
+template <int BM>
+struct Cfg {
+  static_assert(BM == 128 || BM == 64, "row tiles of 128 or 64");
+  static constexpr int THREADS = BM * 2;        // (BM / 32) x 2 warps
+  static constexpr int CTAS_PER_SM = BM == 128 ? 2 : 3;
+  static constexpr int LDA_M = BM + 4;          // MN-major A: [k][m]
+  static constexpr int A_STAGE = BM * LDA_K > BK * LDA_M ? BM * LDA_K : BK * LDA_M;   // doubles
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE + B_STAGE) * sizeof(double);
+};
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -134,10 +142,11 @@ __device__ __forceinline__ double log_positive(double x) {
 // One k-slab of both operands into stage buffers As / Bs (zero-filled outside the operands).
 // A is [K x Mdim] MN-major (element (k, m) at A[k*lda + m]) or, A_KMAJOR, [Mdim x K] (at A[m*lda + k]);
 // B is [K x Ndim] MN-major.  All row starts and the 2-element chunks are 16-byte aligned (checked by the host).
-template <bool A_KMAJOR>
+template <bool A_KMAJOR, int BM>
 __device__ __forceinline__ void load_slab(double *As, double *Bs, const double *__restrict__ A, long lda,
                                           const double *__restrict__ Bm, long ldb, long m0, long Mdim, long n0,
                                           long Ndim, int k0, int kend) {
+  constexpr int THREADS = Cfg<BM>::THREADS, LDA_M = Cfg<BM>::LDA_M;
   const int tid = threadIdx.x;
   if constexpr (A_KMAJOR) {
 #pragma unroll
@@ -175,10 +184,11 @@ __device__ __forceinline__ void load_slab(double *As, double *Bs, const double *
 // k-split z covers [z*kper, min(K, (z+1)*kper)), kper a multiple of BK.  The epilogue receives the thread's
 // accumulators: ep.tile(acc, m, n, z) with acc[mi][ni][e] = output element (m + 8*mi, n + 8*ni + e), n even;
 // ep.prefetch(m, n, lane) is called before the main loop with the first element of the warp's 32 x 32 block.
-template <bool A_KMAJOR, class Epilogue>
-__global__ void __launch_bounds__(THREADS, 2)
+template <bool A_KMAJOR, int BM, class Epilogue>
+__global__ void __launch_bounds__(Cfg<BM>::THREADS, Cfg<BM>::CTAS_PER_SM)
     contraction_kernel(const double *__restrict__ A, long lda, const double *__restrict__ Bm, long ldb, long Mdim,
                        long Ndim, int K, int kper, bool cols_fastest, Epilogue ep) {
+  constexpr int A_STAGE = Cfg<BM>::A_STAGE, LDA_M = Cfg<BM>::LDA_M;
   extern __shared__ __align__(16) double smem[];
   double *As = smem, *Bs = smem + STAGES * A_STAGE;
   const long m0 = (long)(cols_fastest ? blockIdx.y : blockIdx.x) * BM;
@@ -187,7 +197,7 @@ __global__ void __launch_bounds__(THREADS, 2)
   const int kend = min(K, kbeg + kper);
   const int nk = kend > kbeg ? (kend - kbeg + BK - 1) / BK : 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;   // the warp's 32 x 32 block of the tile
+  const int wm = (warp % (BM / 32)) * 32, wn = (warp / (BM / 32)) * 32;   // the warp's 32 x 32 block of the tile
   const int g = lane >> 2, t = lane & 3;
 
   double acc[4][4][2];
@@ -199,7 +209,7 @@ __global__ void __launch_bounds__(THREADS, 2)
   ep.prefetch(m0 + wm, n0 + wn, lane);
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < nk) load_slab<A_KMAJOR>(As + s * A_STAGE, Bs + s * B_STAGE, A, lda, Bm, ldb, m0, Mdim, n0, Ndim, kbeg + s * BK, kend);
+    if (s < nk) load_slab<A_KMAJOR, BM>(As + s * A_STAGE, Bs + s * B_STAGE, A, lda, Bm, ldb, m0, Mdim, n0, Ndim, kbeg + s * BK, kend);
     cp_async_commit();
   }
   for (int kt = 0; kt < nk; ++kt) {
@@ -209,7 +219,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       const int nx = kt + STAGES - 1;
       if (nx < nk) {
         const int s = nx % STAGES;
-        load_slab<A_KMAJOR>(As + s * A_STAGE, Bs + s * B_STAGE, A, lda, Bm, ldb, m0, Mdim, n0, Ndim, kbeg + nx * BK, kend);
+        load_slab<A_KMAJOR, BM>(As + s * A_STAGE, Bs + s * B_STAGE, A, lda, Bm, ldb, m0, Mdim, n0, Ndim, kbeg + nx * BK, kend);
       }
       cp_async_commit();
     }

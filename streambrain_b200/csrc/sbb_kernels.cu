@@ -570,27 +570,47 @@ static bool f64_mma_enabled() {
   return on;
 }
 
-template <bool A_KMAJOR, class Pairs>
-static cudaError_t launch_f64_mma(const double *A, long lda, const double *Bm, long ldb, long Mdim, long Ndim, int K,
-                                  int splits, bool cols_fastest, Pairs ep, cudaStream_t st) {
+static int sm_count();
+
+template <bool A_KMAJOR, int BM, class Pairs>
+static cudaError_t launch_f64_mma_tiles(const double *A, long lda, const double *Bm, long ldb, long Mdim, long Ndim,
+                                        int K, int splits, bool cols_fastest, Pairs ep, cudaStream_t st) {
   namespace F = f64mma;
-  auto kernel = F::contraction_kernel<A_KMAJOR, Pairs>;
+  using C = F::Cfg<BM>;
+  auto kernel = F::contraction_kernel<A_KMAJOR, BM, Pairs>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const unsigned mt = (unsigned)((Mdim + F::BM - 1) / F::BM), nt = (unsigned)((Ndim + F::BN - 1) / F::BN);
+  const unsigned mt = (unsigned)((Mdim + BM - 1) / BM), nt = (unsigned)((Ndim + F::BN - 1) / F::BN);
   if (cols_fastest && mt > 65535u) cols_fastest = false;
   dim3 grid(cols_fastest ? nt : mt, cols_fastest ? mt : nt, (unsigned)splits);
   if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidConfiguration;
   const int slabs = (K + F::BK - 1) / F::BK;
   const int kper = (slabs + splits - 1) / splits * F::BK;
-  kernel<<<grid, F::THREADS, F::SMEM_BYTES, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, cols_fastest, ep);
+  kernel<<<grid, C::THREADS, C::SMEM_BYTES, st>>>(A, lda, Bm, ldb, Mdim, Ndim, K, kper, cols_fastest, ep);
   return launched();
+}
+
+// Row tiles of 128 unless 64 finishes in fewer rounds of resident CTAs: time ~ rounds x (rows of a tile) x (CTAs
+// that share an SM).  1568 x 3000 outputs: 611 tiles of 128 rows are two full rounds of 296 CTAs and a third with
+// 19, 1175 tiles of 64 rows three rounds of 444 half-sized CTAs.
+template <bool A_KMAJOR, class Pairs>
+static cudaError_t launch_f64_mma(const double *A, long lda, const double *Bm, long ldb, long Mdim, long Ndim, int K,
+                                  int splits, bool cols_fastest, Pairs ep, cudaStream_t st) {
+  namespace F = f64mma;
+  const long nt = (Ndim + F::BN - 1) / F::BN, sms = sm_count();
+  auto cost = [&](long bm, long ctas_per_sm) {
+    const long tiles = ((Mdim + bm - 1) / bm) * nt * splits, slots = sms * ctas_per_sm;
+    return ((tiles + slots - 1) / slots) * bm * ctas_per_sm;
+  };
+  if (cost(64, F::Cfg<64>::CTAS_PER_SM) < cost(128, F::Cfg<128>::CTAS_PER_SM))
+    return launch_f64_mma_tiles<A_KMAJOR, 64>(A, lda, Bm, ldb, Mdim, Ndim, K, splits, cols_fastest, ep, st);
+  return launch_f64_mma_tiles<A_KMAJOR, 128>(A, lda, Bm, ldb, Mdim, Ndim, K, splits, cols_fastest, ep, st);
 }
 
 template <typename T, bool A_KMAJOR, class Ep>
