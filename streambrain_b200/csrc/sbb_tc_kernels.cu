@@ -32,6 +32,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -194,6 +195,53 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+// ---- CTA pairs (cluster of two CTAs driving one 256-row tcgen05.mma.cta_group::2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrival on the mbarrier at the same shared-memory offset in CTA `rank` of the cluster (own rank: local).
+__device__ __forceinline__ void mbar_arrive_rank(uint32_t bar, uint32_t rank) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+      ::"r"(bar), "r"(rank)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[256 x N] (+)= A[256 x 8] * B[8 x N] over the pair: each CTA holds its 128 rows of A and D in its own tensor
+// memory and N / 2 columns of B in its own shared memory, all at the same addresses; issued by the leader alone.
+__device__ __forceinline__ void mma_tf32_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Completion of the pair's MMAs issued so far, signalled on the mbarrier at this offset in both CTAs.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -303,10 +351,11 @@ constexpr int kSlabBytes = 32 * 32 * 4;  // one epilogue warp's 32-row x 32-colu
 // PRESPLIT: the low parts of both operands come from memory (written by the column-sum kernels that run just
 // before), so a stage is four TMA landing zones [A | B | B lo | A lo], nothing is converted inside the kernel
 // and the tensor core takes both operands from shared memory.
-template <int BN, int BK, int STAGES, bool SLABS, bool PRESPLIT = false>
+// PAIR: two CTAs share one 256-row MMA; each stages its own 128 rows of A and BN / 2 columns of B.
+template <int BN, int BK, int STAGES, bool SLABS, bool PRESPLIT = false, bool PAIR = false>
 struct TcSmem {
   static constexpr int A_BYTES = 128 * BK * 4;
-  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 4;
   static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // TMA landing zone: the raw values serve as "hi"
   static constexpr int STAGE_BYTES = PRESPLIT ? 2 * RAW_BYTES : RAW_BYTES + B_BYTES;   // + B's lo parts (+ A's)
   static constexpr int TX_BYTES = PRESPLIT ? 2 * RAW_BYTES : RAW_BYTES;                // bytes TMA lands per stage
@@ -360,7 +409,8 @@ __device__ __forceinline__ void tmem_ld_pair(uint32_t taddr_lo, uint32_t taddr_h
 // MULTI (kernels without register-resident sums, CHAIN == 0): the k-range of a tile is cut into chains of
 // wk.chain_kb k-blocks and the epilogue carries the running sum through its output in memory; without it a
 // tile is one chain and the epilogue is the plain one.
-template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false, bool PRESPLIT = false>
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false, bool PRESPLIT = false,
+          bool PAIR = false>
 // 14 warps are allocated registers as 16: 128 registers per thread is the most that fits one CTA per SM.
 __global__ void __launch_bounds__(kThreads, 1)
     tc_contraction_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -368,8 +418,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                           const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAlo,
                           const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmA3lo,
                           const __grid_constant__ CUtensorMap tmB3lo, TcWork wk, TcEpilogue ep, int *status) {
-  using SM = TcSmem<BN, BK, STAGES, FUSED || !A_KMAJOR, PRESPLIT>;
+  using SM = TcSmem<BN, BK, STAGES, FUSED || !A_KMAJOR, PRESPLIT, PAIR>;
   static_assert(!(PRESPLIT && A_KMAJOR), "pre-split operands are the two MN-major ones of the batch contractions");
+  static_assert(!PAIR || (FUSED && !A_KMAJOR && !PRESPLIT && !MULTI && CHAIN == 0 && BN % 64 == 0),
+                "CTA pairs are built for the single-chain fused trace update");
+  // In a pair, CTA `rank` of the cluster works on row tile 2 * (pair's tile) + rank; the leader (rank 0) issues the MMAs.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  constexpr int BNH = PAIR ? BN / 2 : BN;   // columns of B this CTA stages
   static_assert(!A_KMAJOR || BK == 32, "a K-major operand is loaded as one 128-byte-wide box");
   static_assert(BN % 64 == 0 && BN <= 256 && BK % 8 == 0 && BK <= 32, "tile shape");
   static_assert(!(FUSED && CHAIN > 0), "the fused epilogue consumes a whole-range accumulator");
@@ -395,12 +450,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_conv(s), kConvWarps * 32);
+      mbar_init(bar_conv(s), (PAIR ? 2 : 1) * kConvWarps * 32);   // the leader's counts both CTAs' converters
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full(b), 1);
-      mbar_init(bar_acc_empty(b), kEpiWarps * 32);
+      mbar_init(bar_acc_empty(b), (PAIR ? 2 : 1) * kEpiWarps * 32);
     }
     mbar_init(bar_drain, 1);
     for (int e = 0; e < kEpiWarps; ++e) {
@@ -412,28 +467,39 @@ __global__ void __launch_bounds__(kThreads, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(tmem_slot), SM::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), SM::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), SM::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const long total = (long)wk.m_tiles * wk.n_tiles * wk.splits;
+  // PAIR: the work items are pairs of row tiles, and the two CTAs of a cluster walk them together
+  const int m_units = PAIR ? (wk.m_tiles + 1) / 2 : wk.m_tiles;
+  const long total = (long)m_units * wk.n_tiles * wk.splits;
+  const long w_first = PAIR ? (long)(blockIdx.x >> 1) : (long)blockIdx.x;
+  const long w_step = PAIR ? (long)(gridDim.x >> 1) : (long)gridDim.x;
   // Decode a work index into (m_tile, n_tile, split) and its k-block range.
   auto decode = [&](long w, int &mt, int &nt, int &sp, int &kbeg, int &nkb) {
     if (wk.m_fastest) {
-      mt = (int)(w % wk.m_tiles);
-      const long r = w / wk.m_tiles;
+      mt = (int)(w % m_units);
+      const long r = w / m_units;
       nt = (int)(r % wk.n_tiles);
       sp = (int)(r / wk.n_tiles);
     } else {
       nt = (int)(w % wk.n_tiles);
       const long r = w / wk.n_tiles;
-      mt = (int)(r % wk.m_tiles);
-      sp = (int)(r / wk.m_tiles);
+      mt = (int)(r % m_units);
+      sp = (int)(r / m_units);
     }
+    if (PAIR) mt = 2 * mt + (int)rank;   // may be one past the last row tile: such a CTA stages zeros and stores nothing
     kbeg = sp * wk.k_per_split;
     const int kend = min(wk.k_total, kbeg + wk.k_per_split);
     nkb = (kend - kbeg + BK - 1) / BK;
@@ -444,7 +510,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      for (long w = w_first; w < total && ok; w += w_step) {
         int mt, nt, sp, kbeg, nkb;
         decode(w, mt, nt, sp, kbeg, nkb);
         auto prefetch_b = [&](int kb) {   // k-block kb of this unit's B operand -> L2
@@ -462,8 +528,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t ph = (it / STAGES) & 1u;
           if (wk.b_prefetch > 0 && kb + wk.b_prefetch < nkb) prefetch_b(kb + wk.b_prefetch);
           if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status, kWaitEmpty)) { ok = false; break; }
-          if (kb == 0) TC_TRACE((w - blockIdx.x) / gridDim.x, 0);
-          if (kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 8);
+          if (kb == 0) TC_TRACE((w - w_first) / w_step, 0);
+          if (kb == nkb - 1) TC_TRACE((w - w_first) / w_step, 8);
           mbar_arrive_expect_tx(bar_full(s), SM::TX_BYTES);
           const uint32_t a_dst = base + s * SM::STAGE_BYTES;
           const uint32_t b_dst = a_dst + SM::A_BYTES;
@@ -494,12 +560,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int c = 0; c < 4; ++c)
               tma_load_2d(a_dst + c * (BK * 128), &tmA, wk.a_row0 + mt * 128 + 32 * c, k0, bar_full(s));
           }
+          // (PAIR: this CTA's half of the tile's columns; the 3-D map's box is BNH / 32 chunks deep)
           if (nt < wk.b_box3_tiles) {
-            tma_load_3d(b_dst, &tmB3, 0, k0, nt * (BN / 32), bar_full(s));
+            tma_load_3d(b_dst, &tmB3, 0, k0, nt * (BN / 32) + (int)rank * (BNH / 32), bar_full(s));
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c)
-              tma_load_2d(b_dst + c * (BK * 128), &tmB, nt * BN + 32 * c, k0, bar_full(s));
+            for (int c = 0; c < BNH / 32; ++c)
+              tma_load_2d(b_dst + c * (BK * 128), &tmB, nt * BN + (int)rank * BNH + 32 * c, k0, bar_full(s));
           }
         }
       }
@@ -513,14 +580,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       // D float32, A and B TF32; A (tensor memory) K-major, B (shared memory) MN-major
-      // (PRESPLIT: A from shared memory too, MN-major like B)
+      // (PRESPLIT: A from shared memory too, MN-major like B; PAIR: 256 rows over the two CTAs)
       constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((PRESPLIT ? 1u : 0u) << 15) | (1u << 16) |
-                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((PAIR ? 256 : 128) >> 4) << 24);
       uint32_t it = 0, chain = 0;
       bool ok = true;
-      for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      for (long w = w_first; w < total && ok; w += w_step) {
         int mt, nt, sp, kbeg, nkb;
         decode(w, mt, nt, sp, kbeg, nkb);
         int kb = 0;
@@ -554,6 +621,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mma_tf32_ss(d_tmem, da_lo, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
                 mma_tf32_ss(d_tmem, da_hi, db_lo, idesc, 1u);
                 mma_tf32_ss(d_tmem, da_hi, db_hi, idesc, 1u);
+              } else if constexpr (PAIR) {
+                mma_tf32_ts_pair(d_tmem, ta_hi + BK + kk * 8, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
+                mma_tf32_ts_pair(d_tmem, ta_hi + kk * 8, db_lo, idesc, 1u);
+                mma_tf32_ts_pair(d_tmem, ta_hi + kk * 8, db_hi, idesc, 1u);
               } else {
                 mma_tf32_ts(d_tmem, ta_hi + BK + kk * 8, db_hi, idesc, (first && kk == 0) ? 0u : 1u);
                 mma_tf32_ts(d_tmem, ta_hi + kk * 8, db_lo, idesc, 1u);
@@ -561,33 +632,37 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
             }
             first = false;
-            mma_commit(bar_empty(s));  // the stage may be refilled once these MMAs have read it
+            // the stage may be refilled once these MMAs have read it (PAIR: in both CTAs)
+            if constexpr (PAIR) mma_commit_pair(bar_empty(s));
+            else mma_commit(bar_empty(s));
           }
           if (ok) {
             TC_TRACE(chain, 2);
-            mma_commit(bar_acc_full(buf));
+            if constexpr (PAIR) mma_commit_pair(bar_acc_full(buf));
+            else mma_commit(bar_acc_full(buf));
             ++chain;
           }
         }
       }
       // Drain: nothing of this CTA may still be running in the tensor pipe when TMEM is freed.
       // (bounded by time alone: also a CTA that is giving up lets its MMAs in flight finish before TMEM goes)
-      mma_commit(bar_drain);
+      if constexpr (PAIR) mma_commit_pair(bar_drain);   // (the peer's copy of this barrier is not waited on)
+      else mma_commit(bar_drain);
       if (!mbar_try_wait(bar_drain, 0)) mbar_wait_slow(bar_drain, 0, abort_flag, status, kWaitDrain, false);
     }
   } else if (warp < kConvWarps) {
     // ------------------------------------------------------------ hi / lo converters (idle when PRESPLIT)
     uint32_t it = 0;
     bool ok = true;
-    for (long w = blockIdx.x; !PRESPLIT && w < total && ok; w += gridDim.x) {
+    for (long w = w_first; !PRESPLIT && w < total && ok; w += w_step) {
       int mt, nt, sp, kbeg, nkb;
       decode(w, mt, nt, sp, kbeg, nkb);
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         if (!mbar_wait(bar_full(s), ph, abort_flag, status, kWaitFull)) { ok = false; break; }
-        if (threadIdx.x == 0 && kb == 0) TC_TRACE((w - blockIdx.x) / gridDim.x, 5);
-        if (threadIdx.x == 0 && kb == nkb - 1) TC_TRACE((w - blockIdx.x) / gridDim.x, 9);
+        if (threadIdx.x == 0 && kb == 0) TC_TRACE((w - w_first) / w_step, 5);
+        if (threadIdx.x == 0 && kb == nkb - 1) TC_TRACE((w - w_first) / w_step, 9);
         static_assert(kConvWarps == 4, "one A row (tensor-memory lane) per converter thread");
         // A: this thread's row of the tile goes to its lane of tensor memory, hi (the raw bits) in BK
         // columns and lo in the next BK.
@@ -632,7 +707,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_before();
         fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
         // (test hook: one lost arrival leaves the MMA warp waiting until its time limit, see tc_debug_lose_arrive)
-        if (!(wk.lose_arrive && it == 0 && threadIdx.x == 0 && blockIdx.x == 0)) mbar_arrive(bar_conv(s));
+        if (!(wk.lose_arrive && it == 0 && threadIdx.x == 0 && blockIdx.x == 0)) {
+          if constexpr (PAIR) mbar_arrive_rank(bar_conv(s), 0);   // the leader's MMA warp waits for both CTAs
+          else mbar_arrive(bar_conv(s));
+        }
       }
     }
   } else {
@@ -662,9 +740,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       tma_load_2d(base + SM::SLAB_OFFSET + (ew * 2 + b) * kSlabBytes, &tmC, nt * BN + ch * (BN / 2) + g * 32,
                   (int)ep.row0 + mt * 128 + 32 * q, bar_slab(ew, b));
     };
-    if (FUSED && lane == 0 && (long)blockIdx.x < total) {
+    if (FUSED && lane == 0 && w_first < total) {
       int mt, nt, sp, kbeg, nkb;
-      decode(blockIdx.x, mt, nt, sp, kbeg, nkb);
+      decode(w_first, mt, nt, sp, kbeg, nkb);
       issue_slab_at(0, mt, nt, 0);
       issue_slab_at(1, mt, nt, 1);
     }
@@ -694,13 +772,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ++stores;
     };
-    for (long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+    for (long w = w_first; w < total && ok; w += w_step) {
       int mt, nt, sp, kbeg, nkb;
       decode(w, mt, nt, sp, kbeg, nkb);
       int mt_next = 0, nt_next = 0;
-      if (FUSED && w + gridDim.x < total) {
+      if (FUSED && w + w_step < total) {
         int sp2, kb2, nk2;
-        decode(w + gridDim.x, mt_next, nt_next, sp2, kb2, nk2);
+        decode(w + w_step, mt_next, nt_next, sp2, kb2, nk2);
       }
       const long m_base = (long)mt * 128 + 32 * q;   // first tile row of this warp's lane quarter
       const long n_base = (long)nt * BN + ch * (BN / 2);
@@ -890,7 +968,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                   // block slab+2: two column groups ahead in this tile, or the next tile's first groups.  With
                   // several chains the blocks of the next pass are fetched at the end of this one (below).
                   if (g + 2 < NG) issue_slab_at(slab + 2, mt, nt, g + 2);
-                  else if (!MULTI && w + gridDim.x < total) issue_slab_at(slab + 2, mt_next, nt_next, g + 2 - NG);
+                  else if (!MULTI && w + w_step < total) issue_slab_at(slab + 2, mt_next, nt_next, g + 2 - NG);
                 }
               }
               if (g_fast) {
@@ -974,7 +1052,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               if (!last_chain) {
                 issue_slab_at(slab, mt, nt, 0);
                 issue_slab_at(slab + 1, mt, nt, 1);
-              } else if (w + gridDim.x < total) {
+              } else if (w + w_step < total) {
                 issue_slab_at(slab, mt_next, nt_next, 0);
                 issue_slab_at(slab + 1, mt_next, nt_next, 1);
               }
@@ -1015,7 +1093,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) break;
         if (threadIdx.x == kConvWarps * 32) TC_TRACE(chain, 4);
         tc_fence_before();
-        mbar_arrive(bar_acc_empty(buf));  // the accumulator buffer may be overwritten
+        // the accumulator buffer may be overwritten (PAIR: the leader's MMA warp waits for both CTAs' epilogues)
+        if constexpr (PAIR) mbar_arrive_rank(bar_acc_empty(buf), 0);
+        else mbar_arrive(bar_acc_empty(buf));
         ++chain;
        }   // chains of this tile
       }
@@ -1027,10 +1107,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ------------------------------------------------------------ tear-down
   __syncwarp();
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // neither CTA retires while the other may still signal it or read its operands
+  else __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, SM::TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, SM::TMEM_COLS);
+    else tmem_dealloc(tmem_base, SM::TMEM_COLS);
   }
 }
 
@@ -1210,6 +1292,52 @@ cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, 
   return cudaGetLastError();
 }
 
+// The CTA-pair form of the fused trace update: clusters of two CTAs, one 256 x BN tile per pair.
+template <int BN, int BK, int STAGES>
+cudaError_t launch_tc_pair(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st) {
+  using SM = TcSmem<BN, BK, STAGES, true, false, true>;
+  int *status = status_word();
+  if (status == nullptr) return cudaErrorMemoryAllocation;
+  auto kernel = tc_contraction_kernel<false, BN, BK, STAGES, true, 0, false, false, true>;
+  static std::atomic<bool> configured[64];
+  const int dev = current_device();
+  if (!configured[dev].load()) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured[dev].store(true);
+  }
+  const long pairs = (long)((wk.m_tiles + 1) / 2) * wk.n_tiles * wk.splits;
+  if (pairs <= 0) return cudaSuccess;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = SM::TOTAL;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // as many pairs as can be resident at once (one CTA per SM; pairs must share a GPC's SMs)
+  static int max_clusters[64] = {0};
+  if (max_clusters[dev] == 0) {
+    cfg.gridDim = dim3((unsigned)(g_sm_count_tc[dev] / 2 * 2), 1, 1);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) n = g_sm_count_tc[dev] / 2;
+    max_clusters[dev] = n;
+  }
+  long clusters = max_clusters[dev] < g_sm_count_tc[dev] / 2 ? max_clusters[dev] : g_sm_count_tc[dev] / 2;
+  if (clusters > pairs) clusters = pairs;
+  cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+  if (getenv("SBB_TC_DEBUG")) {
+    static int said = 0;
+    if (!said++) fprintf(stderr, "pair launch: max active clusters %d, grid %ld CTAs, pairs %ld\n", max_clusters[dev], 2 * clusters, pairs);
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, tm.a, tm.b, tm.a3, tm.b3, tm.c, tm.alo, tm.blo, tm.a3lo, tm.b3lo, wk, ep,
+                            status);
+}
+
 }  // namespace
 
 // Launch counter shared with the general-shape kernels (defined in sbb_kernels.cu).
@@ -1237,6 +1365,7 @@ constexpr int kTrBN = 192, kTrBK = 16, kTrStages = 4;
 // epilogue takes the partial sum over in float32.  Measured on B200: the tensor-memory accumulate truncates,
 // so a chain's sum is low by about 1e-8 x (samples in the chain) relative; 256 keeps that below 4e-6.
 constexpr int kTrChainKb = 16;
+constexpr int kPairStages = 4;   // (tensor memory holds the A parts of four stages beside the two accumulators)
 constexpr int kLongBN = 128, kLongStages = 5;   // tiles of the row-block product when the batch spans several chains
 
 // k-blocks per split and the number of (non-empty) splits for the forward product: the split count
@@ -1392,7 +1521,17 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   // The fused kernel splits its operands itself (A's parts go to tensor memory): with pre-split planes both
   // operands would come from shared memory, whose bandwidth the Cij blocks of the epilogue also need; measured
   // on the 55296 x 3000 layer the launch takes 0.608 ms that way against 0.587 ms.
-  if (!batch_operand_maps(tm, x, y, nullptr, nullptr, false, B, N, M, kTrBN, a3, b3)) return cudaErrorInvalidValue;
+  // a batch of more than one chain carries its running sum through the trace matrix (see the kernel)
+  const bool multi = B > (long)kTrChainKb * kTrBK;
+  // CTA pairs (one 256-row MMA over two SMs, each staging half of the tile's columns of y): single-chain batches
+  static const bool pair_wanted = [] {   // SBB_TC_PAIR=0 keeps one CTA per tile
+    const char *e = getenv("SBB_TC_PAIR");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  const bool pair = pair_wanted && !multi;
+  // (pairs: y's one-box 3-D map covers half a tile's column chunks)
+  if (!batch_operand_maps(tm, x, y, nullptr, nullptr, false, B, N, M, pair ? kTrBN / 2 : kTrBN, a3, b3))
+    return cudaErrorInvalidValue;
   if (!make_map(&tm.c, Cij, M, N, 32, 32, false)) return cudaErrorInvalidValue;   // 32 x 32 blocks, 128-byte swizzle
   const long rows = row_end - row_begin;
   const int kper = (int)((B + kTrBK - 1) / kTrBK) * kTrBK;
@@ -1425,10 +1564,9 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   ep.row0 = row_begin;
   ep.p = p;
   ep.ema_scale = p.taupdt / p.batch;
-  // a batch of more than one chain carries its running sum through the trace matrix (see the kernel)
-  const bool multi = B > (long)kTrChainKb * kTrBK;
-  cudaError_t e = multi ? launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0, true>(tm, wk, ep, st)
-                        : launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
+  cudaError_t e = multi  ? launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0, true>(tm, wk, ep, st)
+                  : pair ? launch_tc_pair<kTrBN, kTrBK, kPairStages>(tm, wk, ep, st)
+                         : launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
