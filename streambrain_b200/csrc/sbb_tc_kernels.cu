@@ -420,8 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                           const __grid_constant__ CUtensorMap tmB3lo, TcWork wk, TcEpilogue ep, int *status) {
   using SM = TcSmem<BN, BK, STAGES, FUSED || !A_KMAJOR, PRESPLIT, PAIR>;
   static_assert(!(PRESPLIT && A_KMAJOR), "pre-split operands are the two MN-major ones of the batch contractions");
-  static_assert(!PAIR || (FUSED && !A_KMAJOR && !PRESPLIT && !MULTI && CHAIN == 0 && BN % 64 == 0),
-                "CTA pairs are built for the single-chain fused trace update");
+  static_assert(!PAIR || (!PRESPLIT && BN % 64 == 0), "CTA pairs convert their operands themselves");
   // In a pair, CTA `rank` of the cluster works on row tile 2 * (pair's tile) + rank; the leader (rank 0) issues the MMAs.
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
   constexpr int BNH = PAIR ? BN / 2 : BN;   // columns of B this CTA stages
@@ -817,7 +816,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
           tc_fence_before();
-          mbar_arrive(bar_acc_empty(buf));
+          if constexpr (PAIR) mbar_arrive_rank(bar_acc_empty(buf), 0);
+          else mbar_arrive(bar_acc_empty(buf));
         }
         if (ok && !A_KMAJOR && ep.tma_store) {
 #pragma unroll
@@ -1292,13 +1292,22 @@ cudaError_t launch_tc(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, 
   return cudaGetLastError();
 }
 
-// The CTA-pair form of the fused trace update: clusters of two CTAs, one 256 x BN tile per pair.
-template <int BN, int BK, int STAGES>
+// SBB_TC_PAIR=0 keeps one CTA per tile (read once).
+bool pairs_enabled() {
+  static const bool on = [] {
+    const char *e = getenv("SBB_TC_PAIR");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+// The CTA-pair form of a kernel: clusters of two CTAs, one 256 x BN tile per pair.
+template <bool A_KMAJOR, int BN, int BK, int STAGES, bool FUSED, int CHAIN, bool MULTI = false>
 cudaError_t launch_tc_pair(const TcMaps &tm, const TcWork &wk, const TcEpilogue &ep, cudaStream_t st) {
-  using SM = TcSmem<BN, BK, STAGES, true, false, true>;
+  using SM = TcSmem<BN, BK, STAGES, FUSED || !A_KMAJOR, false, true>;
   int *status = status_word();
   if (status == nullptr) return cudaErrorMemoryAllocation;
-  auto kernel = tc_contraction_kernel<false, BN, BK, STAGES, true, 0, false, false, true>;
+  auto kernel = tc_contraction_kernel<A_KMAJOR, BN, BK, STAGES, FUSED, CHAIN, MULTI, false, true>;
   static std::atomic<bool> configured[64];
   const int dev = current_device();
   if (!configured[dev].load()) {
@@ -1417,7 +1426,9 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   if (!make_map(&tm.a, x, N, B, 32, 128, false) || !make_map(&tm.b, w, M, N, 32, kFwdBK, true)) return cudaErrorInvalidValue;
   tm.a3 = tm.a;
   tm.c = tm.a;
-  const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, kFwdBN / 32);
+  // CTA pairs when the row tiles pair up: the two CTAs that need the same tile of W each fetch half of it
+  const bool pair = pairs_enabled() && ((B + 127) / 128) % 2 == 0;
+  const bool b3 = make_map_chunks(&tm.b3, w, M, N, kFwdBK, (pair ? kFwdBN / 2 : kFwdBN) / 32);
   if (!b3) tm.b3 = tm.b;
   tm.alo = tm.blo = tm.a3lo = tm.b3lo = tm.a;
   TcWork wk{(int)((B + 127) / 128), (int)((M + kFwdBN - 1) / kFwdBN), splits, (int)N, k_per_split, 1, 0, 0,
@@ -1430,7 +1441,8 @@ cudaError_t launch_forward_product_tc(const float *x, const float *w, float *par
   ep.rows = B;
   ep.cols = M;
   ep.ld = M;
-  cudaError_t e = launch_tc<true, kFwdBN, kFwdBK, kFwdStages, false, kFwdChain>(tm, wk, ep, st);
+  cudaError_t e = pair ? launch_tc_pair<true, kFwdBN, kFwdBK, kFwdStages, false, kFwdChain>(tm, wk, ep, st)
+                       : launch_tc<true, kFwdBN, kFwdBK, kFwdStages, false, kFwdChain>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
@@ -1524,11 +1536,7 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   // a batch of more than one chain carries its running sum through the trace matrix (see the kernel)
   const bool multi = B > (long)kTrChainKb * kTrBK;
   // CTA pairs (one 256-row MMA over two SMs, each staging half of the tile's columns of y): single-chain batches
-  static const bool pair_wanted = [] {   // SBB_TC_PAIR=0 keeps one CTA per tile
-    const char *e = getenv("SBB_TC_PAIR");
-    return !(e != nullptr && e[0] == '0');
-  }();
-  const bool pair = pair_wanted && !multi;
+  const bool pair = pairs_enabled();
   // (pairs: y's one-box 3-D map covers half a tile's column chunks)
   if (!batch_operand_maps(tm, x, y, nullptr, nullptr, false, B, N, M, pair ? kTrBN / 2 : kTrBN, a3, b3))
     return cudaErrorInvalidValue;
@@ -1564,9 +1572,13 @@ cudaError_t launch_trace_update_tc(const float *x, const float *y, long B, long 
   ep.row0 = row_begin;
   ep.p = p;
   ep.ema_scale = p.taupdt / p.batch;
-  cudaError_t e = multi  ? launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0, true>(tm, wk, ep, st)
-                  : pair ? launch_tc_pair<kTrBN, kTrBK, kPairStages>(tm, wk, ep, st)
-                         : launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
+  cudaError_t e;
+  if (pair)
+    e = multi ? launch_tc_pair<false, kTrBN, kTrBK, kPairStages, true, 0, true>(tm, wk, ep, st)
+              : launch_tc_pair<false, kTrBN, kTrBK, kPairStages, true, 0>(tm, wk, ep, st);
+  else
+    e = multi ? launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0, true>(tm, wk, ep, st)
+              : launch_tc<false, kTrBN, kTrBK, kTrStages, true, 0>(tm, wk, ep, st);
   if (e == cudaSuccess) count_launches(1);
   return e;
 }
