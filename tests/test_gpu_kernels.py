@@ -253,3 +253,56 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(k):
     assert np.array_equal(got, want)
     status = ctypes.c_int(7)
     assert lib.sbb_device_wait_status(ctypes.byref(status)) == 0 and status.value == 0
+
+
+def test_one_cta_form_of_the_tensor_kernels(port_kernels, tmp_path):
+    """The tensor-core contractions run as CTA pairs by default; SBB_TC_PAIR=0 (read once per process, hence the
+    child process) keeps one CTA per tile.  Both forms of the forward product, of the single-chain and of the
+    multi-chain trace update must agree with the oracle."""
+    import os
+    import subprocess
+    import sys
+    from conftest import REPO
+    script = r'''
+import sys
+import numpy as np
+sys.path.insert(0, %r)
+from streambrain_b200 import kernels_b200 as k
+from streambrain_b200._lib import check, lib
+check(lib.sbb_set_contraction_path(1))
+out = {}
+for tag, (B, N, H, Mc) in {"single": (256, 388, 3, 44), "multi": (600, 260, 2, 130)}.items():
+    rs = np.random.RandomState(B + N)
+    M = H * Mc
+    x, y = rs.rand(B, N).astype(np.float32), rs.rand(B, M).astype(np.float32)
+    st = [rs.rand(N).astype(np.float32), rs.rand(M).astype(np.float32), rs.rand(N, M).astype(np.float32)]
+    w = rs.randn(N, M).astype(np.float32)
+    b = rs.randn(M).astype(np.float32)
+    out[tag + "_fwd"] = k.update_state(np.zeros((B, M), dtype=np.float32), w, b, x)
+    got = k.update_weights(*[v.copy() for v in st], x, y, 0.05, np.zeros((N, M), dtype=np.float32), 0.025)
+    for name, v in zip(("Ci", "Cj", "Cij", "W"), got):
+        out[tag + "_" + name] = v
+np.savez(sys.argv[1], **out)
+''' % REPO
+    results = {}
+    for pair in ("0", "1"):
+        path = str(tmp_path / ("pair%s.npz" % pair))
+        env = dict(os.environ, SBB_TC_PAIR=pair)
+        subprocess.run([sys.executable, "-c", script, path], check=True, env=env, timeout=300)
+        results[pair] = np.load(path)
+    tol = TOL[np.dtype(np.float32)]
+    for tag, (B, N, H, Mc) in {"single": (256, 388, 3, 44), "multi": (600, 260, 2, 130)}.items():
+        rs = np.random.RandomState(B + N)
+        M = H * Mc
+        x, y = rs.rand(B, N).astype(np.float32), rs.rand(B, M).astype(np.float32)
+        st = [rs.rand(N).astype(np.float32), rs.rand(M).astype(np.float32), rs.rand(N, M).astype(np.float32)]
+        w = rs.randn(N, M).astype(np.float32)
+        b = rs.randn(M).astype(np.float32)
+        fwd = port_kernels.update_state(np.zeros((B, M), dtype=np.float32), w, b, x)
+        want = port_kernels.update_weights(*[v.copy() for v in st], x, y, 0.05, np.zeros((N, M), dtype=np.float32), 0.025)
+        for pair in ("0", "1"):
+            r = results[pair]
+            assert rel_inf(r[tag + "_fwd"], fwd) < tol, (tag, pair)
+            for name, v in zip(("Ci", "Cj", "Cij"), want):
+                assert rel_inf(r[tag + "_" + name], v) < tol, (tag, pair, name)
+            assert weight_err(r[tag + "_W"], want[3]) < 10 * tol, (tag, pair)
