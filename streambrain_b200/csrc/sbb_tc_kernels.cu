@@ -23,6 +23,12 @@
 //               stages in shared memory two blocks ahead
 //   warp 12     TMA producer (one lane): cp.async.bulk.tensor loads, no multicast
 //   warp 13     MMA issuer (one lane) and owner of the TMEM allocation
+// CTA pairs (PAIR; the forward product and the fused trace update): the kernel is launched in clusters of
+// two CTAs that work on two vertically adjacent row tiles with one 256-row tcgen05.mma.cta_group::2 per k-step,
+// issued by the leader CTA.  Each CTA stages and converts its own 128 rows of A into its own tensor memory and
+// half of the tile's columns of B into its own shared memory; the converters and the epilogue warps of both
+// CTAs report to the leader's mbarriers (mapa + remote arrive), tcgen05.commit with a cluster multicast reports
+// back to both.  No TMA load uses multicast: every CTA loads into its own shared memory only.
 // Hand-offs use mbarriers; every wait is bounded by a count of SM clock cycles:
 // a wait that gives up records a code in a global status word, raises the CTA's
 // abort flag, and every role falls through to the common tear-down (drain the
