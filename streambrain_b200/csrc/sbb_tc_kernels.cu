@@ -38,7 +38,6 @@
 #include <cuda.h>
 
 #include <atomic>
-#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -1345,10 +1344,6 @@ cudaError_t launch_tc_pair(const TcMaps &tm, const TcWork &wk, const TcEpilogue 
   long clusters = max_clusters[dev] < g_sm_count_tc[dev] / 2 ? max_clusters[dev] : g_sm_count_tc[dev] / 2;
   if (clusters > pairs) clusters = pairs;
   cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-  if (getenv("SBB_TC_DEBUG")) {
-    static int said = 0;
-    if (!said++) fprintf(stderr, "pair launch: max active clusters %d, grid %ld CTAs, pairs %ld\n", max_clusters[dev], 2 * clusters, pairs);
-  }
   return cudaLaunchKernelEx(&cfg, kernel, tm.a, tm.b, tm.a3, tm.b3, tm.c, tm.alo, tm.blo, tm.a3lo, tm.b3lo, wk, ep,
                             status);
 }
