@@ -14,9 +14,10 @@
 // lo parts beside the raw tile in shared memory: the tensor core fetches only B
 // from shared memory.
 //
-// Roles inside a CTA (448 threads, one CTA per SM, tiles walked persistently):
-//   warps 0-3   converters: wait for a TMA stage, write A's hi / lo parts to tensor
-//               memory (one tile row per thread) and B's lo parts to shared memory
+// Roles inside a CTA (512 threads, one CTA per SM, tiles walked persistently):
+//   warps 0-3   A converters: wait for a TMA stage, write A's hi / lo parts to tensor
+//               memory (one tile row per thread)
+//   warps 14-15 B converters: B's lo parts to shared memory
 //   warps 4-11  epilogue: tcgen05.ld the accumulator (16x256b shape, so that four
 //               lanes cover 32 contiguous bytes of a row) and either store it or run
 //               the trace / weight arithmetic against 32 x 32 blocks of Cij that TMA
@@ -50,7 +51,8 @@ constexpr int kConvWarps = 4;
 constexpr int kEpiWarps = 8;
 constexpr int kTmaWarp = kConvWarps + kEpiWarps;
 constexpr int kMmaWarp = kTmaWarp + 1;
-constexpr int kThreads = (kMmaWarp + 1) * 32;  // 448
+constexpr int kBConvWarps = 2;                 // warps kMmaWarp + 1 ..: the low parts of B
+constexpr int kThreads = (kMmaWarp + 1 + kBConvWarps) * 32;  // 512: with 128 registers each, the whole register file
 constexpr long long kWaitLimitCycles = 4000000000ll;  // default limit of one wait: about 2 s of SM clock
 
 enum WaitCode { kWaitEmpty = 1, kWaitFull = 2, kWaitConv = 3, kWaitAccEmpty = 4, kWaitAccFull = 5, kWaitDrain = 6, kWaitSlab = 7 };
@@ -454,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_conv(s), (PAIR ? 2 : 1) * kConvWarps * 32);   // the leader's counts both CTAs' converters
+      mbar_init(bar_conv(s), (PAIR ? 2 : 1) * (kConvWarps + kBConvWarps) * 32);   // the leader's counts both CTAs' converters
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -693,28 +695,45 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int k = 0; k < BK; ++k) r[k] = __float_as_uint(tf32_lo(__uint_as_float(r[k])));
         tmem_st_32x32b<BK>(ta + BK, r);
-        // B: lo parts beside the raw tile in shared memory.  Every load is issued before the first
-        // store: the hand-off to the MMA warp costs one shared-memory round trip, not one per piece.
-        constexpr int kConvThreads = kConvWarps * 32;
-        const float4 *rawb = reinterpret_cast<const float4 *>(smem + s * SM::STAGE_BYTES + SM::A_BYTES);
-        float4 *lob = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
-        constexpr int kPieces = SM::B_BYTES / 16 / kConvThreads;
-        static_assert(SM::B_BYTES % (16 * kConvThreads) == 0, "a whole number of 16-byte pieces per thread");
-        float4 v[kPieces];
-#pragma unroll
-        for (int i = 0; i < kPieces; ++i) v[i] = rawb[threadIdx.x + i * kConvThreads];
-#pragma unroll
-        for (int i = 0; i < kPieces; ++i)
-          lob[threadIdx.x + i * kConvThreads] =
-              make_float4(tf32_lo(v[i].x), tf32_lo(v[i].y), tf32_lo(v[i].z), tf32_lo(v[i].w));
         tmem_wait_st();
         tc_fence_before();
-        fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
         // (test hook: one lost arrival leaves the MMA warp waiting until its time limit, see tc_debug_lose_arrive)
         if (!(wk.lose_arrive && it == 0 && threadIdx.x == 0 && blockIdx.x == 0)) {
           if constexpr (PAIR) mbar_arrive_rank(bar_conv(s), 0);   // the leader's MMA warp waits for both CTAs
           else mbar_arrive(bar_conv(s));
         }
+      }
+    }
+  } else if (warp > kMmaWarp) {
+    // ------------------------------------------------------------ B's lo parts (idle when PRESPLIT)
+    // Two warps of their own: on the A converters' path this work lengthened the chain (wait for the stage, load,
+    // split, store, fence, arrive) that every k-block of the MMA stream waits for -- without it the trace update
+    // ran 4 % and the forward product 6 % faster in a timing-only experiment.
+    uint32_t it = 0;
+    bool ok = true;
+    const int t = threadIdx.x - (kMmaWarp + 1) * 32;   // 0 .. 63
+    for (long w = w_first; !PRESPLIT && w < total && ok; w += w_step) {
+      int mt, nt, sp, kbeg, nkb;
+      decode(w, mt, nt, sp, kbeg, nkb);
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        if (!mbar_wait(bar_full(s), ph, abort_flag, status, kWaitFull)) { ok = false; break; }
+        // lo parts beside the raw tile in shared memory; every load is issued before the first store
+        constexpr int kBThreads = kBConvWarps * 32;
+        const float4 *rawb = reinterpret_cast<const float4 *>(smem + s * SM::STAGE_BYTES + SM::A_BYTES);
+        float4 *lob = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
+        constexpr int kPieces = SM::B_BYTES / 16 / kBThreads;
+        static_assert(SM::B_BYTES % (16 * kBThreads) == 0, "a whole number of 16-byte pieces per thread");
+        float4 v[kPieces];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) v[i] = rawb[t + i * kBThreads];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i)
+          lob[t + i * kBThreads] = make_float4(tf32_lo(v[i].x), tf32_lo(v[i].y), tf32_lo(v[i].z), tf32_lo(v[i].w));
+        fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
+        if constexpr (PAIR) mbar_arrive_rank(bar_conv(s), 0);
+        else mbar_arrive(bar_conv(s));
       }
     }
   } else {
