@@ -17,7 +17,8 @@
 // Roles inside a CTA (512 threads, one CTA per SM, tiles walked persistently):
 //   warps 0-3   A converters: wait for a TMA stage, write A's hi / lo parts to tensor
 //               memory (one tile row per thread)
-//   warps 14-15 B converters: B's lo parts to shared memory
+//               and (multi-chain trace update, raw products) B's lo parts to shared memory
+//   warps 14-15 B converters (forward product, single-chain trace update): B's lo parts to shared memory
 //   warps 4-11  epilogue: tcgen05.ld the accumulator (16x256b shape, so that four
 //               lanes cover 32 contiguous bytes of a row) and either store it or run
 //               the trace / weight arithmetic against 32 x 32 blocks of Cij that TMA
@@ -429,6 +430,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   static_assert(!(PRESPLIT && A_KMAJOR), "pre-split operands are the two MN-major ones of the batch contractions");
   static_assert(!PAIR || (!PRESPLIT && BN % 64 == 0), "CTA pairs convert their operands themselves");
   // In a pair, CTA `rank` of the cluster works on row tile 2 * (pair's tile) + rank; the leader (rank 0) issues the MMAs.
+  // B's low parts by the two extra warps (see their role below): forward product and single-chain trace update
+  constexpr bool BWARPS = !PRESPLIT && !MULTI && (A_KMAJOR || FUSED);
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
   constexpr int BNH = PAIR ? BN / 2 : BN;   // columns of B this CTA stages
   static_assert(!A_KMAJOR || BK == 32, "a K-major operand is loaded as one 128-byte-wide box");
@@ -456,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_conv(s), (PAIR ? 2 : 1) * (kConvWarps + kBConvWarps) * 32);   // the leader's counts both CTAs' converters
+      mbar_init(bar_conv(s), (PAIR ? 2 : 1) * (kConvWarps + (BWARPS ? kBConvWarps : 0)) * 32);   // the leader's counts both CTAs' converters
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -695,6 +698,23 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int k = 0; k < BK; ++k) r[k] = __float_as_uint(tf32_lo(__uint_as_float(r[k])));
         tmem_st_32x32b<BK>(ta + BK, r);
+        if constexpr (!BWARPS) {
+          // B: lo parts beside the raw tile in shared memory.  Every load is issued before the first
+          // store: the hand-off to the MMA warp costs one shared-memory round trip, not one per piece.
+          constexpr int kConvThreads = kConvWarps * 32;
+          const float4 *rawb = reinterpret_cast<const float4 *>(smem + s * SM::STAGE_BYTES + SM::A_BYTES);
+          float4 *lob = reinterpret_cast<float4 *>(smem + s * SM::STAGE_BYTES + SM::RAW_BYTES);
+          constexpr int kPieces = SM::B_BYTES / 16 / kConvThreads;
+          static_assert(SM::B_BYTES % (16 * kConvThreads) == 0, "a whole number of 16-byte pieces per thread");
+          float4 v[kPieces];
+#pragma unroll
+          for (int i = 0; i < kPieces; ++i) v[i] = rawb[threadIdx.x + i * kConvThreads];
+#pragma unroll
+          for (int i = 0; i < kPieces; ++i)
+            lob[threadIdx.x + i * kConvThreads] =
+                make_float4(tf32_lo(v[i].x), tf32_lo(v[i].y), tf32_lo(v[i].z), tf32_lo(v[i].w));
+          fence_async_smem();  // make the generic-proxy writes visible to the tensor pipe
+        }
         tmem_wait_st();
         tc_fence_before();
         // (test hook: one lost arrival leaves the MMA warp waiting until its time limit, see tc_debug_lose_arrive)
@@ -705,14 +725,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp > kMmaWarp) {
-    // ------------------------------------------------------------ B's lo parts (idle when PRESPLIT)
-    // Two warps of their own: on the A converters' path this work lengthened the chain (wait for the stage, load,
-    // split, store, fence, arrive) that every k-block of the MMA stream waits for -- without it the trace update
-    // ran 4 % and the forward product 6 % faster in a timing-only experiment.
+    // ------------------------------------------------------------ B's lo parts (BWARPS kernels)
+    // Two warps of their own: on the A converters' path this work lengthens the chain (wait for the stage, load,
+    // split, store, fence, arrive) that every k-block of the MMA stream waits for.  Measured: forward product
+    // 0.437 -> 0.396 ms, single-chain trace update 0.561 -> 0.557 ms; the multi-chain trace update, whose eight
+    // epilogue warps keep the SM's issue slots and shared memory busier, lost 5 %, so there the A converters
+    // keep this work and these two warps go straight to the tear-down.
     uint32_t it = 0;
     bool ok = true;
     const int t = threadIdx.x - (kMmaWarp + 1) * 32;   // 0 .. 63
-    for (long w = w_first; !PRESPLIT && w < total && ok; w += w_step) {
+    for (long w = w_first; BWARPS && w < total && ok; w += w_step) {
       int mt, nt, sp, kbeg, nkb;
       decode(w, mt, nt, sp, kbeg, nkb);
       for (int kb = 0; kb < nkb; ++kb, ++it) {
