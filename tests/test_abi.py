@@ -105,3 +105,25 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(root, f)).read()
                 assert "oracle" not in src.lower() or f == "synthetic.py" and False, os.path.join(root, f)
+
+
+def test_header_constants_match_the_binding():
+    """The numeric constants the ctypes binding repeats (error codes, dtypes, layer kinds, state indices, the
+    size of the sharding hand-shake) are the header's."""
+    import re
+    from conftest import REPO
+    from streambrain_b200 import _lib
+    text = open(os.path.join(REPO, "include", "sbb200.h")).read()
+    defs = {m.group(1): int(m.group(2)) for m in re.finditer(r"^#define\s+(SBB_[A-Z0-9_]+)\s+(-?\d+)\b", text, re.M)}
+    assert defs["SBB_OK"] == _lib.SBB_OK == 0
+    for name, value in _lib.ERR_NAMES.items():
+        assert defs[value] == name
+    assert (defs["SBB_ERR_INVALID"], defs["SBB_ERR_CUDA"], defs["SBB_ERR_NO_DEVICE"], defs["SBB_ERR_UNSUPPORTED"],
+            defs["SBB_ERR_TIMEOUT"]) == (_lib.ERR_INVALID, _lib.ERR_CUDA, _lib.ERR_NO_DEVICE, _lib.ERR_UNSUPPORTED,
+                                         _lib.ERR_TIMEOUT)
+    assert (defs["SBB_F32"], defs["SBB_F64"]) == (_lib.F32, _lib.F64)
+    assert (defs["SBB_LAYER_DENSE"], defs["SBB_LAYER_PLASTIC"]) == (_lib.DENSE, _lib.PLASTIC)
+    assert (defs["SBB_SHARD_BUFFERS"], defs["SBB_SHARD_HANDLE_BYTES"]) == (_lib.SHARD_BUFFERS, _lib.SHARD_HANDLE_BYTES)
+    for name, index in _lib.STATE.items():
+        key = {"weights": "WEIGHTS", "bias": "BIAS", "Ci": "CI", "Cj": "CJ", "Cij": "CIJ", "kbi": "KBI", "wmask": "WMASK"}[name]
+        assert defs["SBB_STATE_" + key] == index
