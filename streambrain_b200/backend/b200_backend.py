@@ -253,6 +253,7 @@ class _DeviceLayer:
         blob = b"".join(parts)
         check(lib.sbb_layer_shard_attach(self._handle, ctypes.c_char_p(blob)))
         self._shard = (rank, world_size)
+        self._shard_max_batch = int(max_local_batch)
         self._support = None
 
     def owned_rows(self, rank=None):
@@ -602,6 +603,10 @@ class Network:
                 # every rank takes floor(batch / world_size) samples of a batch (sbb_network_batch_plan)
                 target.shard_rows(self.world_rank, self.world_size, self._all_gather_bytes,
                                   max(1, maximal_batch_size // self.world_size))
+            if (getattr(target, "_shard", None) is not None and layer + 1 < len(self._layers)
+                    and maximal_batch_size // self.world_size > target._shard_max_batch):
+                raise ValueError("layer %d was sharded for local batches of up to %d samples; this fit needs %d" % (
+                    layer, target._shard_max_batch, maximal_batch_size // self.world_size))
             for epoch in range(epochs):
                 if self.world_rank == 0 and self.verbose:
                     print('Layer - %d/%d' % (layer + 1, len(self._layers)), flush=True)

@@ -1165,8 +1165,6 @@ template <typename T>
 int shard_scatter(sbb_layer *L, const T *x, long B, cudaStream_t st) {
   auto &S = L->shard;
   const int slot = (S.cur + 1 + S.staged) % 3;   // every rank makes the same calls, so the slots agree
-  S.staged += 1;
-  S.slot_batch[slot] = B;
   // rank o receives this rank's samples as rows [rank * B, (rank + 1) * B) of its [world * B, rows of o] buffer
   sbb::PeerTable t{};
   t.n = (int)S.world;
@@ -1176,6 +1174,8 @@ int shard_scatter(sbb_layer *L, const T *x, long B, cudaStream_t st) {
   }
   if (S.world == 1) {
     SBB_CUDA(sbb::launch_scatter_columns<T>(x, B, L->N, S.rows_per_rank, t, st));
+    S.staged += 1;   // (recorded only once everything is queued: a failed call stages nothing)
+    S.slot_batch[slot] = B;
     return SBB_OK;
   }
   // Across ranks the column blocks travel by copy engines (strided 2-D copies over NVLink): the exchange of a
@@ -1189,6 +1189,8 @@ int shard_scatter(sbb_layer *L, const T *x, long B, cudaStream_t st) {
     SBB_CUDA(cudaMemcpy2DAsync(t.ptr[o], (size_t)width * sizeof(T), x + rb, (size_t)L->N * sizeof(T),
                                (size_t)width * sizeof(T), (size_t)B, cudaMemcpyDeviceToDevice, st));
   }
+  S.staged += 1;
+  S.slot_batch[slot] = B;
   return SBB_OK;
 }
 
@@ -1402,8 +1404,15 @@ int sbb_layer_shard_forward(sbb_layer *L, long B_local, void *support_dev, void 
     S.batch = B_local;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return DISPATCH(L->desc.dtype, shard_forward<float>(L, B_local, (float *)support_dev, st),
-                  shard_forward<double>(L, B_local, (double *)support_dev, st));
+  const int rc = DISPATCH(L->desc.dtype, shard_forward<float>(L, B_local, (float *)support_dev, st),
+                          shard_forward<double>(L, B_local, (double *)support_dev, st));
+  if (rc != SBB_OK) {   // nothing was consumed: the batch stays staged
+    auto &S = L->shard;
+    S.cur = (S.cur + 2) % 3;
+    S.staged += 1;
+    S.batch = 0;
+  }
+  return rc;
 }
 
 int sbb_layer_shard_activate(sbb_layer *L, long B_local, const void *support_dev, void *y_local_dev, void *stream) {
