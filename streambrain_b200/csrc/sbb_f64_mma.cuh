@@ -5,7 +5,7 @@
 // two CTAs of eight warps per SM instead of one.
 //
 // CTA tile 128 x 64 (eight warps, two CTAs per SM) or 64 x 64 (four warps, three CTAs per SM: for
-// launches whose 128-row tiles would leave most of a last round of CTAs empty), k-slabs of 16 in a
+// launches whose 128-row tiles would leave most of a last wave of CTAs empty), k-slabs of 16 in a
 // three-stage cp.async pipeline, warp tile 32 x 32 (4 x 4 instruction tiles).  Shared-memory rows
 // are padded so that a half-warp's fragment loads (four rows of four consecutive doubles) fall into
 // 16 different bank pairs.

@@ -596,9 +596,9 @@ static cudaError_t launch_f64_mma_tiles(const double *A, long lda, const double 
   return launched();
 }
 
-// Row tiles of 128 unless 64 finishes in fewer rounds of resident CTAs: time ~ rounds x (rows of a tile) x (CTAs
-// that share an SM).  1568 x 3000 outputs: 611 tiles of 128 rows are two full rounds of 296 CTAs and a third with
-// 19, 1175 tiles of 64 rows three rounds of 444 half-sized CTAs.
+// Row tiles of 128 unless 64 finishes in fewer waves of resident CTAs: time ~ waves x (rows of a tile) x (CTAs
+// that share an SM).  1568 x 3000 outputs: 611 tiles of 128 rows are two full waves of 296 CTAs and a third with
+// 19, 1175 tiles of 64 rows three waves of 444 half-sized CTAs.
 template <bool A_KMAJOR, class Pairs>
 static cudaError_t launch_f64_mma(const double *A, long lda, const double *Bm, long ldb, long Mdim, long Ndim, int K,
                                   int splits, bool cols_fastest, Pairs ep, cudaStream_t st) {
